@@ -1,0 +1,250 @@
+/*
+ * mytorch_b200 — C ABI of the sm_100a library behind MyTorch's GPT training step.
+ *
+ * Every entry point is what a Python `ctypes` binding of the reference would
+ * bind in place of one of its Triton/CuPy calls; the comment above each group
+ * names the reference function it replaces (path:line inside the reference
+ * project). Conventions:
+ *   - plain device pointers, sizes and scalars; the CALLER owns every buffer
+ *     (the library keeps no reference after a call returns, except for objects
+ *     with an explicit destroy call);
+ *   - `dtype` is an mt_dtype code for the floating-point tensors of the call;
+ *   - `stream` is a cudaStream_t passed as void* (NULL = legacy default stream);
+ *     no compute entry point synchronises with the host;
+ *   - the return value is an mt_status (0 = ok); mt_last_error() returns the
+ *     text of the last failure on the calling thread.
+ * Rows are the flattened leading dimensions ([B,T,E] is passed as rows=B*T).
+ */
+#ifndef MYTORCH_B200_H
+#define MYTORCH_B200_H
+
+#include <stdint.h>
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum { MT_F32 = 0, MT_F16 = 1, MT_BF16 = 2 } mt_dtype;
+typedef enum {
+  MT_OK = 0, MT_ERR_INVALID = 1, MT_ERR_DTYPE = 2, MT_ERR_CUDA = 3,
+  MT_ERR_NCCL = 4, MT_ERR_TIMEOUT = 5, MT_ERR_UNSUPPORTED = 6, MT_ERR_DEVICE_FLAG = 7
+} mt_status;
+typedef enum { MT_ACT_NONE = 0, MT_ACT_GELU = 1, MT_ACT_RELU2 = 2, MT_ACT_RELU = 3 } mt_act;
+
+/* ---- runtime: device arrays, copies, streams, events ----------------------
+ * Replaces the CuPy allocator / cp.asarray / cp.asnumpy / cp.cuda.Event used
+ * through mytorch/_array.py:199-249 and mytorch/tensor.py:221-261. */
+const char* mt_last_error(void);
+int mt_version(void);
+int mt_device_count(int* count);
+int mt_set_device(int device);
+int mt_get_device(int* device);
+int mt_device_sm_count(int* count);
+int mt_malloc(void** ptr, size_t bytes, void* stream);      /* stream-ordered, pooled */
+int mt_free(void* ptr, void* stream);
+int mt_host_alloc(void** ptr, size_t bytes);                /* pinned host memory */
+int mt_host_free(void* ptr);
+int mt_memcpy_h2d(void* dst, const void* src, size_t bytes, void* stream);
+int mt_memcpy_d2h(void* dst, const void* src, size_t bytes, void* stream);
+int mt_memcpy_d2d(void* dst, const void* src, size_t bytes, void* stream);
+int mt_memset(void* dst, int byte, size_t bytes, void* stream);
+int mt_stream_create(void** stream);
+int mt_stream_destroy(void* stream);
+int mt_stream_sync(void* stream);
+int mt_device_sync(void);
+int mt_event_create(void** event);
+int mt_event_destroy(void* event);
+int mt_event_record(void* event, void* stream);
+int mt_event_sync(void* event);
+int mt_event_elapsed_ms(void* start, void* stop, float* ms);
+int mt_stream_wait_event(void* stream, void* event);
+int mt_mem_info(size_t* free_bytes, size_t* total_bytes);
+/* Device status word: kernels that give up on a bounded wait or see an
+ * out-of-range index record a code here instead of trapping. Reads it back
+ * (synchronising `stream`) and clears it. */
+int mt_device_flag_read(int* flag, void* stream);
+
+/* Per-kernel-class timing with CUDA events on the launching stream.
+ * kind: 0 = off, 1 = tensor-core GEMM launches, 2 = attention launches. */
+int mt_prof_begin(int kind);
+int mt_prof_end(double* total_ms, int64_t* launches, double* total_flops);
+int64_t mt_launch_count(void);            /* kernels launched by this library so far */
+
+/* ---- elementwise (CuPy ufuncs reached through mytorch/_array.py:422-470 and
+ * the autograd closures of mytorch/tensor.py:272-330, 596-640) -------------- */
+int mt_cast(const void* src, int src_dtype, void* dst, int dst_dtype, int64_t n, void* stream);
+int mt_fill(void* dst, int dtype, float value, int64_t n, void* stream);
+int mt_add(const void* a, const void* b, void* out, int64_t n, int dtype, void* stream);          /* out = a + b */
+int mt_axpby(const void* x, float alpha, void* y, float beta, int64_t n, int x_dtype, int y_dtype, void* stream); /* y = alpha*x + beta*y */
+int mt_scale(void* x, float alpha, int64_t n, int dtype, void* stream);
+int mt_add_rowvec(const void* a, const void* v, void* out, int64_t rows, int64_t cols, int dtype, void* stream); /* out[r,:] = a[r,:] + v */
+int mt_colsum(const void* a, void* out, int64_t rows, int64_t cols, int dtype, int out_dtype, int accumulate, void* stream); /* out[c] (+)= sum_r a[r,c] */
+int mt_sum_f32(const void* x, int dtype, int64_t n, float* out, void* stream);                    /* out[0] = sum x (fp32) */
+
+/* fused_activation_forward / fused_activation_backward
+ * (mytorch/nn/functional/fused_ops/activations.py:212, :273) */
+int mt_act_fwd(const void* x, void* y, int64_t n, int act, int dtype, void* stream);
+int mt_act_bwd(const void* x, const void* dy, void* dx, int64_t n, int act, int dtype, void* stream);
+
+/* fused_layernorm_forward / fused_layernorm_backward
+ * (mytorch/nn/functional/fused_ops/layernorm.py:244, :342). mean/rstd are fp32
+ * [rows]. dgamma/dbeta are fp32 [cols] and may be NULL; `accumulate` adds to
+ * them instead of overwriting. Column sums are two-stage and deterministic. */
+int mt_layernorm_fwd(const void* x, const void* gamma, const void* beta, void* y,
+                     float* mean, float* rstd, int64_t rows, int64_t cols, float eps,
+                     int dtype, void* stream);
+int mt_layernorm_bwd(const void* x, const float* mean, const float* rstd, const void* dy,
+                     const void* gamma, void* dx, float* dgamma, float* dbeta,
+                     int64_t rows, int64_t cols, int accumulate, int dtype, void* stream);
+
+/* fused_rmsnorm_forward / fused_rmsnorm_backward
+ * (mytorch/nn/functional/fused_ops/rmsnorm.py:159, :251) */
+int mt_rmsnorm_fwd(const void* x, const void* gamma, void* y, float* rstd,
+                   int64_t rows, int64_t cols, float eps, int dtype, void* stream);
+int mt_rmsnorm_bwd(const void* x, const float* rstd, const void* dy, const void* gamma,
+                   void* dx, float* dgamma, int64_t rows, int64_t cols, int accumulate,
+                   int dtype, void* stream);
+
+/* fused_softmax_forward / fused_softmax_backward
+ * (mytorch/nn/functional/fused_ops/softmax.py:358, :408) */
+int mt_softmax_fwd(const void* x, void* y, int64_t rows, int64_t cols, int dtype, void* stream);
+int mt_softmax_bwd(const void* dy, const void* s, void* dx, int64_t rows, int64_t cols, int dtype, void* stream);
+
+/* fused_cross_entropy_forward / fused_cross_entropy_backward
+ * (mytorch/nn/functional/fused_ops/cross_entropy.py:263, :324). `ld` is the row
+ * stride of logits in elements (>= classes). Labels are int32, -100 = ignored.
+ * fwd writes loss[rows], lse[rows] (fp32) and, if loss_sum/valid_count are not
+ * NULL, adds sum(loss) and the number of valid rows to them (device scalars).
+ * bwd writes (softmax - onehot) * scale into dlogits (may alias logits);
+ * scale = *scale_dev * scale_host, and if inv_count_dev != NULL the result is
+ * also divided by that device scalar (the valid-row count), so no host
+ * read-back is needed. */
+int mt_ce_fwd(const void* logits, const int32_t* labels, float* loss, float* lse,
+              float* loss_sum, float* valid_count, int64_t rows, int64_t classes, int64_t ld,
+              float softcap, int dtype, void* stream);
+int mt_ce_bwd(const void* logits, const int32_t* labels, const float* lse, void* dlogits,
+              float scale_host, const float* scale_dev, const float* count_dev,
+              int64_t rows, int64_t classes, int64_t ld, float softcap, int dtype, void* stream);
+
+/* fused_embedding_forward / fused_embedding_backward
+ * (mytorch/nn/functional/fused_ops/embedding.py:108, :219). Indices int32.
+ * An out-of-range index sets the device status word and is skipped.
+ * bwd adds into dweight (fp32 [vocab, dim]); rows are summed in token order
+ * (sorted segments, no atomics), so the result is deterministic. `scratch`
+ * must hold mt_embedding_bwd_scratch_bytes(n_tokens) bytes. */
+int mt_embedding_fwd(const void* weight, const int32_t* idx, void* out, int64_t n_tokens,
+                     int64_t dim, int64_t vocab, int dtype, void* stream);
+size_t mt_embedding_bwd_scratch_bytes(int64_t n_tokens);
+int mt_embedding_bwd(const void* dy, const int32_t* idx, float* dweight, void* scratch,
+                     int64_t n_tokens, int64_t dim, int64_t vocab, int dtype, void* stream);
+/* GPT-2 embedding pair fused: out = wte[idx] + wpe[pos], pos = token % seq_len
+ * (gpt2_trainer/gpt2.py:105-119). */
+int mt_embedding_pos_fwd(const void* wte, const void* wpe, const int32_t* idx, void* out,
+                         int64_t n_tokens, int64_t seq_len, int64_t dim, int64_t vocab,
+                         int dtype, void* stream);
+/* dwpe[t,:] += sum_b dy[b,t,:]  (fp32 accumulate) */
+int mt_pos_embedding_bwd(const void* dy, float* dwpe, int64_t batch, int64_t seq_len,
+                         int64_t dim, int dtype, void* stream);
+
+/* fused_rope_forward / fused_rope_backward
+ * (mytorch/nn/functional/fused_ops/rope.py:178, :265): x [B,T,H,D] in place,
+ * cos/sin fp32 [T,D] (halves duplicated), backward = rotation by -angle. */
+int mt_rope(void* x, const float* cos, const float* sin, int64_t batch, int64_t seq,
+            int64_t heads, int64_t head_dim, int backward, int dtype, void* stream);
+
+/* fused_linear_forward (mytorch/nn/functional/fused_ops/linear.py:118),
+ * fused_grouped_matmul (mytorch/nn/functional/fused_ops/matmul.py:842) and
+ * cupy.matmul reached from mytorch/nn/functional/layers/linear.py:86,104,123.
+ *   C[M,N] = act(alpha * op(A)·op(B) + bias)    (+ C if accumulate)
+ * op(A) is [M,K]: trans_a=0 -> A stored [M,K] (lda>=K); trans_a=1 -> A stored [K,M].
+ * op(B) is [K,N]: trans_b=0 -> B stored [K,N] (ldb>=N); trans_b=1 -> B stored [N,K].
+ * Linear forward is (trans_a=0, trans_b=1); dgrad (0,0); wgrad (1,0).
+ * in_dtype f16/bf16 runs on tcgen05 tensor cores (fp32 accumulate in TMEM)
+ * when pointers/strides are 16-byte aligned, else on a CUDA-core kernel;
+ * in_dtype f32 runs on the CUDA-core kernel in full fp32.
+ * bias: [N] in in_dtype or NULL. preact: optional second output receiving the
+ * value before the activation (same dtype/ld as C), or NULL.
+ * accumulate: 0 = overwrite, 1 = C += result (read-modify-write),
+ * 2 = split-K with fp32 atomic adds (C must be fp32; order not deterministic). */
+int mt_gemm(const void* A, const void* B, void* C, void* preact, const void* bias,
+            int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc,
+            int trans_a, int trans_b, int in_dtype, int out_dtype, int act,
+            float alpha, int accumulate, void* stream);
+/* Forces the CUDA-core kernel (1) or restores automatic choice (0); used by
+ * the tests to cross-check the tensor-core path on the device. */
+int mt_gemm_force_simt(int on);
+
+/* fused_sdpa_forward / fused_sdpa_backward
+ * (mytorch/nn/functional/fused_ops/flash_attention.py:1269, :1441), causal or
+ * full softmax(QK^T*scale)V. Tensors are addressed with explicit element
+ * strides (batch, head, row; the head_dim stride is 1), so the per-head
+ * interleaved [q|k|v] projection of gpt2_trainer/gpt2.py:168-177 and
+ * [B,H,S,D] tensors are both read in place. lse is fp32 [B,H,S], natural log.
+ * bwd needs delta scratch fp32 [B,H,S] and, for the tensor-core path, a fp32
+ * dq accumulator of B*H*S*D floats (dq_accum; may be NULL on the CUDA-core path). */
+typedef struct { int64_t b, h, s; } mt_strides3;
+int mt_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse,
+                mt_strides3 sq, mt_strides3 sk, mt_strides3 sv, mt_strides3 so,
+                int64_t batch, int64_t heads, int64_t seq, int64_t head_dim,
+                float scale, int causal, int dtype, void* stream);
+int mt_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o,
+                const float* lse, void* dq, void* dk, void* dv, float* delta, float* dq_accum,
+                mt_strides3 sq, mt_strides3 sk, mt_strides3 sv, mt_strides3 so, mt_strides3 sdo,
+                mt_strides3 sdq, mt_strides3 sdk, mt_strides3 sdv,
+                int64_t batch, int64_t heads, int64_t seq, int64_t head_dim,
+                float scale, int causal, int dtype, void* stream);
+int mt_attn_force_simt(int on);
+
+/* AdamW.step (mytorch/optim/optimizers.py:342-371), GradScaler.unscale_grads +
+ * the inf/nan scan (mytorch/accelerate.py:71-89, 716-729), clip_grad_norm_
+ * (mytorch/accelerate.py:799-856) and the master->half copy of
+ * OptimizerWrapper.step (mytorch/accelerate.py:342-361), over MANY tensors per
+ * launch. A tensor list is described by device arrays built once by the caller:
+ *   ptr tables (void*[n]), sizes (int64[n]), and a chunk table mapping each
+ *   4096-element chunk to (tensor, offset) so one grid covers all tensors. */
+typedef struct {
+  void** p;          /* fp32 master parameters                      [n] */
+  void** g;          /* gradients (g_dtype)                          [n] */
+  void** m;          /* fp32 first moment                            [n] */
+  void** v;          /* fp32 second moment                           [n] */
+  void** p_half;     /* optional low-precision copies, or NULL table [n] */
+  const int64_t* size;       /* elements per tensor                  [n] */
+  const float* weight_decay; /* per tensor                           [n] */
+  const int32_t* chunk_tensor;  /* [n_chunks] */
+  const int64_t* chunk_offset;  /* [n_chunks] */
+  int64_t n_tensors, n_chunks;
+} mt_tensor_list;
+/* sumsq[0] += sum g^2 (fp32, of g * *inv_scale if inv_scale != NULL);
+ * found_inf[0] = 1.0 if any g is inf/nan. Both device scalars. */
+int mt_gradnorm_multi(const mt_tensor_list* L, int g_dtype, const float* inv_scale_dev,
+                      float* sumsq, float* found_inf, void* stream);
+/* One launch: g' = g * (*inv_scale) * clip_coef where
+ * clip_coef = min(1, max_norm / (sqrt(*sumsq) + 1e-6)) (max_norm <= 0: no clip);
+ * skipped entirely when *found_inf != 0. Then the reference AdamW update
+ * (decay applied after the Adam step, eps not bias-corrected) and, if p_half
+ * is given, the low-precision copy. lr_t = lr*sqrt(1-beta2^t)/(1-beta1^t) is
+ * computed on the host and passed in. zero_grad != 0 clears g afterwards. */
+int mt_adamw_multi(const mt_tensor_list* L, int g_dtype, int half_dtype,
+                   float lr, float lr_t, float beta1, float beta2, float eps,
+                   const float* inv_scale_dev, const float* sumsq_dev, float max_norm,
+                   const float* found_inf_dev, int zero_grad, void* stream);
+
+/* cupyx.distributed.NCCLBackend as used by mytorch/accelerate.py:154-159
+ * (init), :249-250 (broadcast), :732-736/:757-772/:833-837 (all_reduce),
+ * :873-880 (barrier), :1050-1052 (stop). NCCL is loaded with dlopen at first
+ * use. The 128-byte unique id is produced on rank 0 and carried to the other
+ * ranks by the caller (TCP store on CUPYX_DISTRIBUTED_HOST/PORT). */
+int mt_comm_unique_id(void* id128);
+int mt_comm_init(void** comm, const void* id128, int rank, int world_size);
+int mt_comm_broadcast(void* comm, void* buf, int64_t count, int dtype, int root, void* stream);
+/* op: 0 = sum, 1 = max, 2 = avg */
+int mt_comm_allreduce(void* comm, const void* send, void* recv, int64_t count, int dtype, int op, void* stream);
+int mt_comm_barrier(void* comm, void* stream);
+int mt_comm_abort(void* comm);
+int mt_comm_destroy(void* comm);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MYTORCH_B200_H */

@@ -1,0 +1,156 @@
+"""ctypes binding of libmytorch_b200.so (the C ABI in include/mytorch_b200.h).
+
+The library is the product: nothing here computes. If the shared object is
+missing the import fails with instructions to build it; there is no fallback.
+Every `mt_*` function that returns a status is wrapped so that a non-zero code
+raises `MTError` carrying `mt_last_error()`.
+"""
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libmytorch_b200.so")
+
+F32, F16, BF16 = 0, 1, 2
+ACT = {None: 0, "none": 0, "gelu": 1, "relu_squared": 2, "relu2": 2, "relu": 3}
+
+
+class MTError(RuntimeError):
+    def __init__(self, code, text):
+        super().__init__(f"mytorch_b200 error {code}: {text}")
+        self.code = code
+
+
+class Strides3(C.Structure):
+    _fields_ = [("b", C.c_int64), ("h", C.c_int64), ("s", C.c_int64)]
+
+
+class TensorList(C.Structure):
+    _fields_ = [("p", C.c_void_p), ("g", C.c_void_p), ("m", C.c_void_p), ("v", C.c_void_p),
+                ("p_half", C.c_void_p), ("size", C.c_void_p), ("weight_decay", C.c_void_p),
+                ("chunk_tensor", C.c_void_p), ("chunk_offset", C.c_void_p),
+                ("n_tensors", C.c_int64), ("n_chunks", C.c_int64)]
+
+
+if not os.path.exists(LIB_PATH):
+    raise ImportError(
+        f"{LIB_PATH} is missing: build it with `python mytorch_b200/csrc/build.py` "
+        "(nvcc, sm_100a). mytorch_b200 has no CPU or PyTorch fallback.")
+
+lib = C.CDLL(LIB_PATH)
+
+_p, _i, _i64, _f, _sz = C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_size_t
+_pp = C.POINTER(C.c_void_p)
+_S = Strides3
+
+# name -> argtypes (all return int status unless listed in _RAW)
+_SIG = {
+    "mt_device_count": [C.POINTER(_i)],
+    "mt_set_device": [_i],
+    "mt_get_device": [C.POINTER(_i)],
+    "mt_device_sm_count": [C.POINTER(_i)],
+    "mt_malloc": [_pp, _sz, _p],
+    "mt_free": [_p, _p],
+    "mt_host_alloc": [_pp, _sz],
+    "mt_host_free": [_p],
+    "mt_memcpy_h2d": [_p, _p, _sz, _p],
+    "mt_memcpy_d2h": [_p, _p, _sz, _p],
+    "mt_memcpy_d2d": [_p, _p, _sz, _p],
+    "mt_memset": [_p, _i, _sz, _p],
+    "mt_stream_create": [_pp],
+    "mt_stream_destroy": [_p],
+    "mt_stream_sync": [_p],
+    "mt_device_sync": [],
+    "mt_event_create": [_pp],
+    "mt_event_destroy": [_p],
+    "mt_event_record": [_p, _p],
+    "mt_event_sync": [_p],
+    "mt_event_elapsed_ms": [_p, _p, C.POINTER(_f)],
+    "mt_stream_wait_event": [_p, _p],
+    "mt_mem_info": [C.POINTER(_sz), C.POINTER(_sz)],
+    "mt_device_flag_read": [C.POINTER(_i), _p],
+    "mt_prof_begin": [_i],
+    "mt_prof_end": [C.POINTER(C.c_double), C.POINTER(_i64), C.POINTER(C.c_double)],
+    "mt_cast": [_p, _i, _p, _i, _i64, _p],
+    "mt_fill": [_p, _i, _f, _i64, _p],
+    "mt_add": [_p, _p, _p, _i64, _i, _p],
+    "mt_axpby": [_p, _f, _p, _f, _i64, _i, _i, _p],
+    "mt_scale": [_p, _f, _i64, _i, _p],
+    "mt_add_rowvec": [_p, _p, _p, _i64, _i64, _i, _p],
+    "mt_colsum": [_p, _p, _i64, _i64, _i, _i, _i, _p],
+    "mt_sum_f32": [_p, _i, _i64, _p, _p],
+    "mt_act_fwd": [_p, _p, _i64, _i, _i, _p],
+    "mt_act_bwd": [_p, _p, _p, _i64, _i, _i, _p],
+    "mt_layernorm_fwd": [_p, _p, _p, _p, _p, _p, _i64, _i64, _f, _i, _p],
+    "mt_layernorm_bwd": [_p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i, _i, _p],
+    "mt_rmsnorm_fwd": [_p, _p, _p, _p, _i64, _i64, _f, _i, _p],
+    "mt_rmsnorm_bwd": [_p, _p, _p, _p, _p, _p, _i64, _i64, _i, _i, _p],
+    "mt_softmax_fwd": [_p, _p, _i64, _i64, _i, _p],
+    "mt_softmax_bwd": [_p, _p, _p, _i64, _i64, _i, _p],
+    "mt_ce_fwd": [_p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _f, _i, _p],
+    "mt_ce_bwd": [_p, _p, _p, _p, _f, _p, _p, _i64, _i64, _i64, _f, _i, _p],
+    "mt_embedding_fwd": [_p, _p, _p, _i64, _i64, _i64, _i, _p],
+    "mt_embedding_bwd": [_p, _p, _p, _p, _i64, _i64, _i64, _i, _p],
+    "mt_embedding_pos_fwd": [_p, _p, _p, _p, _i64, _i64, _i64, _i64, _i, _p],
+    "mt_pos_embedding_bwd": [_p, _p, _i64, _i64, _i64, _i, _p],
+    "mt_rope": [_p, _p, _p, _i64, _i64, _i64, _i64, _i, _i, _p],
+    "mt_gemm": [_p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _i, _f, _i, _p],
+    "mt_gemm_force_simt": [_i],
+    "mt_attn_fwd": [_p, _p, _p, _p, _p, _S, _S, _S, _S, _i64, _i64, _i64, _i64, _f, _i, _i, _p],
+    "mt_attn_bwd": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _S, _S, _S, _S, _S, _S, _S, _S,
+                    _i64, _i64, _i64, _i64, _f, _i, _i, _p],
+    "mt_attn_force_simt": [_i],
+    "mt_gradnorm_multi": [C.POINTER(TensorList), _i, _p, _p, _p, _p],
+    "mt_adamw_multi": [C.POINTER(TensorList), _i, _i, _f, _f, _f, _f, _f, _p, _p, _f, _p, _i, _p],
+    "mt_comm_unique_id": [_p],
+    "mt_comm_init": [_pp, _p, _i, _i],
+    "mt_comm_broadcast": [_p, _p, _i64, _i, _i, _p],
+    "mt_comm_allreduce": [_p, _p, _p, _i64, _i, _i, _p],
+    "mt_comm_barrier": [_p, _p],
+    "mt_comm_abort": [_p],
+    "mt_comm_destroy": [_p],
+}
+# functions that do not return a status code
+_RAW = {
+    "mt_last_error": ([], C.c_char_p),
+    "mt_version": ([], _i),
+    "mt_launch_count": ([], _i64),
+    "mt_embedding_bwd_scratch_bytes": ([_i64], _sz),
+}
+
+lib.mt_last_error.restype = C.c_char_p
+
+
+def _checked(name, fn):
+    def call(*args):
+        rc = fn(*args)
+        if rc != 0:
+            raise MTError(rc, (lib.mt_last_error() or b"").decode(errors="replace") + f" [{name}]")
+    call.__name__ = name
+    return call
+
+
+_g = globals()
+for _name, _args in _SIG.items():
+    _fn = getattr(lib, _name)
+    _fn.argtypes = _args
+    _fn.restype = _i
+    _g[_name[3:]] = _checked(_name, _fn)
+for _name, (_args, _res) in _RAW.items():
+    _fn = getattr(lib, _name)
+    _fn.argtypes = _args
+    _fn.restype = _res
+    _g[_name[3:]] = _fn
+
+DECLARED = sorted(list(_SIG) + list(_RAW))
+
+
+def device_count():
+    n = C.c_int(0)
+    lib.mt_device_count(C.byref(n))
+    return n.value
+
+
+def require_device():
+    if device_count() == 0:
+        raise MTError(3, "no CUDA device: mytorch_b200 runs on B200 (sm_100a) only, there is no CPU path")

@@ -1,0 +1,447 @@
+// Tensor-core GEMM for sm_100a: C[M,N] = act(alpha * op(A) op(B) + bias) with
+// fp16/bf16 operands and fp32 accumulation in tensor memory.
+//
+// One persistent CTA per SM walks output tiles of 128 x BN (BN = 256 or 128).
+// Warp roles:
+//   warp 0    TMA producer: 128-byte-swizzled 64-deep K slices of A and B into
+//             a ring of shared-memory stages (full/empty mbarriers);
+//   warp 1    MMA issuer: one thread issues tcgen05.mma (128 x BN x 16) per
+//             16 of K, accumulating into one of two TMEM buffers, and commits
+//             stage-release and accumulator-ready barriers;
+//   warps 2-5 epilogue: tcgen05.ld the finished accumulator (thread = row),
+//             apply alpha / bias / activation, write C (store, read-modify-
+//             write, or fp32 atomic add for split-K) while the MMA warp is
+//             already on the next tile in the other TMEM buffer.
+// Operands may be K-major or MN-major in global memory (all four transpose
+// combinations), selected by the TMA box and the UMMA descriptors; no
+// transposed copies are made. Loads are plain (non-multicast) TMA.
+//
+// Roofline: tensor pipe; algorithmic work 2*M*N*K FLOP per launch.
+#include "common.cuh"
+#include "gemm.cuh"
+#include "sm100.cuh"
+#include "prof.cuh"
+#include <mutex>
+
+namespace mt {
+
+using namespace sm100;
+
+constexpr int BM = 128, BK = 64;
+constexpr int kGemmThreads = 192;
+constexpr int kABytes = BM * BK * 2;  // 16 KB
+
+template <int BN> struct GemmCfg {
+  static constexpr int kBBytes = BN * BK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStages = BN == 256 ? 4 : 6;
+  static constexpr int kTmemCols = 2 * BN;  // two accumulator buffers
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+struct GemmParams {
+  void* C; void* preact; const void* bias;
+  int64_t M, N, K, ldc;
+  int out_dtype, in_bf16, act, accumulate, vec_store;
+  float alpha;
+  int tiles_m, tiles_n, splits, kb_per_split, kb_total;
+  int* flag;
+};
+
+__device__ __forceinline__ float act_apply_tc(float x, int act) {
+  switch (act) {
+    case MT_ACT_GELU: {
+      float inner = 0.7978845608f * (x + 0.044715f * x * x * x);
+      return 0.5f * x * (1.f + tanhf(inner));
+    }
+    case MT_ACT_RELU2: { float r = fmaxf(x, 0.f); return r * r; }
+    case MT_ACT_RELU: return fmaxf(x, 0.f);
+    default: return x;
+  }
+}
+
+// Writes 8 consecutive outputs of one row.
+template <typename TO>
+__device__ __forceinline__ void store8(TO* p, const float* v, int n_valid, bool vec, int accumulate) {
+  if (vec && n_valid == 8) {
+    if (sizeof(TO) == 2) {
+      __align__(16) TO o[8];
+      if (accumulate) {
+        *reinterpret_cast<uint4*>(o) = *reinterpret_cast<const uint4*>(p);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = from_f<TO>(to_f(o[e]) + v[e]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = from_f<TO>(v[e]);
+      }
+      *reinterpret_cast<uint4*>(p) = *reinterpret_cast<uint4*>(o);
+    } else {
+      float4* q = reinterpret_cast<float4*>(p);
+      if (accumulate == 2) {
+        atomicAdd(q, make_float4(v[0], v[1], v[2], v[3]));
+        atomicAdd(q + 1, make_float4(v[4], v[5], v[6], v[7]));
+      } else {
+        float4 a = make_float4(v[0], v[1], v[2], v[3]), b = make_float4(v[4], v[5], v[6], v[7]);
+        if (accumulate) {
+          float4 c0 = q[0], c1 = q[1];
+          a.x += c0.x; a.y += c0.y; a.z += c0.z; a.w += c0.w;
+          b.x += c1.x; b.y += c1.y; b.z += c1.z; b.w += c1.w;
+        }
+        q[0] = a;
+        q[1] = b;
+      }
+    }
+  } else {
+    for (int e = 0; e < n_valid; ++e) {
+      if (accumulate == 2 && sizeof(TO) == 4) atomicAdd(reinterpret_cast<float*>(p) + e, v[e]);
+      else p[e] = from_f<TO>(accumulate ? to_f(p[e]) + v[e] : v[e]);
+    }
+  }
+}
+
+template <bool A_MN, bool B_MN, int BN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams P) {
+  using Cfg = GemmCfg<BN>;
+  constexpr int S = Cfg::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;  // 1024-byte alignment for the 128B swizzle
+  uint8_t* base_ptr = smem_raw + (base - raw);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(base_ptr + S * Cfg::kStageBytes);
+  // barrier slots: full[S], empty[S], acc_full[2], acc_empty[2]
+  const uint32_t bar0 = base + S * Cfg::kStageBytes;
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (S + s); };
+  auto accf_bar = [&](int b) { return bar0 + 8u * (2 * S + b); };
+  auto acce_bar = [&](int b) { return bar0 + 8u * (2 * S + 2 + b); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(accf_bar(b), 1); mbar_init(acce_bar(b), 4); }
+    *abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int tiles_mn = P.tiles_m * P.tiles_n;
+  const int total_tiles = tiles_mn * P.splits;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer --
+    if (lane == 0) {
+      prefetch_tmap(&tmA);
+      prefetch_tmap(&tmB);
+      int stage = 0;
+      uint32_t phase = 0;
+      long long issued = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        const int mn = t % tiles_mn, split = t / tiles_mn;
+        const int m0 = (mn % P.tiles_m) * BM, n0 = (mn / P.tiles_m) * BN;
+        const int kb0 = split * P.kb_per_split;
+        const int kb1 = min(kb0 + P.kb_per_split, P.kb_total);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
+          const uint32_t sa = base + stage * Cfg::kStageBytes, sb = sa + kABytes;
+          mbar_expect_tx(full_bar(stage), Cfg::kStageBytes);
+          const int k0 = kb * BK;
+          if (!A_MN) {
+            tma_load_2d(sa, &tmA, full_bar(stage), k0, m0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j) tma_load_2d(sa + j * (BK * 128), &tmA, full_bar(stage), m0 + j * 64, k0);
+          }
+          if (!B_MN) {
+            tma_load_2d(sb, &tmB, full_bar(stage), k0, n0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * (BK * 128), &tmB, full_bar(stage), n0 + j * 64, k0);
+          }
+          ++issued;
+          if (++stage == S) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok) {
+        // Bounded drain: let the copies already issued into each stage land
+        // before the CTA's shared memory is released.
+        long long n = issued < S ? issued : S;
+        int s = stage;
+        uint32_t ph = phase;
+        for (long long i = 0; i < n; ++i) {
+          if (--s < 0) { s = S - 1; ph ^= 1u; }
+          const long long t0 = clock64();
+          while (!mbar_try_wait(full_bar(s), ph) && clock64() - t0 < kWaitLimitCycles) {}
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------- MMA issuer --
+    if (lane == 0) {
+      const uint32_t idesc = idesc_f16(P.in_bf16, A_MN, B_MN, BM, BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
+        const int split = t / tiles_mn;
+        const int kb0 = split * P.kb_per_split;
+        const int kb1 = min(kb0 + P.kb_per_split, P.kb_total);
+        const int buf = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        if (!mbar_wait(acce_bar(buf), acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = base + stage * Cfg::kStageBytes, sb = sa + kABytes;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t ad = A_MN ? smem_desc_sw128(sa + k * 2048, BK * 128, 1024)
+                                     : smem_desc_sw128(sa + k * 32, 16, 1024);
+            const uint64_t bd = B_MN ? smem_desc_sw128(sb + k * 2048, BK * 128, 1024)
+                                     : smem_desc_sw128(sb + k * 32, 16, 1024);
+            umma_f16(d_tmem, ad, bd, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(empty_bar(stage));  // stage reusable once these MMAs have read it
+          if (++stage == S) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) umma_commit(accf_bar(buf));  // accumulator complete
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue --
+    const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32)
+    int it = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
+      const int mn = t % tiles_mn;
+      const bool add_bias = P.bias != nullptr && t / tiles_mn == 0;  // only the first K split adds it
+      const int64_t m0 = (int64_t)(mn % P.tiles_m) * BM, n0 = (int64_t)(mn / P.tiles_m) * BN;
+      const int buf = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      // warp-uniform outcome: tcgen05.ld below needs all 32 lanes together
+      if (!__all_sync(0xffffffffu, mbar_wait(accf_bar(buf), acc_phase, abort_flag))) { ok = false; break; }
+      tc_fence_after();
+      const int64_t row = m0 + quarter * 32 + lane;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(taddr + c * 32, r);
+        tmem_ld_wait();
+        const int64_t col0 = n0 + c * 32;
+        if (row < P.M && col0 < P.N) {
+#pragma unroll
+          for (int g8 = 0; g8 < 4; ++g8) {
+            const int64_t col = col0 + g8 * 8;
+            if (col >= P.N) break;
+            const int n_valid = (int)(P.N - col < 8 ? P.N - col : 8);
+            float v[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              float x = P.alpha * __uint_as_float(r[g8 * 8 + e]);
+              if (add_bias && e < n_valid)
+                x += P.in_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(P.bias)[col + e])
+                               : __half2float(reinterpret_cast<const __half*>(P.bias)[col + e]);
+              v[e] = x;
+            }
+            const int64_t off = row * P.ldc + col;
+            if (P.preact) {
+              if (P.out_dtype == MT_F16) store8(reinterpret_cast<__half*>(P.preact) + off, v, n_valid, P.vec_store, 0);
+              else if (P.out_dtype == MT_BF16) store8(reinterpret_cast<__nv_bfloat16*>(P.preact) + off, v, n_valid, P.vec_store, 0);
+              else store8(reinterpret_cast<float*>(P.preact) + off, v, n_valid, P.vec_store, 0);
+            }
+            if (P.act != MT_ACT_NONE) {
+#pragma unroll
+              for (int e = 0; e < 8; ++e) v[e] = act_apply_tc(v[e], P.act);
+            }
+            if (P.out_dtype == MT_F16) store8(reinterpret_cast<__half*>(P.C) + off, v, n_valid, P.vec_store, P.accumulate);
+            else if (P.out_dtype == MT_BF16) store8(reinterpret_cast<__nv_bfloat16*>(P.C) + off, v, n_valid, P.vec_store, P.accumulate);
+            else store8(reinterpret_cast<float*>(P.C) + off, v, n_valid, P.vec_store, P.accumulate);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acce_bar(buf));  // this warp is done with the buffer
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown --
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag && P.flag) atomicMax(P.flag, 100);  // a bounded wait expired
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------------ host ----
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn g_encode = nullptr;
+static std::once_flag g_encode_once;
+
+static EncodeTiledFn get_encode() {
+  std::call_once(g_encode_once, [] {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      g_encode = (EncodeTiledFn)fn;
+  });
+  return g_encode;
+}
+
+int make_tmap_nd(CUtensorMap* map, const void* base_ptr, int is_bf16, int rank, const uint64_t* dims,
+                 const uint64_t* strides_elems, const uint32_t* box) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) { set_error("cuTensorMapEncodeTiled is not available from this driver"); return MT_ERR_CUDA; }
+  cuuint64_t gdim[5], gstr[5];
+  cuuint32_t bx[5], es[5];
+  for (int i = 0; i < rank; ++i) { gdim[i] = dims[i]; bx[i] = box[i]; es[i] = 1; }
+  for (int i = 1; i < rank; ++i) gstr[i - 1] = strides_elems[i - 1] * 2;  // bytes
+  CUresult r = enc(map, is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, (cuuint32_t)rank,
+                   const_cast<void*>(base_ptr), gdim, gstr, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled failed with code %d", (int)r); return MT_ERR_CUDA; }
+  return MT_OK;
+}
+
+int make_tmap_2d(CUtensorMap* map, const void* base_ptr, int is_bf16, uint64_t inner, uint64_t outer,
+                 uint64_t ld_elems, uint32_t box_inner, uint32_t box_outer) {
+  uint64_t dims[2] = {inner, outer}, str[1] = {ld_elems};
+  uint32_t box[2] = {box_inner, box_outer};
+  return make_tmap_nd(map, base_ptr, is_bf16, 2, dims, str, box);
+}
+
+bool gemm_tc_supported(const GemmArgs& g) {
+  if (g.in_dtype != MT_F16 && g.in_dtype != MT_BF16) return false;
+  if (g.M <= 0 || g.N <= 0 || g.K <= 0) return false;
+  if (!aligned16(g.A) || !aligned16(g.B)) return false;
+  if (g.lda % 8 || g.ldb % 8) return false;
+  if (g.M >= (1ll << 31) || g.N >= (1ll << 31) || g.K >= (1ll << 31)) return false;
+  if (g.accumulate == 2 && g.out_dtype != MT_F32) return false;
+  return true;
+}
+
+template <bool A_MN, bool B_MN, int BN>
+static int launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& P, int grid, cudaStream_t st) {
+  using Cfg = GemmCfg<BN>;
+  static bool attr_set[16] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  auto kern = gemm_tc_kernel<A_MN, B_MN, BN>;
+  if (dev < 16 && !attr_set[dev]) {
+    MT_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    attr_set[dev] = true;
+  }
+  kern<<<grid, kGemmThreads, Cfg::kSmemBytes, st>>>(ta, tb, P);
+  MT_LAUNCH_CHECK();
+  return MT_OK;
+}
+
+int gemm_tc(const GemmArgs& g, cudaStream_t st) {
+  const int sms = sm_count();
+  const int tiles_m = (int)((g.M + BM - 1) / BM);
+  const int kb_total = (int)((g.K + BK - 1) / BK);
+  // Choose BN and the split count by wave efficiency on this many SMs.
+  int best_bn = 256, best_splits = 1;
+  double best = -1.0;
+  for (int bn : {256, 128}) {
+    const int tiles = tiles_m * (int)((g.N + bn - 1) / bn);
+    const int max_splits = g.accumulate == 2 ? 16 : 1;
+    for (int s = 1; s <= max_splits; ++s) {
+      if (s > 1 && kb_total / s < 8) break;
+      const int per = (kb_total + s - 1) / s;
+      if ((s - 1) * per >= kb_total) continue;  // an empty split
+      const long long work = (long long)tiles * s;
+      const long long waves = (work + sms - 1) / sms;
+      double eff = (double)work / (double)(waves * sms);
+      // padded work in the last N tile counts against the wider tile
+      eff *= (double)g.N / (double)(((g.N + bn - 1) / bn) * bn);
+      if (bn == 128) eff *= 0.92;
+      eff *= 1.0 - 0.01 * (s - 1);
+      if (eff > best) { best = eff; best_bn = bn; best_splits = s; }
+    }
+  }
+  const int bn = best_bn;
+  GemmParams P;
+  P.C = g.C; P.preact = g.preact; P.bias = g.bias;
+  P.M = g.M; P.N = g.N; P.K = g.K; P.ldc = g.ldc;
+  P.out_dtype = g.out_dtype; P.in_bf16 = g.in_dtype == MT_BF16; P.act = g.act; P.accumulate = g.accumulate;
+  P.alpha = g.alpha;
+  const int out_vec = g.out_dtype == MT_F32 ? 4 : 8;
+  P.vec_store = aligned16(g.C) && (!g.preact || aligned16(g.preact)) && g.ldc % out_vec == 0;
+  P.tiles_m = tiles_m;
+  P.tiles_n = (int)((g.N + bn - 1) / bn);
+  P.splits = best_splits;
+  P.kb_total = kb_total;
+  P.kb_per_split = (kb_total + best_splits - 1) / best_splits;
+  P.flag = device_flag_ptr();
+  const long long total = (long long)P.tiles_m * P.tiles_n * P.splits;
+  const int grid = (int)(total < sms ? total : sms);
+
+  CUtensorMap ta, tb;
+  int rc;
+  const int bf = P.in_bf16;
+  if (!g.trans_a) rc = make_tmap_2d(&ta, g.A, bf, (uint64_t)g.K, (uint64_t)g.M, (uint64_t)g.lda, BK, BM);
+  else rc = make_tmap_2d(&ta, g.A, bf, (uint64_t)g.M, (uint64_t)g.K, (uint64_t)g.lda, 64, BK);
+  if (rc) return rc;
+  if (g.trans_b) rc = make_tmap_2d(&tb, g.B, bf, (uint64_t)g.K, (uint64_t)g.N, (uint64_t)g.ldb, BK, (uint32_t)bn);
+  else rc = make_tmap_2d(&tb, g.B, bf, (uint64_t)g.N, (uint64_t)g.K, (uint64_t)g.ldb, 64, BK);
+  if (rc) return rc;
+
+  ProfScope prof(PROF_GEMM, st, 2.0 * (double)g.M * (double)g.N * (double)g.K);
+  const bool a_mn = g.trans_a != 0, b_mn = g.trans_b == 0;
+#define MT_TC(AM, BMN)                                                         \
+  (bn == 256 ? launch_tc<AM, BMN, 256>(ta, tb, P, grid, st) : launch_tc<AM, BMN, 128>(ta, tb, P, grid, st))
+  if (!a_mn && !b_mn) return MT_TC(false, false);
+  if (!a_mn && b_mn) return MT_TC(false, true);
+  if (a_mn && !b_mn) return MT_TC(true, false);
+  return MT_TC(true, true);
+#undef MT_TC
+}
+
+}  // namespace mt
+
+using namespace mt;
+
+static int g_force_simt = 0;
+
+extern "C" {
+
+int mt_gemm_force_simt(int on) { g_force_simt = on; return MT_OK; }
+
+int mt_gemm(const void* A, const void* B, void* C, void* preact, const void* bias, int64_t M, int64_t N, int64_t K,
+            int64_t lda, int64_t ldb, int64_t ldc, int trans_a, int trans_b, int in_dtype, int out_dtype, int act,
+            float alpha, int accumulate, void* stream) {
+  MT_REQUIRE(A && B && C && M >= 0 && N >= 0 && K >= 0, "gemm: bad arguments");
+  MT_REQUIRE(lda >= (trans_a ? M : K) && ldb >= (trans_b ? K : N) && ldc >= N, "gemm: leading dimension too small");
+  MT_REQUIRE(accumulate >= 0 && accumulate <= 2, "gemm: bad accumulate mode");
+  MT_REQUIRE(accumulate != 2 || out_dtype == MT_F32, "gemm: atomic accumulation needs an fp32 output");
+  MT_REQUIRE(accumulate != 2 || (act == MT_ACT_NONE && !preact), "gemm: split-K accumulation cannot apply an activation");
+  if (M == 0 || N == 0) return MT_OK;
+  GemmArgs g{A, B, C, preact, bias, M, N, K, lda, ldb, ldc, trans_a, trans_b, in_dtype, out_dtype, act, alpha, accumulate};
+  cudaStream_t st = as_stream(stream);
+  if (!g_force_simt && gemm_tc_supported(g)) return gemm_tc(g, st);
+  return gemm_simt(g, st);
+}
+
+}  // extern "C"

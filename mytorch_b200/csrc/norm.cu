@@ -1,0 +1,381 @@
+// LayerNorm and RMSNorm, forward and backward.
+//
+// Fast path: one warp per row, the row held in registers as 16-byte vectors
+// (lane owns vectors lane, lane+32, ...), fp32 math, two warp-shuffle
+// reductions. Because a lane owns the same columns for every row it visits,
+// the backward kernel keeps dgamma/dbeta partial sums in registers across
+// rows; blocks write one partial row each and a second kernel adds them in a
+// fixed order (no atomics: results are bit-reproducible).
+// Fallback (unaligned or very wide rows): one block per row, scalar loads.
+//
+// Algorithmic traffic (HBM roofline): forward 2*rows*cols*sizeof(T); backward
+// 3*rows*cols*sizeof(T) (+ negligible stats and partials).
+#include "common.cuh"
+#include "tempbuf.cuh"
+
+namespace mt {
+
+constexpr int kWarpsPerBlock = 4;
+
+// ---------------------------------------------------------------- forward ---
+template <typename T, int MAXV, bool RMS>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+norm_fwd_warp(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta,
+              T* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out,
+              int64_t rows, int cols, float eps) {
+  constexpr int VN = Vec16<T>::N;
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int nvec = cols / VN;
+  const T* xr = x + row * cols;
+  Vec16<T> v[MAXV];
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    int vi = lane + i * 32;
+    if (vi < nvec) {
+      v[i].load(xr + vi * VN);
+#pragma unroll
+      for (int e = 0; e < VN; ++e) s += RMS ? v[i].get(e) * v[i].get(e) : v[i].get(e);
+    }
+  }
+  s = warp_sum(s);
+  float mu = 0.f, rstd;
+  if (RMS) {
+    rstd = rsqrtf(s / cols + eps);
+  } else {
+    mu = s / cols;
+    float q = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+      int vi = lane + i * 32;
+      if (vi < nvec) {
+#pragma unroll
+        for (int e = 0; e < VN; ++e) { float d = v[i].get(e) - mu; q += d * d; }
+      }
+    }
+    q = warp_sum(q);
+    rstd = rsqrtf(q / cols + eps);
+  }
+  if (lane == 0) {
+    if (mean_out) mean_out[row] = mu;
+    if (rstd_out) rstd_out[row] = rstd;
+  }
+  T* yr = y + row * cols;
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    int vi = lane + i * 32;
+    if (vi < nvec) {
+      Vec16<T> g, b, o;
+      if (gamma) g.load(gamma + vi * VN);
+      if (beta) b.load(beta + vi * VN);
+#pragma unroll
+      for (int e = 0; e < VN; ++e) {
+        float h = (v[i].get(e) - mu) * rstd;
+        if (gamma) h *= g.get(e);
+        if (beta) h += b.get(e);
+        o.set(e, h);
+      }
+      o.store(yr + vi * VN);
+    }
+  }
+}
+
+template <typename T, bool RMS>
+__global__ void __launch_bounds__(256)
+norm_fwd_block(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta,
+               T* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out,
+               int64_t rows, int64_t cols, float eps) {
+  __shared__ float sh[32];
+  const int64_t row = blockIdx.x;
+  const T* xr = x + row * cols;
+  float s = 0.f;
+  for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) {
+    float a = to_f(xr[c]);
+    s += RMS ? a * a : a;
+  }
+  s = block_sum(s, sh);
+  float mu = 0.f, rstd;
+  if (RMS) {
+    rstd = rsqrtf(s / cols + eps);
+  } else {
+    mu = s / cols;
+    float q = 0.f;
+    for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) { float d = to_f(xr[c]) - mu; q += d * d; }
+    q = block_sum(q, sh);
+    rstd = rsqrtf(q / cols + eps);
+  }
+  if (threadIdx.x == 0) {
+    if (mean_out) mean_out[row] = mu;
+    if (rstd_out) rstd_out[row] = rstd;
+  }
+  T* yr = y + row * cols;
+  for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) {
+    float h = (to_f(xr[c]) - mu) * rstd;
+    if (gamma) h *= to_f(gamma[c]);
+    if (beta) h += to_f(beta[c]);
+    yr[c] = from_f<T>(h);
+  }
+}
+
+// --------------------------------------------------------------- backward ---
+// partial layout: [gridDim.x][2][cols] fp32 (dgamma partials, then dbeta).
+template <typename T, int MAXV, bool RMS>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+norm_bwd_warp(const T* __restrict__ x, const float* __restrict__ mean, const float* __restrict__ rstd_in,
+              const T* __restrict__ dy, const T* __restrict__ gamma, T* __restrict__ dx,
+              float* __restrict__ partial, int64_t rows, int cols, bool want_dg, bool want_db) {
+  constexpr int VN = Vec16<T>::N;
+  __shared__ float red[kWarpsPerBlock][32 * VN + 1];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nvec = cols / VN;
+  float dg[MAXV][VN], db[MAXV][VN];
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i)
+#pragma unroll
+    for (int e = 0; e < VN; ++e) { dg[i][e] = 0.f; db[i][e] = 0.f; }
+  Vec16<T> gv[MAXV];
+  if (gamma) {
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+      int vi = lane + i * 32;
+      if (vi < nvec) gv[i].load(gamma + vi * VN);
+    }
+  }
+  const float inv_cols = 1.f / cols;
+  for (int64_t row = (int64_t)blockIdx.x * kWarpsPerBlock + warp; row < rows;
+       row += (int64_t)gridDim.x * kWarpsPerBlock) {
+    const float mu = RMS ? 0.f : mean[row];
+    const float rs = rstd_in[row];
+    const T* xr = x + row * cols;
+    const T* dyr = dy + row * cols;
+    Vec16<T> xv[MAXV], dv[MAXV];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+      int vi = lane + i * 32;
+      if (vi < nvec) {
+        xv[i].load(xr + vi * VN);
+        dv[i].load(dyr + vi * VN);
+#pragma unroll
+        for (int e = 0; e < VN; ++e) {
+          float xh = (xv[i].get(e) - mu) * rs;
+          float d = dv[i].get(e);
+          dg[i][e] += d * xh;
+          db[i][e] += d;
+          float dxh = gamma ? d * gv[i].get(e) : d;
+          s1 += dxh;
+          s2 += dxh * xh;
+        }
+      }
+    }
+    s1 = warp_sum(s1) * inv_cols;
+    s2 = warp_sum(s2) * inv_cols;
+    if (RMS) s1 = 0.f;
+    T* dxr = dx + row * cols;
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+      int vi = lane + i * 32;
+      if (vi < nvec) {
+        Vec16<T> o;
+#pragma unroll
+        for (int e = 0; e < VN; ++e) {
+          float xh = (xv[i].get(e) - mu) * rs;
+          float dxh = gamma ? dv[i].get(e) * gv[i].get(e) : dv[i].get(e);
+          o.set(e, rs * (dxh - s1 - xh * s2));
+        }
+        o.store(dxr + vi * VN);
+      }
+    }
+  }
+  if (!want_dg && !want_db) return;
+  // Reduce the per-warp partials of this block in a fixed order, one vector
+  // slot at a time, and write the block's partial row.
+  float* pg = partial + (size_t)blockIdx.x * 2 * cols;
+  float* pb = pg + cols;
+  for (int pass = 0; pass < 2; ++pass) {
+    if (pass == 0 && !want_dg) continue;
+    if (pass == 1 && !want_db) continue;
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+      __syncthreads();
+#pragma unroll
+      for (int e = 0; e < VN; ++e) red[warp][lane * VN + e] = pass == 0 ? dg[i][e] : db[i][e];
+      __syncthreads();
+      for (int t = threadIdx.x; t < 32 * VN; t += blockDim.x) {
+        int col = (i * 32) * VN + t;
+        if (col < cols) {
+          float a = 0.f;
+#pragma unroll
+          for (int w = 0; w < kWarpsPerBlock; ++w) a += red[w][t];
+          (pass == 0 ? pg : pb)[col] = a;
+        }
+      }
+    }
+  }
+}
+
+template <typename T, bool RMS>
+__global__ void __launch_bounds__(256)
+norm_bwd_block(const T* __restrict__ x, const float* __restrict__ mean, const float* __restrict__ rstd_in,
+               const T* __restrict__ dy, const T* __restrict__ gamma, T* __restrict__ dx,
+               int64_t rows, int64_t cols) {
+  __shared__ float sh[32];
+  const int64_t row = blockIdx.x;
+  const float mu = RMS ? 0.f : mean[row];
+  const float rs = rstd_in[row];
+  const T* xr = x + row * cols;
+  const T* dyr = dy + row * cols;
+  float s1 = 0.f, s2 = 0.f;
+  for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) {
+    float xh = (to_f(xr[c]) - mu) * rs;
+    float dxh = to_f(dyr[c]) * (gamma ? to_f(gamma[c]) : 1.f);
+    s1 += dxh;
+    s2 += dxh * xh;
+  }
+  s1 = block_sum(s1, sh) / cols;
+  s2 = block_sum(s2, sh) / cols;
+  if (RMS) s1 = 0.f;
+  for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) {
+    float xh = (to_f(xr[c]) - mu) * rs;
+    float dxh = to_f(dyr[c]) * (gamma ? to_f(gamma[c]) : 1.f);
+    dx[row * cols + c] = from_f<T>(rs * (dxh - s1 - xh * s2));
+  }
+}
+
+// Column sums for the fallback path: block (32 x 8) owns 32 columns, walks all rows.
+template <typename T, bool RMS>
+__global__ void __launch_bounds__(256)
+norm_bwd_colsum(const T* __restrict__ x, const float* __restrict__ mean, const float* __restrict__ rstd_in,
+                const T* __restrict__ dy, float* __restrict__ dgamma, float* __restrict__ dbeta,
+                int64_t rows, int64_t cols, int accumulate) {
+  __shared__ float sg[8][33], sb[8][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int64_t c = (int64_t)blockIdx.x * 32 + tx;
+  float g = 0.f, b = 0.f;
+  if (c < cols) {
+    for (int64_t r = ty; r < rows; r += 8) {
+      float d = to_f(dy[r * cols + c]);
+      float xh = (to_f(x[r * cols + c]) - (RMS ? 0.f : mean[r])) * rstd_in[r];
+      g += d * xh;
+      b += d;
+    }
+  }
+  sg[ty][tx] = g;
+  sb[ty][tx] = b;
+  __syncthreads();
+  if (ty == 0 && c < cols) {
+    float ag = 0.f, ab = 0.f;
+    for (int i = 0; i < 8; ++i) { ag += sg[i][tx]; ab += sb[i][tx]; }
+    if (dgamma) dgamma[c] = accumulate ? dgamma[c] + ag : ag;
+    if (dbeta) dbeta[c] = accumulate ? dbeta[c] + ab : ab;
+  }
+}
+
+__global__ void norm_bwd_finalize(const float* __restrict__ partial, int nblocks, int cols,
+                                  float* __restrict__ dgamma, float* __restrict__ dbeta, int accumulate) {
+  int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= cols) return;
+  float g = 0.f, b = 0.f;
+  for (int i = 0; i < nblocks; ++i) {
+    const float* p = partial + (size_t)i * 2 * cols;
+    if (dgamma) g += p[c];
+    if (dbeta) b += p[cols + c];
+  }
+  if (dgamma) dgamma[c] = accumulate ? dgamma[c] + g : g;
+  if (dbeta) dbeta[c] = accumulate ? dbeta[c] + b : b;
+}
+
+template <typename T, bool RMS>
+static int norm_fwd_launch(const void* x, const void* gamma, const void* beta, void* y, float* mean,
+                           float* rstd, int64_t rows, int64_t cols, float eps, cudaStream_t st) {
+  constexpr int VN = Vec16<T>::N;
+  const T* xp = (const T*)x; const T* gp = (const T*)gamma; const T* bp = (const T*)beta; T* yp = (T*)y;
+  bool vec = cols % VN == 0 && aligned16(x) && aligned16(y) && (!gamma || aligned16(gamma)) &&
+             (!beta || aligned16(beta)) && cols / VN <= 32 * 8;
+  if (rows == 0) return MT_OK;
+  if (vec) {
+    int nvec = (int)(cols / VN);
+    dim3 grid((unsigned)((rows + kWarpsPerBlock - 1) / kWarpsPerBlock)), block(kWarpsPerBlock * 32);
+#define MT_FWD(MV) norm_fwd_warp<T, MV, RMS><<<grid, block, 0, st>>>(xp, gp, bp, yp, mean, rstd, rows, (int)cols, eps)
+    if (nvec <= 32) MT_FWD(1); else if (nvec <= 64) MT_FWD(2); else if (nvec <= 128) MT_FWD(4); else MT_FWD(8);
+#undef MT_FWD
+  } else {
+    norm_fwd_block<T, RMS><<<(unsigned)rows, 256, 0, st>>>(xp, gp, bp, yp, mean, rstd, rows, cols, eps);
+  }
+  MT_LAUNCH_CHECK();
+  return MT_OK;
+}
+
+template <typename T, bool RMS>
+static int norm_bwd_launch(const void* x, const float* mean, const float* rstd, const void* dy,
+                           const void* gamma, void* dx, float* dgamma, float* dbeta, int64_t rows,
+                           int64_t cols, int accumulate, cudaStream_t st) {
+  constexpr int VN = Vec16<T>::N;
+  const T* xp = (const T*)x; const T* dyp = (const T*)dy; const T* gp = (const T*)gamma; T* dxp = (T*)dx;
+  if (rows == 0) return MT_OK;
+  bool vec = cols % VN == 0 && aligned16(x) && aligned16(dy) && aligned16(dx) &&
+             (!gamma || aligned16(gamma)) && cols / VN <= 32 * 4;
+  if (vec) {
+    int nvec = (int)(cols / VN);
+    int64_t want = (rows + kWarpsPerBlock - 1) / kWarpsPerBlock;
+    int grid = (int)(want < (int64_t)sm_count() * 8 ? want : (int64_t)sm_count() * 8);
+    bool wg = dgamma != nullptr, wb = dbeta != nullptr;
+    TempBuf part((wg || wb) ? (size_t)grid * 2 * cols * sizeof(float) : 0, st);
+    if (!part.ok()) return MT_ERR_CUDA;
+    dim3 block(kWarpsPerBlock * 32);
+#define MT_BWD(MV) norm_bwd_warp<T, MV, RMS><<<grid, block, 0, st>>>(xp, mean, rstd, dyp, gp, dxp, (float*)part.ptr, rows, (int)cols, wg, wb)
+    if (nvec <= 32) MT_BWD(1); else if (nvec <= 64) MT_BWD(2); else MT_BWD(4);
+#undef MT_BWD
+    MT_LAUNCH_CHECK();
+    if (wg || wb) {
+      norm_bwd_finalize<<<(unsigned)((cols + 127) / 128), 128, 0, st>>>((const float*)part.ptr, grid, (int)cols,
+                                                                        dgamma, dbeta, accumulate);
+      MT_LAUNCH_CHECK();
+    }
+  } else {
+    norm_bwd_block<T, RMS><<<(unsigned)rows, 256, 0, st>>>(xp, mean, rstd, dyp, gp, dxp, rows, cols);
+    MT_LAUNCH_CHECK();
+    if (dgamma || dbeta) {
+      norm_bwd_colsum<T, RMS><<<(unsigned)((cols + 31) / 32), 256, 0, st>>>(xp, mean, rstd, dyp, dgamma, dbeta,
+                                                                           rows, cols, accumulate);
+      MT_LAUNCH_CHECK();
+    }
+  }
+  return MT_OK;
+}
+
+}  // namespace mt
+
+using namespace mt;
+
+extern "C" {
+
+int mt_layernorm_fwd(const void* x, const void* gamma, const void* beta, void* y, float* mean, float* rstd,
+                     int64_t rows, int64_t cols, float eps, int dtype, void* stream) {
+  MT_REQUIRE(x && y && rows >= 0 && cols > 0, "layernorm_fwd: bad arguments");
+  MT_DISPATCH_FLOAT(dtype, T, return (norm_fwd_launch<T, false>(x, gamma, beta, y, mean, rstd, rows, cols, eps, as_stream(stream))));
+  return MT_OK;
+}
+int mt_layernorm_bwd(const void* x, const float* mean, const float* rstd, const void* dy, const void* gamma,
+                     void* dx, float* dgamma, float* dbeta, int64_t rows, int64_t cols, int accumulate,
+                     int dtype, void* stream) {
+  MT_REQUIRE(x && dy && dx && mean && rstd && rows >= 0 && cols > 0, "layernorm_bwd: bad arguments");
+  MT_DISPATCH_FLOAT(dtype, T, return (norm_bwd_launch<T, false>(x, mean, rstd, dy, gamma, dx, dgamma, dbeta, rows, cols, accumulate, as_stream(stream))));
+  return MT_OK;
+}
+int mt_rmsnorm_fwd(const void* x, const void* gamma, void* y, float* rstd, int64_t rows, int64_t cols,
+                   float eps, int dtype, void* stream) {
+  MT_REQUIRE(x && y && rows >= 0 && cols > 0, "rmsnorm_fwd: bad arguments");
+  MT_DISPATCH_FLOAT(dtype, T, return (norm_fwd_launch<T, true>(x, gamma, nullptr, y, nullptr, rstd, rows, cols, eps, as_stream(stream))));
+  return MT_OK;
+}
+int mt_rmsnorm_bwd(const void* x, const float* rstd, const void* dy, const void* gamma, void* dx,
+                   float* dgamma, int64_t rows, int64_t cols, int accumulate, int dtype, void* stream) {
+  MT_REQUIRE(x && dy && dx && rstd && rows >= 0 && cols > 0, "rmsnorm_bwd: bad arguments");
+  MT_DISPATCH_FLOAT(dtype, T, return (norm_bwd_launch<T, true>(x, nullptr, rstd, dy, gamma, dx, dgamma, nullptr, rows, cols, accumulate, as_stream(stream))));
+  return MT_OK;
+}
+
+}  // extern "C"

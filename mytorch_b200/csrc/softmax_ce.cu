@@ -1,0 +1,338 @@
+// Row softmax (forward/backward) and cross entropy over the vocabulary
+// (forward: one pass, online log-sum-exp in vocabulary chunks; backward:
+// (softmax - onehot) * scale written over the logits).
+//
+// Algorithmic traffic: softmax fwd 2*R*C*s, bwd 3*R*C*s; cross entropy fwd
+// R*C*s (one read), bwd 2*R*C*s (read + write).
+#include "common.cuh"
+
+namespace mt {
+
+constexpr float kLog2e = 1.4426950408889634f;
+
+// ------------------------------------------------------------- softmax ------
+template <typename T, int MAXV>
+__global__ void __launch_bounds__(128)
+softmax_fwd_warp(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int cols) {
+  constexpr int VN = Vec16<T>::N;
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int nvec = cols / VN;
+  Vec16<T> v[MAXV];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    int vi = lane + i * 32;
+    if (vi < nvec) {
+      v[i].load(x + row * cols + vi * VN);
+#pragma unroll
+      for (int e = 0; e < VN; ++e) mx = fmaxf(mx, v[i].get(e));
+    }
+  }
+  mx = warp_max(mx);
+  float f[MAXV][VN];
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    int vi = lane + i * 32;
+    if (vi < nvec) {
+#pragma unroll
+      for (int e = 0; e < VN; ++e) { f[i][e] = exp2f((v[i].get(e) - mx) * kLog2e); s += f[i][e]; }
+    }
+  }
+  s = warp_sum(s);
+  const float inv = 1.f / s;
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    int vi = lane + i * 32;
+    if (vi < nvec) {
+      Vec16<T> o;
+#pragma unroll
+      for (int e = 0; e < VN; ++e) o.set(e, f[i][e] * inv);
+      o.store(y + row * cols + vi * VN);
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+softmax_fwd_block(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int64_t cols) {
+  __shared__ float sh[32];
+  const T* xr = x + (int64_t)blockIdx.x * cols;
+  T* yr = y + (int64_t)blockIdx.x * cols;
+  float mx = -INFINITY;
+  for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) mx = fmaxf(mx, to_f(xr[c]));
+  mx = block_max(mx, sh);
+  float s = 0.f;
+  for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) s += exp2f((to_f(xr[c]) - mx) * kLog2e);
+  s = block_sum(s, sh);
+  const float inv = 1.f / s;
+  for (int64_t c = threadIdx.x; c < cols; c += blockDim.x)
+    yr[c] = from_f<T>(exp2f((to_f(xr[c]) - mx) * kLog2e) * inv);
+}
+
+template <typename T, int MAXV>
+__global__ void __launch_bounds__(128)
+softmax_bwd_warp(const T* __restrict__ dy, const T* __restrict__ s, T* __restrict__ dx, int64_t rows, int cols) {
+  constexpr int VN = Vec16<T>::N;
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int nvec = cols / VN;
+  Vec16<T> a[MAXV], b[MAXV];
+  float dot = 0.f;
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    int vi = lane + i * 32;
+    if (vi < nvec) {
+      a[i].load(dy + row * cols + vi * VN);
+      b[i].load(s + row * cols + vi * VN);
+#pragma unroll
+      for (int e = 0; e < VN; ++e) dot += a[i].get(e) * b[i].get(e);
+    }
+  }
+  dot = warp_sum(dot);
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    int vi = lane + i * 32;
+    if (vi < nvec) {
+      Vec16<T> o;
+#pragma unroll
+      for (int e = 0; e < VN; ++e) o.set(e, b[i].get(e) * (a[i].get(e) - dot));
+      o.store(dx + row * cols + vi * VN);
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+softmax_bwd_block(const T* __restrict__ dy, const T* __restrict__ s, T* __restrict__ dx, int64_t rows, int64_t cols) {
+  __shared__ float sh[32];
+  const int64_t off = (int64_t)blockIdx.x * cols;
+  float dot = 0.f;
+  for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) dot += to_f(dy[off + c]) * to_f(s[off + c]);
+  dot = block_sum(dot, sh);
+  for (int64_t c = threadIdx.x; c < cols; c += blockDim.x)
+    dx[off + c] = from_f<T>(to_f(s[off + c]) * (to_f(dy[off + c]) - dot));
+}
+
+// ------------------------------------------------------- cross entropy ------
+__device__ __forceinline__ float softcap_f(float x, float cap) { return cap > 0.f ? cap * tanhf(x / cap) : x; }
+
+constexpr int kCeThreads = 512;
+
+template <typename T>
+__global__ void __launch_bounds__(kCeThreads)
+ce_fwd_kernel(const T* __restrict__ logits, const int32_t* __restrict__ labels, float* __restrict__ loss,
+              float* __restrict__ lse_out, int64_t classes, int64_t ld, float softcap, int vec_ok, int* __restrict__ flag) {
+  constexpr int VN = Vec16<T>::N;
+  __shared__ float shm[32], shs[32];
+  const int64_t row = blockIdx.x;
+  const T* xr = logits + row * ld;
+  float m = -INFINITY, s = 0.f;  // running max (natural units) and sum of exp(x - m)
+  int64_t vec_end = 0;
+  if (vec_ok) {
+    const int64_t nvec = classes / VN;
+    vec_end = nvec * VN;
+    for (int64_t vi = threadIdx.x; vi < nvec; vi += kCeThreads) {
+      Vec16<T> v;
+      v.load(xr + vi * VN);
+      float f[VN];
+      float vm = -INFINITY;
+#pragma unroll
+      for (int e = 0; e < VN; ++e) { f[e] = softcap_f(v.get(e), softcap); vm = fmaxf(vm, f[e]); }
+      if (vm > m) { s *= exp2f((m - vm) * kLog2e); m = vm; }
+#pragma unroll
+      for (int e = 0; e < VN; ++e) s += exp2f((f[e] - m) * kLog2e);
+    }
+  }
+  for (int64_t c = vec_end + threadIdx.x; c < classes; c += kCeThreads) {
+    float f = softcap_f(to_f(xr[c]), softcap);
+    if (f > m) { s *= exp2f((m - f) * kLog2e); m = f; }
+    s += exp2f((f - m) * kLog2e);
+  }
+  // combine (m, s) pairs across the block
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    float m2 = __shfl_xor_sync(0xffffffffu, m, o), s2 = __shfl_xor_sync(0xffffffffu, s, o);
+    float mm = fmaxf(m, m2);
+    s = (m == -INFINITY ? 0.f : s * exp2f((m - mm) * kLog2e)) + (m2 == -INFINITY ? 0.f : s2 * exp2f((m2 - mm) * kLog2e));
+    m = mm;
+  }
+  if (lane == 0) { shm[w] = m; shs[w] = s; }
+  __syncthreads();
+  if (w == 0) {
+    m = lane < kCeThreads / 32 ? shm[lane] : -INFINITY;
+    s = lane < kCeThreads / 32 ? shs[lane] : 0.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      float m2 = __shfl_xor_sync(0xffffffffu, m, o), s2 = __shfl_xor_sync(0xffffffffu, s, o);
+      float mm = fmaxf(m, m2);
+      s = (m == -INFINITY ? 0.f : s * exp2f((m - mm) * kLog2e)) + (m2 == -INFINITY ? 0.f : s2 * exp2f((m2 - mm) * kLog2e));
+      m = mm;
+    }
+    if (lane == 0) {
+      float lse = m + logf(s);
+      lse_out[row] = lse;
+      int32_t lab = labels[row];
+      float l = 0.f;
+      if (lab >= 0 && lab < classes) l = lse - softcap_f(to_f(xr[lab]), softcap);
+      else if (lab != -100 && flag) atomicMax(flag, 2);  // label out of range: recorded, row ignored
+      loss[row] = l;
+    }
+  }
+}
+
+// loss_sum[0] = sum(loss), valid_count[0] = #labels != -100; one block, fixed order.
+__global__ void __launch_bounds__(1024)
+ce_reduce_kernel(const float* __restrict__ loss, const int32_t* __restrict__ labels, int64_t rows,
+                 float* __restrict__ loss_sum, float* __restrict__ valid_count) {
+  __shared__ float sh[32];
+  float s = 0.f, n = 0.f;
+  for (int64_t r = threadIdx.x; r < rows; r += blockDim.x) {
+    s += loss[r];
+    n += labels[r] != -100 ? 1.f : 0.f;
+  }
+  s = block_sum(s, sh);
+  n = block_sum(n, sh);
+  if (threadIdx.x == 0) {
+    if (loss_sum) loss_sum[0] = s;
+    if (valid_count) valid_count[0] = n;
+  }
+}
+
+constexpr int kCeBwdChunk = 4096;  // elements of one row handled by one block
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+ce_bwd_kernel(const T* __restrict__ logits, const int32_t* __restrict__ labels, const float* __restrict__ lse,
+              T* __restrict__ dlogits, float scale_host, const float* __restrict__ scale_dev,
+              const float* __restrict__ count_dev, int64_t classes, int64_t ld, float softcap, int vec_ok) {
+  constexpr int VN = Vec16<T>::N;
+  const int64_t row = blockIdx.y;
+  const int64_t c0 = (int64_t)blockIdx.x * kCeBwdChunk;
+  const int64_t c1 = c0 + kCeBwdChunk < classes ? c0 + kCeBwdChunk : classes;
+  const int32_t lab = labels[row];
+  float scale = scale_host;
+  if (scale_dev) scale *= scale_dev[0];
+  if (count_dev) scale /= count_dev[0];
+  const bool ignored = !(lab >= 0 && lab < classes);
+  if (ignored) scale = 0.f;
+  const float l = lse[row];
+  const T* xr = logits + row * ld;
+  T* dr = dlogits + row * ld;
+  int64_t c = c0;
+  if (vec_ok) {
+    const int64_t v1 = c1 / VN * VN;
+    for (int64_t cc = c0 + (int64_t)threadIdx.x * VN; cc < v1; cc += 256 * VN) {
+      Vec16<T> v, o;
+      v.load(xr + cc);
+#pragma unroll
+      for (int e = 0; e < VN; ++e) {
+        float x = v.get(e), f = x, dcap = 1.f;
+        if (softcap > 0.f) { float t = tanhf(x / softcap); f = softcap * t; dcap = 1.f - t * t; }
+        float p = ignored ? 0.f : exp2f((f - l) * kLog2e);
+        if (cc + e == lab) p -= 1.f;
+        o.set(e, p * scale * dcap);
+      }
+      o.store(dr + cc);
+    }
+    c = v1 > c0 ? v1 : c0;
+  }
+  for (int64_t cc = c + threadIdx.x; cc < c1; cc += 256) {
+    float x = to_f(xr[cc]), f = x, dcap = 1.f;
+    if (softcap > 0.f) { float t = tanhf(x / softcap); f = softcap * t; dcap = 1.f - t * t; }
+    float p = ignored ? 0.f : exp2f((f - l) * kLog2e);
+    if (cc == lab) p -= 1.f;
+    dr[cc] = from_f<T>(p * scale * dcap);
+  }
+}
+
+template <typename T>
+static int softmax_launch(bool bwd, const void* a, const void* b, void* out, int64_t rows, int64_t cols, cudaStream_t st) {
+  constexpr int VN = Vec16<T>::N;
+  if (rows == 0) return MT_OK;
+  bool vec = cols % VN == 0 && aligned16(a) && aligned16(out) && (!b || aligned16(b)) && cols / VN <= 32 * (bwd ? 4 : 8);
+  const T* ap = (const T*)a; const T* bp = (const T*)b; T* op = (T*)out;
+  if (vec) {
+    int nvec = (int)(cols / VN);
+    unsigned grid = (unsigned)((rows + 3) / 4);
+    if (!bwd) {
+#define MT_SF(MV) softmax_fwd_warp<T, MV><<<grid, 128, 0, st>>>(ap, op, rows, (int)cols)
+      if (nvec <= 32) MT_SF(1); else if (nvec <= 64) MT_SF(2); else if (nvec <= 128) MT_SF(4); else MT_SF(8);
+#undef MT_SF
+    } else {
+#define MT_SB(MV) softmax_bwd_warp<T, MV><<<grid, 128, 0, st>>>(ap, bp, op, rows, (int)cols)
+      if (nvec <= 32) MT_SB(1); else if (nvec <= 64) MT_SB(2); else MT_SB(4);
+#undef MT_SB
+    }
+  } else {
+    if (!bwd) softmax_fwd_block<T><<<(unsigned)rows, 256, 0, st>>>(ap, op, rows, cols);
+    else softmax_bwd_block<T><<<(unsigned)rows, 256, 0, st>>>(ap, bp, op, rows, cols);
+  }
+  MT_LAUNCH_CHECK();
+  return MT_OK;
+}
+
+}  // namespace mt
+
+using namespace mt;
+
+extern "C" {
+
+int mt_softmax_fwd(const void* x, void* y, int64_t rows, int64_t cols, int dtype, void* stream) {
+  MT_REQUIRE(x && y && rows >= 0 && cols > 0, "softmax_fwd: bad arguments");
+  MT_DISPATCH_FLOAT(dtype, T, return softmax_launch<T>(false, x, nullptr, y, rows, cols, as_stream(stream)));
+  return MT_OK;
+}
+int mt_softmax_bwd(const void* dy, const void* s, void* dx, int64_t rows, int64_t cols, int dtype, void* stream) {
+  MT_REQUIRE(dy && s && dx && rows >= 0 && cols > 0, "softmax_bwd: bad arguments");
+  MT_DISPATCH_FLOAT(dtype, T, return softmax_launch<T>(true, dy, s, dx, rows, cols, as_stream(stream)));
+  return MT_OK;
+}
+
+int mt_ce_fwd(const void* logits, const int32_t* labels, float* loss, float* lse, float* loss_sum,
+              float* valid_count, int64_t rows, int64_t classes, int64_t ld, float softcap, int dtype,
+              void* stream) {
+  MT_REQUIRE(logits && labels && loss && lse && rows >= 0 && classes > 0 && ld >= classes, "ce_fwd: bad arguments");
+  cudaStream_t st = as_stream(stream);
+  if (rows > 0) {
+    int* flag = device_flag_ptr();
+    MT_DISPATCH_FLOAT(dtype, T, {
+      int vec_ok = aligned16(logits) && (ld % Vec16<T>::N == 0);
+      ce_fwd_kernel<T><<<(unsigned)rows, kCeThreads, 0, st>>>((const T*)logits, labels, loss, lse, classes, ld, softcap, vec_ok, flag);
+    });
+    MT_LAUNCH_CHECK();
+  }
+  if (loss_sum || valid_count) {
+    ce_reduce_kernel<<<1, 1024, 0, st>>>(loss, labels, rows, loss_sum, valid_count);
+    MT_LAUNCH_CHECK();
+  }
+  return MT_OK;
+}
+
+int mt_ce_bwd(const void* logits, const int32_t* labels, const float* lse, void* dlogits, float scale_host,
+              const float* scale_dev, const float* count_dev, int64_t rows, int64_t classes, int64_t ld,
+              float softcap, int dtype, void* stream) {
+  MT_REQUIRE(logits && labels && lse && dlogits && rows >= 0 && classes > 0 && ld >= classes, "ce_bwd: bad arguments");
+  MT_REQUIRE(rows <= 65535 * 1024, "ce_bwd: too many rows");
+  if (rows == 0) return MT_OK;
+  cudaStream_t st = as_stream(stream);
+  // rows on grid.y is limited to 65535: loop over slabs of rows
+  const int64_t slab = 65535;
+  for (int64_t r0 = 0; r0 < rows; r0 += slab) {
+    int64_t nr = rows - r0 < slab ? rows - r0 : slab;
+    dim3 grid((unsigned)((classes + kCeBwdChunk - 1) / kCeBwdChunk), (unsigned)nr);
+    MT_DISPATCH_FLOAT(dtype, T, {
+      int vec_ok = aligned16(logits) && aligned16(dlogits) && (ld % Vec16<T>::N == 0);
+      ce_bwd_kernel<T><<<grid, 256, 0, st>>>((const T*)logits + r0 * ld, labels + r0, lse + r0, (T*)dlogits + r0 * ld,
+                                             scale_host, scale_dev, count_dev, classes, ld, softcap, vec_ok);
+    });
+    MT_LAUNCH_CHECK();
+  }
+  return MT_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,305 @@
+"""Differentiable ops of the GPT training step: the `fused=True` branch of the
+reference's mytorch/nn/functional/* dispatchers, each op a forward call into
+the CUDA library plus a backward closure (same structure as e.g.
+mytorch/nn/functional/layers/linear.py:149-236).
+
+Inputs keep their leading dimensions; kernels see them flattened to rows.
+"""
+import math
+
+from .. import _lib
+from .. import fused_ops as K
+from ..array import DeviceArray, stream
+from ..tensor import Tensor
+
+
+def _needs_graph(*ts):
+    return Tensor.build_graph_enabled() and any(t is not None and t.requires_grad for t in ts)
+
+
+def _flat2d(arr):
+    return arr.reshape(-1, arr.shape[-1])
+
+
+def _param_grad_gemm(dy2, x2, weight):
+    """weight.grad (fp32) += dy2^T @ x2, straight into the accumulation buffer."""
+    buf = weight.param_grad_buffer() if weight.is_param else None
+    if buf is not None:
+        K.gemm(dy2, x2, trans_a=True, out=buf, accumulate=2 if dy2.dtype != "float32" else 1)
+    else:
+        weight._accumulate(K.gemm(dy2, x2, trans_a=True))
+
+
+# ---------------------------------------------------------------- linear ----
+def linear(x, weight, bias=None, auto=False, fused=True, act_func=None):
+    """y = act(x @ weight^T + bias), weight [out, in]
+    (mytorch/nn/functional/layers/linear.py:149-236). No transposed copy of the
+    weight is made: the GEMM reads it K-major in place."""
+    x2 = _flat2d(x.data)
+    want_pre = act_func is not None and _needs_graph(x, weight, bias)
+    res = K.gemm(x2, weight.data, trans_b=True, bias=None if bias is None else bias.data,
+                 act=act_func, preact=want_pre)
+    y2, pre = res if want_pre else (res, None)
+    out = Tensor(y2.reshape(*x.shape[:-1], weight.shape[0]))
+    if _needs_graph(x, weight, bias):
+        def _bw(g):
+            g2 = _flat2d(g)
+            if act_func is not None:
+                g2 = K.fused_activation_backward(pre, g2, act_func)
+            if weight.requires_grad:
+                _param_grad_gemm(g2, x2, weight)
+            if bias is not None and bias.requires_grad:
+                buf = bias.param_grad_buffer()
+                _lib.colsum(g2.ptr, buf.ptr, g2.shape[0], g2.shape[1], g2.code, buf.code, 1, stream())
+            if x.requires_grad:
+                x._accumulate(K.gemm(g2, weight.data).reshape(x.shape))
+        out.requires_grad = True
+        out.grad_fn, out.grad_fn_name = _bw, "<LinearBackward>"
+        out._add_parents(x, weight, bias)
+    return out
+
+
+# ------------------------------------------------------------- embedding ----
+def embedding(indices, weight, fused=True):
+    """weight[indices] (mytorch/nn/functional/layers/embedding.py:11-43)."""
+    idx = indices.data if isinstance(indices, Tensor) else DeviceArray.from_numpy(indices, "int32")
+    out = Tensor(K.fused_embedding_forward(weight.data, idx))
+    if _needs_graph(weight):
+        def _bw(g):
+            K.fused_embedding_backward(g.reshape(-1, weight.shape[1]), weight.data, idx, out=weight.param_grad_buffer())
+        out.requires_grad = True
+        out.grad_fn, out.grad_fn_name = _bw, "<EmbeddingBackward>"
+        out._add_parents(weight)
+    return out
+
+
+def token_position_embedding(indices, wte, wpe):
+    """wte[ids] + wpe[arange(T)] in one pass: the Embeddings module of
+    gpt2_trainer/gpt2.py:105-119."""
+    idx = indices.data if isinstance(indices, Tensor) else DeviceArray.from_numpy(indices, "int32")
+    B, T = idx.shape
+    V, E = wte.shape
+    out_arr = DeviceArray.empty((B, T, E), wte.dtype)
+    _lib.embedding_pos_fwd(wte.data.ptr, wpe.data.ptr, idx.ptr, out_arr.ptr, B * T, T, E, V, wte.data.code, stream())
+    out = Tensor(out_arr)
+    if _needs_graph(wte, wpe):
+        def _bw(g):
+            if wte.requires_grad:
+                K.fused_embedding_backward(g.reshape(-1, E), wte.data, idx, out=wte.param_grad_buffer())
+            if wpe.requires_grad:
+                _lib.pos_embedding_bwd(g.ptr, wpe.param_grad_buffer().ptr, B, T, E, g.code, stream())
+        out.requires_grad = True
+        out.grad_fn, out.grad_fn_name = _bw, "<EmbeddingsBackward>"
+        out._add_parents(wte, wpe)
+    return out
+
+
+# ------------------------------------------------------------------ norms ----
+def layernorm(x, weight=None, bias=None, eps=1e-5, training=True, auto=False, fused=True):
+    """mytorch/nn/functional/norm/layernorm.py:138-212."""
+    x2 = _flat2d(x.data)
+    g_arr = None if weight is None else weight.data
+    b_arr = None if bias is None else bias.data
+    y, mean, rstd = K.fused_layernorm_forward(x2, g_arr, b_arr, eps)
+    out = Tensor(y.reshape(x.shape))
+    if _needs_graph(x, weight, bias):
+        def _bw(g):
+            dg = weight.param_grad_buffer() if (weight is not None and weight.requires_grad) else None
+            db = bias.param_grad_buffer() if (bias is not None and bias.requires_grad) else None
+            dx, _, _ = K.fused_layernorm_backward(x2, mean, rstd, _flat2d(g), g_arr, None, dgamma_out=dg, dbeta_out=db)
+            if x.requires_grad:
+                x._accumulate(dx.reshape(x.shape))
+        out.requires_grad = True
+        out.grad_fn, out.grad_fn_name = _bw, "<LayerNormBackward>"
+        out._add_parents(x, weight, bias)
+    return out
+
+
+def rmsnorm(x, weight=None, eps=1e-5, training=True, auto=False, fused=True):
+    """mytorch/nn/functional/norm/rmsnorm.py:115-189."""
+    x2 = _flat2d(x.data)
+    g_arr = None if weight is None else weight.data
+    y, rstd = K.fused_rmsnorm_forward(x2, g_arr, eps)
+    out = Tensor(y.reshape(x.shape))
+    if _needs_graph(x, weight):
+        def _bw(g):
+            dg = weight.param_grad_buffer() if (weight is not None and weight.requires_grad) else None
+            dx, _ = K.fused_rmsnorm_backward(x2, rstd, _flat2d(g), g_arr, dgamma_out=dg)
+            if x.requires_grad:
+                x._accumulate(dx.reshape(x.shape))
+        out.requires_grad = True
+        out.grad_fn, out.grad_fn_name = _bw, "<RMSNormBackward>"
+        out._add_parents(x, weight)
+    return out
+
+
+# ------------------------------------------------------------ activations ----
+def _activation(x, name, label):
+    out = Tensor(K.fused_activation_forward(x.data, name))
+    if _needs_graph(x):
+        def _bw(g):
+            x._accumulate(K.fused_activation_backward(x.data, g, name))
+        out.requires_grad = True
+        out.grad_fn, out.grad_fn_name = _bw, label
+        out._add_parents(x)
+    return out
+
+
+def gelu(x, auto=False, fused=True):
+    """tanh-GELU (mytorch/nn/functional/activations/gelu.py:8-95)."""
+    return _activation(x, "gelu", "<GELUBackward>")
+
+
+def relu_squared(x, auto=False, fused=True):
+    """relu(x)^2 (mytorch/nn/functional/activations/relu_squared.py:8-80; the
+    gradient is 2*relu(x), i.e. the reference's `auto` path)."""
+    return _activation(x, "relu_squared", "<ReLUSquaredBackward>")
+
+
+def relu(x, auto=False, fused=True):
+    return _activation(x, "relu", "<ReLUBackward>")
+
+
+def softmax(x, dim=-1, auto=False, fused=True):
+    """Softmax over the last axis (mytorch/nn/functional/activations/softmax.py:15-159)."""
+    if dim not in (-1, x.ndim - 1):
+        raise NotImplementedError("softmax is implemented over the last axis")
+    s = K.fused_softmax_forward(_flat2d(x.data))
+    out = Tensor(s.reshape(x.shape))
+    if _needs_graph(x):
+        def _bw(g):
+            x._accumulate(K.fused_softmax_backward(_flat2d(g), s).reshape(x.shape))
+        out.requires_grad = True
+        out.grad_fn, out.grad_fn_name = _bw, "<SoftmaxBackward>"
+        out._add_parents(x)
+    return out
+
+
+# --------------------------------------------------------- cross entropy ----
+def cross_entropy(logits, targets, ignore_index=-100, softcap=None, auto=False, fused=True):
+    """Mean over valid rows of lse - logit[target]
+    (mytorch/nn/functional/losses/cross_entropy.py:107-178). The valid count and
+    the upstream gradient stay on the device (the reference reads both back to
+    the host, :120 and :144); the backward overwrites the logits buffer, as the
+    reference's fused kernel does. Unlike the reference's dispatcher (:178),
+    `softcap` is honoured when given."""
+    assert ignore_index == -100, "ignore_index is fixed to -100 like the reference's fused kernel"
+    lg = _flat2d(logits.data)
+    tg = targets.data if isinstance(targets, Tensor) else DeviceArray.from_numpy(targets, "int32")
+    tg = tg.reshape(-1)
+    loss_rows, lse, tot = K.fused_cross_entropy_forward(lg, tg, softcap, reduce=True)
+    loss_arr = DeviceArray.empty((), "float32")
+    # loss = sum / count, computed on the device: gemm-free scalar divide via axpby would
+    # need the count on the host, so a 1-element kernel-free trick is used: ce_bwd and
+    # this division both read the device scalars.
+    _lib.colsum(tot.ptr, loss_arr.ptr, 1, 1, tot.code, loss_arr.code, 0, stream())   # loss_arr = sum
+    out = Tensor(loss_arr)
+    out._ce_total = tot            # (sum, count) device scalars
+    out._mean_pending = True
+    if _needs_graph(logits):
+        def _bw(g):
+            # g is the upstream gradient of the MEAN loss (device scalar, fp32)
+            cnt = DeviceArray(tot.ptr + 4, (1,), "float32", base=tot)
+            K.fused_cross_entropy_backward(lg, tg, lse, softcap, scale=1.0, scale_dev=g, count_dev=cnt)
+            logits._accumulate(lg.reshape(logits.shape))
+        out.requires_grad = True
+        out.grad_fn, out.grad_fn_name = _bw, "<CrossEntropyBackward>"
+        out._add_parents(logits)
+    return out
+
+
+# -------------------------------------------------------------- attention ----
+def scaled_dot_product_attention(q, k, v, attn_mask=None, is_causal=False, softmax_scale=None, enable_gqa=False):
+    """q,k,v [B,H,S,D] contiguous (mytorch/nn/functional/flash_attention/
+    flash_attention.py:20-127). One backward launch (the reference runs its
+    backward kernel twice, :73-91)."""
+    _, _, _, o, m = K.fused_sdpa_forward(q.data, k.data, v.data, attn_mask, is_causal, softmax_scale)
+    out = Tensor(o)
+    if _needs_graph(q, k, v):
+        def _bw(g):
+            dq, dk, dv = K.fused_sdpa_backward(g, q.data, k.data, v.data, o, m, None, is_causal, softmax_scale)
+            for t, d in ((q, dq), (k, dk), (v, dv)):
+                if t.requires_grad:
+                    t._accumulate(d)
+        out.requires_grad = True
+        out.grad_fn, out.grad_fn_name = _bw, "<SDPABackward>"
+        out._add_parents(q, k, v)
+    return out
+
+
+def qkv_attention(qkv, num_heads, is_causal=True):
+    """Causal self-attention straight on the fused projection: qkv [B,T,3E] holds,
+    per head, a contiguous [q|k|v] group of 3*D columns — the layout produced by
+    `reshape(B,T,H,3D).transpose(1,2).chunk(3)` in gpt2_trainer/gpt2.py:168-177.
+    Q, K and V are read in place through strides and the output is written as
+    [B,T,E], so none of the reference's transpose/contiguous copies exist."""
+    B, T, E3 = qkv.shape
+    E = E3 // 3
+    D = E // num_heads
+    a = qkv.data
+    item = a.itemsize
+    sin = _lib.Strides3(T * E3, 3 * D, E3)
+    qv = DeviceArray(a.ptr, (B, num_heads, T, D), a.dtype, base=a)
+    kv = DeviceArray(a.ptr + D * item, (B, num_heads, T, D), a.dtype, base=a)
+    vv = DeviceArray(a.ptr + 2 * D * item, (B, num_heads, T, D), a.dtype, base=a)
+    o_arr = DeviceArray.empty((B, T, E), a.dtype)
+    sout = _lib.Strides3(T * E, D, E)
+    ov = DeviceArray(o_arr.ptr, (B, num_heads, T, D), a.dtype, base=o_arr)
+    _, _, _, _, m = K.fused_sdpa_forward(qv, kv, vv, None, is_causal, None, strides=(sin, sin, sin), out=ov, out_strides=sout)
+    out = Tensor(o_arr)
+    if _needs_graph(qkv):
+        def _bw(g):
+            dqkv = DeviceArray.empty((B, T, E3), a.dtype)
+            dqv = DeviceArray(dqkv.ptr, (B, num_heads, T, D), a.dtype, base=dqkv)
+            dkv = DeviceArray(dqkv.ptr + D * item, (B, num_heads, T, D), a.dtype, base=dqkv)
+            dvv = DeviceArray(dqkv.ptr + 2 * D * item, (B, num_heads, T, D), a.dtype, base=dqkv)
+            gv = DeviceArray(g.ptr, (B, num_heads, T, D), a.dtype, base=g)
+            K.fused_sdpa_backward(gv, qv, kv, vv, ov, m, None, is_causal, None, strides=(sin, sin, sin),
+                                  out=(dqv, dkv, dvv), out_strides=(sin, sin, sin), o_strides=sout, do_strides=sout)
+            qkv._accumulate(dqkv)
+        out.requires_grad = True
+        out.grad_fn, out.grad_fn_name = _bw, "<QKVAttentionBackward>"
+        out._add_parents(qkv)
+    return out
+
+
+# ------------------------------------------------------------------- rope ----
+def precompute_rotary_cos_sin(head_dim, max_position_embeddings=2048, base=10000, scaling_factor=1.0):
+    """cos/sin tables [T, D] fp32 with duplicated halves
+    (mytorch/nn/functional/other/rotary_embeddings.py:57-88)."""
+    import numpy as np
+    every_other = np.arange(0, head_dim, 2, dtype=np.float32)
+    inv_freq = (1.0 / (base ** (every_other / head_dim))).astype(np.float32)
+    t = np.arange(max_position_embeddings, dtype=np.float32) / scaling_factor
+    freqs = t[:, None] @ inv_freq[None, :]
+    freqs = np.concatenate([freqs, freqs], axis=-1)
+    return (DeviceArray.from_numpy(np.cos(freqs).astype(np.float32)),
+            DeviceArray.from_numpy(np.sin(freqs).astype(np.float32)))
+
+
+def apply_rotary_pos_embed(q, k, cos, sin, unsqueeze_dim=2, auto=False, fused=True):
+    """Half-split rotary embedding of q and k [B,T,H,D]
+    (mytorch/nn/functional/other/rotary_embeddings.py:111-158). Out of place
+    here (the reference rotates in place), so the inputs stay valid."""
+    outs = []
+    for x in (q, k):
+        arr = x.data.copy()
+        K.fused_rope_forward(arr, cos, sin)
+        o = Tensor(arr)
+        if _needs_graph(x):
+            def _bw(g, x=x):
+                gg = g.copy()
+                K.fused_rope_backward(gg, cos, sin)
+                x._accumulate(gg)
+            o.requires_grad = True
+            o.grad_fn, o.grad_fn_name = _bw, "<RopeBackward>"
+            o._add_parents(x)
+        outs.append(o)
+    return outs[0], outs[1]
+
+
+def dropout(x, dropout_p=0.0, training=True):
+    """Only p = 0 is on the GPT training path (all configs use 0.0)."""
+    if dropout_p != 0.0 and training:
+        raise NotImplementedError("dropout with p > 0 is outside the GPT training-step path")
+    return x

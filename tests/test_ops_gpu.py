@@ -1,0 +1,325 @@
+"""Parity of every op of the C ABI (called through mytorch_b200.fused_ops, i.e.
+ctypes -> libmytorch_b200.so) against the NumPy oracle on the same seeded
+inputs. Tolerances: fp32 1e-4, fp16/bf16 1e-2, relative to the largest
+magnitude of the expected tensor (the path's stated per-op bars). Half cases
+use the fp32 oracle evaluated on half-rounded inputs."""
+import numpy as np
+import pytest
+
+from oracle import ops as O
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = ["float32", "float16", "bfloat16"]
+TOL = {"float32": 1e-4, "float16": 1e-2, "bfloat16": 2e-2}
+
+
+@pytest.fixture(scope="module")
+def mt():
+    import mytorch_b200 as m
+    return m
+
+
+def rnd(a, dtype):
+    """Round host data to the device dtype, returned as fp32."""
+    from mytorch_b200.array import f32_to_bf16_bits, bf16_bits_to_f32
+    a = np.asarray(a, dtype=np.float32)
+    if dtype == "float16":
+        return a.astype(np.float16).astype(np.float32)
+    if dtype == "bfloat16":
+        return bf16_bits_to_f32(f32_to_bf16_bits(a)).reshape(a.shape)
+    return a
+
+
+def dev(mt, a, dtype):
+    return mt.DeviceArray.from_numpy(a, dtype)
+
+
+def close(got, want, rel, what=""):
+    got = np.asarray(got, dtype=np.float64)
+    want = np.asarray(want, dtype=np.float64)
+    assert got.shape == want.shape, (what, got.shape, want.shape)
+    assert np.isfinite(got).all(), f"{what}: non-finite values"
+    scale = max(np.abs(want).max(), 1e-6)   # an all-zero expectation is compared absolutely
+    err = np.abs(got - want).max() / scale
+    assert err <= rel, f"{what}: max err {err:.3e} (scale {scale:.3e}) > {rel}"
+
+
+def no_device_flag(mt):
+    import ctypes
+    f = ctypes.c_int(0)
+    mt._lib.device_flag_read(ctypes.byref(f), mt.stream())
+    assert f.value == 0, f"device status word = {f.value}"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", [(37, 96), (64, 768), (5, 1000), (130, 2048), (3, 52)])
+@pytest.mark.parametrize("bias", [True, False])
+def test_layernorm(mt, dtype, shape, bias):
+    F = mt.fused_ops
+    r = np.random.default_rng(1)
+    x, g, b, dy = (rnd(r.standard_normal(s), dtype) for s in (shape, shape[1:], shape[1:], shape))
+    y, mu, rs = O.layernorm_fwd(x, g, b if bias else None)
+    dx, dg, db = O.layernorm_bwd(x, mu, rs, dy, g)
+    dx_, dg_, db_ = None, None, None
+    X, G, B, DY = dev(mt, x, dtype), dev(mt, g, dtype), dev(mt, b, dtype), dev(mt, dy, dtype)
+    Y, MU, RS = F.fused_layernorm_forward(X, G, B if bias else None)
+    DX, DG, DB = F.fused_layernorm_backward(X, MU, RS, DY, G, B if bias else None)
+    t = TOL[dtype]
+    close(Y.numpy(), y, t, "y"); close(MU.numpy(), mu, max(t, 1e-4) if dtype == "float32" else t, "mean")
+    close(RS.numpy(), rs, t, "rstd"); close(DX.numpy(), dx, t, "dx")
+    close(DG.numpy(), dg, 1e-4 if dtype == "float32" else t, "dgamma")
+    if bias:
+        close(DB.numpy(), db, 1e-4 if dtype == "float32" else t, "dbeta")
+    # accumulate form adds into existing buffers; two runs are bit-identical
+    acc = mt.DeviceArray.from_numpy(np.ones(shape[1], np.float32))
+    F.fused_layernorm_backward(X, MU, RS, DY, G, None, dgamma_out=acc)
+    close(acc.numpy(), dg + 1, 1e-4 if dtype == "float32" else t, "dgamma+=")
+    DG2 = F.fused_layernorm_backward(X, MU, RS, DY, G, None)[1]
+    assert np.array_equal(DG2.numpy(), DG.numpy())
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", [(29, 128), (77, 1280), (9, 50)])
+@pytest.mark.parametrize("weight", [True, False])
+def test_rmsnorm(mt, dtype, shape, weight):
+    F = mt.fused_ops
+    r = np.random.default_rng(2)
+    x, g, dy = (rnd(r.standard_normal(s), dtype) for s in (shape, shape[1:], shape))
+    y, rs = O.rmsnorm_fwd(x, g if weight else None)
+    dx, dg = O.rmsnorm_bwd(x, rs, dy, g if weight else None)
+    X, G, DY = dev(mt, x, dtype), dev(mt, g, dtype), dev(mt, dy, dtype)
+    Y, RS = F.fused_rmsnorm_forward(X, G if weight else None)
+    DX, DG = F.fused_rmsnorm_backward(X, RS, DY, G if weight else None)
+    t = TOL[dtype]
+    close(Y.numpy(), y, t, "y"); close(RS.numpy(), rs, t, "rstd"); close(DX.numpy(), dx, t, "dx")
+    if weight:
+        close(DG.numpy(), dg, t, "dgamma")
+    else:
+        assert DG is None
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", [(33, 200), (64, 1024), (7, 4096), (5, 33)])
+def test_softmax(mt, dtype, shape):
+    F = mt.fused_ops
+    r = np.random.default_rng(3)
+    x, dy = rnd(r.standard_normal(shape), dtype), rnd(r.standard_normal(shape), dtype)
+    s = O.softmax_fwd(x)
+    S = F.fused_softmax_forward(dev(mt, x, dtype))
+    close(S.numpy(), s, TOL[dtype], "softmax")
+    s_r = rnd(s, dtype)
+    DX = F.fused_softmax_backward(dev(mt, dy, dtype), dev(mt, s_r, dtype))
+    close(DX.numpy(), O.softmax_bwd(dy, s_r), TOL[dtype], "softmax bwd")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("act", ["gelu", "relu_squared", "relu"])
+def test_activations(mt, dtype, act):
+    F = mt.fused_ops
+    r = np.random.default_rng(4)
+    x, dy = rnd(r.standard_normal((31, 1003)) * 2, dtype), rnd(r.standard_normal((31, 1003)), dtype)
+    fwd = {"gelu": O.gelu_fwd, "relu_squared": O.relu2_fwd, "relu": lambda v: np.maximum(v, 0)}[act]
+    bwd = {"gelu": O.gelu_bwd, "relu_squared": O.relu2_bwd, "relu": lambda v, d: (v > 0) * d}[act]
+    close(F.fused_activation_forward(dev(mt, x, dtype), act).numpy(), fwd(x), TOL[dtype], act)
+    close(F.fused_activation_backward(dev(mt, x, dtype), dev(mt, dy, dtype), act).numpy(), bwd(x, dy), TOL[dtype], act + " bwd")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows,classes,ld", [(41, 131, 131), (64, 50257, 50264), (16, 50304, 50304), (3, 7, 16)])
+def test_cross_entropy(mt, dtype, rows, classes, ld):
+    F = mt.fused_ops
+    r = np.random.default_rng(5)
+    x = rnd(r.standard_normal((rows, classes)) * 2, dtype)
+    y = r.integers(0, classes, rows).astype(np.int32)
+    y[rows // 3] = -100
+    buf = np.zeros((rows, ld), np.float32)
+    buf[:, :classes] = x
+    L = dev(mt, buf, dtype)
+    Lv = mt.DeviceArray(L.ptr, (rows, classes), dtype, base=L)   # logical [rows, classes] view, row stride ld
+    Y = mt.DeviceArray.from_numpy(y)
+    loss, lse, tot = F.fused_cross_entropy_forward(Lv, Y, ld=ld, reduce=True)
+    want_loss, want_lse = O.cross_entropy_rows(x, y)
+    close(lse.numpy(), want_lse, 1e-5, "lse"); close(loss.numpy(), want_loss, 1e-4, "loss")
+    t = tot.numpy()
+    assert t[1] == rows - 1
+    close(t[0] / t[1], O.cross_entropy_fwd(x, y), 1e-5, "mean loss")
+    # backward over the logits, scale taken from device scalars (grad_output 3.0 / valid count)
+    three = mt.DeviceArray.from_numpy(np.array([3.0], np.float32))
+    cnt = mt.DeviceArray(tot.ptr + 4, (1,), "float32", base=tot)
+    G = F.fused_cross_entropy_backward(Lv, Y, lse, scale=1.0, ld=ld, scale_dev=three, count_dev=cnt)
+    assert G.ptr == L.ptr
+    got = L.numpy()[:, :classes]
+    close(got, O.cross_entropy_bwd(x, y, 3.0), 2e-2 if dtype != "float32" else 1e-4, "dlogits")
+    assert np.all(got[rows // 3] == 0)
+    no_device_flag(mt)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embedding(mt, dtype):
+    F = mt.fused_ops
+    r = np.random.default_rng(6)
+    V, D = 97, 72
+    w = rnd(r.standard_normal((V, D)), dtype)
+    idx = r.integers(0, V, (6, 50)).astype(np.int32)
+    idx[0, :20] = 5                      # a long run of one token
+    dy = rnd(r.standard_normal((6, 50, D)), dtype)
+    W, I, DY = dev(mt, w, dtype), mt.DeviceArray.from_numpy(idx), dev(mt, dy, dtype)
+    close(F.fused_embedding_forward(W, I).numpy(), O.embedding_fwd(w, idx), 0.0, "gather")
+    dw = F.fused_embedding_backward(DY, W, I)
+    close(dw.numpy(), O.embedding_bwd(dy, idx, V), 1e-5, "scatter-add")
+    dw2 = F.fused_embedding_backward(DY, W, I)
+    assert np.array_equal(dw.numpy(), dw2.numpy()), "scatter-add must be reproducible"
+    F.fused_embedding_backward(DY, W, I, out=dw)
+    close(dw.numpy(), 2 * O.embedding_bwd(dy, idx, V), 1e-5, "scatter-add accumulate")
+    no_device_flag(mt)
+
+
+def test_embedding_empty_and_out_of_range(mt):
+    import ctypes
+    F = mt.fused_ops
+    W = mt.DeviceArray.from_numpy(np.ones((4, 8), np.float32))
+    out = F.fused_embedding_forward(W, mt.DeviceArray.from_numpy(np.zeros((0,), np.int32)))
+    assert out.shape == (0, 8)
+    out = F.fused_embedding_forward(W, mt.DeviceArray.from_numpy(np.array([1, 9], np.int32)))
+    f = ctypes.c_int(0)
+    mt._lib.device_flag_read(ctypes.byref(f), mt.stream())
+    assert f.value == 1, "an out-of-range index must be recorded in the device status word"
+    assert np.all(out.numpy()[1] == 0) and np.all(out.numpy()[0] == 1)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_rope(mt, dtype):
+    F = mt.fused_ops
+    r = np.random.default_rng(7)
+    B, T, H, D = 2, 19, 3, 32
+    x, dy = rnd(r.standard_normal((B, T, H, D)), dtype), rnd(r.standard_normal((B, T, H, D)), dtype)
+    cos, sin = O.rope_cos_sin(D, T)
+    C_, S_ = mt.DeviceArray.from_numpy(cos), mt.DeviceArray.from_numpy(sin)
+    X = dev(mt, x, dtype)
+    F.fused_rope_forward(X, C_, S_)
+    close(X.numpy(), O.rope_fwd(x, cos, sin), TOL[dtype], "rope")
+    DY = dev(mt, dy, dtype)
+    F.fused_rope_backward(DY, C_, S_)
+    close(DY.numpy(), O.rope_bwd(dy, cos, sin), TOL[dtype], "rope bwd")
+
+
+GEMM_SHAPES = [(128, 256, 64), (256, 512, 128), (200, 136, 72), (1024, 768, 768), (64, 72, 40),
+               (384, 2304, 768), (130, 520, 1032), (8, 8, 8), (1, 24, 16)]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("ta,tb", [(0, 1), (0, 0), (1, 0), (1, 1)])
+@pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
+def test_gemm(mt, dtype, ta, tb, M, N, K):
+    F = mt.fused_ops
+    r = np.random.default_rng(8)
+    a = rnd(r.standard_normal((K, M) if ta else (M, K)), dtype)
+    b = rnd(r.standard_normal((N, K) if tb else (K, N)), dtype)
+    want = (a.T if ta else a).astype(np.float64) @ (b.T if tb else b).astype(np.float64)
+    C = F.gemm(dev(mt, a, dtype), dev(mt, b, dtype), trans_a=bool(ta), trans_b=bool(tb))
+    close(C.numpy(), want, TOL[dtype], "gemm")
+    no_device_flag(mt)
+
+
+@pytest.mark.parametrize("dtype", ["float16", "bfloat16"])
+def test_gemm_epilogues_and_fp32_out(mt, dtype):
+    F = mt.fused_ops
+    r = np.random.default_rng(9)
+    M, N, K = 300, 264, 200
+    x, w, b = rnd(r.standard_normal((M, K)), dtype), rnd(r.standard_normal((N, K)) * 0.1, dtype), rnd(r.standard_normal(N), dtype)
+    pre = x @ w.T + b
+    X, W, B = dev(mt, x, dtype), dev(mt, w, dtype), dev(mt, b, dtype)
+    for act, f in (("gelu", O.gelu_fwd), ("relu_squared", O.relu2_fwd), (None, lambda v: v)):
+        out, p = F.gemm(X, W, trans_b=True, bias=B, act=act, preact=True)
+        close(p.numpy(), pre, TOL[dtype], "preact"); close(out.numpy(), f(pre), TOL[dtype], f"act {act}")
+    # fp32 output, overwrite then read-modify-write then split-K atomic accumulation
+    acc = F.gemm(X, W, trans_b=True, out_dtype="float32")
+    close(acc.numpy(), x @ w.T, 1e-3, "fp32 out")
+    F.gemm(X, W, trans_b=True, out=acc, accumulate=1)
+    close(acc.numpy(), 2 * (x @ w.T), 1e-3, "accumulate=1")
+    dy = rnd(r.standard_normal((4096, 136)), dtype)
+    xx = rnd(r.standard_normal((4096, 200)), dtype)
+    g = mt.DeviceArray.from_numpy(np.ones((136, 200), np.float32))
+    F.gemm(dev(mt, dy, dtype), dev(mt, xx, dtype), trans_a=True, out=g, accumulate=2)
+    close(g.numpy(), 1 + dy.T.astype(np.float64) @ xx, 1e-3, "split-K wgrad")
+    # the reference-shaped entry points
+    pre_, post_ = F.fused_linear_forward(X, dev(mt, np.ascontiguousarray(w.T), dtype), B, "gelu")
+    close(pre_.numpy(), pre, TOL[dtype], "fused_linear pre"); close(post_.numpy(), O.gelu_fwd(pre), TOL[dtype], "fused_linear post")
+    no_device_flag(mt)
+
+
+def test_gemm_tensor_core_matches_cuda_core_kernel(mt):
+    """Same fp16 inputs through both device kernels: differences are only
+    accumulation order (fp32), far below the fp16 output rounding."""
+    F = mt.fused_ops
+    r = np.random.default_rng(10)
+    a = mt.DeviceArray.from_numpy(r.standard_normal((512, 384)), "float16")
+    b = mt.DeviceArray.from_numpy(r.standard_normal((640, 384)), "float16")
+    tc = F.gemm(a, b, trans_b=True, out_dtype="float32").numpy()
+    mt._lib.gemm_force_simt(1)
+    try:
+        cc = F.gemm(a, b, trans_b=True, out_dtype="float32").numpy()
+    finally:
+        mt._lib.gemm_force_simt(0)
+    close(tc, cc, 1e-5, "tcgen05 vs CUDA-core")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("B,H,S,D,causal", [(2, 3, 70, 32, True), (1, 2, 128, 64, True), (2, 2, 257, 64, True),
+                                            (1, 2, 100, 128, True), (1, 2, 64, 64, False), (1, 1, 1, 64, True),
+                                            (1, 2, 33, 64, False)])
+def test_attention(mt, dtype, B, H, S, D, causal):
+    F = mt.fused_ops
+    r = np.random.default_rng(11)
+    q, k, v, do = (rnd(r.standard_normal((B, H, S, D)), dtype) for _ in range(4))
+    o, p = O.attention_fwd(q, k, v, causal=causal)
+    dq, dk, dv = O.attention_bwd(q, k, v, p, do)
+    Q, K, V, DO = (dev(mt, t, dtype) for t in (q, k, v, do))
+    _, _, _, Ou, M = F.fused_sdpa_forward(Q, K, V, causal=causal)
+    t = TOL[dtype]
+    close(Ou.numpy(), o, t, "o")
+    s = np.einsum("bhid,bhjd->bhij", q, k) / np.sqrt(D)
+    if causal:
+        s = s + np.triu(np.full((S, S), -np.inf), 1)
+    lse = np.log(np.exp(s - s.max(-1, keepdims=True)).sum(-1)) + s.max(-1)
+    close(M.numpy(), lse, 1e-3 if dtype != "float32" else 1e-5, "lse")
+    DQ, DK, DV = F.fused_sdpa_backward(DO, Q, K, V, Ou, M, causal=causal)
+    close(DQ.numpy(), dq, 2 * t, "dq"); close(DK.numpy(), dk, 2 * t, "dk"); close(DV.numpy(), dv, 2 * t, "dv")
+    no_device_flag(mt)
+
+
+def test_golden_small_vectors_fp32(mt, golden_ops, op_inputs):
+    """The committed reference outputs, fp32, through the library."""
+    F = mt.fused_ops
+    d, g = op_inputs, golden_ops
+    D = lambda a: mt.DeviceArray.from_numpy(a)
+    X, G, B = D(d["ln_x"]), D(d["ln_g"]), D(d["ln_b"])
+    Y, MU, RS = F.fused_layernorm_forward(X, G, B)
+    DX, DG, DB = F.fused_layernorm_backward(X, MU, RS, D(d["ln_dy"]), G, B)
+    close(Y.numpy(), g["ln_y"], 1e-4); close(DX.numpy(), g["ln_dx"], 1e-4)
+    close(DG.numpy(), g["ln_dg"], 1e-4); close(DB.numpy(), g["ln_db"], 1e-4)
+    Y, RS = F.fused_rmsnorm_forward(D(d["rms_x"]), D(d["rms_g"]))
+    close(Y.numpy(), g["rms_y"], 1e-4)
+    close(F.fused_softmax_forward(D(d["sm_x"])).numpy(), g["sm_y"], 1e-4)
+    close(F.gemm(D(d["lin_x"]), D(d["lin_w"]), trans_b=True, bias=D(d["lin_b"])).numpy(), g["lin_y"], 1e-4)
+    close(F.gemm(D(d["lin_dy"]), D(d["lin_w"])).numpy(), g["lin_dx"], 1e-4)
+    close(F.gemm(D(d["lin_dy"]), D(d["lin_x"]), trans_a=True).numpy(), g["lin_dw"], 1e-4)
+    close(F.fused_activation_forward(D(d["act_x"]), "gelu").numpy(), g["gelu_y"], 1e-4)
+    close(F.fused_activation_backward(D(d["act_x"]), D(d["act_dy"]), "gelu").numpy(), g["gelu_dx"], 1e-4)
+    close(F.fused_activation_backward(D(d["act_x"]), D(d["act_dy"]), "relu_squared").numpy(), g["relu2_dx"], 1e-4)
+    L = D(d["ce_x"]); Yl = D(d["ce_y"])
+    loss, lse, tot = F.fused_cross_entropy_forward(L, Yl, reduce=True)
+    t = tot.numpy()
+    close(t[0] / t[1], g["ce_loss"], 1e-5)
+    F.fused_cross_entropy_backward(L, Yl, lse, scale=1.0 / t[1])
+    close(L.numpy(), g["ce_dx"], 1e-4)
+    close(F.fused_embedding_backward(D(d["emb_dy"]), D(d["emb_w"]), D(d["emb_idx"])).numpy(), g["emb_dw"], 1e-5)
+    Q, K, V = D(d["at_q"]), D(d["at_k"]), D(d["at_v"])
+    _, _, _, Ou, M = F.fused_sdpa_forward(Q, K, V, causal=True)
+    close(Ou.numpy(), g["at_o"], 1e-4)
+    DQ, DK, DV = F.fused_sdpa_backward(D(d["at_do"]), Q, K, V, Ou, M, causal=True)
+    close(DQ.numpy(), g["at_dq"], 1e-4); close(DK.numpy(), g["at_dk"], 1e-4); close(DV.numpy(), g["at_dv"], 1e-4)
+    Xr = D(d["rope_x"])
+    F.fused_rope_forward(Xr, D(g["rope_cos"]), D(g["rope_sin"]))
+    close(Xr.numpy(), g["rope_y"], 1e-4)
