@@ -114,15 +114,15 @@ int mt_softmax_bwd(const void* dy, const void* s, void* dx, int64_t rows, int64_
 /* fused_cross_entropy_forward / fused_cross_entropy_backward
  * (mytorch/nn/functional/fused_ops/cross_entropy.py:263, :324). `ld` is the row
  * stride of logits in elements (>= classes). Labels are int32, -100 = ignored.
- * fwd writes loss[rows], lse[rows] (fp32) and, if loss_sum/valid_count are not
- * NULL, adds sum(loss) and the number of valid rows to them (device scalars).
+ * fwd writes loss[rows], lse[rows] (fp32) and, where the pointers are not NULL,
+ * the device scalars loss_sum = sum(loss), valid_count = number of rows whose
+ * label is not -100, loss_mean = loss_sum / valid_count (summed in a fixed order).
  * bwd writes (softmax - onehot) * scale into dlogits (may alias logits);
- * scale = *scale_dev * scale_host, and if inv_count_dev != NULL the result is
- * also divided by that device scalar (the valid-row count), so no host
- * read-back is needed. */
+ * scale = scale_host * (*scale_dev if given) / (*count_dev if given), so the
+ * upstream gradient and the valid-row count never have to be read back to the host. */
 int mt_ce_fwd(const void* logits, const int32_t* labels, float* loss, float* lse,
-              float* loss_sum, float* valid_count, int64_t rows, int64_t classes, int64_t ld,
-              float softcap, int dtype, void* stream);
+              float* loss_sum, float* valid_count, float* loss_mean, int64_t rows, int64_t classes,
+              int64_t ld, float softcap, int dtype, void* stream);
 int mt_ce_bwd(const void* logits, const int32_t* labels, const float* lse, void* dlogits,
               float scale_host, const float* scale_dev, const float* count_dev,
               int64_t rows, int64_t classes, int64_t ld, float softcap, int dtype, void* stream);
@@ -229,6 +229,15 @@ int mt_adamw_multi(const mt_tensor_list* L, int g_dtype, int half_dtype,
                    float lr, float lr_t, float beta1, float beta2, float eps,
                    const float* inv_scale_dev, const float* sumsq_dev, float max_norm,
                    const float* found_inf_dev, int zero_grad, void* stream);
+
+/* GradScaler.update (mytorch/accelerate.py:91-121) on the device, so the step never
+ * waits for the host: state = {scale, 1/(scale*accum_steps), clean-step counter,
+ * skipped-step counter} (4 floats). On *found_inf != 0 the scale is multiplied by
+ * `backoff` and the counter reset; otherwise the counter grows and at `interval`
+ * the scale is multiplied by `growth`. dynamic = 0 keeps the scale fixed (fp32 /
+ * bf16 training) and only refreshes state[1] and the skipped-step counter. */
+int mt_scaler_update(float* state, const float* found_inf, float growth, float backoff,
+                     int interval, float inv_accum, int dynamic, void* stream);
 
 /* cupyx.distributed.NCCLBackend as used by mytorch/accelerate.py:154-159
  * (init), :249-250 (broadcast), :732-736/:757-772/:833-837 (all_reduce),

@@ -87,7 +87,7 @@ _SIG = {
     "mt_rmsnorm_bwd": [_p, _p, _p, _p, _p, _p, _i64, _i64, _i, _i, _p],
     "mt_softmax_fwd": [_p, _p, _i64, _i64, _i, _p],
     "mt_softmax_bwd": [_p, _p, _p, _i64, _i64, _i, _p],
-    "mt_ce_fwd": [_p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _f, _i, _p],
+    "mt_ce_fwd": [_p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _f, _i, _p],
     "mt_ce_bwd": [_p, _p, _p, _p, _f, _p, _p, _i64, _i64, _i64, _f, _i, _p],
     "mt_embedding_fwd": [_p, _p, _p, _i64, _i64, _i64, _i, _p],
     "mt_embedding_bwd": [_p, _p, _p, _p, _i64, _i64, _i64, _i, _p],
@@ -102,6 +102,7 @@ _SIG = {
     "mt_attn_force_simt": [_i],
     "mt_gradnorm_multi": [C.POINTER(TensorList), _i, _p, _p, _p, _p],
     "mt_adamw_multi": [C.POINTER(TensorList), _i, _i, _f, _f, _f, _f, _f, _p, _p, _f, _p, _i, _p],
+    "mt_scaler_update": [_p, _p, _f, _f, _i, _f, _i, _p],
     "mt_comm_unique_id": [_p],
     "mt_comm_init": [_pp, _p, _i, _i],
     "mt_comm_broadcast": [_p, _p, _i64, _i, _i, _p],

@@ -93,11 +93,41 @@ adamw_kernel(mt_tensor_list L, float lr, float lr_t, float beta1, float beta2, f
   }
 }
 
+// Loss-scale state machine on the device. state = {scale, inv_total, unskipped, skipped_steps}
+// with inv_total = 1 / (scale * accumulation_steps).
+__global__ void scaler_update_kernel(float* state, const float* found_inf, float growth, float backoff,
+                                     int interval, float inv_accum, int dynamic) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  float scale = state[0], unskipped = state[2];
+  const bool bad = found_inf && found_inf[0] != 0.f;
+  if (bad) state[3] += 1.f;
+  if (dynamic) {
+    if (bad) {
+      scale *= backoff;
+      unskipped = 0.f;
+    } else {
+      unskipped += 1.f;
+      if ((int)unskipped == interval) { scale *= growth; unskipped = 0.f; }
+    }
+  }
+  state[0] = scale;
+  state[1] = inv_accum / scale;
+  state[2] = unskipped;
+}
+
 }  // namespace mt
 
 using namespace mt;
 
 extern "C" {
+
+int mt_scaler_update(float* state, const float* found_inf, float growth, float backoff, int interval,
+                     float inv_accum, int dynamic, void* stream) {
+  MT_REQUIRE(state, "scaler_update: bad arguments");
+  scaler_update_kernel<<<1, 32, 0, as_stream(stream)>>>(state, found_inf, growth, backoff, interval, inv_accum, dynamic);
+  MT_LAUNCH_CHECK();
+  return MT_OK;
+}
 
 int mt_gradnorm_multi(const mt_tensor_list* L, int g_dtype, const float* inv_scale_dev, float* sumsq,
                       float* found_inf, void* stream) {

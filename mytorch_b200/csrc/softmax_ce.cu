@@ -188,7 +188,7 @@ ce_fwd_kernel(const T* __restrict__ logits, const int32_t* __restrict__ labels, 
 // loss_sum[0] = sum(loss), valid_count[0] = #labels != -100; one block, fixed order.
 __global__ void __launch_bounds__(1024)
 ce_reduce_kernel(const float* __restrict__ loss, const int32_t* __restrict__ labels, int64_t rows,
-                 float* __restrict__ loss_sum, float* __restrict__ valid_count) {
+                 float* __restrict__ loss_sum, float* __restrict__ valid_count, float* __restrict__ loss_mean) {
   __shared__ float sh[32];
   float s = 0.f, n = 0.f;
   for (int64_t r = threadIdx.x; r < rows; r += blockDim.x) {
@@ -200,6 +200,7 @@ ce_reduce_kernel(const float* __restrict__ loss, const int32_t* __restrict__ lab
   if (threadIdx.x == 0) {
     if (loss_sum) loss_sum[0] = s;
     if (valid_count) valid_count[0] = n;
+    if (loss_mean) loss_mean[0] = s / n;
   }
 }
 
@@ -294,7 +295,7 @@ int mt_softmax_bwd(const void* dy, const void* s, void* dx, int64_t rows, int64_
 }
 
 int mt_ce_fwd(const void* logits, const int32_t* labels, float* loss, float* lse, float* loss_sum,
-              float* valid_count, int64_t rows, int64_t classes, int64_t ld, float softcap, int dtype,
+              float* valid_count, float* loss_mean, int64_t rows, int64_t classes, int64_t ld, float softcap, int dtype,
               void* stream) {
   MT_REQUIRE(logits && labels && loss && lse && rows >= 0 && classes > 0 && ld >= classes, "ce_fwd: bad arguments");
   cudaStream_t st = as_stream(stream);
@@ -306,8 +307,8 @@ int mt_ce_fwd(const void* logits, const int32_t* labels, float* loss, float* lse
     });
     MT_LAUNCH_CHECK();
   }
-  if (loss_sum || valid_count) {
-    ce_reduce_kernel<<<1, 1024, 0, st>>>(loss, labels, rows, loss_sum, valid_count);
+  if (loss_sum || valid_count || loss_mean) {
+    ce_reduce_kernel<<<1, 1024, 0, st>>>(loss, labels, rows, loss_sum, valid_count, loss_mean);
     MT_LAUNCH_CHECK();
   }
   return MT_OK;

@@ -168,17 +168,17 @@ def fused_softmax_backward(dy, s):
 # ------------------------------------------------------------- cross entropy ----
 def fused_cross_entropy_forward(logits, labels, softcap=None, ld=None, reduce=False):
     """logits [N,C], labels int32 [N] -> (loss[N], lse[N]) fp32
-    (fused_ops/cross_entropy.py:263). With reduce=True also returns device
-    scalars (sum of loss, number of valid rows) so no host read is needed."""
+    (fused_ops/cross_entropy.py:263). With reduce=True also returns a device
+    array (sum of loss, number of valid rows, mean loss) so no host read is needed."""
     logits, labels = _A(logits), _A(labels)
     n, c = logits.shape
     ld = ld or c
     assert labels.dtype == "int32"
     loss = DeviceArray.empty((n,), "float32")
     lse = DeviceArray.empty((n,), "float32")
-    tot = DeviceArray.empty((2,), "float32") if reduce else None
+    tot = DeviceArray.empty((3,), "float32") if reduce else None
     _lib.ce_fwd(logits.ptr, labels.ptr, loss.ptr, lse.ptr, tot.ptr if reduce else None,
-                tot.ptr + 4 if reduce else None, n, c, ld, float(softcap or 0.0), logits.code, stream())
+                tot.ptr + 4 if reduce else None, tot.ptr + 8 if reduce else None, n, c, ld, float(softcap or 0.0), logits.code, stream())
     if reduce:
         return loss, lse, tot
     return loss, lse

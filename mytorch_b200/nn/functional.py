@@ -188,14 +188,7 @@ def cross_entropy(logits, targets, ignore_index=-100, softcap=None, auto=False, 
     tg = targets.data if isinstance(targets, Tensor) else DeviceArray.from_numpy(targets, "int32")
     tg = tg.reshape(-1)
     loss_rows, lse, tot = K.fused_cross_entropy_forward(lg, tg, softcap, reduce=True)
-    loss_arr = DeviceArray.empty((), "float32")
-    # loss = sum / count, computed on the device: gemm-free scalar divide via axpby would
-    # need the count on the host, so a 1-element kernel-free trick is used: ce_bwd and
-    # this division both read the device scalars.
-    _lib.colsum(tot.ptr, loss_arr.ptr, 1, 1, tot.code, loss_arr.code, 0, stream())   # loss_arr = sum
-    out = Tensor(loss_arr)
-    out._ce_total = tot            # (sum, count) device scalars
-    out._mean_pending = True
+    out = Tensor(DeviceArray(tot.ptr + 8, (), "float32", base=tot))   # the mean, a device scalar
     if _needs_graph(logits):
         def _bw(g):
             # g is the upstream gradient of the MEAN loss (device scalar, fp32)

@@ -1,0 +1,169 @@
+"""End-to-end parity of the training step on the GPU: model + loss + backward +
+AdamW through the public Python interface (which calls the C ABI), against the
+reference's own loss trajectory (tests/golden/tiny_gpt2_fp32.json, produced by
+the unmodified reference) and against the NumPy oracle."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+from oracle import gpt2 as og
+from oracle import ops as O
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def build(cfg, params, dtype="float32"):
+    import mytorch_b200 as mt
+    from mytorch_b200.gpt2 import GPT2, GPT2Config
+    np.random.seed(0)
+    model = GPT2(GPT2Config(vocab_size=cfg.vocab_size, max_seq_len=cfg.max_seq_len, embed_dim=cfg.embed_dim,
+                            mlp_ratio=cfg.mlp_ratio, num_blocks=cfg.num_blocks, num_heads=cfg.num_heads))
+    sd = dict(params)
+    sd["lm_head.weight"] = params["embeddings.char_embeddings.weight"]
+    model.load_state_dict(sd)
+    return mt, model
+
+
+def groups(model, wd=0.1):
+    decay, no_decay = [], []
+    for _, p in model.named_parameters():
+        (no_decay if len(p.shape) < 2 else decay).append(p)
+    return [{"params": decay, "weight_decay": wd}, {"params": no_decay, "weight_decay": 0.0}]
+
+
+def test_tiny_gpt2_fp32_50_steps_match_reference_losses():
+    """Config: L4 H4 d256 ctx256 vocab65 batch16, AdamW lr3e-4 betas(0.9,0.95)
+    wd0.1, seed-0 token ids; the first 50 losses must be within 1e-3 relative
+    of the reference fp32 run."""
+    with open(os.path.join(GOLDEN, "tiny_gpt2_fp32.json")) as fh:
+        gold = json.load(fh)
+    cfg = og.GPT2Config(65, 256, 256, 4, 4, 4)
+    mt, model = build(cfg, og.init_params(cfg, seed=0))
+    opt = mt.optim.AdamW(groups(model), lr=3e-4, beta1=0.9, beta2=0.95)
+    loss_fn = mt.nn.CrossEntropyLoss()
+    rng = np.random.default_rng(0)
+    losses = []
+    for step in range(50):
+        x, y = og.synthetic_batch(rng, 16, 256, 65)
+        logits = model(mt.Tensor(x))
+        loss = loss_fn(logits, mt.Tensor(y))
+        loss.backward()
+        opt.step()
+        opt.zero_grad()
+        losses.append(loss.item())
+    ref = np.array(gold["losses"])
+    rel = np.abs(np.array(losses) - ref) / np.abs(ref)
+    assert rel.max() <= 1e-3, (rel.max(), losses[:5], ref[:5])
+    final = model.state_dict()
+    for k, want in gold["final_weight_l2"].items():
+        got = float(np.sqrt(np.sum(final[k].astype(np.float64) ** 2)))
+        assert abs(got - want) <= 1e-3 * want, (k, got, want)
+
+
+def test_first_step_gradients_match_reference():
+    cfg = og.GPT2Config(65, 256, 256, 4, 4, 4)
+    mt, model = build(cfg, og.init_params(cfg, seed=0))
+    x, y = og.synthetic_batch(np.random.default_rng(0), 16, 256, 65)
+    loss = mt.nn.CrossEntropyLoss()(model(mt.Tensor(x)), mt.Tensor(y))
+    loss.backward()
+    whole = np.load(os.path.join(GOLDEN, "tiny_gpt2_first_grads.npz"))
+    grads = {n: p.grad.numpy() for n, p in model.named_parameters()}
+    for k in whole.files:
+        want = whole[k]
+        err = np.abs(grads[k] - want).max() / np.abs(want).max()
+        assert err <= 1e-4, (k, err)
+
+
+@pytest.mark.parametrize("half", ["float16", "bfloat16"])
+def test_mixed_precision_step_tracks_fp32_oracle(half):
+    """Small GPT-2 under the Accelerator (half activations, fp32 masters, loss
+    scaling, accumulation 2, clip 1.0): losses stay within 1e-2 of the fp32
+    oracle driven with the same batches, and the weights move the same way."""
+    cfg = og.GPT2Config(vocab_size=264, max_seq_len=64, embed_dim=128, mlp_ratio=4, num_blocks=2, num_heads=2)
+    params = og.init_params(cfg, seed=3)
+    mt, model = build(cfg, params)
+    acc = mt.Accelerator(num_gpus=1, rank=0, gradient_accumulation_steps=2, mixed_precision=True, half_dtype=half)
+    opt = mt.optim.AdamW(groups(model), lr=1e-3, beta1=0.9, beta2=0.95)
+    model, opt = acc.prepare(model, opt)
+    loss_fn = mt.nn.CrossEntropyLoss()
+    ref_params = {k: v.copy() for k, v in params.items()}
+    ref_opt = og.AdamW(ref_params, 1e-3, 0.9, 0.95, 1e-8, 0.1)
+    rng = np.random.default_rng(5)
+    got, want = [], []
+    for step in range(6):
+        gsum = None
+        for micro in range(2):
+            x, y = og.synthetic_batch(rng, 4, 64, 264)
+            loss = loss_fn(model(mt.Tensor(x)), mt.Tensor(y))
+            acc.backward(loss)
+            acc.clip_grad_norm_(1.0)
+            opt.step()
+            opt.zero_grad()
+            got.append(loss.item())
+            rl, _, cache = og.forward(ref_params, cfg, x, y)
+            g = og.backward(ref_params, cfg, cache)
+            gsum = g if gsum is None else {k: gsum[k] + g[k] for k in g}
+            want.append(float(rl))
+        gsum = {k: v / 2 for k, v in gsum.items()}
+        O.clip_grad_norm(list(gsum.values()), 1.0)
+        ref_opt.step(ref_params, gsum)
+    got, want = np.array(got), np.array(want)
+    assert np.abs(got - want).max() / want.max() <= 1e-2, (got, want)
+    assert acc.scaler.skipped_steps == 0
+    # masters follow the oracle's weights
+    for name, p in model._named_parameters_no_dedup():
+        i = acc._param_index[id(p)]
+        m = acc._flat.view(acc._flat.master, i).numpy()
+        ref = ref_params.get(name, ref_params["embeddings.char_embeddings.weight"])
+        assert np.abs(m - ref).max() <= 6e-3 * max(1.0, np.abs(ref).max()), name   # 6 steps of lr 1e-3
+
+
+def test_overflow_skips_the_step_and_halves_the_scale():
+    """An inf planted in the gradient buffer (host-made input, no device fault):
+    the fused update must leave weights and moments untouched, clear nothing it
+    should not, and the device-side scaler must back off."""
+    cfg = og.GPT2Config(vocab_size=64, max_seq_len=32, embed_dim=64, mlp_ratio=4, num_blocks=1, num_heads=2)
+    mt, model = build(cfg, og.init_params(cfg, seed=1))
+    acc = mt.Accelerator(num_gpus=1, rank=0, mixed_precision=True)
+    opt = mt.optim.AdamW(groups(model), lr=1e-3)
+    model, opt = acc.prepare(model, opt)
+    before = acc._flat.master.numpy().copy()
+    x, y = og.synthetic_batch(np.random.default_rng(0), 2, 32, 64)
+    loss = mt.nn.CrossEntropyLoss()(model(mt.Tensor(x)), mt.Tensor(y))
+    acc.step_counter = 0
+    loss.backward(acc.scaler.scale_dev)
+    g = acc._flat.grad.numpy()
+    g[5] = np.inf
+    acc._flat.grad.set_from_numpy(g)
+    acc.step_counter = 1
+    acc._grads_ready = False
+    acc.clip_grad_norm_(1.0)
+    opt.step()
+    opt.zero_grad()
+    assert acc.scaler.scale == 2.0 ** 15 and acc.scaler.skipped_steps == 1
+    assert np.array_equal(acc._flat.master.numpy(), before)
+    assert not acc._flat.m.numpy().any()
+    assert not acc._flat.grad.numpy().any()
+    # the next clean step proceeds
+    loss = mt.nn.CrossEntropyLoss()(model(mt.Tensor(x)), mt.Tensor(y))
+    acc.backward(loss)
+    opt.step()
+    assert not np.array_equal(acc._flat.master.numpy(), before)
+    assert acc.scaler.unskipped == 1
+
+
+def test_adamw_multi_tensor_matches_reference_golden(golden_ops, op_inputs):
+    import mytorch_b200 as mt
+    d, g = op_inputs, golden_ops
+    p = mt.Tensor(d["adam_p"].copy(), requires_grad=True)
+    p.is_param = True
+    opt = mt.optim.AdamW([{"params": [p], "weight_decay": 0.1}], lr=3e-3, beta1=0.9, beta2=0.95)
+    for i in range(3):
+        p.grad = mt.DeviceArray.from_numpy(d["adam_g"][i])
+        opt.step()
+        assert np.abs(p.numpy() - g["adam_p"][i]).max() <= 1e-6 * np.abs(g["adam_p"][i]).max() + 1e-7
+    assert np.abs(opt.param_groups[0]["m"][0].numpy() - g["adam_m"]).max() <= 1e-6
+    assert np.abs(opt.param_groups[0]["v"][0].numpy() - g["adam_v"]).max() <= 1e-6
