@@ -40,7 +40,7 @@ def close(got, want, rel, what=""):
     want = np.asarray(want, dtype=np.float64)
     assert got.shape == want.shape, (what, got.shape, want.shape)
     assert np.isfinite(got).all(), f"{what}: non-finite values"
-    scale = max(np.abs(want).max(), 1e-6)   # an all-zero expectation is compared absolutely
+    scale = max(np.abs(want).max(), 1e-3)   # an all-zero expectation is compared absolutely
     err = np.abs(got - want).max() / scale
     assert err <= rel, f"{what}: max err {err:.3e} (scale {scale:.3e}) > {rel}"
 
@@ -268,7 +268,8 @@ def test_gemm_tensor_core_matches_cuda_core_kernel(mt):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("B,H,S,D,causal", [(2, 3, 70, 32, True), (1, 2, 128, 64, True), (2, 2, 257, 64, True),
                                             (1, 2, 100, 128, True), (1, 2, 64, 64, False), (1, 1, 1, 64, True),
-                                            (1, 2, 33, 64, False)])
+                                            (1, 2, 33, 64, False), (2, 4, 1024, 64, True), (1, 2, 300, 128, False),
+                                            (1, 3, 640, 128, True), (2, 2, 512, 64, False)])
 def test_attention(mt, dtype, B, H, S, D, causal):
     F = mt.fused_ops
     r = np.random.default_rng(11)
