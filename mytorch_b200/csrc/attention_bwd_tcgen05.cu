@@ -1,0 +1,355 @@
+// Tensor-core attention backward for sm_100a, fp16/bf16, head_dim 64 or 128.
+//
+// One CTA per (batch, head, block of 128 key/value rows); it walks the query
+// blocks that attend to it (all of them, or those at/after the diagonal when
+// causal). Per query block, five tcgen05 MMAs with accumulators in tensor memory:
+//   S^T  = K Q^T            dP^T = V dO^T          (both 128x128xD, recomputed)
+//   dV  += P^T dO           dK  += dS^T Q          (128xDx128, accumulated)
+//   dQ   = dS K             (128xDx128, added to a fp32 buffer with atomics,
+//                            since every key block contributes to every dQ row)
+// Warp roles: warp 4 TMA producer (K, V once; Q and dO per query block, read in
+// place through 4-D strided tensor maps), warp 5 MMA issuer, warps 0-3 the
+// elementwise stage: thread = key row = TMEM lane; it reads S^T and dP^T,
+// forms P^T = exp2(S^T*scale*log2e - lse*log2e) and dS^T = P^T (dP^T - delta) *
+// scale, and writes both as half into shared memory in the swizzled layout that
+// serves as K-major A operand for dV/dK and, read the other way, as M-major A
+// operand for dQ. No transposes are materialised anywhere.
+//
+// Roofline: tensor pipe, 10*B*H*S^2*D FLOP (half when causal).
+#include "common.cuh"
+#include "attention.cuh"
+#include "sm100.cuh"
+#include "attention_tc.cuh"
+
+namespace mt {
+
+using namespace sm100;
+
+constexpr int kBwdThreads = 192;
+
+template <int D> struct BwdCfg {
+  static constexpr int kChunks = D / 64;
+  static constexpr int kTile = 128 * D * 2;                 // one 128-row block of K/V/Q/dO
+  static constexpr int kStages = D == 64 ? 2 : 1;           // Q+dO ring
+  static constexpr int kOffK = 0;
+  static constexpr int kOffV = kTile;
+  static constexpr int kOffQ = 2 * kTile;                   // stage s: Q at +s*2*kTile, dO right after it
+  static constexpr int kOffPT = kOffQ + kStages * 2 * kTile;
+  static constexpr int kOffDST = kOffPT + 32768;
+  static constexpr int kOffStat = kOffDST + 32768;          // lse2[2][128], delta[2][128] floats
+  static constexpr int kOffBar = kOffStat + 2048;
+  static constexpr int kSmem = kOffBar + 256 + 1024;
+  static constexpr int kTmemCols = 512;
+  static constexpr int kColST = 0, kColDPT = 128, kColDV = 256, kColDK = 256 + D;
+  static constexpr bool kAliasDQ = D == 128;                // dQ shares the S^T columns when TMEM is full
+  static constexpr int kColDQ = kAliasDQ ? 0 : 256 + 2 * D;
+};
+
+struct AttnBwdParams {
+  const float* lse; const float* delta; float* dq_accum;
+  void* dk; void* dv;
+  MapPos pq, pk, pv, pdo;
+  mt_strides3 sdk, sdv;
+  int B, H, S, nqb, causal, is_bf16;
+  float scale, scale_log2;
+  int* flag;
+};
+
+template <int D, typename T>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
+                   const AttnBwdParams P) {
+  using Cfg = BwdCfg<D>;
+  constexpr int ST = Cfg::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* base_ptr = smem_raw + (base - raw);
+  const uint32_t bar0 = base + Cfg::kOffBar;
+  const uint32_t bar_kv = bar0, bar_qfull0 = bar0 + 8, bar_qempty0 = bar0 + 24, bar_sdp = bar0 + 40,
+                 bar_pds = bar0 + 48, bar_dq = bar0 + 56, bar_dqfree = bar0 + 64, bar_stat = bar0 + 72;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + Cfg::kOffBar + 96);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + Cfg::kOffBar + 100);
+  float* stat = reinterpret_cast<float*>(base_ptr + Cfg::kOffStat);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int bh_count = P.B * P.H;
+  const int jb = (int)(blockIdx.x / bh_count);     // key block; small j = most query blocks when causal, so heavy first
+  const int bh = blockIdx.x % bh_count;
+  const int b = bh / P.H, h = bh % P.H;
+  const int q_start = P.causal ? jb : 0;
+  const int n_q = P.nqb - q_start;
+
+  if (threadIdx.x == 0) {
+    mbar_init(bar_kv, 1);
+    for (int s = 0; s < 2; ++s) { mbar_init(bar_qfull0 + 8 * s, 1); mbar_init(bar_qempty0 + 8 * s, 1); }
+    mbar_init(bar_sdp, 1); mbar_init(bar_pds, 128); mbar_init(bar_dq, 1); mbar_init(bar_dqfree, 128); mbar_init(bar_stat, 128);
+    *abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  if (warp == 5) {
+    tmem_alloc(smem_u32(tmem_slot), Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 4) {
+    // ------------------------------------------------------------ producer --
+    if (lane == 0) {
+      prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV); prefetch_tmap(&tmDO);
+      mbar_expect_tx(bar_kv, 2 * Cfg::kTile);
+#pragma unroll
+      for (int dc = 0; dc < Cfg::kChunks; ++dc) {
+        load_rows(base + Cfg::kOffK + dc * 16384, &tmK, bar_kv, P.pk, dc * 64, jb * 128, h, b);
+        load_rows(base + Cfg::kOffV + dc * 16384, &tmV, bar_kv, P.pv, dc * 64, jb * 128, h, b);
+      }
+      for (int i = 0; i < n_q; ++i) {
+        const int s = i % ST;
+        if (!mbar_wait(bar_qempty0 + 8 * s, ((i / ST) & 1) ^ 1u, abort_flag)) break;
+        mbar_expect_tx(bar_qfull0 + 8 * s, 2 * Cfg::kTile);
+        const uint32_t sq = base + Cfg::kOffQ + s * 2 * Cfg::kTile, sdo = sq + Cfg::kTile;
+#pragma unroll
+        for (int dc = 0; dc < Cfg::kChunks; ++dc) {
+          load_rows(sq + dc * 16384, &tmQ, bar_qfull0 + 8 * s, P.pq, dc * 64, (q_start + i) * 128, h, b);
+          load_rows(sdo + dc * 16384, &tmDO, bar_qfull0 + 8 * s, P.pdo, dc * 64, (q_start + i) * 128, h, b);
+        }
+      }
+    }
+  } else if (warp == 5) {
+    // ---------------------------------------------------------- MMA issuer --
+    if (lane == 0) {
+      const uint32_t idesc_kk = idesc_f16(P.is_bf16, 0, 0, 128, 128);   // S^T, dP^T: both operands K-major
+      const uint32_t idesc_kn = idesc_f16(P.is_bf16, 0, 1, 128, D);     // dV, dK: A K-major, B N-major
+      const uint32_t idesc_mn = idesc_f16(P.is_bf16, 1, 1, 128, D);     // dQ: A M-major, B N-major
+      const uint32_t sk = base + Cfg::kOffK, sv = base + Cfg::kOffV;
+      const uint32_t spt = base + Cfg::kOffPT, sdst = base + Cfg::kOffDST;
+      bool ok = mbar_wait(bar_kv, 0, abort_flag);
+      for (int i = 0; i < n_q && ok; ++i) {
+        const int s = i % ST;
+        const uint32_t sq = base + Cfg::kOffQ + s * 2 * Cfg::kTile, sdo = sq + Cfg::kTile;
+        if (!mbar_wait(bar_qfull0 + 8 * s, (i / ST) & 1, abort_flag)) break;
+        if (Cfg::kAliasDQ && i > 0 && !mbar_wait(bar_dqfree, (i - 1) & 1, abort_flag)) break;
+        tc_fence_after();
+#pragma unroll
+        for (int dc = 0; dc < Cfg::kChunks; ++dc)
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            umma_f16(tmem_base + Cfg::kColST, smem_desc_sw128(sk + dc * 16384 + k * 32, 16, 1024),
+                     smem_desc_sw128(sq + dc * 16384 + k * 32, 16, 1024), idesc_kk, (dc | k) ? 1u : 0u);
+#pragma unroll
+        for (int dc = 0; dc < Cfg::kChunks; ++dc)
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            umma_f16(tmem_base + Cfg::kColDPT, smem_desc_sw128(sv + dc * 16384 + k * 32, 16, 1024),
+                     smem_desc_sw128(sdo + dc * 16384 + k * 32, 16, 1024), idesc_kk, (dc | k) ? 1u : 0u);
+        umma_commit(bar_sdp);
+        if (!mbar_wait(bar_pds, i & 1, abort_flag)) break;     // P^T, dS^T written; S^T, dP^T consumed
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)   // dV += P^T dO, reduction over the 128 queries
+          umma_f16(tmem_base + Cfg::kColDV, smem_desc_sw128(spt + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024),
+                   smem_desc_sw128(sdo + ks * 2048, 16384, 1024), idesc_kn, (i > 0 || ks > 0) ? 1u : 0u);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)   // dK += dS^T Q
+          umma_f16(tmem_base + Cfg::kColDK, smem_desc_sw128(sdst + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024),
+                   smem_desc_sw128(sq + ks * 2048, 16384, 1024), idesc_kn, (i > 0 || ks > 0) ? 1u : 0u);
+        if (!Cfg::kAliasDQ && i > 0 && !mbar_wait(bar_dqfree, (i - 1) & 1, abort_flag)) break;
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)   // dQ = dS K, reduction over the 128 keys
+          umma_f16(tmem_base + Cfg::kColDQ, smem_desc_sw128(sdst + ks * 2048, 16384, 1024),
+                   smem_desc_sw128(sk + ks * 2048, 16384, 1024), idesc_mn, ks > 0 ? 1u : 0u);
+        umma_commit(bar_qempty0 + 8 * s);
+        umma_commit(bar_dq);
+      }
+    }
+  } else {
+    // ------------------------------------------------- elementwise stage --
+    const int t = threadIdx.x;                        // key row within the block = TMEM lane
+    const int kg = jb * 128 + t;                      // global key index
+    const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+    uint8_t* pt_row = base_ptr + Cfg::kOffPT + t * 128;
+    uint8_t* dst_row = base_ptr + Cfg::kOffDST + t * 128;
+    bool ok = true;
+    for (int i = 0; i < n_q && ok; ++i) {
+      const int qi = q_start + i;
+      float* lse2 = stat + (i & 1) * 256;
+      float* dlt = lse2 + 128;
+      {
+        const int q = qi * 128 + t;
+        lse2[t] = q < P.S ? P.lse[(int64_t)bh * P.S + q] * kLog2eF : INFINITY;   // +inf -> p = 0 for padded queries
+        dlt[t] = q < P.S ? P.delta[(int64_t)bh * P.S + q] : 0.f;
+      }
+      // publish the block's statistics to the other 127 threads through a bounded mbarrier wait
+      mbar_arrive(bar_stat);
+      if (!__all_sync(0xffffffffu, mbar_wait(bar_stat, i & 1, abort_flag))) { ok = false; break; }
+      if (!__all_sync(0xffffffffu, mbar_wait(bar_sdp, i & 1, abort_flag))) { ok = false; break; }
+      tc_fence_after();
+      const bool diag = P.causal && qi == jb;
+      const bool dead = kg >= P.S;                    // padded key row: contributes nothing
+#pragma unroll 1
+      for (int hh = 0; hh < 2; ++hh) {                // 64 query columns at a time
+        uint32_t s_[64], d_[64];
+        tmem_ld32(tmem_base + Cfg::kColST + lane_addr + hh * 64, s_);
+        tmem_ld32(tmem_base + Cfg::kColST + lane_addr + hh * 64 + 32, s_ + 32);
+        tmem_ld32(tmem_base + Cfg::kColDPT + lane_addr + hh * 64, d_);
+        tmem_ld32(tmem_base + Cfg::kColDPT + lane_addr + hh * 64 + 32, d_ + 32);
+        tmem_ld_wait();
+#pragma unroll
+        for (int c16 = 0; c16 < 8; ++c16) {
+          uint32_t pp[4], dd[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            float pv[2], dv[2];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+              const int c = hh * 64 + c16 * 8 + 2 * e + u;     // query column within the block
+              float p = ex2_approx(fmaf(__uint_as_float(s_[c16 * 8 + 2 * e + u]), P.scale_log2, -lse2[c]));
+              if (dead || (diag && c < t)) p = 0.f;
+              pv[u] = p;
+              dv[u] = p * (__uint_as_float(d_[c16 * 8 + 2 * e + u]) - dlt[c]) * P.scale;
+            }
+            pp[e] = pack2<T>(pv[0], pv[1]);
+            dd[e] = pack2<T>(dv[0], dv[1]);
+          }
+          const int off = hh * 16384 + ((c16 ^ (t & 7)) << 4);
+          *reinterpret_cast<uint4*>(pt_row + off) = make_uint4(pp[0], pp[1], pp[2], pp[3]);
+          *reinterpret_cast<uint4*>(dst_row + off) = make_uint4(dd[0], dd[1], dd[2], dd[3]);
+        }
+      }
+      fence_proxy_async();
+      tc_fence_before();
+      mbar_arrive(bar_pds);
+      // dQ of this query block: thread t now stands for query row qi*128 + t
+      if (!__all_sync(0xffffffffu, mbar_wait(bar_dq, i & 1, abort_flag))) { ok = false; break; }
+      tc_fence_after();
+      {
+        const int q = qi * 128 + t;
+        float* dst = P.dq_accum + ((int64_t)bh * P.S + q) * D;
+#pragma unroll 1
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld32(tmem_base + Cfg::kColDQ + lane_addr + c * 32, r);
+          tmem_ld_wait();
+          if (q < P.S) {
+#pragma unroll
+            for (int e = 0; e < 32; e += 4)
+              atomicAdd(reinterpret_cast<float4*>(dst + c * 32 + e),
+                        make_float4(__uint_as_float(r[e]), __uint_as_float(r[e + 1]), __uint_as_float(r[e + 2]),
+                                    __uint_as_float(r[e + 3])));
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(bar_dqfree);
+    }
+    if (ok) {
+      // all MMAs are complete (the last bar_dq was waited above): write dK, dV of this key row
+      T* dkrow = reinterpret_cast<T*>(P.dk) + (int64_t)b * P.sdk.b + (int64_t)h * P.sdk.h + (int64_t)kg * P.sdk.s;
+      T* dvrow = reinterpret_cast<T*>(P.dv) + (int64_t)b * P.sdv.b + (int64_t)h * P.sdv.h + (int64_t)kg * P.sdv.s;
+#pragma unroll 1
+      for (int which = 0; which < 2; ++which) {
+        T* orow = which ? dvrow : dkrow;
+        const int col0 = which ? Cfg::kColDV : Cfg::kColDK;
+#pragma unroll 1
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld32(tmem_base + col0 + lane_addr + c * 32, r);
+          tmem_ld_wait();
+          if (kg < P.S) {
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+              uint4 v;
+              v.x = pack2<T>(__uint_as_float(r[q4 * 8 + 0]), __uint_as_float(r[q4 * 8 + 1]));
+              v.y = pack2<T>(__uint_as_float(r[q4 * 8 + 2]), __uint_as_float(r[q4 * 8 + 3]));
+              v.z = pack2<T>(__uint_as_float(r[q4 * 8 + 4]), __uint_as_float(r[q4 * 8 + 5]));
+              v.w = pack2<T>(__uint_as_float(r[q4 * 8 + 6]), __uint_as_float(r[q4 * 8 + 7]));
+              *reinterpret_cast<uint4*>(orow + c * 32 + q4 * 8) = v;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag && P.flag) atomicMax(P.flag, 102);
+  if (warp == 5) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+// dq[b,h,s,:] = (T) dq_accum[b,h,s,:]
+template <typename T>
+__global__ void __launch_bounds__(256)
+dq_convert_kernel(const float* __restrict__ acc, T* __restrict__ dq, mt_strides3 sdq, int H, int S, int D, int64_t n_vec) {
+  const int vec_per_row = D / 8;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t row = i / vec_per_row;
+    const int v = (int)(i - row * vec_per_row);
+    const int64_t bh = row / S;
+    const int s = (int)(row - bh * S);
+    const int b = (int)(bh / H), h = (int)(bh % H);
+    const float4 a0 = reinterpret_cast<const float4*>(acc + row * D + v * 8)[0];
+    const float4 a1 = reinterpret_cast<const float4*>(acc + row * D + v * 8)[1];
+    uint4 o;
+    o.x = pack2<T>(a0.x, a0.y); o.y = pack2<T>(a0.z, a0.w); o.z = pack2<T>(a1.x, a1.y); o.w = pack2<T>(a1.z, a1.w);
+    *reinterpret_cast<uint4*>(dq + (int64_t)b * sdq.b + (int64_t)h * sdq.h + (int64_t)s * sdq.s + v * 8) = o;
+  }
+}
+
+bool attn_bwd_tc_supported(const AttnArgs& a) {
+  if (!a.dq_accum) return false;
+  if (!aligned16(a.d_o) || !aligned16(a.dq) || !aligned16(a.dk) || !aligned16(a.dv) || !aligned16(a.dq_accum)) return false;
+  if (!strides_ok(a.sdo) || !strides_ok(a.sdq) || !strides_ok(a.sdk) || !strides_ok(a.sdv)) return false;
+  return true;
+}
+
+template <int D, typename T>
+static int launch_bwd(const AttnArgs& a, cudaStream_t st) {
+  using Cfg = BwdCfg<D>;
+  const int bf = a.dtype == MT_BF16;
+  int rc = attn_delta(a, st);
+  if (rc) return rc;
+  const int64_t n_acc = a.batch * a.heads * a.seq * D;
+  MT_CHECK_CUDA(cudaMemsetAsync(a.dq_accum, 0, (size_t)n_acc * sizeof(float), st));
+  CUtensorMap tq, tk, tv, tdo;
+  AttnBwdParams P;
+  if ((rc = make_qkv_map(&tq, &P.pq, a.q, bf, a.sq, a.batch, a.heads, a.seq, D))) return rc;
+  if ((rc = make_qkv_map(&tk, &P.pk, a.k, bf, a.sk, a.batch, a.heads, a.seq, D))) return rc;
+  if ((rc = make_qkv_map(&tv, &P.pv, a.v, bf, a.sv, a.batch, a.heads, a.seq, D))) return rc;
+  if ((rc = make_qkv_map(&tdo, &P.pdo, a.d_o, bf, a.sdo, a.batch, a.heads, a.seq, D))) return rc;
+  P.lse = a.lse; P.delta = a.delta; P.dq_accum = a.dq_accum; P.dk = a.dk; P.dv = a.dv;
+  P.sdk = a.sdk; P.sdv = a.sdv;
+  P.B = (int)a.batch; P.H = (int)a.heads; P.S = (int)a.seq; P.nqb = (int)((a.seq + 127) / 128);
+  P.causal = a.causal; P.is_bf16 = bf; P.scale = a.scale; P.scale_log2 = a.scale * kLog2eF; P.flag = device_flag_ptr();
+  auto kern = attn_bwd_tc_kernel<D, T>;
+  MT_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
+  const unsigned grid = (unsigned)(P.nqb * P.B * P.H);
+  kern<<<grid, kBwdThreads, Cfg::kSmem, st>>>(tq, tk, tv, tdo, P);
+  MT_LAUNCH_CHECK();
+  const int64_t n_vec = n_acc / 8;
+  int64_t blocks = (n_vec + 255) / 256;
+  if (blocks > (int64_t)sm_count() * 16) blocks = (int64_t)sm_count() * 16;
+  dq_convert_kernel<T><<<(unsigned)blocks, 256, 0, st>>>(a.dq_accum, (T*)a.dq, a.sdq, (int)a.heads, (int)a.seq, D, n_vec);
+  MT_LAUNCH_CHECK();
+  return MT_OK;
+}
+
+int attn_bwd_tc(const AttnArgs& a, cudaStream_t st) {
+  if (a.head_dim == 64) {
+    if (a.dtype == MT_F16) return launch_bwd<64, __half>(a, st);
+    return launch_bwd<64, __nv_bfloat16>(a, st);
+  }
+  if (a.dtype == MT_F16) return launch_bwd<128, __half>(a, st);
+  return launch_bwd<128, __nv_bfloat16>(a, st);
+}
+
+}  // namespace mt

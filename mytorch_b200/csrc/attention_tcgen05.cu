@@ -20,14 +20,13 @@
 #include "common.cuh"
 #include "attention.cuh"
 #include "sm100.cuh"
+#include "attention_tc.cuh"
 
 namespace mt {
 
 using namespace sm100;
 
 constexpr int kAttnThreads = 192;
-constexpr float kLog2eF = 1.4426950408889634f;
-constexpr float kLn2F = 0.6931471805599453f;
 
 template <int D> struct FwdCfg {
   static constexpr int kChunks = D / 64;               // 64-wide (128-byte) slices of head_dim
@@ -41,16 +40,6 @@ template <int D> struct FwdCfg {
   static constexpr int kTmemCols = 256;                // S: [0,128), O: [128,128+D)
 };
 
-// Position (1..3) of the seq / head / batch coordinate in each 4-D tensor map;
-// the outer dimensions are ordered by ascending stride when the map is built.
-struct MapPos { int s, h, b; };
-
-__device__ __forceinline__ void load_rows(uint32_t dst, const CUtensorMap* map, uint32_t bar, MapPos pos, int d0, int row0,
-                                          int h, int b) {
-  int c[4];
-  c[0] = d0; c[pos.s] = row0; c[pos.h] = h; c[pos.b] = b;
-  sm100::tma_load_4d(dst, map, bar, c[0], c[1], c[2], c[3]);
-}
 
 struct AttnFwdParams {
   void* o; float* lse;
@@ -61,21 +50,6 @@ struct AttnFwdParams {
   int* flag;
 };
 
-__device__ __forceinline__ float ex2_approx(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-
-template <typename T> __device__ __forceinline__ uint32_t pack2(float a, float b);
-template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
-  __half2 h = __floats2half2_rn(a, b);
-  return *reinterpret_cast<uint32_t*>(&h);
-}
-template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
-  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
-  return *reinterpret_cast<uint32_t*>(&h);
-}
 
 template <int D, typename T>
 __global__ void __launch_bounds__(kAttnThreads, D == 64 ? 2 : 1)
@@ -296,10 +270,9 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   }
 }
 
-static bool strides_ok(const mt_strides3& s) { return s.b % 8 == 0 && s.h % 8 == 0 && s.s % 8 == 0; }
 
 bool attn_tc_supported(const AttnArgs& a, bool backward) {
-  if (backward) return false;
+  if (backward && !attn_bwd_tc_supported(a)) return false;
   if (a.dtype != MT_F16 && a.dtype != MT_BF16) return false;
   if (a.head_dim != 64 && a.head_dim != 128) return false;
   if (a.seq < 1 || a.batch < 1) return false;
@@ -309,25 +282,6 @@ bool attn_tc_supported(const AttnArgs& a, bool backward) {
   return true;
 }
 
-// 4-D map {head_dim, x, y, z} with (seq, head, batch) placed by ascending stride;
-// the box covers 64 of head_dim and 128 rows of seq.
-static int make_qkv_map(CUtensorMap* m, MapPos* pos, const void* p, int bf16, const mt_strides3& s, int64_t B, int64_t H,
-                        int64_t S, int64_t D) {
-  struct Dim { uint64_t extent, stride; uint32_t box; int role; };
-  Dim d[3] = {{(uint64_t)S, (uint64_t)s.s, 128, 0}, {(uint64_t)H, (uint64_t)s.h, 1, 1}, {(uint64_t)B, (uint64_t)s.b, 1, 2}};
-  for (int i = 0; i < 3; ++i)
-    for (int j = i + 1; j < 3; ++j)
-      if (d[j].stride < d[i].stride) { Dim t = d[i]; d[i] = d[j]; d[j] = t; }
-  uint64_t dims[4] = {(uint64_t)D, d[0].extent, d[1].extent, d[2].extent};
-  uint64_t str[3] = {d[0].stride, d[1].stride, d[2].stride};
-  uint32_t box[4] = {64, d[0].box, d[1].box, d[2].box};
-  for (int i = 0; i < 3; ++i) {
-    if (d[i].role == 0) pos->s = i + 1;
-    else if (d[i].role == 1) pos->h = i + 1;
-    else pos->b = i + 1;
-  }
-  return make_tmap_nd(m, p, bf16, 4, dims, str, box);
-}
 
 template <int D, typename T>
 static int launch_fwd(const AttnArgs& a, cudaStream_t st) {
@@ -359,9 +313,5 @@ int attn_fwd_tc(const AttnArgs& a, cudaStream_t st) {
   return launch_fwd<128, __nv_bfloat16>(a, st);
 }
 
-int attn_bwd_tc(const AttnArgs&, cudaStream_t) {
-  set_error("tensor-core attention backward not built");
-  return MT_ERR_UNSUPPORTED;
-}
 
 }  // namespace mt
