@@ -22,6 +22,7 @@
 #include "sm100.cuh"
 #include "prof.cuh"
 #include <mutex>
+#include <string.h>
 
 namespace mt {
 
@@ -36,13 +37,14 @@ template <int BN> struct GemmCfg {
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kStages = BN == 256 ? 4 : 6;
   static constexpr int kTmemCols = 2 * BN;  // two accumulator buffers
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int kEpiBytes = 4 * 2 * 4096;  // per epilogue warp: two 32-row x 128-byte staging buffers
+  static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024 /*align*/ + 256 /*barriers*/;
 };
 
 struct GemmParams {
   void* C; void* preact; const void* bias;
   int64_t M, N, K, ldc;
-  int out_dtype, in_bf16, act, accumulate, vec_store;
+  int out_dtype, in_bf16, act, accumulate, vec_store, tma_store;
   float alpha;
   int tiles_m, tiles_n, splits, kb_per_split, kb_total;
   int* flag;
@@ -99,18 +101,94 @@ __device__ __forceinline__ void store8(TO* p, const float* v, int n_valid, bool 
   }
 }
 
+template <typename TO> __device__ __forceinline__ uint32_t pack_pair(float a, float b);
+template <> __device__ __forceinline__ uint32_t pack_pair<__half>(float a, float b) {
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+template <> __device__ __forceinline__ uint32_t pack_pair<__nv_bfloat16>(float a, float b) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+template <> __device__ __forceinline__ uint32_t pack_pair<float>(float a, float) { return __float_as_uint(a); }
+
+// One warp stages 32 rows x 128 bytes (its 32 TMEM lanes, CW columns) in shared
+// memory with the 128-byte swizzle and hands it to TMA: coalesced global writes,
+// rows/columns past M/N clipped by the tensor map, optional fp32 reduce-add.
+template <typename TO, int CW>
+__device__ __forceinline__ void stage_store(const CUtensorMap* map, const uint32_t* r, uint8_t* stage, int lane, int x,
+                                            int y, bool reduce, int& sidx) {
+  uint8_t* buf = stage + (sidx & 1) * 4096;
+  if (lane == 0) bulk_wait_read<1>();   // the store issued two stagings ago has released this buffer
+  __syncwarp();
+  uint8_t* rowp = buf + lane * 128;
+#pragma unroll
+  for (int c16 = 0; c16 < 8; ++c16) {
+    uint4 v;
+    if (sizeof(TO) == 4) {
+      v = make_uint4(r[c16 * 4], r[c16 * 4 + 1], r[c16 * 4 + 2], r[c16 * 4 + 3]);
+    } else {
+      v.x = pack_pair<TO>(__uint_as_float(r[c16 * 8 + 0]), __uint_as_float(r[c16 * 8 + 1]));
+      v.y = pack_pair<TO>(__uint_as_float(r[c16 * 8 + 2]), __uint_as_float(r[c16 * 8 + 3]));
+      v.z = pack_pair<TO>(__uint_as_float(r[c16 * 8 + 4]), __uint_as_float(r[c16 * 8 + 5]));
+      v.w = pack_pair<TO>(__uint_as_float(r[c16 * 8 + 6]), __uint_as_float(r[c16 * 8 + 7]));
+    }
+    *reinterpret_cast<uint4*>(rowp + ((c16 ^ (lane & 7)) << 4)) = v;
+  }
+  fence_proxy_async();
+  __syncwarp();
+  if (lane == 0) {
+    if (reduce) tma_reduce_add_2d(map, smem_u32(buf), x, y);
+    else tma_store_2d(map, smem_u32(buf), x, y);
+    bulk_commit();
+  }
+  ++sidx;
+}
+
+template <int BN, typename TO>
+__device__ __forceinline__ void epilogue_staged(const GemmParams& P, const CUtensorMap* tmC, const CUtensorMap* tmPre,
+                                                uint32_t taddr, uint8_t* stage, int lane, int y0, int64_t n0,
+                                                bool add_bias, int& sidx) {
+  constexpr int CW = 128 / (int)sizeof(TO);   // accumulator columns per 128-byte staged row
+#pragma unroll 1
+  for (int c = 0; c < BN / CW; ++c) {
+    const int64_t col0 = n0 + c * CW;
+    if (col0 >= P.N) break;                   // warp-uniform
+    uint32_t r[CW];
+    tmem_ld32(taddr + c * CW, r);
+    if (CW == 64) tmem_ld32(taddr + c * CW + 32, r + (CW == 64 ? 32 : 0));
+    tmem_ld_wait();
+#pragma unroll
+    for (int e = 0; e < CW; ++e) {
+      float x = P.alpha * __uint_as_float(r[e]);
+      if (add_bias && col0 + e < P.N)
+        x += P.in_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(P.bias)[col0 + e])
+                       : __half2float(reinterpret_cast<const __half*>(P.bias)[col0 + e]);
+      r[e] = __float_as_uint(x);
+    }
+    if (P.preact) stage_store<TO, CW>(tmPre, r, stage, lane, (int)col0, y0, false, sidx);
+    if (P.act != MT_ACT_NONE) {
+#pragma unroll
+      for (int e = 0; e < CW; ++e) r[e] = __float_as_uint(act_apply_tc(__uint_as_float(r[e]), P.act));
+    }
+    stage_store<TO, CW>(tmC, r, stage, lane, (int)col0, y0, P.accumulate != 0, sidx);
+  }
+}
+
 template <bool A_MN, bool B_MN, int BN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams P) {
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+               const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmPre, const GemmParams P) {
   using Cfg = GemmCfg<BN>;
   constexpr int S = Cfg::kStages;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;  // 1024-byte alignment for the 128B swizzle
   uint8_t* base_ptr = smem_raw + (base - raw);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(base_ptr + S * Cfg::kStageBytes);
+  uint8_t* epi_stage = base_ptr + S * Cfg::kStageBytes;   // 1024-byte aligned (stage sizes are multiples of 1 KB)
+  uint64_t* bars = reinterpret_cast<uint64_t*>(epi_stage + Cfg::kEpiBytes);
   // barrier slots: full[S], empty[S], acc_full[2], acc_empty[2]
-  const uint32_t bar0 = base + S * Cfg::kStageBytes;
+  const uint32_t bar0 = base + S * Cfg::kStageBytes + Cfg::kEpiBytes;
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
   auto empty_bar = [&](int s) { return bar0 + 8u * (S + s); };
   auto accf_bar = [&](int b) { return bar0 + 8u * (2 * S + b); };
@@ -226,6 +304,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     // ------------------------------------------------------------ epilogue --
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32)
     int it = 0;
+    int sidx = 0;   // running count of staged stores of this warp (selects the staging buffer)
     bool ok = true;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
       const int mn = t % tiles_mn;
@@ -238,6 +317,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       tc_fence_after();
       const int64_t row = m0 + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN;
+      if (P.tma_store) {
+        uint8_t* stage = epi_stage + (warp - 2) * 8192;
+        const int y0 = (int)m0 + quarter * 32;
+        if (y0 < P.M) {   // warp-uniform: a slab of 32 rows entirely past M has nothing to write
+          if (P.out_dtype == MT_F16) epilogue_staged<BN, __half>(P, &tmC, &tmPre, taddr, stage, lane, y0, n0, add_bias, sidx);
+          else if (P.out_dtype == MT_BF16) epilogue_staged<BN, __nv_bfloat16>(P, &tmC, &tmPre, taddr, stage, lane, y0, n0, add_bias, sidx);
+          else epilogue_staged<BN, float>(P, &tmC, &tmPre, taddr, stage, lane, y0, n0, add_bias, sidx);
+        }
+      } else
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
@@ -279,6 +367,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       __syncwarp();
       if (lane == 0) mbar_arrive(acce_bar(buf));  // this warp is done with the buffer
     }
+    if (P.tma_store && lane == 0) bulk_wait_all<0>();   // staged stores must finish before shared memory goes away
   }
 
   // ---------------------------------------------------------------- teardown --
@@ -324,6 +413,21 @@ int make_tmap_nd(CUtensorMap* map, const void* base_ptr, int is_bf16, int rank, 
   return MT_OK;
 }
 
+int make_tmap_2d_typed(CUtensorMap* map, const void* base_ptr, int dt, uint64_t inner, uint64_t outer, uint64_t ld_elems,
+                       uint32_t box_inner, uint32_t box_outer) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) { set_error("cuTensorMapEncodeTiled is not available from this driver"); return MT_ERR_CUDA; }
+  const uint64_t esize = dt == MT_F32 ? 4 : 2;
+  cuuint64_t gdim[2] = {inner, outer}, gstr[1] = {ld_elems * esize};
+  cuuint32_t bx[2] = {box_inner, box_outer}, es[2] = {1, 1};
+  CUtensorMapDataType t = dt == MT_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                        : dt == MT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUresult r = enc(map, t, 2, const_cast<void*>(base_ptr), gdim, gstr, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled (output map) failed with code %d", (int)r); return MT_ERR_CUDA; }
+  return MT_OK;
+}
+
 int make_tmap_2d(CUtensorMap* map, const void* base_ptr, int is_bf16, uint64_t inner, uint64_t outer,
                  uint64_t ld_elems, uint32_t box_inner, uint32_t box_outer) {
   uint64_t dims[2] = {inner, outer}, str[1] = {ld_elems};
@@ -342,7 +446,8 @@ bool gemm_tc_supported(const GemmArgs& g) {
 }
 
 template <bool A_MN, bool B_MN, int BN>
-static int launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& P, int grid, cudaStream_t st) {
+static int launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& tp,
+                     const GemmParams& P, int grid, cudaStream_t st) {
   using Cfg = GemmCfg<BN>;
   static bool attr_set[16] = {false};
   int dev = 0;
@@ -352,7 +457,7 @@ static int launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const GemmPar
     MT_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
     attr_set[dev] = true;
   }
-  kern<<<grid, kGemmThreads, Cfg::kSmemBytes, st>>>(ta, tb, P);
+  kern<<<grid, kGemmThreads, Cfg::kSmemBytes, st>>>(ta, tb, tc, tp, P);
   MT_LAUNCH_CHECK();
   return MT_OK;
 }
@@ -408,10 +513,27 @@ int gemm_tc(const GemmArgs& g, cudaStream_t st) {
   else rc = make_tmap_2d(&tb, g.B, bf, (uint64_t)g.N, (uint64_t)g.K, (uint64_t)g.ldb, 64, BK);
   if (rc) return rc;
 
+  // Output through staged TMA stores when the tensor map can describe C (16-byte aligned base and
+  // row pitch); read-modify-write of a half output keeps the direct path.
+  CUtensorMap tcm, tpm;
+  memset(&tcm, 0, sizeof(tcm));
+  memset(&tpm, 0, sizeof(tpm));
+  const size_t osz = g.out_dtype == MT_F32 ? 4 : 2;
+  P.tma_store = aligned16(g.C) && (g.ldc * osz) % 16 == 0 && (!g.preact || aligned16(g.preact)) &&
+                !(g.accumulate && g.out_dtype != MT_F32);
+  if (P.tma_store) {
+    const uint32_t cw = (uint32_t)(128 / osz);
+    rc = make_tmap_2d_typed(&tcm, g.C, g.out_dtype, (uint64_t)g.N, (uint64_t)g.M, (uint64_t)g.ldc, cw, 32);
+    if (rc) return rc;
+    if (g.preact) {
+      rc = make_tmap_2d_typed(&tpm, g.preact, g.out_dtype, (uint64_t)g.N, (uint64_t)g.M, (uint64_t)g.ldc, cw, 32);
+      if (rc) return rc;
+    }
+  }
   ProfScope prof(PROF_GEMM, st, 2.0 * (double)g.M * (double)g.N * (double)g.K);
   const bool a_mn = g.trans_a != 0, b_mn = g.trans_b == 0;
 #define MT_TC(AM, BMN)                                                         \
-  (bn == 256 ? launch_tc<AM, BMN, 256>(ta, tb, P, grid, st) : launch_tc<AM, BMN, 128>(ta, tb, P, grid, st))
+  (bn == 256 ? launch_tc<AM, BMN, 256>(ta, tb, tcm, tpm, P, grid, st) : launch_tc<AM, BMN, 128>(ta, tb, tcm, tpm, P, grid, st))
   if (!a_mn && !b_mn) return MT_TC(false, false);
   if (!a_mn && b_mn) return MT_TC(false, true);
   if (a_mn && !b_mn) return MT_TC(true, false);

@@ -83,6 +83,23 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst_smem, const CUtensorMap
       ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y), "r"(z), "r"(w)
       : "memory");
 }
+// 2-D tiled store / reduce-add shared -> global through a tensor map (bulk async group).
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src_smem, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src_smem), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, uint32_t src_smem, int x, int y) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src_smem), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Waits until at most N of this thread's bulk groups still READ their shared-memory source.
+template <int N> __device__ __forceinline__ void bulk_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+template <int N> __device__ __forceinline__ void bulk_wait_all() {
+  asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+}
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }
@@ -186,5 +203,8 @@ int make_tmap_2d(CUtensorMap* map, const void* base, int is_bf16, uint64_t inner
 // General form, up to 4 dims (dims[0] innermost; strides in elements for dims 1..rank-1).
 int make_tmap_nd(CUtensorMap* map, const void* base, int is_bf16, int rank, const uint64_t* dims,
                  const uint64_t* strides_elems, const uint32_t* box);
+// 2-D map over a row-major matrix of any library dtype (mt_dtype code), for TMA stores.
+int make_tmap_2d_typed(CUtensorMap* map, const void* base, int mt_dtype_code, uint64_t inner, uint64_t outer,
+                       uint64_t ld_elems, uint32_t box_inner, uint32_t box_outer);
 
 }  // namespace mt
