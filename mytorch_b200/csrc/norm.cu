@@ -273,18 +273,31 @@ norm_bwd_colsum(const T* __restrict__ x, const float* __restrict__ mean, const f
   }
 }
 
-__global__ void norm_bwd_finalize(const float* __restrict__ partial, int nblocks, int cols,
-                                  float* __restrict__ dgamma, float* __restrict__ dbeta, int accumulate) {
-  int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= cols) return;
+// Sums the per-block partial rows in a fixed order: block = 32 columns x 8 row groups.
+__global__ void __launch_bounds__(256)
+norm_bwd_finalize(const float* __restrict__ partial, int nblocks, int cols,
+                  float* __restrict__ dgamma, float* __restrict__ dbeta, int accumulate) {
+  __shared__ float sg[8][33], sb[8][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + tx;
   float g = 0.f, b = 0.f;
-  for (int i = 0; i < nblocks; ++i) {
-    const float* p = partial + (size_t)i * 2 * cols;
-    if (dgamma) g += p[c];
-    if (dbeta) b += p[cols + c];
+  if (c < cols) {
+    for (int i = ty; i < nblocks; i += 8) {
+      const float* p = partial + (size_t)i * 2 * cols;
+      if (dgamma) g += p[c];
+      if (dbeta) b += p[cols + c];
+    }
   }
-  if (dgamma) dgamma[c] = accumulate ? dgamma[c] + g : g;
-  if (dbeta) dbeta[c] = accumulate ? dbeta[c] + b : b;
+  sg[ty][tx] = g;
+  sb[ty][tx] = b;
+  __syncthreads();
+  if (ty == 0 && c < cols) {
+    float ag = 0.f, ab = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { ag += sg[i][tx]; ab += sb[i][tx]; }
+    if (dgamma) dgamma[c] = accumulate ? dgamma[c] + ag : ag;
+    if (dbeta) dbeta[c] = accumulate ? dbeta[c] + ab : ab;
+  }
 }
 
 template <typename T, bool RMS>
@@ -320,7 +333,7 @@ static int norm_bwd_launch(const void* x, const float* mean, const float* rstd, 
   if (vec) {
     int nvec = (int)(cols / VN);
     int64_t want = (rows + kWarpsPerBlock - 1) / kWarpsPerBlock;
-    int grid = (int)(want < (int64_t)sm_count() * 8 ? want : (int64_t)sm_count() * 8);
+    int grid = (int)(want < (int64_t)sm_count() * 4 ? want : (int64_t)sm_count() * 4);
     bool wg = dgamma != nullptr, wb = dbeta != nullptr;
     TempBuf part((wg || wb) ? (size_t)grid * 2 * cols * sizeof(float) : 0, st);
     if (!part.ok()) return MT_ERR_CUDA;
@@ -330,7 +343,7 @@ static int norm_bwd_launch(const void* x, const float* mean, const float* rstd, 
 #undef MT_BWD
     MT_LAUNCH_CHECK();
     if (wg || wb) {
-      norm_bwd_finalize<<<(unsigned)((cols + 127) / 128), 128, 0, st>>>((const float*)part.ptr, grid, (int)cols,
+      norm_bwd_finalize<<<(unsigned)((cols + 31) / 32), 256, 0, st>>>((const float*)part.ptr, grid, (int)cols,
                                                                         dgamma, dbeta, accumulate);
       MT_LAUNCH_CHECK();
     }
