@@ -98,6 +98,27 @@ int mt_layernorm_bwd(const void* x, const float* mean, const float* rstd, const 
                      const void* gamma, void* dx, float* dgamma, float* dbeta,
                      int64_t rows, int64_t cols, int accumulate, int dtype, void* stream);
 
+/* LayerNorm backward that never allocates. It has no counterpart in the
+ * reference (every reference op allocates its outputs and temporaries).
+ * It is for callers that must not touch the device allocator while they run:
+ * a host that has handed all device memory to its own arena, code running
+ * where cudaMalloc/cudaFree would serialise or fail (for example inside a
+ * region that forbids allocation), or a deployment with a fixed memory budget
+ * that is audited up front. Same arguments and results as mt_layernorm_bwd; the
+ * per-block partial sums of dgamma/dbeta go to a fixed 4 MiB device array inside
+ * the library image (every GPU that loads the library holds it until exit).
+ * Limits: cols <= 2048, cols a multiple of 8 (fp16/bf16) or 4 (fp32) and at most
+ * 1024 (fp16/bf16) / 512 (fp32), tensors 16-byte aligned; anything else is
+ * rejected with MT_ERR_INVALID and a message naming the limit. The first call on
+ * a device looks up the array's device address (cudaGetSymbolAddress) and caches
+ * it, so make that first call before starting any stream capture. All calls
+ * share the one array and it keeps the previous call's contents (each call
+ * overwrites every slot it reads, so nothing needs clearing): two calls that
+ * overlap on the GPU, e.g. on different streams, race on it. */
+int mt_layernorm_bwd_noalloc(const void* x, const float* mean, const float* rstd, const void* dy,
+                             const void* gamma, void* dx, float* dgamma, float* dbeta,
+                             int64_t rows, int64_t cols, int accumulate, int dtype, void* stream);
+
 /* fused_rmsnorm_forward / fused_rmsnorm_backward
  * (mytorch/nn/functional/fused_ops/rmsnorm.py:159, :251) */
 int mt_rmsnorm_fwd(const void* x, const void* gamma, void* y, float* rstd,

@@ -83,6 +83,7 @@ _SIG = {
     "mt_act_bwd": [_p, _p, _p, _i64, _i, _i, _p],
     "mt_layernorm_fwd": [_p, _p, _p, _p, _p, _p, _i64, _i64, _f, _i, _p],
     "mt_layernorm_bwd": [_p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i, _i, _p],
+    "mt_layernorm_bwd_noalloc": [_p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i, _i, _p],
     "mt_rmsnorm_fwd": [_p, _p, _p, _p, _i64, _i64, _f, _i, _p],
     "mt_rmsnorm_bwd": [_p, _p, _p, _p, _p, _p, _i64, _i64, _i, _i, _p],
     "mt_softmax_fwd": [_p, _p, _i64, _i64, _i, _p],

@@ -392,3 +392,73 @@ int mt_rmsnorm_bwd(const void* x, const float* rstd, const void* dy, const void*
 }
 
 }  // extern "C"
+
+// ---- LayerNorm backward without any allocation ------------------------------
+// The two-stage column reduction of the backward pass needs a scratch area for
+// per-block partial sums. mt_layernorm_bwd takes it from the stream-ordered
+// pool; this variant keeps it in a fixed device array that lives in the
+// library image, so the call itself never allocates or frees.
+namespace mt {
+constexpr int kNoAllocMaxBlocks = 256;   // partial rows (grid size cap)
+constexpr int kNoAllocMaxCols = 2048;    // widest row accepted
+static __device__ __align__(256) float g_ln_scratch[kNoAllocMaxBlocks * 2 * kNoAllocMaxCols];  // 4 MiB per GPU
+
+// Device address of g_ln_scratch per device; in host code the symbol's name is
+// only a handle, so the address is looked up once per device and cached.
+static float* g_ln_scratch_ptr[16] = {nullptr};
+
+static int ln_scratch_address(float** out) {
+  int dev = 0;
+  MT_CHECK_CUDA(cudaGetDevice(&dev));
+  MT_REQUIRE(dev >= 0 && dev < 16, "layernorm_bwd_noalloc: device index %d out of range", dev);
+  if (!g_ln_scratch_ptr[dev]) {
+    void* p = nullptr;
+    MT_CHECK_CUDA(cudaGetSymbolAddress(&p, g_ln_scratch));
+    g_ln_scratch_ptr[dev] = static_cast<float*>(p);
+  }
+  *out = g_ln_scratch_ptr[dev];
+  return MT_OK;
+}
+
+template <typename T>
+static int layernorm_bwd_noalloc_launch(const void* x, const float* mean, const float* rstd, const void* dy,
+                                        const void* gamma, void* dx, float* dgamma, float* dbeta, int64_t rows,
+                                        int64_t cols, int accumulate, float* scratch, cudaStream_t st) {
+  constexpr int VN = Vec16<T>::N;
+  const T* xp = (const T*)x; const T* dyp = (const T*)dy; const T* gp = (const T*)gamma; T* dxp = (T*)dx;
+  MT_REQUIRE(cols % VN == 0 && cols / VN <= 32 * 4 && aligned16(x) && aligned16(dy) && aligned16(dx) &&
+             (!gamma || aligned16(gamma)),
+             "layernorm_bwd_noalloc: needs 16-byte aligned tensors and cols a multiple of %d, at most %d", VN, 128 * VN);
+  if (rows == 0) return MT_OK;
+  const int nvec = (int)(cols / VN);
+  int64_t want = (rows + kWarpsPerBlock - 1) / kWarpsPerBlock;
+  const int grid = (int)(want < kNoAllocMaxBlocks ? want : kNoAllocMaxBlocks);
+  const bool wg = dgamma != nullptr, wb = dbeta != nullptr;
+  dim3 block(kWarpsPerBlock * 32);
+  // every block writes its whole partial row, so nothing in the shared scratch has to start at zero
+#define MT_BWD(MV) norm_bwd_warp<T, MV, false><<<grid, block, 0, st>>>(xp, mean, rstd, dyp, gp, dxp, scratch, rows, (int)cols, wg, wb)
+  if (nvec <= 32) MT_BWD(1); else if (nvec <= 64) MT_BWD(2); else MT_BWD(4);
+#undef MT_BWD
+  MT_LAUNCH_CHECK();
+  if (wg || wb) {
+    norm_bwd_finalize<<<(unsigned)((cols + 31) / 32), 256, 0, st>>>(scratch, grid, (int)cols, dgamma, dbeta, accumulate);
+    MT_LAUNCH_CHECK();
+  }
+  return MT_OK;
+}
+}  // namespace mt
+
+extern "C" int mt_layernorm_bwd_noalloc(const void* x, const float* mean, const float* rstd, const void* dy,
+                                        const void* gamma, void* dx, float* dgamma, float* dbeta, int64_t rows,
+                                        int64_t cols, int accumulate, int dtype, void* stream) {
+  using namespace mt;
+  MT_REQUIRE(x && dy && dx && mean && rstd && rows >= 0 && cols > 0, "layernorm_bwd_noalloc: bad arguments");
+  MT_REQUIRE(cols <= kNoAllocMaxCols,
+             "layernorm_bwd_noalloc: %lld columns exceed the fixed scratch (at most %d columns); use mt_layernorm_bwd",
+             (long long)cols, kNoAllocMaxCols);
+  float* scratch = nullptr;
+  int rc = ln_scratch_address(&scratch);
+  if (rc) return rc;
+  MT_DISPATCH_FLOAT(dtype, T, return (layernorm_bwd_noalloc_launch<T>(x, mean, rstd, dy, gamma, dx, dgamma, dbeta, rows, cols, accumulate, scratch, as_stream(stream))));
+  return MT_OK;
+}
