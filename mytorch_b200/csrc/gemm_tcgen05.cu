@@ -150,28 +150,68 @@ __device__ __forceinline__ void epilogue_staged(const GemmParams& P, const CUten
                                                 uint32_t taddr, uint8_t* stage, int lane, int y0, int64_t n0,
                                                 bool add_bias, int& sidx) {
   constexpr int CW = 128 / (int)sizeof(TO);   // accumulator columns per 128-byte staged row
+  // 128 accumulator columns are requested at once and waited for once.
+  constexpr int GW = 128;                     // columns per load group
+  const float alpha = P.alpha;
+  const int act = P.act;
 #pragma unroll 1
-  for (int c = 0; c < BN / CW; ++c) {
-    const int64_t col0 = n0 + c * CW;
-    if (col0 >= P.N) break;                   // warp-uniform
-    uint32_t r[CW];
-    tmem_ld32(taddr + c * CW, r);
-    if (CW == 64) tmem_ld32(taddr + c * CW + 32, r + (CW == 64 ? 32 : 0));
+  for (int g0 = 0; g0 < BN; g0 += GW) {
+    if (n0 + g0 >= P.N) break;                // warp-uniform
+    uint32_t r[GW];
+    tmem_ld32(taddr + g0, r);
+    tmem_ld32(taddr + g0 + 32, r + 32);
+    tmem_ld32(taddr + g0 + 64, r + 64);
+    tmem_ld32(taddr + g0 + 96, r + 96);
     tmem_ld_wait();
 #pragma unroll
-    for (int e = 0; e < CW; ++e) {
-      float x = P.alpha * __uint_as_float(r[e]);
-      if (add_bias && col0 + e < P.N)
-        x += P.in_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(P.bias)[col0 + e])
-                       : __half2float(reinterpret_cast<const __half*>(P.bias)[col0 + e]);
-      r[e] = __float_as_uint(x);
-    }
-    if (P.preact) stage_store<TO, CW>(tmPre, r, stage, lane, (int)col0, y0, false, sidx);
-    if (P.act != MT_ACT_NONE) {
+    for (int cc = 0; cc < GW / CW; ++cc) {
+      const int64_t col0 = n0 + g0 + cc * CW;
+      if (col0 >= P.N) break;                 // warp-uniform
+      uint32_t* rc = r + cc * CW;
+      if (alpha != 1.f) {                     // uniform; the common alpha == 1 costs nothing
 #pragma unroll
-      for (int e = 0; e < CW; ++e) r[e] = __float_as_uint(act_apply_tc(__uint_as_float(r[e]), P.act));
+        for (int e = 0; e < CW; ++e) rc[e] = __float_as_uint(alpha * __uint_as_float(rc[e]));
+      }
+      if (add_bias) {                         // uniform; bias is read 8 columns at a time when aligned
+        const bool vec_bias = (P.N % 8 == 0) && ((reinterpret_cast<uintptr_t>(P.bias) & 15) == 0);
+#pragma unroll
+        for (int e8 = 0; e8 < CW; e8 += 8) {
+          if (col0 + e8 >= P.N) break;
+          float bv[8];
+          if (vec_bias) {
+            const uint4 q = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(P.bias) + col0 + e8);
+            const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              if (P.in_bf16) {
+                bv[2 * u] = __uint_as_float(w[u] << 16);
+                bv[2 * u + 1] = __uint_as_float(w[u] & 0xffff0000u);
+              } else {
+                const __half2 h = *reinterpret_cast<const __half2*>(&w[u]);
+                bv[2 * u] = __low2float(h);
+                bv[2 * u + 1] = __high2float(h);
+              }
+            }
+          } else {
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+              const int64_t col = col0 + e8 + u;
+              bv[u] = col >= P.N ? 0.f
+                      : P.in_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(P.bias)[col])
+                                  : __half2float(reinterpret_cast<const __half*>(P.bias)[col]);
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < 8; ++u) rc[e8 + u] = __float_as_uint(__uint_as_float(rc[e8 + u]) + bv[u]);
+        }
+      }
+      if (P.preact) stage_store<TO, CW>(tmPre, rc, stage, lane, (int)col0, y0, false, sidx);
+      if (act != MT_ACT_NONE) {
+#pragma unroll
+        for (int e = 0; e < CW; ++e) rc[e] = __float_as_uint(act_apply_tc(__uint_as_float(rc[e]), act));
+      }
+      stage_store<TO, CW>(tmC, rc, stage, lane, (int)col0, y0, P.accumulate != 0, sidx);
     }
-    stage_store<TO, CW>(tmC, r, stage, lane, (int)col0, y0, P.accumulate != 0, sidx);
   }
 }
 
