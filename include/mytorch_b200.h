@@ -89,8 +89,11 @@ int mt_act_bwd(const void* x, const void* dy, void* dx, int64_t n, int act, int 
 
 /* fused_layernorm_forward / fused_layernorm_backward
  * (mytorch/nn/functional/fused_ops/layernorm.py:244, :342). mean/rstd are fp32
- * [rows]. dgamma/dbeta are fp32 [cols] and may be NULL; `accumulate` adds to
- * them instead of overwriting. Column sums are two-stage and deterministic. */
+ * [rows]. dgamma/dbeta are fp32 [cols] and may be NULL. `accumulate` is a bit
+ * mask: 1 = add to dgamma/dbeta instead of overwriting them, 2 = add to dx
+ * (dx then enters holding the gradient of the residual branch, so the block's
+ * `x + f(norm(x))` backward needs no separate add). Column sums are two-stage
+ * and deterministic. The same mask applies to mt_rmsnorm_bwd. */
 int mt_layernorm_fwd(const void* x, const void* gamma, const void* beta, void* y,
                      float* mean, float* rstd, int64_t rows, int64_t cols, float eps,
                      int dtype, void* stream);
@@ -192,6 +195,20 @@ int mt_gemm(const void* A, const void* B, void* C, void* preact, const void* bia
             int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc,
             int trans_a, int trans_b, int in_dtype, int out_dtype, int act,
             float alpha, int accumulate, void* stream);
+/* mt_gemm with one more elementwise operand, for the fusions of a transformer
+ * block: aux is [M,N] in the output dtype with row stride ldc and is combined
+ * with the result AFTER bias and activation:
+ *   aux_mode 1: C = result + aux            (residual add: x + Linear(...),
+ *               gpt2_trainer/gpt2.py:308-311)
+ *   aux_mode 2: C = result * gelu'(aux)     (backward of Linear(act="gelu"),
+ *               mytorch/nn/functional/layers/linear.py:193-221 + activations.py:182)
+ *   aux_mode 3: C = result * 2*relu(aux)    (backward of relu_squared)
+ *   aux_mode 4: C = result * (aux > 0)      (backward of relu)
+ * aux_mode 0 / aux NULL is mt_gemm. Not combinable with accumulate = 2. */
+int mt_gemm_ex(const void* A, const void* B, void* C, void* preact, const void* bias,
+               const void* aux, int aux_mode, int64_t M, int64_t N, int64_t K,
+               int64_t lda, int64_t ldb, int64_t ldc, int trans_a, int trans_b,
+               int in_dtype, int out_dtype, int act, float alpha, int accumulate, void* stream);
 /* Forces the CUDA-core kernel (1) or restores automatic choice (0); used by
  * the tests to cross-check the tensor-core path on the device. */
 int mt_gemm_force_simt(int on);

@@ -13,6 +13,8 @@ LIB_PATH = os.path.join(_HERE, "libmytorch_b200.so")
 
 F32, F16, BF16 = 0, 1, 2
 ACT = {None: 0, "none": 0, "gelu": 1, "relu_squared": 2, "relu2": 2, "relu": 3}
+# aux_mode of mt_gemm_ex that multiplies by the derivative of an activation
+ACT_BWD_AUX = {"gelu": 2, "relu_squared": 3, "relu2": 3, "relu": 4}
 
 
 class MTError(RuntimeError):
@@ -96,6 +98,7 @@ _SIG = {
     "mt_pos_embedding_bwd": [_p, _p, _i64, _i64, _i64, _i, _p],
     "mt_rope": [_p, _p, _p, _i64, _i64, _i64, _i64, _i, _i, _p],
     "mt_gemm": [_p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _i, _f, _i, _p],
+    "mt_gemm_ex": [_p, _p, _p, _p, _p, _p, _i, _i64, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _i, _f, _i, _p],
     "mt_gemm_force_simt": [_i],
     "mt_attn_fwd": [_p, _p, _p, _p, _p, _S, _S, _S, _S, _i64, _i64, _i64, _i64, _f, _i, _i, _p],
     "mt_attn_bwd": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _S, _S, _S, _S, _S, _S, _S, _S,

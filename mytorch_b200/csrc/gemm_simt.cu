@@ -25,7 +25,8 @@ template <typename TI, typename TO>
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const TI* __restrict__ A, const TI* __restrict__ B, TO* __restrict__ C, TO* __restrict__ preact,
                  const TI* __restrict__ bias, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,
-                 int64_t ldc, int trans_a, int trans_b, int act, float alpha, int accumulate) {
+                 int64_t ldc, int trans_a, int trans_b, int act, float alpha, int accumulate,
+                 const TO* __restrict__ aux, int aux_mode) {
   __shared__ float As[SBK][SBM + 4];
   __shared__ float Bs[SBK][SBN + 4];
   const int tid = threadIdx.x;
@@ -74,6 +75,7 @@ gemm_simt_kernel(const TI* __restrict__ A, const TI* __restrict__ B, TO* __restr
       if (bias) v += to_f(bias[gn]);
       if (preact) preact[gm * ldc + gn] = from_f<TO>(v);
       v = act_apply(v, act);
+      if (aux_mode) v = aux_apply(v, to_f(aux[gm * ldc + gn]), aux_mode);
       if (accumulate) v += to_f(C[gm * ldc + gn]);
       C[gm * ldc + gn] = from_f<TO>(v);
     }
@@ -88,7 +90,7 @@ int gemm_simt(const GemmArgs& g, cudaStream_t st) {
     MT_DISPATCH_FLOAT(g.out_dtype, TO, {
       gemm_simt_kernel<TI, TO><<<grid, 256, 0, st>>>((const TI*)g.A, (const TI*)g.B, (TO*)g.C, (TO*)g.preact,
                                                     (const TI*)g.bias, g.M, g.N, g.K, g.lda, g.ldb, g.ldc,
-                                                    g.trans_a, g.trans_b, g.act, g.alpha, g.accumulate);
+                                                    g.trans_a, g.trans_b, g.act, g.alpha, g.accumulate, (const TO*)g.aux, g.aux_mode);
     });
   });
   MT_LAUNCH_CHECK();

@@ -23,6 +23,7 @@
 #include "prof.cuh"
 #include <mutex>
 #include <string.h>
+#include <type_traits>
 
 namespace mt {
 
@@ -42,7 +43,7 @@ template <int BN> struct GemmCfg {
 };
 
 struct GemmParams {
-  void* C; void* preact; const void* bias;
+  void* C; void* preact; const void* bias; const void* aux; int aux_mode;
   int64_t M, N, K, ldc;
   int out_dtype, in_bf16, act, accumulate, vec_store, tma_store;
   float alpha;
@@ -50,11 +51,33 @@ struct GemmParams {
   int* flag;
 };
 
+// tanh in one MUFU instruction (relative error ~2^-11, below the half-precision
+// rounding of everything this kernel writes).
+__device__ __forceinline__ float tanh_fast(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__device__ __forceinline__ float aux_apply_tc(float x, float a, int mode) {
+  switch (mode) {
+    case 1: return x + a;
+    case 2: {
+      const float a2 = a * a;
+      const float t = tanh_fast(0.7978845608f * (a + 0.044715f * a2 * a));
+      return x * (0.5f * (1.f + t + a * (1.f - t * t) * 0.7978845608f * (1.f + 3.f * 0.044715f * a2)));
+    }
+    case 3: return x * 2.f * fmaxf(a, 0.f);
+    case 4: return a > 0.f ? x : 0.f;
+    default: return x;
+  }
+}
+
 __device__ __forceinline__ float act_apply_tc(float x, int act) {
   switch (act) {
     case MT_ACT_GELU: {
       float inner = 0.7978845608f * (x + 0.044715f * x * x * x);
-      return 0.5f * x * (1.f + tanhf(inner));
+      return 0.5f * x * (1.f + tanh_fast(inner));
     }
     case MT_ACT_RELU2: { float r = fmaxf(x, 0.f); return r * r; }
     case MT_ACT_RELU: return fmaxf(x, 0.f);
@@ -162,6 +185,16 @@ __device__ __forceinline__ void epilogue_staged(const GemmParams& P, const CUten
     tmem_ld32(taddr + g0 + 32, r + 32);
     tmem_ld32(taddr + g0 + 64, r + 64);
     tmem_ld32(taddr + g0 + 96, r + 96);
+    // Half outputs: this thread's 256-byte slice of the aux row is requested now, so its
+    // latency overlaps the TMEM read (fp32 aux is read chunk by chunk below).
+    constexpr bool kPrefetchAux = sizeof(TO) == 2;
+    uint4 ax[kPrefetchAux ? 16 : 1];
+    const bool aux_pref = kPrefetchAux && P.aux_mode && (int64_t)y0 + lane < P.M && n0 + g0 + GW <= P.N;
+    if (aux_pref) {
+      const uint4* ap = reinterpret_cast<const uint4*>(reinterpret_cast<const TO*>(P.aux) + ((int64_t)y0 + lane) * P.ldc + n0 + g0);
+#pragma unroll
+      for (int v = 0; v < 16; ++v) ax[v] = __ldg(ap + v);
+    }
     tmem_ld_wait();
 #pragma unroll
     for (int cc = 0; cc < GW / CW; ++cc) {
@@ -209,6 +242,48 @@ __device__ __forceinline__ void epilogue_staged(const GemmParams& P, const CUten
       if (act != MT_ACT_NONE) {
 #pragma unroll
         for (int e = 0; e < CW; ++e) rc[e] = __float_as_uint(act_apply_tc(__uint_as_float(rc[e]), act));
+      }
+      if (kPrefetchAux && aux_pref) {
+        const int mode = P.aux_mode;
+#pragma unroll
+        for (int v = 0; v < 8; ++v) {
+          const uint4 q = ax[cc * 8 + v];
+          const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            float a0, a1;
+            if (std::is_same<TO, __nv_bfloat16>::value) {   // aux has the output dtype
+              a0 = __uint_as_float(w[u] << 16);
+              a1 = __uint_as_float(w[u] & 0xffff0000u);
+            } else {
+              const __half2 h = *reinterpret_cast<const __half2*>(&w[u]);
+              a0 = __low2float(h);
+              a1 = __high2float(h);
+            }
+            rc[v * 8 + 2 * u] = __float_as_uint(aux_apply_tc(__uint_as_float(rc[v * 8 + 2 * u]), a0, mode));
+            rc[v * 8 + 2 * u + 1] = __float_as_uint(aux_apply_tc(__uint_as_float(rc[v * 8 + 2 * u + 1]), a1, mode));
+          }
+        }
+      } else if (P.aux_mode) {                // uniform: combine with this thread's row of the aux operand
+        const int64_t row = (int64_t)y0 + lane;
+        if (row < P.M) {
+          const TO* arow = reinterpret_cast<const TO*>(P.aux) + row * P.ldc + col0;
+          constexpr int PER = 16 / (int)sizeof(TO);       // elements per 16-byte load
+#pragma unroll
+          for (int v = 0; v < CW / PER; ++v) {
+            if (col0 + v * PER >= P.N) break;
+            if (col0 + v * PER + PER <= P.N) {
+              Vec16<TO> a;
+              a.load(arow + v * PER);
+#pragma unroll
+              for (int u = 0; u < PER; ++u)
+                rc[v * PER + u] = __float_as_uint(aux_apply_tc(__uint_as_float(rc[v * PER + u]), a.get(u), P.aux_mode));
+            } else {
+              for (int u = 0; u < PER && col0 + v * PER + u < P.N; ++u)
+                rc[v * PER + u] = __float_as_uint(aux_apply_tc(__uint_as_float(rc[v * PER + u]), to_f(arow[v * PER + u]), P.aux_mode));
+            }
+          }
+        }
       }
       stage_store<TO, CW>(tmC, rc, stage, lane, (int)col0, y0, P.accumulate != 0, sidx);
     }
@@ -397,6 +472,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
               for (int e = 0; e < 8; ++e) v[e] = act_apply_tc(v[e], P.act);
             }
+            if (P.aux_mode) {
+              for (int e = 0; e < n_valid; ++e) {
+                const float a = P.out_dtype == MT_F16 ? __half2float(reinterpret_cast<const __half*>(P.aux)[off + e])
+                              : P.out_dtype == MT_BF16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(P.aux)[off + e])
+                                                       : reinterpret_cast<const float*>(P.aux)[off + e];
+                v[e] = aux_apply(v[e], a, P.aux_mode);
+              }
+            }
             if (P.out_dtype == MT_F16) store8(reinterpret_cast<__half*>(P.C) + off, v, n_valid, P.vec_store, P.accumulate);
             else if (P.out_dtype == MT_BF16) store8(reinterpret_cast<__nv_bfloat16*>(P.C) + off, v, n_valid, P.vec_store, P.accumulate);
             else store8(reinterpret_cast<float*>(P.C) + off, v, n_valid, P.vec_store, P.accumulate);
@@ -528,7 +611,7 @@ int gemm_tc(const GemmArgs& g, cudaStream_t st) {
   }
   const int bn = best_bn;
   GemmParams P;
-  P.C = g.C; P.preact = g.preact; P.bias = g.bias;
+  P.C = g.C; P.preact = g.preact; P.bias = g.bias; P.aux = g.aux; P.aux_mode = g.aux_mode;
   P.M = g.M; P.N = g.N; P.K = g.K; P.ldc = g.ldc;
   P.out_dtype = g.out_dtype; P.in_bf16 = g.in_dtype == MT_BF16; P.act = g.act; P.accumulate = g.accumulate;
   P.alpha = g.alpha;
@@ -560,7 +643,7 @@ int gemm_tc(const GemmArgs& g, cudaStream_t st) {
   memset(&tpm, 0, sizeof(tpm));
   const size_t osz = g.out_dtype == MT_F32 ? 4 : 2;
   P.tma_store = aligned16(g.C) && (g.ldc * osz) % 16 == 0 && (!g.preact || aligned16(g.preact)) &&
-                !(g.accumulate && g.out_dtype != MT_F32);
+                (!g.aux || aligned16(g.aux)) && !(g.accumulate && g.out_dtype != MT_F32);
   if (P.tma_store) {
     const uint32_t cw = (uint32_t)(128 / osz);
     rc = make_tmap_2d_typed(&tcm, g.C, g.out_dtype, (uint64_t)g.N, (uint64_t)g.M, (uint64_t)g.ldc, cw, 32);
@@ -591,9 +674,22 @@ extern "C" {
 
 int mt_gemm_force_simt(int on) { g_force_simt = on; return MT_OK; }
 
+int mt_gemm_ex(const void* A, const void* B, void* C, void* preact, const void* bias, const void* aux, int aux_mode,
+               int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int trans_a, int trans_b,
+               int in_dtype, int out_dtype, int act, float alpha, int accumulate, void* stream);
+
 int mt_gemm(const void* A, const void* B, void* C, void* preact, const void* bias, int64_t M, int64_t N, int64_t K,
             int64_t lda, int64_t ldb, int64_t ldc, int trans_a, int trans_b, int in_dtype, int out_dtype, int act,
             float alpha, int accumulate, void* stream) {
+  return mt_gemm_ex(A, B, C, preact, bias, nullptr, 0, M, N, K, lda, ldb, ldc, trans_a, trans_b, in_dtype, out_dtype, act,
+                    alpha, accumulate, stream);
+}
+
+int mt_gemm_ex(const void* A, const void* B, void* C, void* preact, const void* bias, const void* aux, int aux_mode,
+               int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int trans_a, int trans_b,
+               int in_dtype, int out_dtype, int act, float alpha, int accumulate, void* stream) {
+  MT_REQUIRE((aux != nullptr) == (aux_mode != 0) && aux_mode >= 0 && aux_mode <= 4, "gemm: aux operand and aux_mode must be given together");
+  MT_REQUIRE(!(aux_mode && accumulate == 2), "gemm: an aux operand cannot be combined with split-K accumulation");
   MT_REQUIRE(A && B && C && M >= 0 && N >= 0 && K >= 0, "gemm: bad arguments");
   MT_REQUIRE(lda >= (trans_a ? M : K) && ldb >= (trans_b ? K : N) && ldc >= N, "gemm: leading dimension too small");
   MT_REQUIRE(accumulate >= 0 && accumulate <= 2, "gemm: bad accumulate mode");
@@ -601,6 +697,8 @@ int mt_gemm(const void* A, const void* B, void* C, void* preact, const void* bia
   MT_REQUIRE(accumulate != 2 || (act == MT_ACT_NONE && !preact), "gemm: split-K accumulation cannot apply an activation");
   if (M == 0 || N == 0) return MT_OK;
   GemmArgs g{A, B, C, preact, bias, M, N, K, lda, ldb, ldc, trans_a, trans_b, in_dtype, out_dtype, act, alpha, accumulate};
+  g.aux = aux;
+  g.aux_mode = aux_mode;
   cudaStream_t st = as_stream(stream);
   if (!g_force_simt && gemm_tc_supported(g)) return gemm_tc(g, st);
   return gemm_simt(g, st);

@@ -125,7 +125,7 @@ template <typename T, int MAXV, bool RMS>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 norm_bwd_warp(const T* __restrict__ x, const float* __restrict__ mean, const float* __restrict__ rstd_in,
               const T* __restrict__ dy, const T* __restrict__ gamma, T* __restrict__ dx,
-              float* __restrict__ partial, int64_t rows, int cols, bool want_dg, bool want_db) {
+              float* __restrict__ partial, int64_t rows, int cols, bool want_dg, bool want_db, bool dx_acc = false) {
   constexpr int VN = Vec16<T>::N;
   __shared__ float red[kWarpsPerBlock][32 * VN + 1];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -185,6 +185,12 @@ norm_bwd_warp(const T* __restrict__ x, const float* __restrict__ mean, const flo
           float dxh = gamma ? dv[i].get(e) * gv[i].get(e) : dv[i].get(e);
           o.set(e, rs * (dxh - s1 - xh * s2));
         }
+        if (dx_acc) {   // dx += result: the incoming buffer already holds the other branch's gradient
+          Vec16<T> old;
+          old.load(dxr + vi * VN);
+#pragma unroll
+          for (int e = 0; e < VN; ++e) o.set(e, o.get(e) + old.get(e));
+        }
         o.store(dxr + vi * VN);
       }
     }
@@ -220,7 +226,7 @@ template <typename T, bool RMS>
 __global__ void __launch_bounds__(256)
 norm_bwd_block(const T* __restrict__ x, const float* __restrict__ mean, const float* __restrict__ rstd_in,
                const T* __restrict__ dy, const T* __restrict__ gamma, T* __restrict__ dx,
-               int64_t rows, int64_t cols) {
+               int64_t rows, int64_t cols, bool dx_acc = false) {
   __shared__ float sh[32];
   const int64_t row = blockIdx.x;
   const float mu = RMS ? 0.f : mean[row];
@@ -240,7 +246,8 @@ norm_bwd_block(const T* __restrict__ x, const float* __restrict__ mean, const fl
   for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) {
     float xh = (to_f(xr[c]) - mu) * rs;
     float dxh = to_f(dyr[c]) * (gamma ? to_f(gamma[c]) : 1.f);
-    dx[row * cols + c] = from_f<T>(rs * (dxh - s1 - xh * s2));
+    const float r_ = rs * (dxh - s1 - xh * s2);
+    dx[row * cols + c] = from_f<T>(dx_acc ? to_f(dx[row * cols + c]) + r_ : r_);
   }
 }
 
@@ -338,21 +345,21 @@ static int norm_bwd_launch(const void* x, const float* mean, const float* rstd, 
     TempBuf part((wg || wb) ? (size_t)grid * 2 * cols * sizeof(float) : 0, st);
     if (!part.ok()) return MT_ERR_CUDA;
     dim3 block(kWarpsPerBlock * 32);
-#define MT_BWD(MV) norm_bwd_warp<T, MV, RMS><<<grid, block, 0, st>>>(xp, mean, rstd, dyp, gp, dxp, (float*)part.ptr, rows, (int)cols, wg, wb)
+#define MT_BWD(MV) norm_bwd_warp<T, MV, RMS><<<grid, block, 0, st>>>(xp, mean, rstd, dyp, gp, dxp, (float*)part.ptr, rows, (int)cols, wg, wb, (accumulate & 2) != 0)
     if (nvec <= 32) MT_BWD(1); else if (nvec <= 64) MT_BWD(2); else MT_BWD(4);
 #undef MT_BWD
     MT_LAUNCH_CHECK();
     if (wg || wb) {
       norm_bwd_finalize<<<(unsigned)((cols + 31) / 32), 256, 0, st>>>((const float*)part.ptr, grid, (int)cols,
-                                                                        dgamma, dbeta, accumulate);
+                                                                        dgamma, dbeta, accumulate & 1);
       MT_LAUNCH_CHECK();
     }
   } else {
-    norm_bwd_block<T, RMS><<<(unsigned)rows, 256, 0, st>>>(xp, mean, rstd, dyp, gp, dxp, rows, cols);
+    norm_bwd_block<T, RMS><<<(unsigned)rows, 256, 0, st>>>(xp, mean, rstd, dyp, gp, dxp, rows, cols, (accumulate & 2) != 0);
     MT_LAUNCH_CHECK();
     if (dgamma || dbeta) {
       norm_bwd_colsum<T, RMS><<<(unsigned)((cols + 31) / 32), 256, 0, st>>>(xp, mean, rstd, dyp, dgamma, dbeta,
-                                                                           rows, cols, accumulate);
+                                                                           rows, cols, accumulate & 1);
       MT_LAUNCH_CHECK();
     }
   }

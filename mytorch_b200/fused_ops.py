@@ -41,8 +41,9 @@ def _check_float(*arrs):
 
 # ------------------------------------------------------------------ matmul ----
 def gemm(a, b, trans_a=False, trans_b=False, out=None, bias=None, act=None, preact=False,
-         out_dtype=None, alpha=1.0, accumulate=0):
-    """out = act(alpha * op(a) @ op(b) + bias); see mt_gemm in the C header."""
+         out_dtype=None, alpha=1.0, accumulate=0, aux=None, aux_mode=0):
+    """out = combine(act(alpha * op(a) @ op(b) + bias), aux); see mt_gemm / mt_gemm_ex in
+    the C header (aux_mode 1 adds aux, 2/3/4 multiply by gelu'/relu2'/relu' of aux)."""
     a, b = _A(a), _A(b)
     dt = _check_float(a, b, bias)
     assert a.ndim == 2 and b.ndim == 2
@@ -56,9 +57,12 @@ def gemm(a, b, trans_a=False, trans_b=False, out=None, bias=None, act=None, prea
             raise ValueError("accumulate needs an existing output")
         out = DeviceArray.empty((M, N), out_dtype)
     pre = DeviceArray.empty((M, N), out_dtype) if preact else None
-    _lib.gemm(a.ptr, b.ptr, out.ptr, _ptr(pre), _ptr(bias), M, N, K, a.shape[1], b.shape[1], N,
-              int(trans_a), int(trans_b), a.code, out.code,
-              _lib.ACT[act], float(alpha), int(accumulate), stream())
+    if aux is not None:
+        aux = _A(aux)
+        assert aux.size == M * N and aux.dtype == out.dtype, "aux must be [M,N] in the output dtype"
+    _lib.gemm_ex(a.ptr, b.ptr, out.ptr, _ptr(pre), _ptr(bias), _ptr(aux), int(aux_mode if aux is not None else 0),
+                 M, N, K, a.shape[1], b.shape[1], N, int(trans_a), int(trans_b), a.code, out.code,
+                 _lib.ACT[act], float(alpha), int(accumulate), stream())
     return (out, pre) if preact else out
 
 
@@ -107,14 +111,16 @@ def fused_layernorm_forward(x, gamma=None, beta=None, eps=1e-5, training=True):
     return y, mean, rstd
 
 
-def fused_layernorm_backward(x, mean, inv_var, dy, gamma=None, beta=None, dgamma_out=None, dbeta_out=None):
+def fused_layernorm_backward(x, mean, inv_var, dy, gamma=None, beta=None, dgamma_out=None, dbeta_out=None,
+                             dx_out=None):
     """-> (dx, dgamma, dbeta) (fused_ops/layernorm.py:342). dgamma/dbeta are
-    fp32; when `*_out` buffers are given the sums are ADDED into them."""
+    fp32; when `*_out` buffers are given the sums are ADDED into them, and
+    `dx_out` (same shape/dtype as x) likewise receives dx ADDED to its contents."""
     x, dy = _A(x), _A(dy)
     _check_float(x, dy, gamma)
     n, e = x.shape
-    dx = DeviceArray.empty((n, e), x.dtype)
-    acc = dgamma_out is not None or dbeta_out is not None
+    dx = dx_out if dx_out is not None else DeviceArray.empty((n, e), x.dtype)
+    acc = int(dgamma_out is not None or dbeta_out is not None) | (2 if dx_out is not None else 0)
     dg = dgamma_out if dgamma_out is not None else (DeviceArray.empty((e,), "float32") if gamma is not None else None)
     db = dbeta_out if dbeta_out is not None else (DeviceArray.empty((e,), "float32") if beta is not None else None)
     _lib.layernorm_bwd(x.ptr, _A(mean).ptr, _A(inv_var).ptr, dy.ptr, _ptr(gamma), dx.ptr, _ptr(dg), _ptr(db),
@@ -133,15 +139,15 @@ def fused_rmsnorm_forward(x, gamma=None, eps=1e-5, training=True):
     return y, rstd
 
 
-def fused_rmsnorm_backward(x, rstd, dy, gamma=None, dgamma_out=None):
-    """-> (dx, dgamma) (fused_ops/rmsnorm.py:251)."""
+def fused_rmsnorm_backward(x, rstd, dy, gamma=None, dgamma_out=None, dx_out=None):
+    """-> (dx, dgamma) (fused_ops/rmsnorm.py:251); `*_out` buffers are added into."""
     x, dy = _A(x), _A(dy)
     _check_float(x, dy, gamma)
     n, e = x.shape
-    dx = DeviceArray.empty((n, e), x.dtype)
+    dx = dx_out if dx_out is not None else DeviceArray.empty((n, e), x.dtype)
     dg = dgamma_out if dgamma_out is not None else (DeviceArray.empty((e,), "float32") if gamma is not None else None)
     _lib.rmsnorm_bwd(x.ptr, _A(rstd).ptr, dy.ptr, _ptr(gamma), dx.ptr, _ptr(dg), n, e,
-                     int(dgamma_out is not None), x.code, stream())
+                     int(dgamma_out is not None) | (2 if dx_out is not None else 0), x.code, stream())
     return dx, dg
 
 

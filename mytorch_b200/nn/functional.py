@@ -31,18 +31,31 @@ def _param_grad_gemm(dy2, x2, weight):
 
 
 # ---------------------------------------------------------------- linear ----
-def linear(x, weight, bias=None, auto=False, fused=True, act_func=None):
-    """y = act(x @ weight^T + bias), weight [out, in]
+def _existing_grad(t):
+    """The gradient buffer of an activation that already holds another branch's
+    gradient (so a kernel can add into it), else None."""
+    if t.requires_grad and not t.is_param and t.grad is not None and t.grad.dtype == t.dtype:
+        return t.grad
+    return None
+
+
+def linear(x, weight, bias=None, auto=False, fused=True, act_func=None, residual=None):
+    """y = act(x @ weight^T + bias) (+ residual), weight [out, in]
     (mytorch/nn/functional/layers/linear.py:149-236). No transposed copy of the
-    weight is made: the GEMM reads it K-major in place."""
+    weight is made: the GEMM reads it K-major in place. `residual` (same shape as
+    y) is added in the GEMM epilogue: the `x + sublayer(x)` of a transformer block
+    (gpt2_trainer/gpt2.py:308-311) without a separate add kernel."""
     x2 = _flat2d(x.data)
     want_pre = act_func is not None and _needs_graph(x, weight, bias)
     res = K.gemm(x2, weight.data, trans_b=True, bias=None if bias is None else bias.data,
-                 act=act_func, preact=want_pre)
+                 act=act_func, preact=want_pre,
+                 aux=None if residual is None else _flat2d(residual.data), aux_mode=1)
     y2, pre = res if want_pre else (res, None)
     out = Tensor(y2.reshape(*x.shape[:-1], weight.shape[0]))
-    if _needs_graph(x, weight, bias):
+    if _needs_graph(x, weight, bias, residual):
         def _bw(g):
+            if residual is not None and residual.requires_grad:
+                residual._accumulate(g)          # the skip connection passes the gradient through
             g2 = _flat2d(g)
             if act_func is not None:
                 g2 = K.fused_activation_backward(pre, g2, act_func)
@@ -55,7 +68,40 @@ def linear(x, weight, bias=None, auto=False, fused=True, act_func=None):
                 x._accumulate(K.gemm(g2, weight.data).reshape(x.shape))
         out.requires_grad = True
         out.grad_fn, out.grad_fn_name = _bw, "<LinearBackward>"
-        out._add_parents(x, weight, bias)
+        out._add_parents(x, weight, bias, residual)
+    return out
+
+
+def mlp(x, w1, w2, act_func="gelu", residual=None):
+    """act(x @ w1^T) @ w2^T (+ residual): the FeedForward of a block
+    (gpt2_trainer/gpt2.py:237-283, bias-free form) as one autograd node. The
+    activation is applied in the first GEMM's epilogue. In the backward its
+    derivative runs as its own bandwidth-bound kernel: measured on B200, folding
+    it into the epilogue of the 16384x3072x768 GEMM (mt_gemm_ex aux_mode 2) makes
+    that GEMM epilogue-bound and slower than the two kernels together."""
+    x2 = _flat2d(x.data)
+    graph = _needs_graph(x, w1, w2, residual)
+    if graph:
+        h, u = K.gemm(x2, w1.data, trans_b=True, act=act_func, preact=True)
+    else:
+        h, u = K.gemm(x2, w1.data, trans_b=True, act=act_func), None
+    y2 = K.gemm(h, w2.data, trans_b=True, aux=None if residual is None else _flat2d(residual.data), aux_mode=1)
+    out = Tensor(y2.reshape(*x.shape[:-1], w2.shape[0]))
+    if graph:
+        def _bw(g):
+            if residual is not None and residual.requires_grad:
+                residual._accumulate(g)
+            g2 = _flat2d(g)
+            if w2.requires_grad:
+                _param_grad_gemm(g2, h, w2)
+            du = K.fused_activation_backward(u, K.gemm(g2, w2.data), act_func)        # (dy @ w2) * act'(u)
+            if w1.requires_grad:
+                _param_grad_gemm(du, x2, w1)
+            if x.requires_grad:
+                x._accumulate(K.gemm(du, w1.data).reshape(x.shape))
+        out.requires_grad = True
+        out.grad_fn, out.grad_fn_name = _bw, "<MLPBackward>"
+        out._add_parents(x, w1, w2, residual)
     return out
 
 
@@ -106,8 +152,10 @@ def layernorm(x, weight=None, bias=None, eps=1e-5, training=True, auto=False, fu
         def _bw(g):
             dg = weight.param_grad_buffer() if (weight is not None and weight.requires_grad) else None
             db = bias.param_grad_buffer() if (bias is not None and bias.requires_grad) else None
-            dx, _, _ = K.fused_layernorm_backward(x2, mean, rstd, _flat2d(g), g_arr, None, dgamma_out=dg, dbeta_out=db)
-            if x.requires_grad:
+            have = _existing_grad(x)
+            dx, _, _ = K.fused_layernorm_backward(x2, mean, rstd, _flat2d(g), g_arr, None, dgamma_out=dg, dbeta_out=db,
+                                                  dx_out=None if have is None else _flat2d(have))
+            if x.requires_grad and have is None:
                 x._accumulate(dx.reshape(x.shape))
         out.requires_grad = True
         out.grad_fn, out.grad_fn_name = _bw, "<LayerNormBackward>"
@@ -124,8 +172,10 @@ def rmsnorm(x, weight=None, eps=1e-5, training=True, auto=False, fused=True):
     if _needs_graph(x, weight):
         def _bw(g):
             dg = weight.param_grad_buffer() if (weight is not None and weight.requires_grad) else None
-            dx, _ = K.fused_rmsnorm_backward(x2, rstd, _flat2d(g), g_arr, dgamma_out=dg)
-            if x.requires_grad:
+            have = _existing_grad(x)
+            dx, _ = K.fused_rmsnorm_backward(x2, rstd, _flat2d(g), g_arr, dgamma_out=dg,
+                                             dx_out=None if have is None else _flat2d(have))
+            if x.requires_grad and have is None:
                 x._accumulate(dx.reshape(x.shape))
         out.requires_grad = True
         out.grad_fn, out.grad_fn_name = _bw, "<RMSNormBackward>"

@@ -324,3 +324,43 @@ def test_golden_small_vectors_fp32(mt, golden_ops, op_inputs):
     Xr = D(d["rope_x"])
     F.fused_rope_forward(Xr, D(g["rope_cos"]), D(g["rope_sin"]))
     close(Xr.numpy(), g["rope_y"], 1e-4)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_gemm_aux_operand_residual_and_activation_backward(mt, dtype):
+    """mt_gemm_ex: result combined with an [M,N] operand in the epilogue."""
+    F = mt.fused_ops
+    r = np.random.default_rng(12)
+    M, N, K = 200, 264, 136
+    a, b, aux = rnd(r.standard_normal((M, K)), dtype), rnd(r.standard_normal((N, K)) * 0.2, dtype), rnd(r.standard_normal((M, N)), dtype)
+    base = a.astype(np.float64) @ b.T.astype(np.float64)
+    A, B, AUX = dev(mt, a, dtype), dev(mt, b, dtype), dev(mt, aux, dtype)
+    t = TOL[dtype]
+    close(F.gemm(A, B, trans_b=True, aux=AUX, aux_mode=1).numpy(), base + aux, t, "residual")
+    close(F.gemm(A, B, trans_b=True, aux=AUX, aux_mode=2).numpy(), O.gelu_bwd(aux.astype(np.float64), base), 2 * t, "gelu'")
+    close(F.gemm(A, B, trans_b=True, aux=AUX, aux_mode=3).numpy(), O.relu2_bwd(aux.astype(np.float64), base), 2 * t, "relu2'")
+    close(F.gemm(A, B, trans_b=True, aux=AUX, aux_mode=4).numpy(), (aux > 0) * base, 2 * t, "relu'")
+    # activation first, then the residual
+    close(F.gemm(A, B, trans_b=True, act="gelu", aux=AUX, aux_mode=1).numpy(), O.gelu_fwd(base) + aux, t, "gelu + residual")
+    no_device_flag(mt)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", [(64, 768), (5, 1000), (3, 52)])
+def test_norm_backward_adds_into_existing_dx(mt, dtype, shape):
+    F = mt.fused_ops
+    r = np.random.default_rng(13)
+    x, g, dy, prev = (rnd(r.standard_normal(s), dtype) for s in (shape, shape[1:], shape, shape))
+    _, mu, rs = O.layernorm_fwd(x, g, None)
+    want = O.layernorm_bwd(x, mu, rs, dy, g)[0] + prev
+    X, G, DY, PREV = dev(mt, x, dtype), dev(mt, g, dtype), dev(mt, dy, dtype), dev(mt, prev, dtype)
+    _, MU, RS = F.fused_layernorm_forward(X, G, None)
+    DX, _, _ = F.fused_layernorm_backward(X, MU, RS, DY, G, None, dx_out=PREV)
+    assert DX.ptr == PREV.ptr
+    close(PREV.numpy(), want, 2 * TOL[dtype], "layernorm dx +=")
+    _, rs2 = O.rmsnorm_fwd(x, None)
+    want = O.rmsnorm_bwd(x, rs2, dy, None)[0] + prev
+    PREV2 = dev(mt, prev, dtype)
+    _, RS2 = F.fused_rmsnorm_forward(X, None)
+    F.fused_rmsnorm_backward(X, RS2, DY, None, dx_out=PREV2)
+    close(PREV2.numpy(), want, 2 * TOL[dtype], "rmsnorm dx +=")
