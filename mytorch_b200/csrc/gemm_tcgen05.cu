@@ -30,7 +30,8 @@ namespace mt {
 using namespace sm100;
 
 constexpr int BM = 128, BK = 64;
-constexpr int kGemmThreads = 192;
+constexpr int kEpiWarps = 8;                       // two warps per TMEM lane quarter, each half of the tile's columns
+constexpr int kGemmThreads = 64 + 32 * kEpiWarps;
 constexpr int kABytes = BM * BK * 2;  // 16 KB
 
 template <int BN> struct GemmCfg {
@@ -38,7 +39,7 @@ template <int BN> struct GemmCfg {
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kStages = BN == 256 ? 4 : 6;
   static constexpr int kTmemCols = 2 * BN;  // two accumulator buffers
-  static constexpr int kEpiBytes = 4 * 2 * 4096;  // per epilogue warp: two 32-row x 128-byte staging buffers
+  static constexpr int kEpiBytes = kEpiWarps * 4096;  // per epilogue warp: one 32-row x 128-byte staging buffer
   static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024 /*align*/ + 256 /*barriers*/;
 };
 
@@ -141,8 +142,8 @@ template <> __device__ __forceinline__ uint32_t pack_pair<float>(float a, float)
 template <typename TO, int CW>
 __device__ __forceinline__ void stage_store(const CUtensorMap* map, const uint32_t* r, uint8_t* stage, int lane, int x,
                                             int y, bool reduce, int& sidx) {
-  uint8_t* buf = stage + (sidx & 1) * 4096;
-  if (lane == 0) bulk_wait_read<1>();   // the store issued two stagings ago has released this buffer
+  uint8_t* buf = stage;
+  if (lane == 0) bulk_wait_read<0>();   // the previous store of this warp has finished reading the buffer
   __syncwarp();
   uint8_t* rowp = buf + lane * 128;
 #pragma unroll
@@ -171,29 +172,21 @@ __device__ __forceinline__ void stage_store(const CUtensorMap* map, const uint32
 template <int BN, typename TO>
 __device__ __forceinline__ void epilogue_staged(const GemmParams& P, const CUtensorMap* tmC, const CUtensorMap* tmPre,
                                                 uint32_t taddr, uint8_t* stage, int lane, int y0, int64_t n0,
-                                                bool add_bias, int& sidx) {
+                                                bool add_bias, int& sidx, int col_begin) {
   constexpr int CW = 128 / (int)sizeof(TO);   // accumulator columns per 128-byte staged row
-  // 128 accumulator columns are requested at once and waited for once.
-  constexpr int GW = 128;                     // columns per load group
+  // This warp's half of the tile's columns is requested at once and waited for once.
+  constexpr int GW = BN / 2;                  // columns per warp = per load group (128 or 64)
   const float alpha = P.alpha;
   const int act = P.act;
 #pragma unroll 1
-  for (int g0 = 0; g0 < BN; g0 += GW) {
+  for (int g0 = col_begin; g0 < col_begin + GW; g0 += GW) {
     if (n0 + g0 >= P.N) break;                // warp-uniform
     uint32_t r[GW];
     tmem_ld32(taddr + g0, r);
     tmem_ld32(taddr + g0 + 32, r + 32);
-    tmem_ld32(taddr + g0 + 64, r + 64);
-    tmem_ld32(taddr + g0 + 96, r + 96);
-    // Half outputs: this thread's 256-byte slice of the aux row is requested now, so its
-    // latency overlaps the TMEM read (fp32 aux is read chunk by chunk below).
-    constexpr bool kPrefetchAux = sizeof(TO) == 2;
-    uint4 ax[kPrefetchAux ? 16 : 1];
-    const bool aux_pref = kPrefetchAux && P.aux_mode && (int64_t)y0 + lane < P.M && n0 + g0 + GW <= P.N;
-    if (aux_pref) {
-      const uint4* ap = reinterpret_cast<const uint4*>(reinterpret_cast<const TO*>(P.aux) + ((int64_t)y0 + lane) * P.ldc + n0 + g0);
-#pragma unroll
-      for (int v = 0; v < 16; ++v) ax[v] = __ldg(ap + v);
+    if (GW == 128) {
+      tmem_ld32(taddr + g0 + 64, r + (GW == 128 ? 64 : 0));
+      tmem_ld32(taddr + g0 + 96, r + (GW == 128 ? 96 : 0));
     }
     tmem_ld_wait();
 #pragma unroll
@@ -243,28 +236,7 @@ __device__ __forceinline__ void epilogue_staged(const GemmParams& P, const CUten
 #pragma unroll
         for (int e = 0; e < CW; ++e) rc[e] = __float_as_uint(act_apply_tc(__uint_as_float(rc[e]), act));
       }
-      if (kPrefetchAux && aux_pref) {
-        const int mode = P.aux_mode;
-#pragma unroll
-        for (int v = 0; v < 8; ++v) {
-          const uint4 q = ax[cc * 8 + v];
-          const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            float a0, a1;
-            if (std::is_same<TO, __nv_bfloat16>::value) {   // aux has the output dtype
-              a0 = __uint_as_float(w[u] << 16);
-              a1 = __uint_as_float(w[u] & 0xffff0000u);
-            } else {
-              const __half2 h = *reinterpret_cast<const __half2*>(&w[u]);
-              a0 = __low2float(h);
-              a1 = __high2float(h);
-            }
-            rc[v * 8 + 2 * u] = __float_as_uint(aux_apply_tc(__uint_as_float(rc[v * 8 + 2 * u]), a0, mode));
-            rc[v * 8 + 2 * u + 1] = __float_as_uint(aux_apply_tc(__uint_as_float(rc[v * 8 + 2 * u + 1]), a1, mode));
-          }
-        }
-      } else if (P.aux_mode) {                // uniform: combine with this thread's row of the aux operand
+      if (P.aux_mode) {                       // uniform: combine with this thread's row of the aux operand
         const int64_t row = (int64_t)y0 + lane;
         if (row < P.M) {
           const TO* arow = reinterpret_cast<const TO*>(P.aux) + row * P.ldc + col0;
@@ -315,7 +287,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(accf_bar(b), 1); mbar_init(acce_bar(b), 4); }
+    for (int b = 0; b < 2; ++b) { mbar_init(accf_bar(b), 1); mbar_init(acce_bar(b), kEpiWarps); }
     *abort_flag = 0;
     fence_barrier_init();
     fence_proxy_async();
@@ -418,6 +390,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   } else {
     // ------------------------------------------------------------ epilogue --
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32)
+    const int col_begin = ((warp - 2) >> 2) * (BN / 2);   // this warp's half of the tile's columns
     int it = 0;
     int sidx = 0;   // running count of staged stores of this warp (selects the staging buffer)
     bool ok = true;
@@ -433,16 +406,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const int64_t row = m0 + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN;
       if (P.tma_store) {
-        uint8_t* stage = epi_stage + (warp - 2) * 8192;
+        uint8_t* stage = epi_stage + (warp - 2) * 4096;
         const int y0 = (int)m0 + quarter * 32;
         if (y0 < P.M) {   // warp-uniform: a slab of 32 rows entirely past M has nothing to write
-          if (P.out_dtype == MT_F16) epilogue_staged<BN, __half>(P, &tmC, &tmPre, taddr, stage, lane, y0, n0, add_bias, sidx);
-          else if (P.out_dtype == MT_BF16) epilogue_staged<BN, __nv_bfloat16>(P, &tmC, &tmPre, taddr, stage, lane, y0, n0, add_bias, sidx);
-          else epilogue_staged<BN, float>(P, &tmC, &tmPre, taddr, stage, lane, y0, n0, add_bias, sidx);
+          if (P.out_dtype == MT_F16) epilogue_staged<BN, __half>(P, &tmC, &tmPre, taddr, stage, lane, y0, n0, add_bias, sidx, col_begin);
+          else if (P.out_dtype == MT_BF16) epilogue_staged<BN, __nv_bfloat16>(P, &tmC, &tmPre, taddr, stage, lane, y0, n0, add_bias, sidx, col_begin);
+          else epilogue_staged<BN, float>(P, &tmC, &tmPre, taddr, stage, lane, y0, n0, add_bias, sidx, col_begin);
         }
       } else
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = col_begin / 32; c < (col_begin + BN / 2) / 32; ++c) {
         uint32_t r[32];
         tmem_ld32(taddr + c * 32, r);
         tmem_ld_wait();
