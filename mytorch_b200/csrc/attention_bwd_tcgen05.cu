@@ -7,9 +7,10 @@
 //   dV  += P^T dO           dK  += dS^T Q          (128xDx128, accumulated)
 //   dQ   = dS K             (128xDx128, added to a fp32 buffer with atomics,
 //                            since every key block contributes to every dQ row)
-// Warp roles: warp 4 TMA producer (K, V once; Q and dO per query block, read in
-// place through 4-D strided tensor maps), warp 5 MMA issuer, warps 0-3 the
-// elementwise stage: thread = key row = TMEM lane; it reads S^T and dP^T,
+// Warp roles: warp 8 TMA producer (K, V once; Q and dO per query block, read in
+// place through 4-D strided tensor maps), warp 9 MMA issuer, warps 0-7 the
+// elementwise stage: thread = key row = TMEM lane (two warps per lane quarter,
+// 64 query columns each); it reads S^T and dP^T,
 // forms P^T = exp2(S^T*scale*log2e - lse*log2e) and dS^T = P^T (dP^T - delta) *
 // scale, and writes both as half into shared memory in the swizzled layout that
 // serves as K-major A operand for dV/dK and, read the other way, as M-major A
@@ -25,7 +26,8 @@ namespace mt {
 
 using namespace sm100;
 
-constexpr int kBwdThreads = 192;
+constexpr int kBwdEwWarps = 8;                 // elementwise warps: two per TMEM lane quarter, 64 query columns each
+constexpr int kBwdThreads = 32 * (kBwdEwWarps + 2);
 
 template <int D> struct BwdCfg {
   static constexpr int kChunks = D / 64;
@@ -84,12 +86,13 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   if (threadIdx.x == 0) {
     mbar_init(bar_kv, 1);
     for (int s = 0; s < 2; ++s) { mbar_init(bar_qfull0 + 8 * s, 1); mbar_init(bar_qempty0 + 8 * s, 1); }
-    mbar_init(bar_sdp, 1); mbar_init(bar_pds, 128); mbar_init(bar_dq, 1); mbar_init(bar_dqfree, 128); mbar_init(bar_stat, 128);
+    mbar_init(bar_sdp, 1); mbar_init(bar_pds, 32 * kBwdEwWarps); mbar_init(bar_dq, 1);
+    mbar_init(bar_dqfree, 32 * kBwdEwWarps); mbar_init(bar_stat, 32 * kBwdEwWarps);
     *abort_flag = 0;
     fence_barrier_init();
     fence_proxy_async();
   }
-  if (warp == 5) {
+  if (warp == kBwdEwWarps + 1) {
     tmem_alloc(smem_u32(tmem_slot), Cfg::kTmemCols);
     tmem_relinquish();
   }
@@ -98,7 +101,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 4) {
+  if (warp == kBwdEwWarps) {
     // ------------------------------------------------------------ producer --
     if (lane == 0) {
       prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV); prefetch_tmap(&tmDO);
@@ -120,7 +123,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == kBwdEwWarps + 1) {
     // ---------------------------------------------------------- MMA issuer --
     if (lane == 0) {
       const uint32_t idesc_kk = idesc_f16(P.is_bf16, 0, 0, 128, 128);   // S^T, dP^T: both operands K-major
@@ -170,9 +173,10 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     }
   } else {
     // ------------------------------------------------- elementwise stage --
-    const int t = threadIdx.x;                        // key row within the block = TMEM lane
+    const int t = (warp & 3) * 32 + lane;             // key row within the block = TMEM lane
+    const int hh = warp >> 2;                         // which 64 of the block's 128 query columns this warp handles
     const int kg = jb * 128 + t;                      // global key index
-    const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+    const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
     uint8_t* pt_row = base_ptr + Cfg::kOffPT + t * 128;
     uint8_t* dst_row = base_ptr + Cfg::kOffDST + t * 128;
     bool ok = true;
@@ -180,20 +184,19 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       const int qi = q_start + i;
       float* lse2 = stat + (i & 1) * 256;
       float* dlt = lse2 + 128;
-      {
+      if (hh == 0) {
         const int q = qi * 128 + t;
         lse2[t] = q < P.S ? P.lse[(int64_t)bh * P.S + q] * kLog2eF : INFINITY;   // +inf -> p = 0 for padded queries
         dlt[t] = q < P.S ? P.delta[(int64_t)bh * P.S + q] : 0.f;
       }
-      // publish the block's statistics to the other 127 threads through a bounded mbarrier wait
+      // publish the block's statistics to the other threads through a bounded mbarrier wait
       mbar_arrive(bar_stat);
       if (!__all_sync(0xffffffffu, mbar_wait(bar_stat, i & 1, abort_flag))) { ok = false; break; }
       if (!__all_sync(0xffffffffu, mbar_wait(bar_sdp, i & 1, abort_flag))) { ok = false; break; }
       tc_fence_after();
       const bool diag = P.causal && qi == jb;
       const bool dead = kg >= P.S;                    // padded key row: contributes nothing
-#pragma unroll 1
-      for (int hh = 0; hh < 2; ++hh) {                // 64 query columns at a time
+      {
         uint32_t s_[64], d_[64];
         tmem_ld32(tmem_base + Cfg::kColST + lane_addr + hh * 64, s_);
         tmem_ld32(tmem_base + Cfg::kColST + lane_addr + hh * 64 + 32, s_ + 32);
@@ -232,7 +235,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         const int q = qi * 128 + t;
         float* dst = P.dq_accum + ((int64_t)bh * P.S + q) * D;
 #pragma unroll 1
-        for (int c = 0; c < D / 32; ++c) {
+        for (int c = hh * (D / 64); c < (hh + 1) * (D / 64); ++c) {   // this warp's half of the dQ columns
           uint32_t r[32];
           tmem_ld32(tmem_base + Cfg::kColDQ + lane_addr + c * 32, r);
           tmem_ld_wait();
@@ -257,7 +260,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         T* orow = which ? dvrow : dkrow;
         const int col0 = which ? Cfg::kColDV : Cfg::kColDK;
 #pragma unroll 1
-        for (int c = 0; c < D / 32; ++c) {
+        for (int c = hh * (D / 64); c < (hh + 1) * (D / 64); ++c) {
           uint32_t r[32];
           tmem_ld32(tmem_base + col0 + lane_addr + c * 32, r);
           tmem_ld_wait();
@@ -280,7 +283,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   tc_fence_before();
   __syncthreads();
   if (threadIdx.x == 0 && *abort_flag && P.flag) atomicMax(P.flag, 102);
-  if (warp == 5) {
+  if (warp == kBwdEwWarps + 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, Cfg::kTmemCols);
   }

@@ -110,23 +110,38 @@ attn_fwd_simt(const T* __restrict__ q, const T* __restrict__ k, const T* __restr
   }
 }
 
-// delta[b,h,i] = sum_d dO[i,d] * O[i,d]
+// delta[b,h,i] = sum_d dO[i,d] * O[i,d]. Eight lanes per row, 16-byte loads when
+// head_dim and the strides allow (traffic: one read of O and dO).
 template <typename T>
 __global__ void __launch_bounds__(256)
 attn_delta_kernel(const T* __restrict__ o, const T* __restrict__ d_o, float* __restrict__ delta, mt_strides3 so,
-                  mt_strides3 sdo, int heads, int S, int D, int64_t total_rows) {
-  const int lane = threadIdx.x & 31;
-  const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
-  if (row >= total_rows) return;
-  const int64_t bh = row / S;
-  const int i = (int)(row - bh * S);
-  const int b = (int)(bh / heads), h = (int)(bh % heads);
-  const T* op = o + (int64_t)b * so.b + (int64_t)h * so.h + (int64_t)i * so.s;
-  const T* dp = d_o + (int64_t)b * sdo.b + (int64_t)h * sdo.h + (int64_t)i * sdo.s;
+                  mt_strides3 sdo, int heads, int S, int D, int64_t total_rows, int vec) {
+  constexpr int VN = Vec16<T>::N;
+  const int sub = threadIdx.x & 7;
+  const int64_t row = (int64_t)blockIdx.x * 32 + (threadIdx.x >> 3);
   float s = 0.f;
-  for (int d = lane; d < D; d += 32) s += to_f(op[d]) * to_f(dp[d]);
-  s = warp_sum(s);
-  if (lane == 0) delta[row] = s;
+  if (row < total_rows) {
+    const int64_t bh = row / S;
+    const int i = (int)(row - bh * S);
+    const int b = (int)(bh / heads), h = (int)(bh % heads);
+    const T* op = o + (int64_t)b * so.b + (int64_t)h * so.h + (int64_t)i * so.s;
+    const T* dp = d_o + (int64_t)b * sdo.b + (int64_t)h * sdo.h + (int64_t)i * sdo.s;
+    if (vec) {
+      for (int d = sub * VN; d < D; d += 8 * VN) {
+        Vec16<T> a, g;
+        a.load(op + d);
+        g.load(dp + d);
+#pragma unroll
+        for (int e = 0; e < VN; ++e) s += a.get(e) * g.get(e);
+      }
+    } else {
+      for (int d = sub; d < D; d += 8) s += to_f(op[d]) * to_f(dp[d]);
+    }
+  }
+  s += __shfl_xor_sync(0xffffffffu, s, 1);
+  s += __shfl_xor_sync(0xffffffffu, s, 2);
+  s += __shfl_xor_sync(0xffffffffu, s, 4);
+  if (sub == 0 && row < total_rows) delta[row] = s;
 }
 
 template <typename T>
@@ -300,8 +315,13 @@ attn_bwd_dkv_simt(const T* __restrict__ q, const T* __restrict__ k, const T* __r
 int attn_delta(const AttnArgs& a, cudaStream_t st) {
   const int64_t rows = a.batch * a.heads * a.seq;
   if (rows == 0) return MT_OK;
-  MT_DISPATCH_FLOAT(a.dtype, T, (attn_delta_kernel<T><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(
-      (const T*)a.o, (const T*)a.d_o, a.delta, a.so, a.sdo, (int)a.heads, (int)a.seq, (int)a.head_dim, rows)));
+  MT_DISPATCH_FLOAT(a.dtype, T, {
+    constexpr int VN = Vec16<T>::N;
+    auto ok = [&](const mt_strides3& s) { return s.b % VN == 0 && s.h % VN == 0 && s.s % VN == 0; };
+    const int vec = a.head_dim % VN == 0 && aligned16(a.o) && aligned16(a.d_o) && ok(a.so) && ok(a.sdo);
+    attn_delta_kernel<T><<<(unsigned)((rows + 31) / 32), 256, 0, st>>>(
+        (const T*)a.o, (const T*)a.d_o, a.delta, a.so, a.sdo, (int)a.heads, (int)a.seq, (int)a.head_dim, rows, vec);
+  });
   MT_LAUNCH_CHECK();
   return MT_OK;
 }
