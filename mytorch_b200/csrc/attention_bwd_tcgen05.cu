@@ -132,11 +132,11 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       const uint32_t sk = base + Cfg::kOffK, sv = base + Cfg::kOffV;
       const uint32_t spt = base + Cfg::kOffPT, sdst = base + Cfg::kOffDST;
       bool ok = mbar_wait(bar_kv, 0, abort_flag);
-      for (int i = 0; i < n_q && ok; ++i) {
+      // S^T = K Q^T and dP^T = V dO^T of query block i into tensor memory
+      auto issue_sdp = [&](int i) -> bool {
         const int s = i % ST;
         const uint32_t sq = base + Cfg::kOffQ + s * 2 * Cfg::kTile, sdo = sq + Cfg::kTile;
-        if (!mbar_wait(bar_qfull0 + 8 * s, (i / ST) & 1, abort_flag)) break;
-        if (Cfg::kAliasDQ && i > 0 && !mbar_wait(bar_dqfree, (i - 1) & 1, abort_flag)) break;
+        if (!mbar_wait(bar_qfull0 + 8 * s, (i / ST) & 1, abort_flag)) return false;
         tc_fence_after();
 #pragma unroll
         for (int dc = 0; dc < Cfg::kChunks; ++dc)
@@ -151,6 +151,17 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             umma_f16(tmem_base + Cfg::kColDPT, smem_desc_sw128(sv + dc * 16384 + k * 32, 16, 1024),
                      smem_desc_sw128(sdo + dc * 16384 + k * 32, 16, 1024), idesc_kk, (dc | k) ? 1u : 0u);
         umma_commit(bar_sdp);
+        return true;
+      };
+      if (ok && !Cfg::kAliasDQ) ok = issue_sdp(0);
+      for (int i = 0; i < n_q && ok; ++i) {
+        const int s = i % ST;
+        const uint32_t sq = base + Cfg::kOffQ + s * 2 * Cfg::kTile, sdo = sq + Cfg::kTile;
+        if (Cfg::kAliasDQ) {
+          // dQ shares the S^T columns: the previous dQ must have been read out first
+          if (i > 0 && !mbar_wait(bar_dqfree, (i - 1) & 1, abort_flag)) break;
+          if (!issue_sdp(i)) break;
+        }
         if (!mbar_wait(bar_pds, i & 1, abort_flag)) break;     // P^T, dS^T written; S^T, dP^T consumed
         tc_fence_after();
 #pragma unroll
@@ -161,8 +172,13 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         for (int ks = 0; ks < 8; ++ks)   // dK += dS^T Q
           umma_f16(tmem_base + Cfg::kColDK, smem_desc_sw128(sdst + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024),
                    smem_desc_sw128(sq + ks * 2048, 16384, 1024), idesc_kn, (i > 0 || ks > 0) ? 1u : 0u);
-        if (!Cfg::kAliasDQ && i > 0 && !mbar_wait(bar_dqfree, (i - 1) & 1, abort_flag)) break;
-        tc_fence_after();
+        if (!Cfg::kAliasDQ) {
+          // the next block's S^T / dP^T go ahead of this block's dQ, so the elementwise stage of
+          // block i+1 never waits for the dQ read-out of block i-1
+          if (i + 1 < n_q && !issue_sdp(i + 1)) break;
+          if (i > 0 && !mbar_wait(bar_dqfree, (i - 1) & 1, abort_flag)) break;
+          tc_fence_after();
+        }
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)   // dQ = dS K, reduction over the 128 keys
           umma_f16(tmem_base + Cfg::kColDQ, smem_desc_sw128(sdst + ks * 2048, 16384, 1024),
@@ -180,18 +196,41 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     uint8_t* pt_row = base_ptr + Cfg::kOffPT + t * 128;
     uint8_t* dst_row = base_ptr + Cfg::kOffDST + t * 128;
     bool ok = true;
+    // statistics of a query block: lse in the log2 domain (+inf for padded queries -> p = 0), delta
+    auto load_stats = [&](int qi, float& l2, float& dl) {
+      const int q = qi * 128 + t;
+      l2 = q < P.S ? P.lse[(int64_t)bh * P.S + q] * kLog2eF : INFINITY;
+      dl = q < P.S ? P.delta[(int64_t)bh * P.S + q] : 0.f;
+    };
+    // adds the finished dQ block (TMEM) into the fp32 accumulator; thread t stands for query row t
+    auto flush_dq = [&](int qi) {
+      const int q = qi * 128 + t;
+      float* dst = P.dq_accum + ((int64_t)bh * P.S + q) * D;
+#pragma unroll 1
+      for (int c = hh * (D / 64); c < (hh + 1) * (D / 64); ++c) {   // this warp's half of the dQ columns
+        uint32_t r[32];
+        tmem_ld32(tmem_base + Cfg::kColDQ + lane_addr + c * 32, r);
+        tmem_ld_wait();
+        if (q < P.S) {
+#pragma unroll
+          for (int e = 0; e < 32; e += 4)
+            atomicAdd(reinterpret_cast<float4*>(dst + c * 32 + e),
+                      make_float4(__uint_as_float(r[e]), __uint_as_float(r[e + 1]), __uint_as_float(r[e + 2]),
+                                  __uint_as_float(r[e + 3])));
+        }
+      }
+    };
+    if (hh == 0) load_stats(q_start, stat[t], stat[128 + t]);
     for (int i = 0; i < n_q && ok; ++i) {
       const int qi = q_start + i;
       float* lse2 = stat + (i & 1) * 256;
       float* dlt = lse2 + 128;
-      if (hh == 0) {
-        const int q = qi * 128 + t;
-        lse2[t] = q < P.S ? P.lse[(int64_t)bh * P.S + q] * kLog2eF : INFINITY;   // +inf -> p = 0 for padded queries
-        dlt[t] = q < P.S ? P.delta[(int64_t)bh * P.S + q] : 0.f;
-      }
-      // publish the block's statistics to the other threads through a bounded mbarrier wait
+      // the block's statistics become visible to all elementwise threads through a bounded mbarrier wait
       mbar_arrive(bar_stat);
       if (!__all_sync(0xffffffffu, mbar_wait(bar_stat, i & 1, abort_flag))) { ok = false; break; }
+      float nl2 = 0.f, ndl = 0.f;                    // next block's statistics, in flight during this block
+      const bool pre = hh == 0 && i + 1 < n_q;
+      if (pre) load_stats(qi + 1, nl2, ndl);
       if (!__all_sync(0xffffffffu, mbar_wait(bar_sdp, i & 1, abort_flag))) { ok = false; break; }
       tc_fence_after();
       const bool diag = P.causal && qi == jb;
@@ -203,6 +242,11 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         tmem_ld32(tmem_base + Cfg::kColDPT + lane_addr + hh * 64, d_);
         tmem_ld32(tmem_base + Cfg::kColDPT + lane_addr + hh * 64 + 32, d_ + 32);
         tmem_ld_wait();
+        if (!Cfg::kAliasDQ && i > 0) {
+          // dS^T of the previous block is still an operand of its dQ MMA, which was issued after
+          // the S^T/dP^T MMAs of this block: it must have completed before dS^T is overwritten
+          if (!__all_sync(0xffffffffu, mbar_wait(bar_dq, (i - 1) & 1, abort_flag))) { ok = false; break; }
+        }
 #pragma unroll
         for (int c16 = 0; c16 < 8; ++c16) {
           uint32_t pp[4], dd[4];
@@ -228,28 +272,25 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       fence_proxy_async();
       tc_fence_before();
       mbar_arrive(bar_pds);
-      // dQ of this query block: thread t now stands for query row qi*128 + t
-      if (!__all_sync(0xffffffffu, mbar_wait(bar_dq, i & 1, abort_flag))) { ok = false; break; }
-      tc_fence_after();
-      {
-        const int q = qi * 128 + t;
-        float* dst = P.dq_accum + ((int64_t)bh * P.S + q) * D;
-#pragma unroll 1
-        for (int c = hh * (D / 64); c < (hh + 1) * (D / 64); ++c) {   // this warp's half of the dQ columns
-          uint32_t r[32];
-          tmem_ld32(tmem_base + Cfg::kColDQ + lane_addr + c * 32, r);
-          tmem_ld_wait();
-          if (q < P.S) {
-#pragma unroll
-            for (int e = 0; e < 32; e += 4)
-              atomicAdd(reinterpret_cast<float4*>(dst + c * 32 + e),
-                        make_float4(__uint_as_float(r[e]), __uint_as_float(r[e + 1]), __uint_as_float(r[e + 2]),
-                                    __uint_as_float(r[e + 3])));
-          }
-        }
+      if (pre) { stat[((i + 1) & 1) * 256 + t] = nl2; stat[((i + 1) & 1) * 256 + 128 + t] = ndl; }
+      // dQ read-out. With its own TMEM columns the PREVIOUS block's dQ is flushed here, while the
+      // tensor core works on this block; when dQ aliases S^T it has to be this block's.
+      const int fi = Cfg::kAliasDQ ? i : i - 1;
+      if (fi >= 0) {
+        if (!__all_sync(0xffffffffu, mbar_wait(bar_dq, fi & 1, abort_flag))) { ok = false; break; }
+        tc_fence_after();
+        flush_dq(q_start + fi);
+        tc_fence_before();
+        mbar_arrive(bar_dqfree);
       }
-      tc_fence_before();
-      mbar_arrive(bar_dqfree);
+    }
+    if (ok && !Cfg::kAliasDQ) {
+      if (__all_sync(0xffffffffu, mbar_wait(bar_dq, (n_q - 1) & 1, abort_flag))) {
+        tc_fence_after();
+        flush_dq(q_start + n_q - 1);
+      } else {
+        ok = false;
+      }
     }
     if (ok) {
       // all MMAs are complete (the last bar_dq was waited above): write dK, dV of this key row
