@@ -270,6 +270,33 @@ def scaled_dot_product_attention(q, k, v, attn_mask=None, is_causal=False, softm
     return out
 
 
+def bthd_attention(q, k, v, is_causal=True):
+    """Self-attention on q, k, v laid out [B, T, H, D] (what a Linear followed by
+    reshape gives, nanochat_trainer/core/nanochat_gpt.py:112-127): heads are
+    addressed through strides, so the reference's transpose(1, 2) + contiguous
+    copies are not made; the result is [B, T, H*D]."""
+    B, T, H, D = q.shape
+    st = _lib.Strides3(T * H * D, D, H * D)
+    as4 = lambda a: DeviceArray(a.ptr, (B, H, T, D), a.dtype, base=a)      # logical [B,H,T,D] over [B,T,H,D] memory
+    qv, kv, vv = as4(q.data), as4(k.data), as4(v.data)
+    o_arr = DeviceArray.empty((B, T, H * D), q.dtype)
+    ov = as4(o_arr)
+    _, _, _, _, m = K.fused_sdpa_forward(qv, kv, vv, None, is_causal, None, strides=(st, st, st), out=ov, out_strides=st)
+    out = Tensor(o_arr)
+    if _needs_graph(q, k, v):
+        def _bw(g):
+            dq, dk, dv = (DeviceArray.empty((B, T, H, D), q.dtype) for _ in range(3))
+            K.fused_sdpa_backward(as4(g), qv, kv, vv, ov, m, None, is_causal, None, strides=(st, st, st),
+                                  out=(as4(dq), as4(dk), as4(dv)), out_strides=(st, st, st), o_strides=st, do_strides=st)
+            for t, d in ((q, dq), (k, dk), (v, dv)):
+                if t.requires_grad:
+                    t._accumulate(d)
+        out.requires_grad = True
+        out.grad_fn, out.grad_fn_name = _bw, "<BTHDAttentionBackward>"
+        out._add_parents(q, k, v)
+    return out
+
+
 def qkv_attention(qkv, num_heads, is_causal=True):
     """Causal self-attention straight on the fused projection: qkv [B,T,3E] holds,
     per head, a contiguous [q|k|v] group of 3*D columns — the layout produced by

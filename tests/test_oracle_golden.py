@@ -153,3 +153,28 @@ def test_tiny_gpt2_loss_trajectory(tiny_golden):
     ref = tiny_golden["losses"][:8]
     for a, b in zip(losses, ref):
         assert abs(a - b) <= 1e-4 * abs(b), (losses, ref)
+
+
+def test_nanochat_tiny_matches_reference():
+    """nanochat-style GPT oracle against the reference run (6 AdamW steps)."""
+    from oracle import nanochat as on
+    with open(os.path.join(GOLDEN, "nanochat_tiny.json")) as fh:
+        gold = json.load(fh)
+    cfg = on.GPTConfig(vocab_size=96, max_seq_len=32, embed_dim=64, mlp_ratio=4, num_blocks=2, num_heads=2)
+    params = on.init_params(cfg, seed=4)
+    m = {k: np.zeros_like(v) for k, v in params.items()}
+    v = {k: np.zeros_like(p) for k, p in params.items()}
+    rng = np.random.default_rng(8)
+    b1p = b2p = 1.0
+    for step in range(6):
+        x, y = og.synthetic_batch(rng, 3, 32, 96)
+        loss, cache = on.forward(params, cfg, x, y)
+        assert abs(float(loss) - gold["losses"][step]) <= 1e-4 * gold["losses"][step], (step, float(loss))
+        grads = on.backward(params, cfg, cache)
+        if step == 0:
+            for k, ref in gold["first_step_grad_l2"].items():
+                got = float(np.sqrt(np.sum(grads[k].astype(np.float64) ** 2)))
+                assert abs(got - ref) <= 1e-4 * ref, (k, got, ref)
+        b1p *= 0.9; b2p *= 0.95
+        for k in params:
+            ops.adamw_step(params[k], grads[k], m[k], v[k], 1e-3, 0.9, 0.95, 1e-8, 0.1, b1p, b2p)

@@ -167,3 +167,65 @@ def test_adamw_multi_tensor_matches_reference_golden(golden_ops, op_inputs):
         assert np.abs(p.numpy() - g["adam_p"][i]).max() <= 1e-6 * np.abs(g["adam_p"][i]).max() + 1e-7
     assert np.abs(opt.param_groups[0]["m"][0].numpy() - g["adam_m"]).max() <= 1e-6
     assert np.abs(opt.param_groups[0]["v"][0].numpy() - g["adam_v"]).max() <= 1e-6
+
+
+def test_nanochat_tiny_fp32_matches_reference_losses():
+    """nanochat-style GPT (RoPE then QK-norm, parameter-free RMSNorm, ReLU^2,
+    untied head, soft-capped loss) through the CUDA library against the
+    reference run in tests/golden/nanochat_tiny.json."""
+    import mytorch_b200 as mt
+    from mytorch_b200.nanochat_gpt import GPT, GPTConfig
+    from oracle import nanochat as on
+    with open(os.path.join(GOLDEN, "nanochat_tiny.json")) as fh:
+        gold = json.load(fh)
+    cfg = on.GPTConfig(vocab_size=96, max_seq_len=32, embed_dim=64, mlp_ratio=4, num_blocks=2, num_heads=2)
+    np.random.seed(0)
+    model = GPT(GPTConfig(vocab_size=96, max_seq_len=32, embed_dim=64, mlp_ratio=4, num_blocks=2,
+                          num_q_heads=2, num_kv_heads=2))
+    model.load_state_dict(on.init_params(cfg, seed=4))
+    opt = mt.optim.AdamW([{"params": model.parameters(), "weight_decay": 0.1}], lr=1e-3, beta1=0.9, beta2=0.95)
+    rng = np.random.default_rng(8)
+    for step in range(6):
+        x, y = og.synthetic_batch(rng, 3, 32, 96)
+        _, loss = model(mt.Tensor(x), mt.Tensor(y))
+        loss.backward()
+        if step == 0:
+            for n, p in model.named_parameters():
+                got = float(np.sqrt(np.sum(p.grad.numpy().astype(np.float64) ** 2)))
+                ref = gold["first_step_grad_l2"][n]
+                assert abs(got - ref) <= 1e-4 * ref, (n, got, ref)
+        opt.step()
+        opt.zero_grad()
+        assert abs(loss.item() - gold["losses"][step]) <= 1e-3 * gold["losses"][step], (step, loss.item())
+    final = model.state_dict()
+    for k, want in gold["final_weight_l2"].items():
+        got = float(np.sqrt(np.sum(final[k].astype(np.float64) ** 2)))
+        assert abs(got - want) <= 1e-3 * want, (k, got, want)
+
+
+def test_nanochat_half_precision_head_dim_128_runs_on_tensor_cores():
+    """bf16 step of a small nanochat model with head_dim 128 (the d20 head size):
+    loss within 2e-2 of the fp32 oracle on the same weights and batch."""
+    import mytorch_b200 as mt
+    from mytorch_b200.nanochat_gpt import GPT, GPTConfig
+    from oracle import nanochat as on
+    cfg = on.GPTConfig(vocab_size=512, max_seq_len=256, embed_dim=256, mlp_ratio=4, num_blocks=2, num_heads=2)
+    params = on.init_params(cfg, seed=6)
+    np.random.seed(0)
+    model = GPT(GPTConfig(vocab_size=512, max_seq_len=256, embed_dim=256, mlp_ratio=4, num_blocks=2,
+                          num_q_heads=2, num_kv_heads=2))
+    model.load_state_dict(params)
+    acc = mt.Accelerator(num_gpus=1, rank=0, mixed_precision=True, half_dtype="bfloat16")
+    opt = mt.optim.AdamW([{"params": model.parameters(), "weight_decay": 0.0}], lr=1e-3)
+    model, opt = acc.prepare(model, opt)
+    x, y = og.synthetic_batch(np.random.default_rng(2), 2, 256, 512)
+    _, loss = model(mt.Tensor(x), mt.Tensor(y))
+    acc.backward(loss)
+    opt.step()
+    want, _ = on.forward(params, cfg, x, y)
+    assert abs(loss.item() - float(want)) <= 2e-2 * float(want), (loss.item(), float(want))
+    assert acc.scaler.skipped_steps == 0
+    import ctypes
+    f = ctypes.c_int(0)
+    mt._lib.device_flag_read(ctypes.byref(f), mt.stream())
+    assert f.value == 0
