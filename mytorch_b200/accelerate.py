@@ -135,7 +135,8 @@ class OptimizerWrapper:
 
 class Accelerator:
     def __init__(self, num_gpus=None, rank=None, gradient_accumulation_steps=1, mixed_precision=False,
-                 log_wandb=False, master_addr=None, master_port=None, half_dtype="float16", bucket_mb=64):
+                 log_wandb=False, master_addr=None, master_port=None, half_dtype="float16", bucket_mb=64,
+                 overlap_comm=True):
         self.rank = rank if rank is not None else int(os.environ.get("RANK", 0))
         self.world_size = num_gpus if num_gpus is not None else int(os.environ.get("WORLD_SIZE", 1))
         self.local_rank = int(os.environ.get("LOCAL_RANK", self.rank))
@@ -168,6 +169,7 @@ class Accelerator:
         self._grad_tables = None
         self._flat = None
         self.bucket_elems = bucket_mb * 1024 * 1024 // 4
+        self.overlap_comm = overlap_comm
         self.model = None
         self.wandb_enabled = False
 
@@ -235,6 +237,8 @@ class Accelerator:
             p.grad = gview                                # persistent fp32 accumulation view
         self._flat = flat
         self._param_index = {id(p): i for i, p in enumerate(params)}
+        # id(model parameter) -> (offset, count) in the flat gradient buffer, for bucket triggering
+        self._param_ranges = {id(p): (flat.offsets[i], p.data.size) for i, p in enumerate(params)}
         wd = [0.0] * len(params)
         self._grad_tables = TensorTables([flat.view(flat.master, i) for i in range(len(params))],
                                          [flat.view(flat.grad, i) for i in range(len(params))], None, None, None, wd)
@@ -273,9 +277,15 @@ class Accelerator:
         """Scaled backward of one micro-batch. The upstream gradient is the
         device-resident loss scale; nothing is read back."""
         g = self.scaler.scale_dev
-        if self.comm is not None and (self.step_counter + 1) % self.gradient_accumulation_steps == 0:
-            self.comm.begin_overlap(self)
-        loss.backward(g)
+        last_micro = (self.step_counter + 1) % self.gradient_accumulation_steps == 0
+        if self.comm is not None and last_micro and self.overlap_comm:
+            # gradients become final during this backward: reduce them bucket by bucket as they do
+            self.comm.begin_overlap(self._flat.grad, self.bucket_elems, self._param_ranges)
+            Tensor.param_ready_hook = self.comm.param_ready
+        try:
+            loss.backward(g)
+        finally:
+            Tensor.param_ready_hook = None
         self.step_counter += 1
         if self.step_counter % self.gradient_accumulation_steps == 0:
             self._grads_ready = False
@@ -287,7 +297,10 @@ class Accelerator:
         if self._grads_ready:
             return
         if self.comm is not None:
-            self.comm.allreduce_grads(self._flat.grad, self.bucket_elems)
+            if self.comm._ov_active:
+                self.comm.finish_overlap()
+            else:
+                self.comm.allreduce_grads(self._flat.grad, self.bucket_elems)
         t = self._grad_tables
         _lib.gradnorm_multi(C.byref(t.c), _lib.F32, self.scaler.inv_total_dev.ptr, self._sumsq.ptr,
                             self._found_inf.ptr, stream())

@@ -8,10 +8,13 @@ store): rank 0 creates the 128-byte NCCL id, serves it to the other ranks and
 every rank then joins the communicator. The exchange has deadlines on every
 socket operation, so a rank that never shows up produces an error, not a hang.
 
-Gradient all-reduce runs on a dedicated non-blocking stream: the compute
-stream records an event when a bucket's gradients are final, the comm stream
-waits for it, reduces the bucket in place (average), and the compute stream
-waits for the comm stream before the first kernel that reads gradients.
+Gradient all-reduce runs on a dedicated non-blocking stream and overlaps the
+backward pass of the last micro-batch: autograd reports each parameter as soon
+as the last kernel writing its gradient has been queued; when all parameters of
+a bucket of the flat gradient buffer have reported, the compute stream records
+an event, the comm stream waits for it and reduces that bucket in place
+(average). The compute stream waits for the comm stream before the first
+kernel that reads gradients (norm / inf scan / AdamW).
 """
 import ctypes as C
 import socket
@@ -108,6 +111,8 @@ class NCCLBackend:
         self.comm_stream = s
         self._ev_ready = self._new_event()
         self._ev_done = self._new_event()
+        self._bucket_events = []
+        self._ov_active = False
 
     @staticmethod
     def _new_event():
@@ -136,11 +141,54 @@ class NCCLBackend:
             self.handle = None
 
     # ---- gradient sync on the side stream ----
-    def begin_overlap(self, accelerator):
-        """Hook called before the last micro-batch's backward (reserved for
-        per-bucket triggering; the buckets are currently launched when the
-        backward has finished)."""
-        return None
+    def begin_overlap(self, grad_flat, bucket_elems, param_ranges):
+        """Arms per-bucket triggering for one backward pass. param_ranges maps
+        id(param) -> (offset, count) in the flat gradient buffer. Each bucket is
+        all-reduced (average, in place, on the comm stream) as soon as every
+        parameter overlapping it has reported ready."""
+        self._ov_flat = grad_flat
+        self._ov_buckets = plan_buckets(grad_flat.size, bucket_elems)
+        self._ov_pending = [0] * len(self._ov_buckets)
+        self._ov_launched = [False] * len(self._ov_buckets)
+        self._ov_param_buckets = {}
+        for pid, (off, cnt) in param_ranges.items():
+            first = off // max(1, bucket_elems)
+            last = (off + max(cnt, 1) - 1) // max(1, bucket_elems)
+            bl = list(range(first, min(last, len(self._ov_buckets) - 1) + 1))
+            self._ov_param_buckets[pid] = bl
+            for b in bl:
+                self._ov_pending[b] += 1
+        while len(self._bucket_events) < len(self._ov_buckets):
+            self._bucket_events.append(self._new_event())
+        self._ov_active = True
+
+    def param_ready(self, param):
+        if not self._ov_active:
+            return
+        for b in self._ov_param_buckets.pop(id(param), ()):
+            self._ov_pending[b] -= 1
+            if self._ov_pending[b] == 0:
+                self._launch_bucket(b)
+
+    def _launch_bucket(self, b):
+        if self._ov_launched[b]:
+            return
+        off, cnt = self._ov_buckets[b]
+        ev = self._bucket_events[b]
+        _lib.event_record(ev, stream())                    # gradients of this bucket are queued up to here
+        _lib.stream_wait_event(self.comm_stream, ev)
+        p = self._ov_flat.ptr + off * 4
+        _lib.comm_allreduce(self.handle, p, p, cnt, _lib.F32, _OPS["avg"], self.comm_stream)
+        self._ov_launched[b] = True
+
+    def finish_overlap(self):
+        """Launches whatever has not been triggered and makes the compute stream
+        wait for all bucket reductions."""
+        for b in range(len(self._ov_buckets)):
+            self._launch_bucket(b)
+        _lib.event_record(self._ev_done, self.comm_stream)
+        _lib.stream_wait_event(stream(), self._ev_done)
+        self._ov_active = False
 
     def allreduce_grads(self, grad_flat, bucket_elems):
         """In-place mean of the flat fp32 gradient buffer across ranks, bucket by

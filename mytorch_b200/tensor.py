@@ -44,6 +44,10 @@ def _to_device_array(data, dtype=None):
 
 
 class Tensor:
+    # Optional callable(param) invoked during backward() as soon as the last closure contributing to
+    # a parameter's gradient has run (set by Accelerator to start that gradient's all-reduce early).
+    param_ready_hook = None
+
     def __init__(self, data, requires_grad=False, grad_fn=None, grad_fn_name=None, dtype=None, device=None):
         self.data = _to_device_array(data, dtype)
         self.requires_grad = bool(requires_grad)
@@ -85,13 +89,27 @@ class Tensor:
                 if id(p) not in seen:
                     stack.append((p, False))
         self.grad = g
-        for node in reversed(order):
+        exec_order = list(reversed(order))
+        hook = Tensor.param_ready_hook
+        last_use = {}
+        if hook is not None:               # index of the last closure that writes each parameter's gradient
+            for k, node in enumerate(exec_order):
+                for p in node._parents:
+                    if p.is_param:
+                        last_use[id(p)] = (k, p)
+            ready_at = {}
+            for k, p in last_use.values():
+                ready_at.setdefault(k, []).append(p)
+        for k, node in enumerate(exec_order):
             if node.grad_fn is not None:
                 node.grad_fn(node.grad)
                 node.grad_fn = None
                 node._parents = ()
                 if not node.is_param:
                     node.grad = None      # activations' gradients are consumed
+            if hook is not None:
+                for p in ready_at.get(k, ()):
+                    hook(p)               # every kernel writing p.grad has been queued
 
     def _accumulate(self, g):
         """grad += g. Takes ownership of g when there is no gradient yet."""
