@@ -151,6 +151,28 @@ int mt_ce_bwd(const void* logits, const int32_t* labels, const float* lse, void*
               float scale_host, const float* scale_dev, const float* count_dev,
               int64_t rows, int64_t classes, int64_t ld, float softcap, int dtype, void* stream);
 
+/* Cross entropy over the vocabulary IN CHUNKS, for a fused lm_head + loss that
+ * never holds the [rows, vocab] logits: the caller computes the logits of one
+ * vocabulary chunk [col_offset, col_offset + chunk_classes) with mt_gemm and
+ * hands them over. No counterpart in the reference, which materialises the
+ * logits (gpt2_trainer/gpt2.py:368) and then calls fused_cross_entropy_*.
+ *   fwd:    merges the chunk's log-sum-exp into lse_running[rows] (initialise it
+ *           to -inf) and stores the target logit in tgt[rows] when the label
+ *           lies inside the chunk;
+ *   finish: loss[row] = lse - tgt for labels != -100, plus the same device
+ *           scalars as mt_ce_fwd;
+ *   bwd:    dlogits_chunk = (exp(logit - lse) - [col == label]) * scale from
+ *           recomputed chunk logits and the FINAL lse (may alias the logits). */
+int mt_ce_chunk_fwd(const void* logits_chunk, const int32_t* labels, float* lse_running, float* tgt,
+                    int64_t rows, int64_t chunk_classes, int64_t ld, int64_t col_offset,
+                    float softcap, int dtype, void* stream);
+int mt_ce_chunk_finish(const float* lse, const float* tgt, const int32_t* labels, float* loss,
+                       float* loss_sum, float* valid_count, float* loss_mean, int64_t rows, void* stream);
+int mt_ce_chunk_bwd(const void* logits_chunk, const int32_t* labels, const float* lse, void* dlogits,
+                    float scale_host, const float* scale_dev, const float* count_dev,
+                    int64_t rows, int64_t chunk_classes, int64_t ld, int64_t col_offset,
+                    float softcap, int dtype, void* stream);
+
 /* fused_embedding_forward / fused_embedding_backward
  * (mytorch/nn/functional/fused_ops/embedding.py:108, :219). Indices int32.
  * An out-of-range index sets the device status word and is skipped.

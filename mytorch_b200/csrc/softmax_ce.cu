@@ -125,7 +125,8 @@ constexpr int kCeThreads = 512;
 template <typename T>
 __global__ void __launch_bounds__(kCeThreads)
 ce_fwd_kernel(const T* __restrict__ logits, const int32_t* __restrict__ labels, float* __restrict__ loss,
-              float* __restrict__ lse_out, int64_t classes, int64_t ld, float softcap, int vec_ok, int* __restrict__ flag) {
+              float* __restrict__ lse_out, int64_t classes, int64_t ld, float softcap, int vec_ok, int* __restrict__ flag,
+              int64_t col_offset = 0, float* __restrict__ tgt = nullptr) {
   constexpr int VN = Vec16<T>::N;
   __shared__ float shm[32], shs[32];
   const int64_t row = blockIdx.x;
@@ -173,7 +174,16 @@ ce_fwd_kernel(const T* __restrict__ logits, const int32_t* __restrict__ labels, 
       s = (m == -INFINITY ? 0.f : s * exp2f((m - mm) * kLog2e)) + (m2 == -INFINITY ? 0.f : s2 * exp2f((m2 - mm) * kLog2e));
       m = mm;
     }
-    if (lane == 0) {
+    if (lane == 0 && tgt) {
+      // vocabulary-chunk mode: merge this chunk's log-sum-exp into the running one and pick up
+      // the target logit if the label falls inside the chunk [col_offset, col_offset + classes)
+      const float lse_c = m + logf(s);
+      const float old = lse_out[row];
+      const float mx = fmaxf(old, lse_c);
+      lse_out[row] = mx == -INFINITY ? -INFINITY : mx + logf(__expf(old - mx) + __expf(lse_c - mx));
+      const int64_t lab = (int64_t)labels[row] - col_offset;
+      if (lab >= 0 && lab < classes) tgt[row] = softcap_f(to_f(xr[lab]), softcap);
+    } else if (lane == 0) {
       float lse = m + logf(s);
       lse_out[row] = lse;
       int32_t lab = labels[row];
@@ -204,22 +214,32 @@ ce_reduce_kernel(const float* __restrict__ loss, const int32_t* __restrict__ lab
   }
 }
 
+// loss[row] = lse - target logit for rows whose label is not -100 (chunked forward, last step)
+__global__ void __launch_bounds__(256)
+ce_finish_kernel(const float* __restrict__ lse, const float* __restrict__ tgt, const int32_t* __restrict__ labels,
+                 float* __restrict__ loss, int64_t rows) {
+  int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (r < rows) loss[r] = labels[r] != -100 ? lse[r] - tgt[r] : 0.f;
+}
+
 constexpr int kCeBwdChunk = 4096;  // elements of one row handled by one block
 
 template <typename T>
 __global__ void __launch_bounds__(256)
 ce_bwd_kernel(const T* __restrict__ logits, const int32_t* __restrict__ labels, const float* __restrict__ lse,
               T* __restrict__ dlogits, float scale_host, const float* __restrict__ scale_dev,
-              const float* __restrict__ count_dev, int64_t classes, int64_t ld, float softcap, int vec_ok) {
+              const float* __restrict__ count_dev, int64_t classes, int64_t ld, float softcap, int vec_ok,
+              int64_t col_offset = 0, int chunk_mode = 0) {
   constexpr int VN = Vec16<T>::N;
   const int64_t row = blockIdx.y;
   const int64_t c0 = (int64_t)blockIdx.x * kCeBwdChunk;
   const int64_t c1 = c0 + kCeBwdChunk < classes ? c0 + kCeBwdChunk : classes;
-  const int32_t lab = labels[row];
+  const int64_t lab = (int64_t)labels[row] - col_offset;   // label position relative to this chunk
   float scale = scale_host;
   if (scale_dev) scale *= scale_dev[0];
   if (count_dev) scale /= count_dev[0];
-  const bool ignored = !(lab >= 0 && lab < classes);
+  // whole-vocabulary mode ignores any label outside [0, classes); in chunk mode only -100 is ignored
+  const bool ignored = chunk_mode ? labels[row] == -100 : !(lab >= 0 && lab < classes);
   if (ignored) scale = 0.f;
   const float l = lse[row];
   const T* xr = logits + row * ld;
@@ -330,6 +350,58 @@ int mt_ce_bwd(const void* logits, const int32_t* labels, const float* lse, void*
       int vec_ok = aligned16(logits) && aligned16(dlogits) && (ld % Vec16<T>::N == 0);
       ce_bwd_kernel<T><<<grid, 256, 0, st>>>((const T*)logits + r0 * ld, labels + r0, lse + r0, (T*)dlogits + r0 * ld,
                                              scale_host, scale_dev, count_dev, classes, ld, softcap, vec_ok);
+    });
+    MT_LAUNCH_CHECK();
+  }
+  return MT_OK;
+}
+
+int mt_ce_chunk_fwd(const void* logits, const int32_t* labels, float* lse_running, float* tgt, int64_t rows,
+                    int64_t chunk_classes, int64_t ld, int64_t col_offset, float softcap, int dtype, void* stream) {
+  MT_REQUIRE(logits && labels && lse_running && tgt && rows >= 0 && chunk_classes > 0 && ld >= chunk_classes && col_offset >= 0,
+             "ce_chunk_fwd: bad arguments");
+  if (rows == 0) return MT_OK;
+  cudaStream_t st = as_stream(stream);
+  MT_DISPATCH_FLOAT(dtype, T, {
+    int vec_ok = aligned16(logits) && (ld % Vec16<T>::N == 0);
+    ce_fwd_kernel<T><<<(unsigned)rows, kCeThreads, 0, st>>>((const T*)logits, labels, nullptr, lse_running, chunk_classes, ld,
+                                                            softcap, vec_ok, nullptr, col_offset, tgt);
+  });
+  MT_LAUNCH_CHECK();
+  return MT_OK;
+}
+
+int mt_ce_chunk_finish(const float* lse, const float* tgt, const int32_t* labels, float* loss, float* loss_sum,
+                       float* valid_count, float* loss_mean, int64_t rows, void* stream) {
+  MT_REQUIRE(lse && tgt && labels && loss && rows >= 0, "ce_chunk_finish: bad arguments");
+  cudaStream_t st = as_stream(stream);
+  if (rows > 0) {
+    ce_finish_kernel<<<(unsigned)((rows + 255) / 256), 256, 0, st>>>(lse, tgt, labels, loss, rows);
+    MT_LAUNCH_CHECK();
+  }
+  if (loss_sum || valid_count || loss_mean) {
+    ce_reduce_kernel<<<1, 1024, 0, st>>>(loss, labels, rows, loss_sum, valid_count, loss_mean);
+    MT_LAUNCH_CHECK();
+  }
+  return MT_OK;
+}
+
+int mt_ce_chunk_bwd(const void* logits, const int32_t* labels, const float* lse, void* dlogits, float scale_host,
+                    const float* scale_dev, const float* count_dev, int64_t rows, int64_t chunk_classes, int64_t ld,
+                    int64_t col_offset, float softcap, int dtype, void* stream) {
+  MT_REQUIRE(logits && labels && lse && dlogits && rows >= 0 && chunk_classes > 0 && ld >= chunk_classes && col_offset >= 0,
+             "ce_chunk_bwd: bad arguments");
+  if (rows == 0) return MT_OK;
+  cudaStream_t st = as_stream(stream);
+  const int64_t slab = 65535;
+  for (int64_t r0 = 0; r0 < rows; r0 += slab) {
+    int64_t nr = rows - r0 < slab ? rows - r0 : slab;
+    dim3 grid((unsigned)((chunk_classes + kCeBwdChunk - 1) / kCeBwdChunk), (unsigned)nr);
+    MT_DISPATCH_FLOAT(dtype, T, {
+      int vec_ok = aligned16(logits) && aligned16(dlogits) && (ld % Vec16<T>::N == 0);
+      ce_bwd_kernel<T><<<grid, 256, 0, st>>>((const T*)logits + r0 * ld, labels + r0, lse + r0, (T*)dlogits + r0 * ld,
+                                             scale_host, scale_dev, count_dev, chunk_classes, ld, softcap, vec_ok,
+                                             col_offset, 1);
     });
     MT_LAUNCH_CHECK();
   }

@@ -251,6 +251,58 @@ def cross_entropy(logits, targets, ignore_index=-100, softcap=None, auto=False, 
     return out
 
 
+def lm_head_cross_entropy(x, weight, targets, chunk=8192, softcap=None):
+    """mean cross entropy of (x @ weight^T) against targets WITHOUT materialising the
+    [rows, vocab] logits: the vocabulary is walked in chunks; each chunk's logits are
+    produced by the tensor-core GEMM into one reusable buffer, reduced to a running
+    log-sum-exp (forward) or turned into dlogits and fed straight to the dX / dW GEMMs
+    (backward, which recomputes the chunk logits). Equivalent to
+    cross_entropy(linear(x, weight), targets) (gpt2_trainer/gpt2.py:368 followed by
+    mytorch/nn/functional/losses/cross_entropy.py:107-178) with vocab/chunk times less
+    logits memory, at the price of one extra lm_head GEMM in the backward."""
+    x2 = _flat2d(x.data)
+    M, E = x2.shape
+    V = weight.shape[0]
+    tg = targets.data if isinstance(targets, Tensor) else DeviceArray.from_numpy(targets, "int32")
+    tg = tg.reshape(-1)
+    chunk = max(8, min(int(chunk), V) // 8 * 8) if V >= 8 else V
+    lse = DeviceArray.empty((M,), "float32").fill_(float("-inf"))
+    tgt = DeviceArray.zeros((M,), "float32")
+    buf = DeviceArray.empty((M, chunk), x2.dtype)
+    cap = float(softcap or 0.0)
+    for c0 in range(0, V, chunk):
+        c1 = min(V, c0 + chunk)
+        view = DeviceArray(buf.ptr, (M, c1 - c0), buf.dtype, base=buf)
+        K.gemm(x2, weight.data.rows(c0, c1), trans_b=True, out=view)
+        _lib.ce_chunk_fwd(view.ptr, tg.ptr, lse.ptr, tgt.ptr, M, c1 - c0, c1 - c0, c0, cap, view.code, stream())
+    loss_rows = DeviceArray.empty((M,), "float32")
+    tot = DeviceArray.empty((3,), "float32")
+    _lib.ce_chunk_finish(lse.ptr, tgt.ptr, tg.ptr, loss_rows.ptr, tot.ptr, tot.ptr + 4, tot.ptr + 8, M, stream())
+    out = Tensor(DeviceArray(tot.ptr + 8, (), "float32", base=tot))
+    if _needs_graph(x, weight):
+        def _bw(g):
+            cnt = DeviceArray(tot.ptr + 4, (1,), "float32", base=tot)
+            dx32 = DeviceArray.zeros((M, E), "float32") if x.requires_grad else None
+            for c0 in range(0, V, chunk):
+                c1 = min(V, c0 + chunk)
+                view = DeviceArray(buf.ptr, (M, c1 - c0), buf.dtype, base=buf)
+                wc = weight.data.rows(c0, c1)
+                K.gemm(x2, wc, trans_b=True, out=view)                       # recompute the chunk's logits
+                _lib.ce_chunk_bwd(view.ptr, tg.ptr, lse.ptr, view.ptr, 1.0, g.ptr, cnt.ptr, M, c1 - c0, c1 - c0, c0,
+                                  cap, view.code, stream())
+                if weight.requires_grad:
+                    gbuf = weight.param_grad_buffer().rows(c0, c1)
+                    K.gemm(view, x2, trans_a=True, out=gbuf, accumulate=2 if view.dtype != "float32" else 1)
+                if dx32 is not None:
+                    K.gemm(view, wc, out=dx32, accumulate=1)                 # dX += dlogits_c @ W_c (fp32)
+            if dx32 is not None:
+                x._accumulate(dx32.astype(x.dtype).reshape(x.shape))
+        out.requires_grad = True
+        out.grad_fn, out.grad_fn_name = _bw, "<LMHeadCrossEntropyBackward>"
+        out._add_parents(x, weight)
+    return out
+
+
 # -------------------------------------------------------------- attention ----
 def scaled_dot_product_attention(q, k, v, attn_mask=None, is_causal=False, softmax_scale=None, enable_gqa=False):
     """q,k,v [B,H,S,D] contiguous (mytorch/nn/functional/flash_attention/

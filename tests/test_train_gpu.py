@@ -229,3 +229,46 @@ def test_nanochat_half_precision_head_dim_128_runs_on_tensor_cores():
     f = ctypes.c_int(0)
     mt._lib.device_flag_read(ctypes.byref(f), mt.stream())
     assert f.value == 0
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 1e-4), ("float16", 1e-2)])
+@pytest.mark.parametrize("softcap", [None, 15.0])
+def test_chunked_lm_head_cross_entropy_matches_unfused(dtype, tol, softcap):
+    """F.lm_head_cross_entropy (vocabulary in chunks, logits never materialised)
+    against linear + cross_entropy of the same library and against the oracle,
+    loss and both gradients; vocab 1000 in chunks of 256 (ragged last chunk)."""
+    import mytorch_b200 as mt
+    F = mt.nn.functional
+    r = np.random.default_rng(21)
+    M, E, V = 192, 64, 1000
+    x = r.standard_normal((M, E)).astype(np.float32)
+    w = (r.standard_normal((V, E)) * 0.3).astype(np.float32)
+    y = r.integers(0, V, M).astype(np.int32)
+    y[5] = -100
+    if dtype == "float16":
+        x, w = x.astype(np.float16).astype(np.float32), w.astype(np.float16).astype(np.float32)
+
+    def run(fused):
+        X = mt.Tensor(mt.DeviceArray.from_numpy(x, dtype), requires_grad=True)
+        W = mt.nn.Parameter(mt.DeviceArray.from_numpy(w, dtype))
+        Y = mt.Tensor(y)
+        loss = (F.lm_head_cross_entropy(X, W, Y, chunk=256, softcap=softcap) if fused
+                else F.cross_entropy(F.linear(X, W), Y, softcap=softcap))
+        loss.backward()
+        return loss.item(), X.grad.numpy().astype(np.float64), W.grad.numpy().astype(np.float64)
+
+    lf, dxf, dwf = run(True)
+    lu, dxu, dwu = run(False)
+    logits = x @ w.T
+    if softcap:
+        t = np.tanh(logits / softcap)
+        want = float(O.cross_entropy_fwd(softcap * t, y))
+        dl = O.cross_entropy_bwd(softcap * t, y) * (1 - t * t)
+    else:
+        want = float(O.cross_entropy_fwd(logits, y))
+        dl = O.cross_entropy_bwd(logits, y)
+    for name, got, ref in (("loss", lf, want), ("loss unfused", lu, want)):
+        assert abs(got - ref) <= tol * abs(ref), (name, got, ref)
+    for name, got, ref in (("dx", dxf, dl @ w), ("dw", dwf, dl.T @ x), ("dx unfused", dxu, dl @ w), ("dw unfused", dwu, dl.T @ x)):
+        err = np.abs(got - ref).max() / np.abs(ref).max()
+        assert err <= 2 * tol, (name, err)
