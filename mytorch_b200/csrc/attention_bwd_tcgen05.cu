@@ -5,7 +5,7 @@
 // causal). Per query block, five tcgen05 MMAs with accumulators in tensor memory:
 //   S^T  = K Q^T            dP^T = V dO^T          (both 128x128xD, recomputed)
 //   dV  += P^T dO           dK  += dS^T Q          (128xDx128, accumulated)
-//   dQ   = dS K             (128xDx128, added to a fp32 buffer with atomics,
+//   dQ   = dS K             (128xDx128, added to a fp32 buffer with TMA reduce-add,
 //                            since every key block contributes to every dQ row)
 // Warp roles: warp 8 TMA producer (K, V once; Q and dO per query block, read in
 // place through 4-D strided tensor maps), warp 9 MMA issuer, warps 0-7 the
@@ -39,7 +39,13 @@ template <int D> struct BwdCfg {
   static constexpr int kOffPT = kOffQ + kStages * 2 * kTile;
   static constexpr int kOffDST = kOffPT + 32768;
   static constexpr int kOffStat = kOffDST + 32768;          // lse2[2][128], delta[2][128] floats
-  static constexpr int kOffBar = kOffStat + 2048;
+  // dQ staging for TMA reduce-add: one 32-row x 128-byte buffer per elementwise warp. With its own
+  // TMEM columns (head_dim 64) dQ is flushed while P^T is live, so it gets its own 32 KB; when dQ
+  // aliases S^T (head_dim 128) the flush happens while P^T is dead and each warp stages in the
+  // part of the P^T buffer that only it writes.
+  static constexpr bool kOwnStage = D == 64;
+  static constexpr int kOffStage = kOwnStage ? kOffStat + 2048 : kOffPT;
+  static constexpr int kOffBar = kOffStat + 2048 + (kOwnStage ? 32768 : 0);
   static constexpr int kSmem = kOffBar + 256 + 1024;
   static constexpr int kTmemCols = 512;
   static constexpr int kColST = 0, kColDPT = 128, kColDV = 256, kColDK = 256 + D;
@@ -61,7 +67,7 @@ template <int D, typename T>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
-                   const AttnBwdParams P) {
+                   const __grid_constant__ CUtensorMap tmDQ, const AttnBwdParams P) {
   using Cfg = BwdCfg<D>;
   constexpr int ST = Cfg::kStages;
   extern __shared__ uint8_t smem_raw[];
@@ -202,21 +208,27 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       l2 = q < P.S ? P.lse[(int64_t)bh * P.S + q] * kLog2eF : INFINITY;
       dl = q < P.S ? P.delta[(int64_t)bh * P.S + q] : 0.f;
     };
-    // adds the finished dQ block (TMEM) into the fp32 accumulator; thread t stands for query row t
+    // adds the finished dQ block (TMEM) into the fp32 accumulator [B*H, S, D]: each warp stages its
+    // 32 rows x 32 columns in swizzled shared memory and one lane issues a TMA reduce-add (rows past
+    // the sequence end are clipped by the tensor map)
+    uint8_t* dq_stage = base_ptr + Cfg::kOffStage + warp * 4096;
     auto flush_dq = [&](int qi) {
-      const int q = qi * 128 + t;
-      float* dst = P.dq_accum + ((int64_t)bh * P.S + q) * D;
 #pragma unroll 1
       for (int c = hh * (D / 64); c < (hh + 1) * (D / 64); ++c) {   // this warp's half of the dQ columns
         uint32_t r[32];
         tmem_ld32(tmem_base + Cfg::kColDQ + lane_addr + c * 32, r);
         tmem_ld_wait();
-        if (q < P.S) {
+        if (lane == 0) bulk_wait_read<0>();     // the previous reduce has finished reading the buffer
+        __syncwarp();
 #pragma unroll
-          for (int e = 0; e < 32; e += 4)
-            atomicAdd(reinterpret_cast<float4*>(dst + c * 32 + e),
-                      make_float4(__uint_as_float(r[e]), __uint_as_float(r[e + 1]), __uint_as_float(r[e + 2]),
-                                  __uint_as_float(r[e + 3])));
+        for (int c16 = 0; c16 < 8; ++c16)
+          *reinterpret_cast<uint4*>(dq_stage + lane * 128 + ((c16 ^ (lane & 7)) << 4)) =
+              make_uint4(r[c16 * 4], r[c16 * 4 + 1], r[c16 * 4 + 2], r[c16 * 4 + 3]);
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) {
+          tma_reduce_add_3d(&tmDQ, smem_u32(dq_stage), c * 32, qi * 128 + (warp & 3) * 32, bh);
+          bulk_commit();
         }
       }
     };
@@ -242,6 +254,10 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         tmem_ld32(tmem_base + Cfg::kColDPT + lane_addr + hh * 64, d_);
         tmem_ld32(tmem_base + Cfg::kColDPT + lane_addr + hh * 64 + 32, d_ + 32);
         tmem_ld_wait();
+        if (!Cfg::kOwnStage) {   // staging aliases this warp's slice of P^T: let the last reduce finish reading it
+          if (lane == 0) bulk_wait_read<0>();
+          __syncwarp();
+        }
         if (!Cfg::kAliasDQ && i > 0) {
           // dS^T of the previous block is still an operand of its dQ MMA, which was issued after
           // the S^T/dP^T MMAs of this block: it must have completed before dS^T is overwritten
@@ -292,6 +308,8 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         ok = false;
       }
     }
+    if (lane == 0) bulk_wait_all<0>();   // reduces must be done with shared memory before the CTA exits
+    __syncwarp();
     if (ok) {
       // all MMAs are complete (the last bar_dq was waited above): write dK, dV of this key row
       T* dkrow = reinterpret_cast<T*>(P.dk) + (int64_t)b * P.sdk.b + (int64_t)h * P.sdk.h + (int64_t)kg * P.sdk.s;
@@ -370,6 +388,13 @@ static int launch_bwd(const AttnArgs& a, cudaStream_t st) {
   if ((rc = make_qkv_map(&tk, &P.pk, a.k, bf, a.sk, a.batch, a.heads, a.seq, D))) return rc;
   if ((rc = make_qkv_map(&tv, &P.pv, a.v, bf, a.sv, a.batch, a.heads, a.seq, D))) return rc;
   if ((rc = make_qkv_map(&tdo, &P.pdo, a.d_o, bf, a.sdo, a.batch, a.heads, a.seq, D))) return rc;
+  CUtensorMap tdq;
+  {
+    uint64_t dims[3] = {(uint64_t)D, (uint64_t)a.seq, (uint64_t)(a.batch * a.heads)};
+    uint64_t str[2] = {(uint64_t)D, (uint64_t)(a.seq * D)};
+    uint32_t box[3] = {32, 32, 1};
+    if ((rc = make_tmap_nd_typed(&tdq, a.dq_accum, MT_F32, 3, dims, str, box))) return rc;
+  }
   P.lse = a.lse; P.delta = a.delta; P.dq_accum = a.dq_accum; P.dk = a.dk; P.dv = a.dv;
   P.sdk = a.sdk; P.sdv = a.sdv;
   P.B = (int)a.batch; P.H = (int)a.heads; P.S = (int)a.seq; P.nqb = (int)((a.seq + 127) / 128);
@@ -377,7 +402,7 @@ static int launch_bwd(const AttnArgs& a, cudaStream_t st) {
   auto kern = attn_bwd_tc_kernel<D, T>;
   MT_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
   const unsigned grid = (unsigned)(P.nqb * P.B * P.H);
-  kern<<<grid, kBwdThreads, Cfg::kSmem, st>>>(tq, tk, tv, tdo, P);
+  kern<<<grid, kBwdThreads, Cfg::kSmem, st>>>(tq, tk, tv, tdo, tdq, P);
   MT_LAUNCH_CHECK();
   const int64_t n_vec = n_acc / 8;
   int64_t blocks = (n_vec + 255) / 256;

@@ -509,6 +509,23 @@ int make_tmap_nd(CUtensorMap* map, const void* base_ptr, int is_bf16, int rank, 
   return MT_OK;
 }
 
+int make_tmap_nd_typed(CUtensorMap* map, const void* base_ptr, int dt, int rank, const uint64_t* dims,
+                       const uint64_t* strides_elems, const uint32_t* box) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) { set_error("cuTensorMapEncodeTiled is not available from this driver"); return MT_ERR_CUDA; }
+  const uint64_t esize = dt == MT_F32 ? 4 : 2;
+  cuuint64_t gdim[5], gstr[5];
+  cuuint32_t bx[5], es[5];
+  for (int i = 0; i < rank; ++i) { gdim[i] = dims[i]; bx[i] = box[i]; es[i] = 1; }
+  for (int i = 1; i < rank; ++i) gstr[i - 1] = strides_elems[i - 1] * esize;
+  CUtensorMapDataType t = dt == MT_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                        : dt == MT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUresult r = enc(map, t, (cuuint32_t)rank, const_cast<void*>(base_ptr), gdim, gstr, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled (typed map) failed with code %d", (int)r); return MT_ERR_CUDA; }
+  return MT_OK;
+}
+
 int make_tmap_2d_typed(CUtensorMap* map, const void* base_ptr, int dt, uint64_t inner, uint64_t outer, uint64_t ld_elems,
                        uint32_t box_inner, uint32_t box_outer) {
   EncodeTiledFn enc = get_encode();

@@ -92,6 +92,10 @@ __device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, uint32
   asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
                ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src_smem), "r"(x), "r"(y) : "memory");
 }
+__device__ __forceinline__ void tma_reduce_add_3d(const CUtensorMap* map, uint32_t src_smem, int x, int y, int z) {
+  asm volatile("cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src_smem), "r"(x), "r"(y), "r"(z) : "memory");
+}
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // Waits until at most N of this thread's bulk groups still READ their shared-memory source.
 template <int N> __device__ __forceinline__ void bulk_wait_read() {
@@ -204,6 +208,9 @@ int make_tmap_2d(CUtensorMap* map, const void* base, int is_bf16, uint64_t inner
 int make_tmap_nd(CUtensorMap* map, const void* base, int is_bf16, int rank, const uint64_t* dims,
                  const uint64_t* strides_elems, const uint32_t* box);
 // 2-D map over a row-major matrix of any library dtype (mt_dtype code), for TMA stores.
+// N-d map of any library dtype (dims[0] innermost, strides in elements for dims 1..rank-1).
+int make_tmap_nd_typed(CUtensorMap* map, const void* base, int mt_dtype_code, int rank, const uint64_t* dims,
+                       const uint64_t* strides_elems, const uint32_t* box);
 int make_tmap_2d_typed(CUtensorMap* map, const void* base, int mt_dtype_code, uint64_t inner, uint64_t outer,
                        uint64_t ld_elems, uint32_t box_inner, uint32_t box_outer);
 
