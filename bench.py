@@ -307,7 +307,12 @@ def run_own(args):
                          "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
                          "frac": (achieved / peaks["tflops"]) if achieved else None, "peak_source": peaks["source"],
                          "launches": int(gemm_n.value), "ms_per_launch": gemm_ms.value / max(1, gemm_n.value),
-                         "share_of_step": gemm_ms.value / ms_total, "traffic": None},
+                         "share_of_step": gemm_ms.value / ms_total,
+                         # dram__bytes_read.sum + dram__bytes_write.sum of one captured launch of the
+                         # qkv projection (16384x2304x768 fp16; profiles/gemm_tc_kernel_*.md): the
+                         # operands are read once (28.7 MB), 28.8 MB of the 75.5 MB output reaches
+                         # DRAM before the kernel ends, the rest stays in L2.
+                         "traffic": 58.6e6, "traffic_unit": "bytes per launch (qkv projection, ncu)"},
             "clocks": clocks, "final_loss": final_loss, "device_flag": flag.value,
         }
         if world == 1 and not args.no_cpu_baseline:

@@ -340,13 +340,16 @@ static int norm_bwd_launch(const void* x, const float* mean, const float* rstd, 
   if (vec) {
     int nvec = (int)(cols / VN);
     int64_t want = (rows + kWarpsPerBlock - 1) / kWarpsPerBlock;
-    int grid = (int)(want < (int64_t)sm_count() * 4 ? want : (int64_t)sm_count() * 4);
+    // One wave: as many blocks as are resident at once (the widest variant holds
+    // three 128-thread blocks per SM), so no block waits for a second wave.
+    const int per_sm = nvec <= 32 ? 8 : nvec <= 64 ? 5 : nvec <= 96 ? 4 : 3;
+    int grid = (int)(want < (int64_t)sm_count() * per_sm ? want : (int64_t)sm_count() * per_sm);
     bool wg = dgamma != nullptr, wb = dbeta != nullptr;
     TempBuf part((wg || wb) ? (size_t)grid * 2 * cols * sizeof(float) : 0, st);
     if (!part.ok()) return MT_ERR_CUDA;
     dim3 block(kWarpsPerBlock * 32);
 #define MT_BWD(MV) norm_bwd_warp<T, MV, RMS><<<grid, block, 0, st>>>(xp, mean, rstd, dyp, gp, dxp, (float*)part.ptr, rows, (int)cols, wg, wb, (accumulate & 2) != 0)
-    if (nvec <= 32) MT_BWD(1); else if (nvec <= 64) MT_BWD(2); else MT_BWD(4);
+    if (nvec <= 32) MT_BWD(1); else if (nvec <= 64) MT_BWD(2); else if (nvec <= 96) MT_BWD(3); else MT_BWD(4);
 #undef MT_BWD
     MT_LAUNCH_CHECK();
     if (wg || wb) {

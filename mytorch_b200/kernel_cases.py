@@ -1,0 +1,68 @@
+"""Small stand-alone cases of each hot kernel, sized for a profiler capture:
+inputs larger than the 126 MB L2 where DRAM figures matter, under 2 GB held on
+the device, a handful of launches.
+
+    python -m mytorch_b200.kernel_cases {gemm|attn|mem|adamw}
+
+gemm : the GPT-2 124M qkv projection of one 16x1024-token micro-batch
+       (16384x768 @ 768x2304, fp16), five launches
+attn : causal flash attention forward + backward, 4x12x1024x64 fp16, three rounds
+mem  : LayerNorm forward/backward (16384x768), cross entropy forward/backward
+       (4096x50304), GELU backward (16384x3072), softmax (16384x1024), three rounds
+adamw: fused AdamW over one 64M-element fp32 tensor, three steps
+"""
+import sys
+
+import numpy as np
+
+from mytorch_b200 import fused_ops as F
+from mytorch_b200.array import DeviceArray, synchronize
+
+ROWS = 16384
+
+
+def main(which):
+    r = np.random.default_rng(0)
+
+    def randn(shape, dt="float16"):
+        return DeviceArray.from_numpy(r.standard_normal(shape).astype(np.float32), dt)
+
+    if which == "gemm":
+        a, b = randn((ROWS, 768)), randn((2304, 768))
+        out = DeviceArray.empty((ROWS, 2304), "float16")
+        for _ in range(5):
+            F.gemm(a, b, trans_b=True, out=out)
+    elif which == "attn":
+        q, k, v, do = (randn((4, 12, 1024, 64)) for _ in range(4))
+        for _ in range(3):
+            _, _, _, o, m = F.fused_sdpa_forward(q, k, v, causal=True)
+            F.fused_sdpa_backward(do, q, k, v, o, m, causal=True)
+    elif which == "mem":
+        x, g, dy = randn((ROWS, 768)), randn((768,)), randn((ROWS, 768))
+        lg = randn((4096, 50304))
+        lab = DeviceArray.from_numpy(r.integers(0, 50257, 4096).astype(np.int32))
+        u, du = randn((ROWS, 3072)), randn((ROWS, 3072))
+        for _ in range(3):
+            y, mu, rs = F.fused_layernorm_forward(x, g, None)
+            F.fused_layernorm_backward(x, mu, rs, dy, g, None)
+            loss, lse = F.fused_cross_entropy_forward(lg, lab)
+            F.fused_cross_entropy_backward(lg, lab, lse, scale=1.0)
+            F.fused_activation_backward(u, du, "gelu")
+            F.fused_softmax_forward(randn((ROWS, 1024)))
+    elif which == "adamw":
+        import mytorch_b200 as mt
+        n = 64 * 1024 * 1024
+        p = mt.Tensor(DeviceArray.zeros((n,), "float32"), requires_grad=True)
+        p.is_param = True
+        opt = mt.optim.AdamW([{"params": [p], "weight_decay": 0.1}], lr=1e-3)
+        for _ in range(3):
+            p.grad = DeviceArray.zeros((n,), "float32")
+            opt.step()
+    else:
+        raise SystemExit(__doc__)
+    synchronize()
+    print("done", which)
+
+
+if __name__ == "__main__":
+    main(sys.argv[1] if len(sys.argv) > 1 else "")
