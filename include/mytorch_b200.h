@@ -234,6 +234,11 @@ int mt_gemm_ex(const void* A, const void* B, void* C, void* preact, const void* 
 /* Forces the CUDA-core kernel (1) or restores automatic choice (0); used by
  * the tests to cross-check the tensor-core path on the device. */
 int mt_gemm_force_simt(int on);
+/* Tile shape of the tensor-core kernel: 0 = chosen per call by estimated
+ * efficiency (default), 1 = one CTA per 128-row tile only, 2 = pairs of CTAs
+ * sharing 256-row tiles whenever M > 128. No reference counterpart; the tests
+ * use it to run both tile shapes on the same inputs. */
+int mt_gemm_tile_policy(int policy);
 
 /* fused_sdpa_forward / fused_sdpa_backward
  * (mytorch/nn/functional/fused_ops/flash_attention.py:1269, :1441), causal or

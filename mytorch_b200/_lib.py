@@ -103,6 +103,7 @@ _SIG = {
     "mt_gemm": [_p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _i, _f, _i, _p],
     "mt_gemm_ex": [_p, _p, _p, _p, _p, _p, _i, _i64, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _i, _f, _i, _p],
     "mt_gemm_force_simt": [_i],
+    "mt_gemm_tile_policy": [_i],
     "mt_attn_fwd": [_p, _p, _p, _p, _p, _S, _S, _S, _S, _i64, _i64, _i64, _i64, _f, _i, _i, _p],
     "mt_attn_bwd": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _S, _S, _S, _S, _S, _S, _S, _S,
                     _i64, _i64, _i64, _i64, _f, _i, _i, _p],

@@ -8,10 +8,15 @@
 //   warp 1    MMA issuer: one thread issues tcgen05.mma (128 x BN x 16) per
 //             16 of K, accumulating into one of two TMEM buffers, and commits
 //             stage-release and accumulator-ready barriers;
-//   warps 2-5 epilogue: tcgen05.ld the finished accumulator (thread = row),
-//             apply alpha / bias / activation, write C (store, read-modify-
-//             write, or fp32 atomic add for split-K) while the MMA warp is
-//             already on the next tile in the other TMEM buffer.
+//   warps 2-9 epilogue: tcgen05.ld the finished accumulator (thread = row, two
+//             warps per 32-row slab, half of the columns each), apply alpha /
+//             bias / activation, stage 32 x 128-byte slabs in shared memory and
+//             hand them to TMA (store, or fp32 reduce-add for split-K) while
+//             the MMA warp is already on the next tile in the other TMEM buffer.
+// With CTA pairs (clusters of two, tcgen05 cta_group::2) the scheduled tile is
+// 256 x BN: each CTA stages its own 128 rows of A and half of the B tile, rank 0
+// issues the MMAs for both and each CTA drains its own 128 accumulator rows, so
+// a byte of B fetched from L2 feeds twice the FLOPs.
 // Operands may be K-major or MN-major in global memory (all four transpose
 // combinations), selected by the TMA box and the UMMA descriptors; no
 // transposed copies are made. Loads are plain (non-multicast) TMA.
@@ -34,10 +39,13 @@ constexpr int kEpiWarps = 8;                       // two warps per TMEM lane qu
 constexpr int kGemmThreads = 64 + 32 * kEpiWarps;
 constexpr int kABytes = BM * BK * 2;  // 16 KB
 
-template <int BN> struct GemmCfg {
-  static constexpr int kBBytes = BN * BK * 2;
+// PAIR: two CTAs of a cluster share each MMA (cta_group::2): the pair's tile is
+// 256 x BN, each CTA stages its own 128 rows of A and half of the B tile.
+template <int BN, bool PAIR = false> struct GemmCfg {
+  static constexpr int kBRows = PAIR ? BN / 2 : BN;      // rows of the B tile this CTA stages
+  static constexpr int kBBytes = kBRows * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kStages = BN == 256 ? 4 : 6;
+  static constexpr int kStages = PAIR ? 6 : (BN == 256 ? 4 : 6);
   static constexpr int kTmemCols = 2 * BN;  // two accumulator buffers
   static constexpr int kEpiBytes = kEpiWarps * 4096;  // per epilogue warp: one 32-row x 128-byte staging buffer
   static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024 /*align*/ + 256 /*barriers*/;
@@ -262,11 +270,17 @@ __device__ __forceinline__ void epilogue_staged(const GemmParams& P, const CUten
   }
 }
 
-template <bool A_MN, bool B_MN, int BN>
+template <bool A_MN, bool B_MN, int BN, bool PAIR>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmPre, const GemmParams P) {
-  using Cfg = GemmCfg<BN>;
+  using Cfg = GemmCfg<BN, PAIR>;
+  // In a pair, rank 0 issues the MMAs and owns the operand-ready and
+  // accumulator-free barriers; both CTAs walk the same list of 256 x BN tiles.
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
+  const int worker = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  const int workers = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+  constexpr int TM = PAIR ? 2 * BM : BM;                  // rows of one scheduled tile
   constexpr int S = Cfg::kStages;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -287,17 +301,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(accf_bar(b), 1); mbar_init(acce_bar(b), kEpiWarps); }
+    for (int b = 0; b < 2; ++b) { mbar_init(accf_bar(b), 1); mbar_init(acce_bar(b), PAIR ? 2 * kEpiWarps : kEpiWarps); }
     *abort_flag = 0;
     fence_barrier_init();
     fence_proxy_async();
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(tmem_slot), Cfg::kTmemCols);
-    tmem_relinquish();
+    if (PAIR) { tmem_alloc_pair(smem_u32(tmem_slot), Cfg::kTmemCols); tmem_relinquish_pair(); }
+    else { tmem_alloc(smem_u32(tmem_slot), Cfg::kTmemCols); tmem_relinquish(); }
   }
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync_all();   // the peer's barriers exist before anything signals them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -313,35 +328,45 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       uint32_t phase = 0;
       long long issued = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      for (int t = worker; t < total_tiles && ok; t += workers) {
         const int mn = t % tiles_mn, split = t / tiles_mn;
-        const int m0 = (mn % P.tiles_m) * BM, n0 = (mn / P.tiles_m) * BN;
+        const int m0 = (mn % P.tiles_m) * TM + (int)rank * BM;
+        const int n0 = (mn / P.tiles_m) * BN + (int)rank * (PAIR ? BN / 2 : 0);   // this CTA's rows of the B tile
         const int kb0 = split * P.kb_per_split;
         const int kb1 = min(kb0 + P.kb_per_split, P.kb_total);
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
           const uint32_t sa = base + stage * Cfg::kStageBytes, sb = sa + kABytes;
-          mbar_expect_tx(full_bar(stage), Cfg::kStageBytes);
+          // Both CTAs' copies of a stage are counted on rank 0's barrier.
+          const uint32_t fb = PAIR ? mapa_shared(full_bar(stage), 0) : full_bar(stage);
+          if (!PAIR) mbar_expect_tx(full_bar(stage), Cfg::kStageBytes);
+          else if (rank == 0) mbar_expect_tx(full_bar(stage), 2 * Cfg::kStageBytes);
+          auto load = [&](uint32_t dst, const CUtensorMap* map, int x, int y) {
+            if (PAIR) tma_load_2d_pair(dst, map, fb, x, y);
+            else tma_load_2d(dst, map, fb, x, y);
+          };
           const int k0 = kb * BK;
           if (!A_MN) {
-            tma_load_2d(sa, &tmA, full_bar(stage), k0, m0);
+            load(sa, &tmA, k0, m0);
           } else {
 #pragma unroll
-            for (int j = 0; j < BM / 64; ++j) tma_load_2d(sa + j * (BK * 128), &tmA, full_bar(stage), m0 + j * 64, k0);
+            for (int j = 0; j < BM / 64; ++j) load(sa + j * (BK * 128), &tmA, m0 + j * 64, k0);
           }
           if (!B_MN) {
-            tma_load_2d(sb, &tmB, full_bar(stage), k0, n0);
+            load(sb, &tmB, k0, n0);
           } else {
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * (BK * 128), &tmB, full_bar(stage), n0 + j * 64, k0);
+            for (int j = 0; j < Cfg::kBRows / 64; ++j) load(sb + j * (BK * 128), &tmB, n0 + j * 64, k0);
           }
           ++issued;
           if (++stage == S) { stage = 0; phase ^= 1u; }
         }
       }
-      if (!ok) {
+      if (!ok && rank == 0) {
         // Bounded drain: let the copies already issued into each stage land
-        // before the CTA's shared memory is released.
+        // before the CTA's shared memory is released (in a pair, rank 0's
+        // barriers count the peer's copies too, and the peer stays resident
+        // until the cluster-wide join at the end).
         long long n = issued < S ? issued : S;
         int s = stage;
         uint32_t ph = phase;
@@ -354,13 +379,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------- MMA issuer --
-    if (lane == 0) {
-      const uint32_t idesc = idesc_f16(P.in_bf16, A_MN, B_MN, BM, BN);
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc = idesc_f16(P.in_bf16, A_MN, B_MN, TM, BN);
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
+      for (int t = worker; t < total_tiles && ok; t += workers, ++it) {
         const int split = t / tiles_mn;
         const int kb0 = split * P.kb_per_split;
         const int kb1 = min(kb0 + P.kb_per_split, P.kb_total);
@@ -379,12 +404,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                                      : smem_desc_sw128(sa + k * 32, 16, 1024);
             const uint64_t bd = B_MN ? smem_desc_sw128(sb + k * 2048, BK * 128, 1024)
                                      : smem_desc_sw128(sb + k * 32, 16, 1024);
-            umma_f16(d_tmem, ad, bd, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+            if (PAIR) umma_f16_pair(d_tmem, ad, bd, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+            else umma_f16(d_tmem, ad, bd, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
           }
-          umma_commit(empty_bar(stage));  // stage reusable once these MMAs have read it
+          // stage reusable once these MMAs have read it (in both CTAs of a pair)
+          if (PAIR) umma_commit_pair(empty_bar(stage)); else umma_commit(empty_bar(stage));
           if (++stage == S) { stage = 0; phase ^= 1u; }
         }
-        if (ok) umma_commit(accf_bar(buf));  // accumulator complete
+        if (ok) { if (PAIR) umma_commit_pair(accf_bar(buf)); else umma_commit(accf_bar(buf)); }  // accumulator complete
       }
     }
   } else {
@@ -394,10 +421,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     int it = 0;
     int sidx = 0;   // running count of staged stores of this warp (selects the staging buffer)
     bool ok = true;
-    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
+    for (int t = worker; t < total_tiles && ok; t += workers, ++it) {
       const int mn = t % tiles_mn;
       const bool add_bias = P.bias != nullptr && t / tiles_mn == 0;  // only the first K split adds it
-      const int64_t m0 = (int64_t)(mn % P.tiles_m) * BM, n0 = (int64_t)(mn / P.tiles_m) * BN;
+      const int64_t m0 = (int64_t)(mn % P.tiles_m) * TM + (int64_t)rank * BM, n0 = (int64_t)(mn / P.tiles_m) * BN;
       const int buf = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       // warp-uniform outcome: tcgen05.ld below needs all 32 lanes together
@@ -461,7 +488,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(acce_bar(buf));  // this warp is done with the buffer
+      if (lane == 0) {   // this warp is done with the buffer
+        if (PAIR) mbar_arrive_cluster(mapa_shared(acce_bar(buf), 0));
+        else mbar_arrive(acce_bar(buf));
+      }
     }
     if (P.tma_store && lane == 0) bulk_wait_all<0>();   // staged stores must finish before shared memory goes away
   }
@@ -469,10 +499,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   // ---------------------------------------------------------------- teardown --
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync_all();   // neither CTA leaves, nor frees tensor memory, while its peer still works
   if (threadIdx.x == 0 && *abort_flag && P.flag) atomicMax(P.flag, 100);  // a bounded wait expired
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+    if (PAIR) tmem_dealloc_pair(tmem_base, Cfg::kTmemCols);
+    else tmem_dealloc(tmem_base, Cfg::kTmemCols);
   }
 }
 
@@ -561,11 +593,11 @@ bool gemm_tc_supported(const GemmArgs& g) {
 template <bool A_MN, bool B_MN, int BN>
 static int launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& tp,
                      const GemmParams& P, int grid, cudaStream_t st) {
-  using Cfg = GemmCfg<BN>;
+  using Cfg = GemmCfg<BN, false>;
   static bool attr_set[16] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
-  auto kern = gemm_tc_kernel<A_MN, B_MN, BN>;
+  auto kern = gemm_tc_kernel<A_MN, B_MN, BN, false>;
   if (dev < 16 && !attr_set[dev]) {
     MT_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
     attr_set[dev] = true;
@@ -575,31 +607,113 @@ static int launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const CUtenso
   return MT_OK;
 }
 
+// CTA-pair variant: clusters of two CTAs; `pairs` = number of clusters to launch.
+template <bool A_MN, bool B_MN, int BN>
+static int launch_tc_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& tp,
+                          const GemmParams& P, int pairs, cudaStream_t st) {
+  using Cfg = GemmCfg<BN, true>;
+  static bool attr_set[16] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  auto kern = gemm_tc_kernel<A_MN, B_MN, BN, true>;
+  if (dev < 16 && !attr_set[dev]) {
+    MT_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    attr_set[dev] = true;
+  }
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3((unsigned)(2 * pairs));
+  cfg.blockDim = dim3(kGemmThreads);
+  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  MT_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, tp, P));
+  return MT_OK;
+}
+
+// Number of two-CTA clusters of the pair kernel that are resident at once on
+// this device (an SM without a free partner in its GPC hosts none).
+static int resident_pairs() {
+  static int cached[16] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 16) return sm_count() / 2;
+  if (cached[dev]) return cached[dev];
+  using Cfg = GemmCfg<256, true>;
+  auto kern = gemm_tc_kernel<false, false, 256, true>;
+  int n = 0;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) == cudaSuccess) {
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3((unsigned)(sm_count() & ~1));
+    cfg.blockDim = dim3(kGemmThreads);
+    cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) { n = 0; cudaGetLastError(); }
+  } else {
+    cudaGetLastError();
+  }
+  if (n <= 0 || n > sm_count() / 2) n = sm_count() / 2;
+  cached[dev] = n;
+  return n;
+}
+
+static int g_tile_policy = 0;   // 0 = choose by estimated efficiency, 1 = single-CTA tiles only, 2 = CTA pairs whenever M > 128
+
 int gemm_tc(const GemmArgs& g, cudaStream_t st) {
   const int sms = sm_count();
   const int tiles_m = (int)((g.M + BM - 1) / BM);
   const int kb_total = (int)((g.K + BK - 1) / BK);
-  // Choose BN and the split count by wave efficiency on this many SMs.
+  // Choose the tile (single CTA 128 x BN, or CTA pair 256 x BN), BN and the
+  // split count by estimated efficiency: wave quantisation on the workers
+  // available, padded rows / columns, and the measured advantage of the wider
+  // and the paired tiles (less operand traffic per FLOP).
   int best_bn = 256, best_splits = 1;
+  bool best_pair = false;
   double best = -1.0;
-  for (int bn : {256, 128}) {
-    const int tiles = tiles_m * (int)((g.N + bn - 1) / bn);
-    const int max_splits = g.accumulate == 2 ? 16 : 1;
-    for (int s = 1; s <= max_splits; ++s) {
-      if (s > 1 && kb_total / s < 8) break;
-      const int per = (kb_total + s - 1) / s;
-      if ((s - 1) * per >= kb_total) continue;  // an empty split
-      const long long work = (long long)tiles * s;
-      const long long waves = (work + sms - 1) / sms;
-      double eff = (double)work / (double)(waves * sms);
-      // padded work in the last N tile counts against the wider tile
-      eff *= (double)g.N / (double)(((g.N + bn - 1) / bn) * bn);
-      if (bn == 128) eff *= 0.92;
-      eff *= 1.0 - 0.01 * (s - 1);
-      if (eff > best) { best = eff; best_bn = bn; best_splits = s; }
+  const int pairs_avail = resident_pairs();
+  for (int pair = 0; pair < 2; ++pair) {
+    if (pair && (g_tile_policy == 1 || g.M <= BM)) continue;
+    if (!pair && g_tile_policy == 2 && g.M > BM) continue;
+    const int tm = pair ? 2 * BM : BM;
+    const int workers = pair ? pairs_avail : sms;
+    const int tiles_rows = (int)((g.M + tm - 1) / tm);
+    for (int bn : {256, 128}) {
+      const int tiles = tiles_rows * (int)((g.N + bn - 1) / bn);
+      const int max_splits = g.accumulate == 2 ? 16 : 1;
+      for (int s = 1; s <= max_splits; ++s) {
+        if (s > 1 && kb_total / s < 8) break;
+        const int per = (kb_total + s - 1) / s;
+        if ((s - 1) * per >= kb_total) continue;  // an empty split
+        const long long work = (long long)tiles * s;
+        const long long waves = (work + workers - 1) / workers;
+        double eff = (double)work / (double)(waves * workers);
+        // a pair's workers are two SMs each; unpaired SMs idle
+        if (pair) eff *= (double)(2 * workers) / (double)sms;
+        // padded work in the last row / column tile counts against the larger tile
+        eff *= (double)g.N / (double)(((g.N + bn - 1) / bn) * bn);
+        eff *= (double)g.M / (double)((long long)tiles_rows * tm);
+        if (bn == 128) eff *= 0.92;
+        if (pair) eff *= 1.12;
+        eff *= 1.0 - 0.01 * (s - 1);
+        if (eff > best) { best = eff; best_bn = bn; best_splits = s; best_pair = pair != 0; }
+      }
     }
   }
   const int bn = best_bn;
+  const bool pair = best_pair;
   GemmParams P;
   P.C = g.C; P.preact = g.preact; P.bias = g.bias; P.aux = g.aux; P.aux_mode = g.aux_mode;
   P.M = g.M; P.N = g.N; P.K = g.K; P.ldc = g.ldc;
@@ -607,14 +721,15 @@ int gemm_tc(const GemmArgs& g, cudaStream_t st) {
   P.alpha = g.alpha;
   const int out_vec = g.out_dtype == MT_F32 ? 4 : 8;
   P.vec_store = aligned16(g.C) && (!g.preact || aligned16(g.preact)) && g.ldc % out_vec == 0;
-  P.tiles_m = tiles_m;
+  P.tiles_m = pair ? (int)((g.M + 2 * BM - 1) / (2 * BM)) : tiles_m;
   P.tiles_n = (int)((g.N + bn - 1) / bn);
   P.splits = best_splits;
   P.kb_total = kb_total;
   P.kb_per_split = (kb_total + best_splits - 1) / best_splits;
   P.flag = device_flag_ptr();
   const long long total = (long long)P.tiles_m * P.tiles_n * P.splits;
-  const int grid = (int)(total < sms ? total : sms);
+  const int grid = pair ? (int)(total < pairs_avail ? total : pairs_avail)   // clusters
+                        : (int)(total < sms ? total : sms);                  // CTAs
 
   CUtensorMap ta, tb;
   int rc;
@@ -622,7 +737,7 @@ int gemm_tc(const GemmArgs& g, cudaStream_t st) {
   if (!g.trans_a) rc = make_tmap_2d(&ta, g.A, bf, (uint64_t)g.K, (uint64_t)g.M, (uint64_t)g.lda, BK, BM);
   else rc = make_tmap_2d(&ta, g.A, bf, (uint64_t)g.M, (uint64_t)g.K, (uint64_t)g.lda, 64, BK);
   if (rc) return rc;
-  if (g.trans_b) rc = make_tmap_2d(&tb, g.B, bf, (uint64_t)g.K, (uint64_t)g.N, (uint64_t)g.ldb, BK, (uint32_t)bn);
+  if (g.trans_b) rc = make_tmap_2d(&tb, g.B, bf, (uint64_t)g.K, (uint64_t)g.N, (uint64_t)g.ldb, BK, (uint32_t)(pair ? bn / 2 : bn));
   else rc = make_tmap_2d(&tb, g.B, bf, (uint64_t)g.N, (uint64_t)g.K, (uint64_t)g.ldb, 64, BK);
   if (rc) return rc;
 
@@ -645,8 +760,11 @@ int gemm_tc(const GemmArgs& g, cudaStream_t st) {
   }
   ProfScope prof(PROF_GEMM, st, 2.0 * (double)g.M * (double)g.N * (double)g.K);
   const bool a_mn = g.trans_a != 0, b_mn = g.trans_b == 0;
-#define MT_TC(AM, BMN)                                                         \
-  (bn == 256 ? launch_tc<AM, BMN, 256>(ta, tb, tcm, tpm, P, grid, st) : launch_tc<AM, BMN, 128>(ta, tb, tcm, tpm, P, grid, st))
+#define MT_TC(AM, BMN)                                                                                              \
+  (pair ? (bn == 256 ? launch_tc_pair<AM, BMN, 256>(ta, tb, tcm, tpm, P, grid, st)                                  \
+                     : launch_tc_pair<AM, BMN, 128>(ta, tb, tcm, tpm, P, grid, st))                                 \
+        : (bn == 256 ? launch_tc<AM, BMN, 256>(ta, tb, tcm, tpm, P, grid, st)                                       \
+                     : launch_tc<AM, BMN, 128>(ta, tb, tcm, tpm, P, grid, st)))
   if (!a_mn && !b_mn) return MT_TC(false, false);
   if (!a_mn && b_mn) return MT_TC(false, true);
   if (a_mn && !b_mn) return MT_TC(true, false);
@@ -663,6 +781,12 @@ static int g_force_simt = 0;
 extern "C" {
 
 int mt_gemm_force_simt(int on) { g_force_simt = on; return MT_OK; }
+
+int mt_gemm_tile_policy(int policy) {
+  MT_REQUIRE(policy >= 0 && policy <= 2, "gemm_tile_policy: 0 (automatic), 1 (single-CTA tiles) or 2 (CTA pairs)");
+  mt::g_tile_policy = policy;
+  return MT_OK;
+}
 
 int mt_gemm_ex(const void* A, const void* B, void* C, void* preact, const void* bias, const void* aux, int aux_mode,
                int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int trans_a, int trans_b,

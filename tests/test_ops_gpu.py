@@ -265,6 +265,55 @@ def test_gemm_tensor_core_matches_cuda_core_kernel(mt):
     close(tc, cc, 1e-5, "tcgen05 vs CUDA-core")
 
 
+@pytest.fixture
+def cta_pairs(mt):
+    """Forces the 256-row tiles shared by a pair of CTAs for the test's duration."""
+    mt._lib.gemm_tile_policy(2)
+    yield
+    mt._lib.gemm_tile_policy(0)
+
+
+@pytest.mark.parametrize("dtype", ["float16", "bfloat16"])
+@pytest.mark.parametrize("ta,tb", [(0, 1), (0, 0), (1, 0), (1, 1)])
+@pytest.mark.parametrize("M,N,K", [(256, 512, 128), (200, 136, 72), (1024, 768, 768), (384, 2304, 768),
+                                   (130, 520, 1032), (513, 300, 200), (2048, 3072, 768), (4096, 264, 64)])
+def test_gemm_cta_pairs(mt, cta_pairs, dtype, ta, tb, M, N, K):
+    """Same cases through the cta_group::2 kernel: ragged last row pair (the
+    second CTA's rows partly or wholly past M), ragged N, every operand layout."""
+    F = mt.fused_ops
+    r = np.random.default_rng(13)
+    a = rnd(r.standard_normal((K, M) if ta else (M, K)), dtype)
+    b = rnd(r.standard_normal((N, K) if tb else (K, N)), dtype)
+    want = (a.T if ta else a).astype(np.float64) @ (b.T if tb else b).astype(np.float64)
+    C = F.gemm(dev(mt, a, dtype), dev(mt, b, dtype), trans_a=bool(ta), trans_b=bool(tb))
+    close(C.numpy(), want, TOL[dtype], "gemm, CTA pairs")
+    no_device_flag(mt)
+
+
+@pytest.mark.parametrize("dtype", ["float16", "bfloat16"])
+def test_gemm_cta_pairs_epilogues_and_split_k(mt, cta_pairs, dtype):
+    F = mt.fused_ops
+    r = np.random.default_rng(14)
+    M, N, K = 600, 264, 200
+    x, w, b = rnd(r.standard_normal((M, K)), dtype), rnd(r.standard_normal((N, K)) * 0.1, dtype), rnd(r.standard_normal(N), dtype)
+    pre = x @ w.T + b
+    X, W, B = dev(mt, x, dtype), dev(mt, w, dtype), dev(mt, b, dtype)
+    out, p = F.gemm(X, W, trans_b=True, bias=B, act="gelu", preact=True)
+    close(p.numpy(), pre, TOL[dtype], "preact"); close(out.numpy(), O.gelu_fwd(pre), TOL[dtype], "gelu")
+    dy = rnd(r.standard_normal((8192, 520)), dtype)
+    xx = rnd(r.standard_normal((8192, 200)), dtype)
+    g = mt.DeviceArray.from_numpy(np.ones((520, 200), np.float32))
+    F.gemm(dev(mt, dy, dtype), dev(mt, xx, dtype), trans_a=True, out=g, accumulate=2)
+    close(g.numpy(), 1 + dy.T.astype(np.float64) @ xx, 1e-3, "split-K wgrad, CTA pairs")
+    # both tile shapes accumulate every output in the same order
+    A2, B2 = dev(mt, rnd(r.standard_normal((1024, 512)), dtype), dtype), dev(mt, rnd(r.standard_normal((768, 512)), dtype), dtype)
+    two = F.gemm(A2, B2, trans_b=True, out_dtype="float32").numpy()
+    mt._lib.gemm_tile_policy(1)
+    one = F.gemm(A2, B2, trans_b=True, out_dtype="float32").numpy()
+    assert np.array_equal(one, two)
+    no_device_flag(mt)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("B,H,S,D,causal", [(2, 3, 70, 32, True), (1, 2, 128, 64, True), (2, 2, 257, 64, True),
                                             (1, 2, 100, 128, True), (1, 2, 64, 64, False), (1, 1, 1, 64, True),
