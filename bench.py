@@ -184,6 +184,8 @@ def run_own(args):
         if args.gpus != 1 or world != 1:
             raise SystemExit(f"--gpus {args.gpus} needs WORLD_SIZE={args.gpus} (launch with torch.distributed.run)")
     accum = accum_for(world)
+    if args.gemm_tile_policy:
+        _lib.gemm_tile_policy(args.gemm_tile_policy)
     acc = mt.Accelerator(num_gpus=world, rank=rank, gradient_accumulation_steps=accum, mixed_precision=True)
     np.random.seed(1234)                      # identical initial weights on every rank
     model = GPT2(GPT2Config(**CFG))
@@ -329,6 +331,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="own", choices=["own", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--gemm-tile-policy", type=int, default=0, choices=[0, 1, 2],
+                    help="0 automatic (default), 1 single-CTA GEMM tiles only, 2 CTA pairs; for A/B runs")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -1,22 +1,28 @@
 // Tensor-core attention for sm_100a, fp16/bf16, causal or full.
 //
-// Forward: one CTA per (batch, head, block of 128 query rows).
-//   warp 4    TMA producer: Q once, then K (two stages) and V (one stage) blocks
-//             of 128 keys, 128-byte swizzled, read in place through 4-D tensor
-//             maps {head_dim, seq, head, batch} (any batch/head/row strides);
-//   warp 5    MMA issuer: S = Q K^T (128x128xD) into tensor memory, then
-//             O += P V (128xDx128) with the accumulator kept in tensor memory;
-//   warps 0-3 softmax: thread = query row = TMEM lane. Pass 1 reads S for the row
-//             maximum, pass 2 re-reads it, computes exp2 in the scaled log2 domain,
-//             accumulates the row sum and writes P (half) to shared memory in the
-//             swizzled K-major layout the second MMA consumes. The running maximum
-//             only moves (and O is only rescaled in tensor memory) when it grew by
-//             more than 2^8, so most iterations skip the correction.
-// head_dim 64 uses 97 KB of shared memory and 256 TMEM columns: two CTAs per SM
-// overlap one CTA's softmax with the other's MMAs.
+// Forward: one CTA per (batch, head, block of 128 query rows), 320 threads.
+//   warp 8    TMA producer: Q once, then K and V blocks of 128 keys (two stages
+//             each, K one block ahead of V), 128-byte swizzled, read in place
+//             through 4-D tensor maps {head_dim, seq, head, batch} (any
+//             batch/head/row strides);
+//   warp 9    MMA issuer: S = Q K^T (128x128xD) into tensor memory - issued for
+//             block j+1 as soon as the softmax warps have copied S_j to registers -
+//             then O += P V (128xDx128) with P read from tensor memory and the
+//             accumulator kept in tensor memory;
+//   warps 0-7 softmax: warps w and w+4 share the 32 query rows of TMEM lane quarter
+//             w&3 and take 64 score columns each. A thread reads its half row once,
+//             agrees with its partner on the row maximum through shared memory,
+//             computes exp2 in the scaled log2 domain and writes P back to tensor
+//             memory as packed half pairs. The running maximum only moves (and O is
+//             only rescaled in tensor memory) when it grew by more than 2^8. On the
+//             causal diagonal, 32-column groups that no row of the warp keeps are
+//             skipped altogether.
+// head_dim 64 uses 82 KB of shared memory, 256 TMEM columns and at most 102
+// registers per thread, so two CTAs share an SM.
 //
 // Roofline: tensor pipe, 4*B*H*S^2*D FLOP (half of that when causal); at
-// head_dim 64 the exp2 (MUFU) rate caps the kernel near half of the MMA peak.
+// head_dim 64 the exp2 (MUFU, 16 per clock per SM) rate caps the kernel at half
+// of the MMA peak.
 #include "common.cuh"
 #include "attention.cuh"
 #include "sm100.cuh"
@@ -26,18 +32,23 @@ namespace mt {
 
 using namespace sm100;
 
-constexpr int kAttnThreads = 192;
+constexpr int kSoftmaxWarps = 8;                       // two per TMEM lane quarter: half a score row each
+constexpr int kAttnThreads = 32 * kSoftmaxWarps + 64;  // + TMA producer warp + MMA issuer warp
 
 template <int D> struct FwdCfg {
   static constexpr int kChunks = D / 64;               // 64-wide (128-byte) slices of head_dim
   static constexpr int kTile = 128 * D * 2;            // bytes of one 128-row Q/K/V block
   static constexpr int kOffQ = 0;
   static constexpr int kOffK = kTile;                  // two stages
-  static constexpr int kOffV = kOffK + 2 * kTile;      // one stage
-  static constexpr int kOffP = kOffV + kTile;          // 128 x 128 half
-  static constexpr int kOffBar = kOffP + 128 * 128 * 2;
-  static constexpr int kSmem = kOffBar + 256 + 1024;
-  static constexpr int kTmemCols = 256;                // S: [0,128), O: [128,128+D)
+  static constexpr int kOffV = kOffK + 2 * kTile;      // two stages
+  static constexpr int kOffBar = kOffV + 2 * kTile;
+  static constexpr int kOffX = kOffBar + 256;          // row statistics exchanged between the two half-row threads
+  // No slack for aligning the base: the dynamic shared-memory window of a kernel
+  // without static shared memory starts 1024-byte aligned (checked at entry).
+  static constexpr int kSmem = kOffX + 2 * 2 * 128 * 4;
+  // Tensor memory: S fp32 [0,128), O fp32 [128,128+D), P as packed half pairs [128+D, 192+D)
+  static constexpr int kTmemP = 128 + D;
+  static constexpr int kTmemCols = D == 64 ? 256 : 512;
 };
 
 
@@ -56,16 +67,21 @@ __global__ void __launch_bounds__(kAttnThreads, D == 64 ? 2 : 1)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const AttnFwdParams P) {
   using Cfg = FwdCfg<D>;
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t raw = smem_u32(smem_raw);
-  const uint32_t base = (raw + 1023u) & ~1023u;
-  uint8_t* base_ptr = smem_raw + (base - raw);
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t base = smem_u32(smem_raw);
+  if (base & 1023u) {   // the 128-byte swizzle needs 1024-byte aligned tiles
+    if (threadIdx.x == 0 && P.flag) atomicMax(P.flag, 101);
+    return;
+  }
+  uint8_t* base_ptr = smem_raw;
   const uint32_t bar0 = base + Cfg::kOffBar;
   // barrier slots
-  const uint32_t bar_q = bar0, bar_kfull0 = bar0 + 8, bar_kempty0 = bar0 + 24, bar_vfull = bar0 + 40,
-                 bar_vempty = bar0 + 48, bar_s = bar0 + 56, bar_p = bar0 + 64, bar_o = bar0 + 72;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + Cfg::kOffBar + 96);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + Cfg::kOffBar + 100);
+  const uint32_t bar_q = bar0, bar_kfull0 = bar0 + 8, bar_kempty0 = bar0 + 24, bar_vfull0 = bar0 + 40,
+                 bar_vempty0 = bar0 + 56, bar_s = bar0 + 72, bar_p = bar0 + 80, bar_o = bar0 + 88,
+                 bar_sfree = bar0 + 96, bar_pair0 = bar0 + 104;   // four pair barriers: +104 .. +135
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + Cfg::kOffBar + 144);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + Cfg::kOffBar + 148);
+  float* xchg = reinterpret_cast<float*>(base_ptr + Cfg::kOffX);   // [2 buffers][2 halves][128 rows]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int bh_count = P.B * P.H;
@@ -79,13 +95,15 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     mbar_init(bar_q, 1);
     mbar_init(bar_kfull0, 1); mbar_init(bar_kfull0 + 8, 1);
     mbar_init(bar_kempty0, 1); mbar_init(bar_kempty0 + 8, 1);
-    mbar_init(bar_vfull, 1); mbar_init(bar_vempty, 1);
-    mbar_init(bar_s, 1); mbar_init(bar_p, 128); mbar_init(bar_o, 1);
+    mbar_init(bar_vfull0, 1); mbar_init(bar_vfull0 + 8, 1);
+    mbar_init(bar_vempty0, 1); mbar_init(bar_vempty0 + 8, 1);
+    mbar_init(bar_s, 1); mbar_init(bar_p, 32 * kSoftmaxWarps); mbar_init(bar_o, 1); mbar_init(bar_sfree, kSoftmaxWarps);
+    for (int i = 0; i < 4; ++i) mbar_init(bar_pair0 + 8 * i, 2);
     *abort_flag = 0;
     fence_barrier_init();
     fence_proxy_async();
   }
-  if (warp == 5) {
+  if (warp == kSoftmaxWarps + 1) {
     tmem_alloc(smem_u32(tmem_slot), Cfg::kTmemCols);
     tmem_relinquish();
   }
@@ -93,9 +111,9 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 128;
+  const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 128, tmem_p = tmem_base + Cfg::kTmemP;
 
-  if (warp == 4) {
+  if (warp == kSoftmaxWarps) {
     // ------------------------------------------------------------ producer --
     if (lane == 0) {
       prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV);
@@ -103,21 +121,29 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 #pragma unroll
       for (int dc = 0; dc < Cfg::kChunks; ++dc)
         load_rows(base + Cfg::kOffQ + dc * 16384, &tmQ, bar_q, P.pq, dc * 64, qb * 128, h, b);
-      for (int j = 0; j < n_kv; ++j) {
+      // K runs one block ahead of V: the scores of block j+1 are issued while the
+      // softmax of block j is still running, so K_{j+1} must already be on its way.
+      auto load_k = [&](int j) -> bool {
         const int st = j & 1;
-        if (!mbar_wait(bar_kempty0 + 8 * st, ((j >> 1) & 1) ^ 1u, abort_flag)) break;
+        if (!mbar_wait(bar_kempty0 + 8 * st, ((j >> 1) & 1) ^ 1u, abort_flag)) return false;
         mbar_expect_tx(bar_kfull0 + 8 * st, Cfg::kTile);
 #pragma unroll
         for (int dc = 0; dc < Cfg::kChunks; ++dc)
           load_rows(base + Cfg::kOffK + st * Cfg::kTile + dc * 16384, &tmK, bar_kfull0 + 8 * st, P.pk, dc * 64, j * 128, h, b);
-        if (!mbar_wait(bar_vempty, (j & 1) ^ 1u, abort_flag)) break;
-        mbar_expect_tx(bar_vfull, Cfg::kTile);
+        return true;
+      };
+      bool okp = load_k(0);
+      for (int j = 0; j < n_kv && okp; ++j) {
+        if (j + 1 < n_kv && !load_k(j + 1)) break;
+        const int st = j & 1;
+        if (!mbar_wait(bar_vempty0 + 8 * st, ((j >> 1) & 1) ^ 1u, abort_flag)) break;
+        mbar_expect_tx(bar_vfull0 + 8 * st, Cfg::kTile);
 #pragma unroll
         for (int dc = 0; dc < Cfg::kChunks; ++dc)
-          load_rows(base + Cfg::kOffV + dc * 16384, &tmV, bar_vfull, P.pv, dc * 64, j * 128, h, b);
+          load_rows(base + Cfg::kOffV + st * Cfg::kTile + dc * 16384, &tmV, bar_vfull0 + 8 * st, P.pv, dc * 64, j * 128, h, b);
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == kSoftmaxWarps + 1) {
     // ---------------------------------------------------------- MMA issuer --
     if (lane == 0) {
       const uint32_t idesc_s = idesc_f16(P.is_bf16, 0, 0, 128, 128);
@@ -140,56 +166,90 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       bool ok = mbar_wait(bar_q, 0, abort_flag);
       if (ok) ok = issue_s(0);
       for (int j = 0; j < n_kv && ok; ++j) {
-        if (!mbar_wait(bar_p, j & 1, abort_flag)) break;      // P_j written, S_j consumed
+        if (j + 1 < n_kv) {
+          // The softmax warps hold S_j in registers: the next block's scores are
+          // computed while they work on this one.
+          if (!mbar_wait(bar_sfree, j & 1, abort_flag)) break;
+          tc_fence_after();
+          if (!issue_s(j + 1)) break;
+        }
+        if (!mbar_wait(bar_p, j & 1, abort_flag)) break;      // P_j written
         tc_fence_after();
-        if (j + 1 < n_kv && !issue_s(j + 1)) break;
-        if (!mbar_wait(bar_vfull, j & 1, abort_flag)) break;
+        if (!mbar_wait(bar_vfull0 + 8 * (j & 1), (j >> 1) & 1, abort_flag)) break;
         tc_fence_after();
-        const uint32_t sp = base + Cfg::kOffP, sv = base + Cfg::kOffV;
+        const uint32_t sv = base + Cfg::kOffV + (j & 1) * Cfg::kTile;
+        // A = P straight from tensor memory: 16 keys = 8 columns of packed half pairs per step
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)
-          umma_f16(tmem_o, smem_desc_sw128(sp + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024),
-                   smem_desc_sw128(sv + ks * 2048, 16384, 1024), idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
-        umma_commit(bar_vempty);
+          umma_f16_ts(tmem_o, tmem_p + ks * 8, smem_desc_sw128(sv + ks * 2048, 16384, 1024), idesc_o,
+                      (j > 0 || ks > 0) ? 1u : 0u);
+        umma_commit(bar_vempty0 + 8 * (j & 1));
         umma_commit(bar_o);
       }
     }
   } else {
     // ------------------------------------------------------------- softmax --
-    const int row = threadIdx.x;                      // 0..127 = TMEM lane
+    // Warps w and w+4 share the 32 query rows of TMEM lane quarter w&3; warp w
+    // takes columns [0,64) of each score block, warp w+4 columns [64,128). The two
+    // threads of a row agree on the running maximum through shared memory; their
+    // partial row sums meet once, after the last block.
+    const int qtr = warp & 3, hf = warp >> 2;
+    const int row = qtr * 32 + lane;                  // query row within the block = TMEM lane
     const int q_glob = qb * 128 + row;
-    const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
-    uint8_t* p_smem = base_ptr + Cfg::kOffP;
+    const uint32_t lane_addr = (uint32_t)(qtr * 32) << 16;
+    const uint32_t bar_pair = bar_pair0 + 8 * qtr;
     float m_used = -INFINITY, l = 0.f;
     bool ok = true;
+    // Both threads of a row see the same values, so `ok` and the rescale decision agree.
+    auto pair_exchange = [&](int use, float mine, float& other) -> bool {
+      float* slot = xchg + (use & 1) * 256;
+      slot[hf * 128 + row] = mine;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_pair);
+      if (!__all_sync(0xffffffffu, mbar_wait(bar_pair, use & 1, abort_flag))) return false;
+      other = slot[(hf ^ 1) * 128 + row];
+      return true;
+    };
     for (int j = 0; j < n_kv && ok; ++j) {
       if (!__all_sync(0xffffffffu, mbar_wait(bar_s, j & 1, abort_flag))) { ok = false; break; }
       tc_fence_after();
-      const bool need_mask = (P.causal && j == qb) || ((j + 1) * 128 > P.S);
-      // the whole row of S (128 fp32) in registers: four loads in flight, one wait
-      uint32_t r[128];
-      tmem_ld32(tmem_s + lane_addr, r);
-      tmem_ld32(tmem_s + lane_addr + 32, r + 32);
-      tmem_ld32(tmem_s + lane_addr + 64, r + 64);
-      tmem_ld32(tmem_s + lane_addr + 96, r + 96);
+      // Valid columns of this block for this row: c < lim. Whole 32-column groups
+      // past every row of the warp are skipped (no max, no exp2, zeros written);
+      // groups that every row keeps entirely need no per-element test.
+      const int nvalid = min(128, P.S - j * 128);
+      const bool diag = P.causal && j == qb;
+      const int lim = (diag ? min(nvalid, row + 1) : nvalid) - hf * 64;             // in this thread's columns
+      const int lim_max = (diag ? min(nvalid, qtr * 32 + 32) : nvalid) - hf * 64;   // warp-uniform
+      const int lim_min = (diag ? min(nvalid, qtr * 32 + 1) : nvalid) - hf * 64;    // warp-uniform
+      uint32_t r[64];
+      tmem_ld32(tmem_s + lane_addr + hf * 64, r);
+      tmem_ld32(tmem_s + lane_addr + hf * 64 + 32, r + 32);
       tmem_ld_wait();
-      if (need_mask) {
-#pragma unroll
-        for (int e = 0; e < 128; ++e) {
-          const int col = j * 128 + e;
-          if (col >= P.S || (P.causal && col > q_glob)) r[e] = 0xff800000u;   // -inf
-        }
-      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_sfree);          // S may be overwritten by the next block's scores
       float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-      for (int e = 0; e < 128; e += 4) {
-        mx0 = fmaxf(mx0, __uint_as_float(r[e]));
-        mx1 = fmaxf(mx1, __uint_as_float(r[e + 1]));
-        mx2 = fmaxf(mx2, __uint_as_float(r[e + 2]));
-        mx3 = fmaxf(mx3, __uint_as_float(r[e + 3]));
+      for (int g = 0; g < 2; ++g) {
+        if (g * 32 < lim_max) {
+          if ((g + 1) * 32 > lim_min) {
+#pragma unroll
+            for (int e = g * 32; e < g * 32 + 32; ++e)
+              if (e >= lim) r[e] = 0xff800000u;   // -inf
+          }
+#pragma unroll
+          for (int e = g * 32; e < g * 32 + 32; e += 8) {
+            mx0 = max3(mx0, __uint_as_float(r[e]), __uint_as_float(r[e + 1]));
+            mx1 = max3(mx1, __uint_as_float(r[e + 2]), __uint_as_float(r[e + 3]));
+            mx2 = max3(mx2, __uint_as_float(r[e + 4]), __uint_as_float(r[e + 5]));
+            mx3 = max3(mx3, __uint_as_float(r[e + 6]), __uint_as_float(r[e + 7]));
+          }
+        }
       }
-      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * P.scale_log2;
-      const float m_new = fmaxf(m_used, mx);
+      const float mx_half = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * P.scale_log2;
+      float mx_other;
+      if (!pair_exchange(j, mx_half, mx_other)) { ok = false; break; }
+      const float m_new = fmaxf(m_used, fmaxf(mx_half, mx_other));
       const bool resc = (m_new > m_used) && (m_used == -INFINITY || m_new - m_used > 8.f);
       float alpha = 1.f;
       if (resc) {
@@ -203,47 +263,52 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       }
       const float msub = m_used == -INFINITY ? 0.f : m_used;   // a fully masked row has only -inf entries
       float l0 = 0.f, l1 = 0.f;
-      uint8_t* prow = p_smem + row * 128;
 #pragma unroll
-      for (int c16 = 0; c16 < 16; ++c16) {          // 16-byte chunks of 8 columns
-        uint32_t pk[4];
+      for (int g = 0; g < 2; ++g) {
+        uint32_t pk[16];                            // 32 probabilities as half pairs
+        if (g * 32 < lim_max) {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float p0 = ex2_approx(fmaf(__uint_as_float(r[c16 * 8 + 2 * e]), P.scale_log2, -msub));
-          const float p1 = ex2_approx(fmaf(__uint_as_float(r[c16 * 8 + 2 * e + 1]), P.scale_log2, -msub));
-          l0 += p0;
-          l1 += p1;
-          pk[e] = pack2<T>(p0, p1);
+          for (int e = 0; e < 16; ++e) {
+            const float p0 = ex2_approx(fmaf(__uint_as_float(r[g * 32 + 2 * e]), P.scale_log2, -msub));
+            const float p1 = ex2_approx(fmaf(__uint_as_float(r[g * 32 + 2 * e + 1]), P.scale_log2, -msub));
+            l0 += p0;
+            l1 += p1;
+            pk[e] = pack2<T>(p0, p1);
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 16; ++e) pk[e] = 0u;
         }
-        // K-slice c16>>3 (64 columns each), chunk c16&7 within the 128-byte row, swizzled
-        *reinterpret_cast<uint4*>(prow + (c16 >> 3) * 16384 + (((c16 & 7) ^ (row & 7)) << 4)) =
-            make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        tmem_st16(tmem_p + lane_addr + hf * 32 + g * 16, pk);   // P never touches shared memory
       }
       l += l0 + l1;
       if (j > 0 && __any_sync(0xffffffffu, resc)) {   // rare: the running maximum moved by more than 2^8
 #pragma unroll 1
-        for (int c = 0; c < D / 32; ++c) {
+        for (int c = 0; c < D / 64; ++c) {            // this thread's half of the O columns
           uint32_t t[32];
-          tmem_ld32(tmem_o + lane_addr + c * 32, t);
+          const uint32_t addr = tmem_o + lane_addr + hf * (D / 2) + c * 32;
+          tmem_ld32(addr, t);
           tmem_ld_wait();
 #pragma unroll
           for (int e = 0; e < 32; ++e) t[e] = __float_as_uint(__uint_as_float(t[e]) * alpha);
-          tmem_st32(tmem_o + lane_addr + c * 32, t);
+          tmem_st32(addr, t);
         }
-        tmem_st_wait();
       }
-      fence_proxy_async();      // generic-proxy writes of P -> visible to the tensor core
+      tmem_st_wait();
       tc_fence_before();
       mbar_arrive(bar_p);
     }
+    float l_other = 0.f;
+    if (ok) ok = pair_exchange(n_kv, l, l_other);
     if (ok && __all_sync(0xffffffffu, mbar_wait(bar_o, (n_kv - 1) & 1, abort_flag))) {
       tc_fence_after();
-      const float inv = l > 0.f ? 1.f / l : 0.f;
-      T* orow = reinterpret_cast<T*>(P.o) + (int64_t)b * P.so.b + (int64_t)h * P.so.h + (int64_t)q_glob * P.so.s;
+      const float l_row = l + l_other;
+      const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
+      T* orow = reinterpret_cast<T*>(P.o) + (int64_t)b * P.so.b + (int64_t)h * P.so.h + (int64_t)q_glob * P.so.s + hf * (D / 2);
 #pragma unroll 1
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = 0; c < D / 64; ++c) {
         uint32_t r[32];
-        tmem_ld32(tmem_o + lane_addr + c * 32, r);
+        tmem_ld32(tmem_o + lane_addr + hf * (D / 2) + c * 32, r);
         tmem_ld_wait();
         if (q_glob < P.S) {
 #pragma unroll
@@ -257,14 +322,14 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           }
         }
       }
-      if (q_glob < P.S) P.lse[(int64_t)bh * P.S + q_glob] = (m_used + log2f(l)) * kLn2F;
+      if (hf == 0 && q_glob < P.S) P.lse[(int64_t)bh * P.S + q_glob] = (m_used + log2f(l_row)) * kLn2F;
     }
   }
 
   tc_fence_before();
   __syncthreads();
   if (threadIdx.x == 0 && *abort_flag && P.flag) atomicMax(P.flag, 101);
-  if (warp == 5) {
+  if (warp == kSoftmaxWarps + 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, Cfg::kTmemCols);
   }

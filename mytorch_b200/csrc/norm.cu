@@ -280,16 +280,20 @@ norm_bwd_colsum(const T* __restrict__ x, const float* __restrict__ mean, const f
   }
 }
 
-// Sums the per-block partial rows in a fixed order: block = 32 columns x 8 row groups.
-__global__ void __launch_bounds__(256)
+// Sums the per-block partial rows in a fixed order: block = 32 columns x 32 row
+// groups (row group g adds rows g, g+32, ... in order; the groups are then added
+// in order), so the result does not depend on scheduling.
+constexpr int kFinalizeGroups = 32;
+__global__ void __launch_bounds__(32 * kFinalizeGroups)
 norm_bwd_finalize(const float* __restrict__ partial, int nblocks, int cols,
                   float* __restrict__ dgamma, float* __restrict__ dbeta, int accumulate) {
-  __shared__ float sg[8][33], sb[8][33];
+  __shared__ float sg[kFinalizeGroups][33], sb[kFinalizeGroups][33];
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
   const int c = blockIdx.x * 32 + tx;
   float g = 0.f, b = 0.f;
   if (c < cols) {
-    for (int i = ty; i < nblocks; i += 8) {
+#pragma unroll 4
+    for (int i = ty; i < nblocks; i += kFinalizeGroups) {
       const float* p = partial + (size_t)i * 2 * cols;
       if (dgamma) g += p[c];
       if (dbeta) b += p[cols + c];
@@ -301,7 +305,7 @@ norm_bwd_finalize(const float* __restrict__ partial, int nblocks, int cols,
   if (ty == 0 && c < cols) {
     float ag = 0.f, ab = 0.f;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) { ag += sg[i][tx]; ab += sb[i][tx]; }
+    for (int i = 0; i < kFinalizeGroups; ++i) { ag += sg[i][tx]; ab += sb[i][tx]; }
     if (dgamma) dgamma[c] = accumulate ? dgamma[c] + ag : ag;
     if (dbeta) dbeta[c] = accumulate ? dbeta[c] + ab : ab;
   }
@@ -353,7 +357,7 @@ static int norm_bwd_launch(const void* x, const float* mean, const float* rstd, 
 #undef MT_BWD
     MT_LAUNCH_CHECK();
     if (wg || wb) {
-      norm_bwd_finalize<<<(unsigned)((cols + 31) / 32), 256, 0, st>>>((const float*)part.ptr, grid, (int)cols,
+      norm_bwd_finalize<<<(unsigned)((cols + 31) / 32), 32 * kFinalizeGroups, 0, st>>>((const float*)part.ptr, grid, (int)cols,
                                                                         dgamma, dbeta, accumulate & 1);
       MT_LAUNCH_CHECK();
     }
@@ -451,7 +455,7 @@ static int layernorm_bwd_noalloc_launch(const void* x, const float* mean, const 
 #undef MT_BWD
   MT_LAUNCH_CHECK();
   if (wg || wb) {
-    norm_bwd_finalize<<<(unsigned)((cols + 31) / 32), 256, 0, st>>>(scratch, grid, (int)cols, dgamma, dbeta, accumulate);
+    norm_bwd_finalize<<<(unsigned)((cols + 31) / 32), 32 * kFinalizeGroups, 0, st>>>(scratch, grid, (int)cols, dgamma, dbeta, accumulate);
     MT_LAUNCH_CHECK();
   }
   return MT_OK;
