@@ -7,20 +7,25 @@
 //   dV  += P^T dO           dK  += dS^T Q          (128xDx128, accumulated)
 //   dQ   = dS K             (128xDx128, added to a fp32 buffer with TMA reduce-add,
 //                            since every key block contributes to every dQ row)
-// Warp roles: warp 8 TMA producer (K, V once; Q and dO per query block, read in
-// place through 4-D strided tensor maps), warp 9 MMA issuer, warps 0-7 the
-// elementwise stage: thread = key row = TMEM lane (two warps per lane quarter,
-// 64 query columns each); it reads S^T and dP^T,
-// forms P^T = exp2(S^T*scale*log2e - lse*log2e) and dS^T = P^T (dP^T - delta) *
-// scale, and writes both as half into shared memory in the swizzled layout that
-// serves as K-major A operand for dV/dK and, read the other way, as M-major A
-// operand for dQ. No transposes are materialised anywhere.
+// Warp roles: warp 8 TMA producer (K, V once; Q, dO and the block's row statistics per query
+// block, read in place through 4-D strided tensor maps, three stages at head_dim 64), warp 9
+// MMA issuer, warps 0-7 the elementwise stage: thread = key row = TMEM lane (two warps per lane
+// quarter, 64 query columns each). It copies S^T and dP^T to registers - which lets the MMA warp
+// start the next block's S^T / dP^T at once - forms P^T = exp2(S^T*scale*log2e - lse*log2e) and
+// dS^T = P^T (dP^T*scale - delta*scale), and writes dS^T as half into shared memory in the
+// swizzled layout that serves as K-major A operand for dK and, read the other way, as M-major A
+// operand for dQ. P^T goes to tensor memory (head_dim 64: A operand of the dV MMA read from
+// TMEM) or to shared memory (head_dim 128, where tensor memory is full). No transposes are
+// materialised anywhere. dK and dV leave through staged TMA stores.
+// A small kernel run first writes the row statistics lse*log2e and delta*scale =
+// scale*rowsum(O*dO), padded to whole blocks.
 //
 // Roofline: tensor pipe, 10*B*H*S^2*D FLOP (half when causal).
 #include "common.cuh"
 #include "attention.cuh"
 #include "sm100.cuh"
 #include "attention_tc.cuh"
+#include "tempbuf.cuh"
 
 namespace mt {
 
@@ -32,32 +37,36 @@ constexpr int kBwdThreads = 32 * (kBwdEwWarps + 2);
 template <int D> struct BwdCfg {
   static constexpr int kChunks = D / 64;
   static constexpr int kTile = 128 * D * 2;                 // one 128-row block of K/V/Q/dO
-  static constexpr int kStages = D == 64 ? 2 : 1;           // Q+dO ring
+  // head_dim 64 has 64 spare TMEM columns: P^T lives there (A operand of the dV MMA read from
+  // tensor memory) and the 32 KB it would take in shared memory buy a third Q/dO stage.
+  static constexpr bool kPTinTmem = D == 64;
+  static constexpr int kStages = D == 64 ? 3 : 1;           // Q+dO ring
   static constexpr int kOffK = 0;
   static constexpr int kOffV = kTile;
   static constexpr int kOffQ = 2 * kTile;                   // stage s: Q at +s*2*kTile, dO right after it
   static constexpr int kOffPT = kOffQ + kStages * 2 * kTile;
-  static constexpr int kOffDST = kOffPT + 32768;
-  static constexpr int kOffStat = kOffDST + 32768;          // lse2[2][128], delta[2][128] floats
+  static constexpr int kOffDST = kOffPT + (kPTinTmem ? 0 : 32768);
+  static constexpr int kOffStat = kOffDST + 32768;          // per Q/dO stage: lse*log2e [128], delta*scale [128] floats
   // dQ staging for TMA reduce-add: one 32-row x 128-byte buffer per elementwise warp. With its own
   // TMEM columns (head_dim 64) dQ is flushed while P^T is live, so it gets its own 32 KB; when dQ
   // aliases S^T (head_dim 128) the flush happens while P^T is dead and each warp stages in the
   // part of the P^T buffer that only it writes.
   static constexpr bool kOwnStage = D == 64;
-  static constexpr int kOffStage = kOwnStage ? kOffStat + 2048 : kOffPT;
-  static constexpr int kOffBar = kOffStat + 2048 + (kOwnStage ? 32768 : 0);
+  static constexpr int kOffStage = kOwnStage ? kOffStat + 4096 : kOffPT;
+  static constexpr int kOffBar = kOffStat + 4096 + (kOwnStage ? 32768 : 0);
   static constexpr int kSmem = kOffBar + 256 + 1024;
   static constexpr int kTmemCols = 512;
   static constexpr int kColST = 0, kColDPT = 128, kColDV = 256, kColDK = 256 + D;
   static constexpr bool kAliasDQ = D == 128;                // dQ shares the S^T columns when TMEM is full
   static constexpr int kColDQ = kAliasDQ ? 0 : 256 + 2 * D;
+  static constexpr int kColPT = 256 + 3 * D;                // packed half pairs, 64 columns (head_dim 64 only)
 };
 
 struct AttnBwdParams {
-  const float* lse; const float* delta; float* dq_accum;
+  const float* stats;      // [2][B*H][nqb*128]: lse*log2e (+inf on padded rows), then delta*scale (0 on padded rows)
+  float* dq_accum;
   void* dk; void* dv;
-  MapPos pq, pk, pv, pdo;
-  mt_strides3 sdk, sdv;
+  MapPos pq, pk, pv, pdo, pdk, pdv;
   int B, H, S, nqb, causal, is_bf16;
   float scale, scale_log2;
   int* flag;
@@ -67,7 +76,8 @@ template <int D, typename T>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
-                   const __grid_constant__ CUtensorMap tmDQ, const AttnBwdParams P) {
+                   const __grid_constant__ CUtensorMap tmDQ, const __grid_constant__ CUtensorMap tmDK,
+                   const __grid_constant__ CUtensorMap tmDV, const AttnBwdParams P) {
   using Cfg = BwdCfg<D>;
   constexpr int ST = Cfg::kStages;
   extern __shared__ uint8_t smem_raw[];
@@ -75,10 +85,10 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - raw);
   const uint32_t bar0 = base + Cfg::kOffBar;
-  const uint32_t bar_kv = bar0, bar_qfull0 = bar0 + 8, bar_qempty0 = bar0 + 24, bar_sdp = bar0 + 40,
-                 bar_pds = bar0 + 48, bar_dq = bar0 + 56, bar_dqfree = bar0 + 64, bar_stat = bar0 + 72;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + Cfg::kOffBar + 96);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + Cfg::kOffBar + 100);
+  const uint32_t bar_kv = bar0, bar_qfull0 = bar0 + 8, bar_qempty0 = bar0 + 32, bar_sdp = bar0 + 56,
+                 bar_pds = bar0 + 64, bar_dq = bar0 + 72, bar_dqfree = bar0 + 80, bar_sdpfree = bar0 + 88;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + Cfg::kOffBar + 112);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + Cfg::kOffBar + 116);
   float* stat = reinterpret_cast<float*>(base_ptr + Cfg::kOffStat);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -91,9 +101,10 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
   if (threadIdx.x == 0) {
     mbar_init(bar_kv, 1);
-    for (int s = 0; s < 2; ++s) { mbar_init(bar_qfull0 + 8 * s, 1); mbar_init(bar_qempty0 + 8 * s, 1); }
+    for (int s = 0; s < 3; ++s) { mbar_init(bar_qfull0 + 8 * s, 1); mbar_init(bar_qempty0 + 8 * s, 1); }
     mbar_init(bar_sdp, 1); mbar_init(bar_pds, 32 * kBwdEwWarps); mbar_init(bar_dq, 1);
-    mbar_init(bar_dqfree, 32 * kBwdEwWarps); mbar_init(bar_stat, 32 * kBwdEwWarps);
+    mbar_init(bar_dqfree, 32 * kBwdEwWarps);
+    mbar_init(bar_sdpfree, kBwdEwWarps);
     *abort_flag = 0;
     fence_barrier_init();
     fence_proxy_async();
@@ -120,8 +131,14 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       for (int i = 0; i < n_q; ++i) {
         const int s = i % ST;
         if (!mbar_wait(bar_qempty0 + 8 * s, ((i / ST) & 1) ^ 1u, abort_flag)) break;
-        mbar_expect_tx(bar_qfull0 + 8 * s, 2 * Cfg::kTile);
+        mbar_expect_tx(bar_qfull0 + 8 * s, 2 * Cfg::kTile + 1024);
         const uint32_t sq = base + Cfg::kOffQ + s * 2 * Cfg::kTile, sdo = sq + Cfg::kTile;
+        {   // the block's row statistics travel with it
+          const int64_t spad = (int64_t)P.nqb * 128;
+          const float* src = P.stats + (int64_t)bh * spad + (int64_t)(q_start + i) * 128;
+          bulk_load_1d(base + Cfg::kOffStat + s * 1024, src, 512, bar_qfull0 + 8 * s);
+          bulk_load_1d(base + Cfg::kOffStat + s * 1024 + 512, src + (int64_t)bh_count * spad, 512, bar_qfull0 + 8 * s);
+        }
 #pragma unroll
         for (int dc = 0; dc < Cfg::kChunks; ++dc) {
           load_rows(sq + dc * 16384, &tmQ, bar_qfull0 + 8 * s, P.pq, dc * 64, (q_start + i) * 128, h, b);
@@ -168,28 +185,37 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           if (i > 0 && !mbar_wait(bar_dqfree, (i - 1) & 1, abort_flag)) break;
           if (!issue_sdp(i)) break;
         }
-        if (!mbar_wait(bar_pds, i & 1, abort_flag)) break;     // P^T, dS^T written; S^T, dP^T consumed
+        if (!Cfg::kAliasDQ && i + 1 < n_q) {
+          // The elementwise warps hold S^T / dP^T of block i in registers: the next block's are
+          // computed while they work, ahead of everything else of this block.
+          if (!mbar_wait(bar_sdpfree, i & 1, abort_flag)) break;
+          tc_fence_after();
+          if (!issue_sdp(i + 1)) break;
+        }
+        if (!mbar_wait(bar_pds, i & 1, abort_flag)) break;     // P^T, dS^T written
         tc_fence_after();
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks)   // dV += P^T dO, reduction over the 128 queries
-          umma_f16(tmem_base + Cfg::kColDV, smem_desc_sw128(spt + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024),
-                   smem_desc_sw128(sdo + ks * 2048, 16384, 1024), idesc_kn, (i > 0 || ks > 0) ? 1u : 0u);
+        for (int ks = 0; ks < 8; ++ks) {  // dV += P^T dO, reduction over the 128 queries
+          if (Cfg::kPTinTmem)
+            umma_f16_ts(tmem_base + Cfg::kColDV, tmem_base + Cfg::kColPT + ks * 8,
+                        smem_desc_sw128(sdo + ks * 2048, 16384, 1024), idesc_kn, (i > 0 || ks > 0) ? 1u : 0u);
+          else
+            umma_f16(tmem_base + Cfg::kColDV, smem_desc_sw128(spt + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024),
+                     smem_desc_sw128(sdo + ks * 2048, 16384, 1024), idesc_kn, (i > 0 || ks > 0) ? 1u : 0u);
+        }
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)   // dK += dS^T Q
           umma_f16(tmem_base + Cfg::kColDK, smem_desc_sw128(sdst + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024),
                    smem_desc_sw128(sq + ks * 2048, 16384, 1024), idesc_kn, (i > 0 || ks > 0) ? 1u : 0u);
+        umma_commit(bar_qempty0 + 8 * s);   // Q and dO of this block are not read again (dQ needs neither)
         if (!Cfg::kAliasDQ) {
-          // the next block's S^T / dP^T go ahead of this block's dQ, so the elementwise stage of
-          // block i+1 never waits for the dQ read-out of block i-1
-          if (i + 1 < n_q && !issue_sdp(i + 1)) break;
-          if (i > 0 && !mbar_wait(bar_dqfree, (i - 1) & 1, abort_flag)) break;
+          if (i > 0 && !mbar_wait(bar_dqfree, (i - 1) & 1, abort_flag)) break;   // dQ columns read out
           tc_fence_after();
         }
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)   // dQ = dS K, reduction over the 128 keys
           umma_f16(tmem_base + Cfg::kColDQ, smem_desc_sw128(sdst + ks * 2048, 16384, 1024),
                    smem_desc_sw128(sk + ks * 2048, 16384, 1024), idesc_mn, ks > 0 ? 1u : 0u);
-        umma_commit(bar_qempty0 + 8 * s);
         umma_commit(bar_dq);
       }
     }
@@ -202,12 +228,6 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     uint8_t* pt_row = base_ptr + Cfg::kOffPT + t * 128;
     uint8_t* dst_row = base_ptr + Cfg::kOffDST + t * 128;
     bool ok = true;
-    // statistics of a query block: lse in the log2 domain (+inf for padded queries -> p = 0), delta
-    auto load_stats = [&](int qi, float& l2, float& dl) {
-      const int q = qi * 128 + t;
-      l2 = q < P.S ? P.lse[(int64_t)bh * P.S + q] * kLog2eF : INFINITY;
-      dl = q < P.S ? P.delta[(int64_t)bh * P.S + q] : 0.f;
-    };
     // adds the finished dQ block (TMEM) into the fp32 accumulator [B*H, S, D]: each warp stages its
     // 32 rows x 32 columns in swizzled shared memory and one lane issues a TMA reduce-add (rows past
     // the sequence end are clipped by the tensor map)
@@ -232,18 +252,14 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         }
       }
     };
-    if (hh == 0) load_stats(q_start, stat[t], stat[128 + t]);
     for (int i = 0; i < n_q && ok; ++i) {
       const int qi = q_start + i;
-      float* lse2 = stat + (i & 1) * 256;
-      float* dlt = lse2 + 128;
-      // the block's statistics become visible to all elementwise threads through a bounded mbarrier wait
-      mbar_arrive(bar_stat);
-      if (!__all_sync(0xffffffffu, mbar_wait(bar_stat, i & 1, abort_flag))) { ok = false; break; }
-      float nl2 = 0.f, ndl = 0.f;                    // next block's statistics, in flight during this block
-      const bool pre = hh == 0 && i + 1 < n_q;
-      if (pre) load_stats(qi + 1, nl2, ndl);
+      // row statistics of this query block arrived with its Q/dO stage (bulk copy); the wait makes
+      // that copy visible to this thread and returns at once, since S^T needed the stage too
+      const float* lse2 = stat + (i % ST) * 256;
+      const float* dlt = lse2 + 128;
       if (!__all_sync(0xffffffffu, mbar_wait(bar_sdp, i & 1, abort_flag))) { ok = false; break; }
+      if (!__all_sync(0xffffffffu, mbar_wait(bar_qfull0 + 8 * (i % ST), (i / ST) & 1, abort_flag))) { ok = false; break; }
       tc_fence_after();
       const bool diag = P.causal && qi == jb;
       const bool dead = kg >= P.S;                    // padded key row: contributes nothing
@@ -254,6 +270,16 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         tmem_ld32(tmem_base + Cfg::kColDPT + lane_addr + hh * 64, d_);
         tmem_ld32(tmem_base + Cfg::kColDPT + lane_addr + hh * 64 + 32, d_ + 32);
         tmem_ld_wait();
+        if (!Cfg::kAliasDQ) {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_sdpfree);   // S^T / dP^T columns may be overwritten
+        }
+        if (diag || __any_sync(0xffffffffu, dead)) {   // masked entries: score -inf -> p = 0, dS = 0
+#pragma unroll
+          for (int e = 0; e < 64; ++e)
+            if (dead || (diag && hh * 64 + e < t)) s_[e] = 0xff800000u;
+        }
         if (!Cfg::kOwnStage) {   // staging aliases this warp's slice of P^T: let the last reduce finish reading it
           if (lane == 0) bulk_wait_read<0>();
           __syncwarp();
@@ -263,32 +289,44 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           // the S^T/dP^T MMAs of this block: it must have completed before dS^T is overwritten
           if (!__all_sync(0xffffffffu, mbar_wait(bar_dq, (i - 1) & 1, abort_flag))) { ok = false; break; }
         }
+        uint32_t ptp[Cfg::kPTinTmem ? 32 : 1];   // P^T of this thread as packed half pairs
+        const float4* lse4 = reinterpret_cast<const float4*>(lse2 + hh * 64);   // per query column, 16-byte loads
+        const float4* dlt4 = reinterpret_cast<const float4*>(dlt + hh * 64);
 #pragma unroll
         for (int c16 = 0; c16 < 8; ++c16) {
           uint32_t pp[4], dd[4];
+          const float4 la = lse4[c16 * 2], lb = lse4[c16 * 2 + 1], da = dlt4[c16 * 2], db = dlt4[c16 * 2 + 1];
+          const float lv[8] = {la.x, la.y, la.z, la.w, lb.x, lb.y, lb.z, lb.w};
+          const float dl8[8] = {da.x, da.y, da.z, da.w, db.x, db.y, db.z, db.w};
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             float pv[2], dv[2];
 #pragma unroll
             for (int u = 0; u < 2; ++u) {
-              const int c = hh * 64 + c16 * 8 + 2 * e + u;     // query column within the block
-              float p = ex2_approx(fmaf(__uint_as_float(s_[c16 * 8 + 2 * e + u]), P.scale_log2, -lse2[c]));
-              if (dead || (diag && c < t)) p = 0.f;
+              const int ce = c16 * 8 + 2 * e + u;              // this thread's column, of 64
+              const float p = ex2_approx(fmaf(__uint_as_float(s_[ce]), P.scale_log2, -lv[2 * e + u]));
               pv[u] = p;
-              dv[u] = p * (__uint_as_float(d_[c16 * 8 + 2 * e + u]) - dlt[c]) * P.scale;
+              dv[u] = p * fmaf(__uint_as_float(d_[ce]), P.scale, -dl8[2 * e + u]);   // p (dP - delta) scale
             }
             pp[e] = pack2<T>(pv[0], pv[1]);
             dd[e] = pack2<T>(dv[0], dv[1]);
           }
           const int off = hh * 16384 + ((c16 ^ (t & 7)) << 4);
-          *reinterpret_cast<uint4*>(pt_row + off) = make_uint4(pp[0], pp[1], pp[2], pp[3]);
+          if (Cfg::kPTinTmem) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) ptp[c16 * 4 + e] = pp[e];
+          } else {
+            *reinterpret_cast<uint4*>(pt_row + off) = make_uint4(pp[0], pp[1], pp[2], pp[3]);
+          }
           *reinterpret_cast<uint4*>(dst_row + off) = make_uint4(dd[0], dd[1], dd[2], dd[3]);
+          if (Cfg::kPTinTmem && (c16 & 3) == 3)   // 32 finished columns = 16 packed words -> tensor memory
+            tmem_st16(tmem_base + Cfg::kColPT + lane_addr + hh * 32 + (c16 >> 2) * 16, ptp + (c16 >> 2) * 16);
         }
+        if (Cfg::kPTinTmem) tmem_st_wait();
       }
       fence_proxy_async();
       tc_fence_before();
       mbar_arrive(bar_pds);
-      if (pre) { stat[((i + 1) & 1) * 256 + t] = nl2; stat[((i + 1) & 1) * 256 + 128 + t] = ndl; }
       // dQ read-out. With its own TMEM columns the PREVIOUS block's dQ is flushed here, while the
       // tensor core works on this block; when dQ aliases S^T it has to be this block's.
       const int fi = Cfg::kAliasDQ ? i : i - 1;
@@ -311,31 +349,39 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     if (lane == 0) bulk_wait_all<0>();   // reduces must be done with shared memory before the CTA exits
     __syncwarp();
     if (ok) {
-      // all MMAs are complete (the last bar_dq was waited above): write dK, dV of this key row
-      T* dkrow = reinterpret_cast<T*>(P.dk) + (int64_t)b * P.sdk.b + (int64_t)h * P.sdk.h + (int64_t)kg * P.sdk.s;
-      T* dvrow = reinterpret_cast<T*>(P.dv) + (int64_t)b * P.sdv.b + (int64_t)h * P.sdv.h + (int64_t)kg * P.sdv.s;
+      // All MMAs are complete (the last bar_dq was waited above). The warps of column half 0 write
+      // dK, those of half 1 dV: 32 key rows x 64 columns at a time are staged (128-byte rows,
+      // swizzled) in the warp's buffer and stored by TMA, which clips rows past the sequence end.
+      const CUtensorMap* map = hh ? &tmDV : &tmDK;
+      const MapPos pos = hh ? P.pdv : P.pdk;
+      const int col0 = hh ? Cfg::kColDV : Cfg::kColDK;
+      uint8_t* stage = base_ptr + Cfg::kOffStage + warp * 4096;
 #pragma unroll 1
-      for (int which = 0; which < 2; ++which) {
-        T* orow = which ? dvrow : dkrow;
-        const int col0 = which ? Cfg::kColDV : Cfg::kColDK;
-#pragma unroll 1
-        for (int c = hh * (D / 64); c < (hh + 1) * (D / 64); ++c) {
-          uint32_t r[32];
-          tmem_ld32(tmem_base + col0 + lane_addr + c * 32, r);
-          tmem_ld_wait();
-          if (kg < P.S) {
+      for (int dc = 0; dc < Cfg::kChunks; ++dc) {
+        uint32_t r[64];
+        tmem_ld32(tmem_base + col0 + lane_addr + dc * 64, r);
+        tmem_ld32(tmem_base + col0 + lane_addr + dc * 64 + 32, r + 32);
+        tmem_ld_wait();
+        if (lane == 0) bulk_wait_read<0>();     // earlier reduce / store out of this buffer has been read
+        __syncwarp();
 #pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4) {
-              uint4 v;
-              v.x = pack2<T>(__uint_as_float(r[q4 * 8 + 0]), __uint_as_float(r[q4 * 8 + 1]));
-              v.y = pack2<T>(__uint_as_float(r[q4 * 8 + 2]), __uint_as_float(r[q4 * 8 + 3]));
-              v.z = pack2<T>(__uint_as_float(r[q4 * 8 + 4]), __uint_as_float(r[q4 * 8 + 5]));
-              v.w = pack2<T>(__uint_as_float(r[q4 * 8 + 6]), __uint_as_float(r[q4 * 8 + 7]));
-              *reinterpret_cast<uint4*>(orow + c * 32 + q4 * 8) = v;
-            }
-          }
+        for (int c16 = 0; c16 < 8; ++c16) {
+          uint4 v;
+          v.x = pack2<T>(__uint_as_float(r[c16 * 8 + 0]), __uint_as_float(r[c16 * 8 + 1]));
+          v.y = pack2<T>(__uint_as_float(r[c16 * 8 + 2]), __uint_as_float(r[c16 * 8 + 3]));
+          v.z = pack2<T>(__uint_as_float(r[c16 * 8 + 4]), __uint_as_float(r[c16 * 8 + 5]));
+          v.w = pack2<T>(__uint_as_float(r[c16 * 8 + 6]), __uint_as_float(r[c16 * 8 + 7]));
+          *reinterpret_cast<uint4*>(stage + lane * 128 + ((c16 ^ (lane & 7)) << 4)) = v;
+        }
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) {
+          store_rows(map, smem_u32(stage), pos, dc * 64, jb * 128 + (warp & 3) * 32, h, b);
+          bulk_commit();
         }
       }
+      if (lane == 0) bulk_wait_all<0>();
+      __syncwarp();
     }
   }
 
@@ -345,6 +391,43 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   if (warp == kBwdEwWarps + 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+// Row statistics for the backward kernel, padded to whole 128-row blocks:
+//   stats[0][bh][i] = lse[bh][i] * log2(e)            (+inf for i >= S: such a row gets p = 0)
+//   stats[1][bh][i] = scale * sum_d o[i][d] * do[i][d]  (0 for i >= S)
+// Eight threads per row read O and dO once.
+template <typename T>
+__global__ void __launch_bounds__(256)
+attn_bwd_stats_kernel(const T* __restrict__ o, const T* __restrict__ d_o, const float* __restrict__ lse,
+                      float* __restrict__ stats, mt_strides3 so, mt_strides3 sdo, int heads, int S, int spad, int D,
+                      int64_t total_rows, float scale) {
+  constexpr int VN = Vec16<T>::N;
+  const int sub = threadIdx.x & 7;
+  const int64_t row = (int64_t)blockIdx.x * 32 + (threadIdx.x >> 3);   // over [B*H][spad]
+  const int64_t bh = row / spad;
+  const int i = (int)(row - bh * spad);
+  const bool real = row < total_rows && i < S;
+  float s = 0.f;
+  if (real) {
+    const int b = (int)(bh / heads), h = (int)(bh % heads);
+    const T* op = o + (int64_t)b * so.b + (int64_t)h * so.h + (int64_t)i * so.s;
+    const T* dp = d_o + (int64_t)b * sdo.b + (int64_t)h * sdo.h + (int64_t)i * sdo.s;
+    for (int d = sub * VN; d < D; d += 8 * VN) {
+      Vec16<T> a, g;
+      a.load(op + d);
+      g.load(dp + d);
+#pragma unroll
+      for (int e = 0; e < VN; ++e) s += a.get(e) * g.get(e);
+    }
+  }
+  s += __shfl_xor_sync(0xffffffffu, s, 1);
+  s += __shfl_xor_sync(0xffffffffu, s, 2);
+  s += __shfl_xor_sync(0xffffffffu, s, 4);
+  if (sub == 0 && row < total_rows) {
+    stats[row] = real ? lse[bh * S + i] * kLog2eF : INFINITY;
+    stats[total_rows + row] = real ? s * scale : 0.f;
   }
 }
 
@@ -369,7 +452,7 @@ dq_convert_kernel(const float* __restrict__ acc, T* __restrict__ dq, mt_strides3
 
 bool attn_bwd_tc_supported(const AttnArgs& a) {
   if (!a.dq_accum) return false;
-  if (!aligned16(a.d_o) || !aligned16(a.dq) || !aligned16(a.dk) || !aligned16(a.dv) || !aligned16(a.dq_accum)) return false;
+  if (!aligned16(a.o) || !aligned16(a.d_o) || !aligned16(a.dq) || !aligned16(a.dk) || !aligned16(a.dv) || !aligned16(a.dq_accum)) return false;
   if (!strides_ok(a.sdo) || !strides_ok(a.sdq) || !strides_ok(a.sdk) || !strides_ok(a.sdv)) return false;
   return true;
 }
@@ -378,8 +461,15 @@ template <int D, typename T>
 static int launch_bwd(const AttnArgs& a, cudaStream_t st) {
   using Cfg = BwdCfg<D>;
   const int bf = a.dtype == MT_BF16;
-  int rc = attn_delta(a, st);
-  if (rc) return rc;
+  int rc;
+  const int nqb = (int)((a.seq + 127) / 128);
+  const int64_t stat_rows = a.batch * a.heads * nqb * 128;
+  TempBuf stats((size_t)stat_rows * 2 * sizeof(float), st);
+  if (!stats.ok()) return MT_ERR_CUDA;
+  attn_bwd_stats_kernel<T><<<(unsigned)((stat_rows + 31) / 32), 256, 0, st>>>(
+      (const T*)a.o, (const T*)a.d_o, a.lse, (float*)stats.ptr, a.so, a.sdo, (int)a.heads, (int)a.seq, nqb * 128, D,
+      stat_rows, a.scale);
+  MT_LAUNCH_CHECK();
   const int64_t n_acc = a.batch * a.heads * a.seq * D;
   MT_CHECK_CUDA(cudaMemsetAsync(a.dq_accum, 0, (size_t)n_acc * sizeof(float), st));
   CUtensorMap tq, tk, tv, tdo;
@@ -388,6 +478,9 @@ static int launch_bwd(const AttnArgs& a, cudaStream_t st) {
   if ((rc = make_qkv_map(&tk, &P.pk, a.k, bf, a.sk, a.batch, a.heads, a.seq, D))) return rc;
   if ((rc = make_qkv_map(&tv, &P.pv, a.v, bf, a.sv, a.batch, a.heads, a.seq, D))) return rc;
   if ((rc = make_qkv_map(&tdo, &P.pdo, a.d_o, bf, a.sdo, a.batch, a.heads, a.seq, D))) return rc;
+  CUtensorMap tdk, tdv;
+  if ((rc = make_qkv_map(&tdk, &P.pdk, a.dk, bf, a.sdk, a.batch, a.heads, a.seq, D, 32))) return rc;
+  if ((rc = make_qkv_map(&tdv, &P.pdv, a.dv, bf, a.sdv, a.batch, a.heads, a.seq, D, 32))) return rc;
   CUtensorMap tdq;
   {
     uint64_t dims[3] = {(uint64_t)D, (uint64_t)a.seq, (uint64_t)(a.batch * a.heads)};
@@ -395,14 +488,13 @@ static int launch_bwd(const AttnArgs& a, cudaStream_t st) {
     uint32_t box[3] = {32, 32, 1};
     if ((rc = make_tmap_nd_typed(&tdq, a.dq_accum, MT_F32, 3, dims, str, box))) return rc;
   }
-  P.lse = a.lse; P.delta = a.delta; P.dq_accum = a.dq_accum; P.dk = a.dk; P.dv = a.dv;
-  P.sdk = a.sdk; P.sdv = a.sdv;
+  P.stats = (const float*)stats.ptr; P.dq_accum = a.dq_accum; P.dk = a.dk; P.dv = a.dv;
   P.B = (int)a.batch; P.H = (int)a.heads; P.S = (int)a.seq; P.nqb = (int)((a.seq + 127) / 128);
   P.causal = a.causal; P.is_bf16 = bf; P.scale = a.scale; P.scale_log2 = a.scale * kLog2eF; P.flag = device_flag_ptr();
   auto kern = attn_bwd_tc_kernel<D, T>;
   MT_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
   const unsigned grid = (unsigned)(P.nqb * P.B * P.H);
-  kern<<<grid, kBwdThreads, Cfg::kSmem, st>>>(tq, tk, tv, tdo, tdq, P);
+  kern<<<grid, kBwdThreads, Cfg::kSmem, st>>>(tq, tk, tv, tdo, tdq, tdk, tdv, P);
   MT_LAUNCH_CHECK();
   const int64_t n_vec = n_acc / 8;
   int64_t blocks = (n_vec + 255) / 256;

@@ -20,6 +20,13 @@ __device__ __forceinline__ void load_rows(uint32_t dst, const CUtensorMap* map, 
   sm100::tma_load_4d(dst, map, bar, c[0], c[1], c[2], c[3]);
 }
 
+// Store of a staged tile (64 of head_dim x `box rows` of seq) through the same kind of map.
+__device__ __forceinline__ void store_rows(const CUtensorMap* map, uint32_t src, MapPos pos, int d0, int row0, int h, int b) {
+  int c[4];
+  c[0] = d0; c[pos.s] = row0; c[pos.h] = h; c[pos.b] = b;
+  sm100::tma_store_4d(map, src, c[0], c[1], c[2], c[3]);
+}
+
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -74,9 +81,9 @@ static inline bool strides_ok(const mt_strides3& s) { return s.b % 8 == 0 && s.h
 // 4-D map {head_dim, x, y, z} with (seq, head, batch) placed by ascending stride;
 // the box covers 64 of head_dim and 128 rows of seq.
 static inline int make_qkv_map(CUtensorMap* m, MapPos* pos, const void* p, int bf16, const mt_strides3& s, int64_t B, int64_t H,
-                        int64_t S, int64_t D) {
+                        int64_t S, int64_t D, uint32_t box_rows = 128) {
   struct Dim { uint64_t extent, stride; uint32_t box; int role; };
-  Dim d[3] = {{(uint64_t)S, (uint64_t)s.s, 128, 0}, {(uint64_t)H, (uint64_t)s.h, 1, 1}, {(uint64_t)B, (uint64_t)s.b, 1, 2}};
+  Dim d[3] = {{(uint64_t)S, (uint64_t)s.s, box_rows, 0}, {(uint64_t)H, (uint64_t)s.h, 1, 1}, {(uint64_t)B, (uint64_t)s.b, 1, 2}};
   for (int i = 0; i < 3; ++i)
     for (int j = i + 1; j < 3; ++j)
       if (d[j].stride < d[i].stride) { Dim t = d[i]; d[i] = d[j]; d[j] = t; }

@@ -53,9 +53,8 @@ template <int D> struct FwdCfg {
 
 
 struct AttnFwdParams {
-  void* o; float* lse;
-  MapPos pq, pk, pv;
-  mt_strides3 so;
+  float* lse;
+  MapPos pq, pk, pv, po;
   int B, H, S, nqb, causal, is_bf16;
   float scale_log2;
   int* flag;
@@ -65,7 +64,8 @@ struct AttnFwdParams {
 template <int D, typename T>
 __global__ void __launch_bounds__(kAttnThreads, D == 64 ? 2 : 1)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                   const __grid_constant__ CUtensorMap tmV, const AttnFwdParams P) {
+                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
+                   const AttnFwdParams P) {
   using Cfg = FwdCfg<D>;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t base = smem_u32(smem_raw);
@@ -304,23 +304,33 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       tc_fence_after();
       const float l_row = l + l_other;
       const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
-      T* orow = reinterpret_cast<T*>(P.o) + (int64_t)b * P.so.b + (int64_t)h * P.so.h + (int64_t)q_glob * P.so.s + hf * (D / 2);
-#pragma unroll 1
-      for (int c = 0; c < D / 64; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tmem_o + lane_addr + hf * (D / 2) + c * 32, r);
+      // O leaves through shared memory: one warp per 32 rows x 64 columns stages 128-byte rows
+      // (swizzled) in the now idle K buffer and one lane issues a TMA store, which clips rows
+      // past the sequence end. At head_dim 64 the warps of column half 1 have nothing to store.
+      if (D == 128 || hf == 0) {
+        const int dc = D == 128 ? hf : 0;
+        uint8_t* stage = base_ptr + Cfg::kOffK + warp * 4096;
+        uint32_t r[64];
+        tmem_ld32(tmem_o + lane_addr + dc * 64, r);
+        tmem_ld32(tmem_o + lane_addr + dc * 64 + 32, r + 32);
         tmem_ld_wait();
-        if (q_glob < P.S) {
 #pragma unroll
-          for (int q4 = 0; q4 < 4; ++q4) {
-            uint4 v;
-            v.x = pack2<T>(__uint_as_float(r[q4 * 8 + 0]) * inv, __uint_as_float(r[q4 * 8 + 1]) * inv);
-            v.y = pack2<T>(__uint_as_float(r[q4 * 8 + 2]) * inv, __uint_as_float(r[q4 * 8 + 3]) * inv);
-            v.z = pack2<T>(__uint_as_float(r[q4 * 8 + 4]) * inv, __uint_as_float(r[q4 * 8 + 5]) * inv);
-            v.w = pack2<T>(__uint_as_float(r[q4 * 8 + 6]) * inv, __uint_as_float(r[q4 * 8 + 7]) * inv);
-            *reinterpret_cast<uint4*>(orow + c * 32 + q4 * 8) = v;
-          }
+        for (int c16 = 0; c16 < 8; ++c16) {
+          uint4 v;
+          v.x = pack2<T>(__uint_as_float(r[c16 * 8 + 0]) * inv, __uint_as_float(r[c16 * 8 + 1]) * inv);
+          v.y = pack2<T>(__uint_as_float(r[c16 * 8 + 2]) * inv, __uint_as_float(r[c16 * 8 + 3]) * inv);
+          v.z = pack2<T>(__uint_as_float(r[c16 * 8 + 4]) * inv, __uint_as_float(r[c16 * 8 + 5]) * inv);
+          v.w = pack2<T>(__uint_as_float(r[c16 * 8 + 6]) * inv, __uint_as_float(r[c16 * 8 + 7]) * inv);
+          *reinterpret_cast<uint4*>(stage + lane * 128 + ((c16 ^ (lane & 7)) << 4)) = v;
         }
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) {
+          store_rows(&tmO, smem_u32(stage), P.po, dc * 64, qb * 128 + qtr * 32, h, b);
+          bulk_commit();
+          bulk_wait_all<0>();   // shared memory must stay valid until the store has read it
+        }
+        __syncwarp();
       }
       if (hf == 0 && q_glob < P.S) P.lse[(int64_t)bh * P.S + q_glob] = (m_used + log2f(l_row)) * kLn2F;
     }
@@ -352,19 +362,20 @@ template <int D, typename T>
 static int launch_fwd(const AttnArgs& a, cudaStream_t st) {
   using Cfg = FwdCfg<D>;
   const int bf = a.dtype == MT_BF16;
-  CUtensorMap tq, tk, tv;
+  CUtensorMap tq, tk, tv, to;
   int rc;
   AttnFwdParams P;
+  if ((rc = make_qkv_map(&to, &P.po, a.o_out, bf, a.so, a.batch, a.heads, a.seq, D, 32))) return rc;
   if ((rc = make_qkv_map(&tq, &P.pq, a.q, bf, a.sq, a.batch, a.heads, a.seq, D))) return rc;
   if ((rc = make_qkv_map(&tk, &P.pk, a.k, bf, a.sk, a.batch, a.heads, a.seq, D))) return rc;
   if ((rc = make_qkv_map(&tv, &P.pv, a.v, bf, a.sv, a.batch, a.heads, a.seq, D))) return rc;
-  P.o = a.o_out; P.lse = a.lse; P.so = a.so;
+  P.lse = a.lse;
   P.B = (int)a.batch; P.H = (int)a.heads; P.S = (int)a.seq; P.nqb = (int)((a.seq + 127) / 128);
   P.causal = a.causal; P.is_bf16 = bf; P.scale_log2 = a.scale * kLog2eF; P.flag = device_flag_ptr();
   auto kern = attn_fwd_tc_kernel<D, T>;
   MT_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
   const unsigned grid = (unsigned)(P.nqb * P.B * P.H);
-  kern<<<grid, kAttnThreads, Cfg::kSmem, st>>>(tq, tk, tv, P);
+  kern<<<grid, kAttnThreads, Cfg::kSmem, st>>>(tq, tk, tv, to, P);
   MT_LAUNCH_CHECK();
   return MT_OK;
 }
