@@ -397,12 +397,13 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 // Row statistics for the backward kernel, padded to whole 128-row blocks:
 //   stats[0][bh][i] = lse[bh][i] * log2(e)            (+inf for i >= S: such a row gets p = 0)
 //   stats[1][bh][i] = scale * sum_d o[i][d] * do[i][d]  (0 for i >= S)
-// Eight threads per row read O and dO once.
+// Eight threads per row read O and dO once; the same threads clear the row of the fp32 dQ
+// accumulator [B*H, S, D] that the backward kernel adds into.
 template <typename T>
 __global__ void __launch_bounds__(256)
 attn_bwd_stats_kernel(const T* __restrict__ o, const T* __restrict__ d_o, const float* __restrict__ lse,
-                      float* __restrict__ stats, mt_strides3 so, mt_strides3 sdo, int heads, int S, int spad, int D,
-                      int64_t total_rows, float scale) {
+                      float* __restrict__ stats, float* __restrict__ dq_accum, mt_strides3 so, mt_strides3 sdo, int heads,
+                      int S, int spad, int D, int64_t total_rows, float scale) {
   constexpr int VN = Vec16<T>::N;
   const int sub = threadIdx.x & 7;
   const int64_t row = (int64_t)blockIdx.x * 32 + (threadIdx.x >> 3);   // over [B*H][spad]
@@ -421,6 +422,8 @@ attn_bwd_stats_kernel(const T* __restrict__ o, const T* __restrict__ d_o, const 
 #pragma unroll
       for (int e = 0; e < VN; ++e) s += a.get(e) * g.get(e);
     }
+    float4* acc = reinterpret_cast<float4*>(dq_accum + (bh * S + i) * D);
+    for (int d4 = sub; d4 < D / 4; d4 += 8) acc[d4] = make_float4(0.f, 0.f, 0.f, 0.f);
   }
   s += __shfl_xor_sync(0xffffffffu, s, 1);
   s += __shfl_xor_sync(0xffffffffu, s, 2);
@@ -467,11 +470,10 @@ static int launch_bwd(const AttnArgs& a, cudaStream_t st) {
   TempBuf stats((size_t)stat_rows * 2 * sizeof(float), st);
   if (!stats.ok()) return MT_ERR_CUDA;
   attn_bwd_stats_kernel<T><<<(unsigned)((stat_rows + 31) / 32), 256, 0, st>>>(
-      (const T*)a.o, (const T*)a.d_o, a.lse, (float*)stats.ptr, a.so, a.sdo, (int)a.heads, (int)a.seq, nqb * 128, D,
+      (const T*)a.o, (const T*)a.d_o, a.lse, (float*)stats.ptr, a.dq_accum, a.so, a.sdo, (int)a.heads, (int)a.seq, nqb * 128, D,
       stat_rows, a.scale);
   MT_LAUNCH_CHECK();
   const int64_t n_acc = a.batch * a.heads * a.seq * D;
-  MT_CHECK_CUDA(cudaMemsetAsync(a.dq_accum, 0, (size_t)n_acc * sizeof(float), st));
   CUtensorMap tq, tk, tv, tdo;
   AttnBwdParams P;
   if ((rc = make_qkv_map(&tq, &P.pq, a.q, bf, a.sq, a.batch, a.heads, a.seq, D))) return rc;
