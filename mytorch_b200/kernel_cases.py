@@ -10,6 +10,11 @@ attn : causal flash attention forward + backward, 4x12x1024x64 fp16, three round
 mem  : LayerNorm forward/backward (16384x768), cross entropy forward/backward
        (4096x50304), GELU backward (16384x3072), softmax (16384x1024), three rounds
 adamw: fused AdamW over one 64M-element fp32 tensor, three steps
+gemm_vs_library : the lm_head GEMM (16384x50304x768, fp16) timed for 300 back-to-back launches
+       with CUDA events, this library's kernel and torch.matmul (cuBLAS) side by side, on
+       random-normal, small-integer and all-zero operands. Throughput on a power-capped B200
+       depends on the operand values (bit toggling), so a roofline fraction only means
+       something against a library number taken on the same data.
 """
 import sys
 
@@ -58,10 +63,64 @@ def main(which):
         for _ in range(3):
             p.grad = DeviceArray.zeros((n,), "float32")
             opt.step()
+    elif which == "gemm_vs_library":
+        gemm_vs_library(r)
+        return
     else:
         raise SystemExit(__doc__)
     synchronize()
     print("done", which)
+
+
+def gemm_vs_library(r, m=16384, n=50304, k=768, iters=300):
+    import ctypes as C
+    import torch
+    from mytorch_b200 import _lib
+    from mytorch_b200.array import stream
+
+    def time_own(fn):
+        for _ in range(3):
+            fn()
+        e0, e1 = C.c_void_p(), C.c_void_p()
+        _lib.event_create(C.byref(e0)); _lib.event_create(C.byref(e1))
+        _lib.event_record(e0, stream())
+        for _ in range(iters):
+            fn()
+        _lib.event_record(e1, stream())
+        _lib.event_sync(e1)
+        ms = C.c_float()
+        _lib.event_elapsed_ms(e0, e1, C.byref(ms))
+        return ms.value / iters
+
+    def time_torch(fn):
+        for _ in range(3):
+            fn()
+        e0, e1 = torch.cuda.Event(True), torch.cuda.Event(True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / iters
+
+    flop = 2.0 * m * n * k
+    for dist in ("randn", "small_ints", "zeros"):
+        if dist == "randn":
+            a, b = r.standard_normal((m, k)), r.standard_normal((n, k))
+        elif dist == "small_ints":
+            a, b = r.integers(-2, 3, (m, k)), r.integers(-2, 3, (n, k))
+        else:
+            a, b = np.zeros((m, k)), np.zeros((n, k))
+        a, b = a.astype(np.float32), b.astype(np.float32)
+        A, B = DeviceArray.from_numpy(a, "float16"), DeviceArray.from_numpy(b, "float16")
+        out = DeviceArray.empty((m, n), "float16")
+        own = time_own(lambda: F.gemm(A, B, trans_b=True, out=out))
+        ta, tb = torch.from_numpy(a).cuda().half(), torch.from_numpy(b).cuda().half()
+        to = torch.empty((m, n), device="cuda", dtype=torch.float16)
+        lib = time_torch(lambda: torch.matmul(ta, tb.t(), out=to))
+        print(f"{dist:10s}: this library {own * 1e3:7.1f} us {flop / own / 1e9:5.0f} TFLOP/s | "
+              f"torch.matmul {lib * 1e3:7.1f} us {flop / lib / 1e9:5.0f} TFLOP/s", flush=True)
+        del ta, tb, to
 
 
 if __name__ == "__main__":
