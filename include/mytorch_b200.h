@@ -74,6 +74,9 @@ int64_t mt_launch_count(void);            /* kernels launched by this library so
 /* ---- elementwise (CuPy ufuncs reached through mytorch/_array.py:422-470 and
  * the autograd closures of mytorch/tensor.py:272-330, 596-640) -------------- */
 int mt_cast(const void* src, int src_dtype, void* dst, int dst_dtype, int64_t n, void* stream);
+/* uint16 token ids (the on-disk format of gpt2_trainer/train_gpt2.py:150) -> int32 indices,
+ * so that batches cross PCIe at two bytes per token. */
+int mt_widen_u16_i32(const void* src_u16, void* dst_i32, int64_t n, void* stream);
 int mt_fill(void* dst, int dtype, float value, int64_t n, void* stream);
 int mt_add(const void* a, const void* b, void* out, int64_t n, int dtype, void* stream);          /* out = a + b */
 int mt_axpby(const void* x, float alpha, void* y, float beta, int64_t n, int x_dtype, int y_dtype, void* stream); /* y = alpha*x + beta*y */

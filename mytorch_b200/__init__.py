@@ -11,7 +11,7 @@ from . import fused_ops
 __all__ = ["DeviceArray", "as_device_array", "stream", "synchronize", "fused_ops", "MTError"]
 
 from .tensor import Tensor, no_grad, zeros, ones, zeros_like, randn, arange
-from . import nn, optim
+from . import nn, optim, utils
 from .accelerate import Accelerator, GradScaler
 
 __all__ += ["Tensor", "no_grad", "zeros", "ones", "zeros_like", "randn", "arange", "nn", "optim",

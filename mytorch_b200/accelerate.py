@@ -335,39 +335,72 @@ class Accelerator:
             self.comm.stop()
             self.comm = None
 
-    # ---- checkpoint (accelerate.py:916-1048): fp32 masters + optimizer + scaler ----
-    def save_state(self, path):
-        os.makedirs(path, exist_ok=True)
+    # ---- checkpoint, same files and layouts as the reference (accelerate.py:916-1048) ----
+    #   model.safetensors  fp32 master of every parameter, keyed by _named_parameters_no_dedup
+    #   optimizer.bin      pickled AdamW.state_dict()
+    #   mp_config.bin      pickled {scale, growth_factor, backoff_factor, growth_interval, unskipped}
+    # so a run can move between the two implementations mid-training.
+    def save_state(self, path_to_checkpoint, save_model_only=False):
+        import pickle
+        from safetensors.numpy import save_file
         if self.rank == 0:
+            os.makedirs(path_to_checkpoint, exist_ok=True)
             sd = {}
             for name, p in self.model._named_parameters_no_dedup():
                 i = self._param_index.get(id(p))
-                sd[name] = self._flat.view(self._flat.master, i).numpy() if i is not None else p.numpy()
-            np.savez(os.path.join(path, "model.npz"), **sd)
-            import pickle
-            with open(os.path.join(path, "optimizer.bin"), "wb") as fh:
-                pickle.dump(self.optimizer.state_dict(), fh)
-            with open(os.path.join(path, "mp_config.bin"), "wb") as fh:
-                pickle.dump({"state": self.scaler.state.numpy(), "step_counter": self.step_counter}, fh)
+                a = self._flat.view(self._flat.master, i).numpy() if i is not None else p.numpy()
+                sd[name] = np.ascontiguousarray(a, dtype=np.float32)
+            save_file(sd, os.path.join(path_to_checkpoint, "model.safetensors"))
+            if not save_model_only:
+                if getattr(self, "optimizer", None) is not None:
+                    with open(os.path.join(path_to_checkpoint, "optimizer.bin"), "wb") as fh:
+                        pickle.dump(self.optimizer.state_dict(), fh)
+                if self.mixed_precision:
+                    st = self.scaler.state.numpy()
+                    cfg = {"scale": float(st[0]), "growth_factor": self.scaler.growth_factor,
+                           "backoff_factor": self.scaler.backoff_factor, "growth_interval": self.scaler.growth_interval,
+                           "unskipped": int(st[2])}
+                    with open(os.path.join(path_to_checkpoint, "mp_config.bin"), "wb") as fh:
+                        pickle.dump(cfg, fh)
         self.wait_for_everyone()
 
-    def load_state(self, path):
+    def load_state(self, path_to_checkpoint):
         import pickle
-        sd = dict(np.load(os.path.join(path, "model.npz")))
-        for name, p in self.model._named_parameters_no_dedup():
-            i = self._param_index.get(id(p))
-            if i is None or name not in sd:
-                continue
-            mview = self._flat.view(self._flat.master, i)
-            mview.set_from_numpy(sd[name])
-            if self.mixed_precision:
-                hview = self._flat.view(self._flat.half, i)
-                _lib.cast(mview.ptr, mview.code, hview.ptr, hview.code, mview.size, stream())
-        with open(os.path.join(path, "optimizer.bin"), "rb") as fh:
-            self.optimizer.load_state_dict(pickle.load(fh))
-        with open(os.path.join(path, "mp_config.bin"), "rb") as fh:
-            cfg = pickle.load(fh)
-        self.scaler.state.set_from_numpy(cfg["state"])
-        self.step_counter = cfg["step_counter"]
-        if self.comm is not None:
-            self.comm.broadcast(self._flat.master, root=0)
+        import warnings
+        from safetensors.numpy import load_file
+        path_to_model = os.path.join(path_to_checkpoint, "model.safetensors")
+        if os.path.exists(path_to_model):
+            sd = load_file(path_to_model)
+            for name, p in self.model._named_parameters_no_dedup():
+                i = self._param_index.get(id(p))
+                if i is None:
+                    continue
+                mview = self._flat.view(self._flat.master, i)
+                mview.set_from_numpy(np.asarray(sd[name], dtype=np.float32).reshape(mview.shape))
+                if self.mixed_precision:
+                    hview = self._flat.view(self._flat.half, i)
+                    _lib.cast(mview.ptr, mview.code, hview.ptr, hview.code, mview.size, stream())
+            if self.comm is not None:          # every rank starts from rank 0's weights
+                self.comm.broadcast(self._flat.master, root=0)
+                if self.mixed_precision:
+                    self.comm.broadcast(self._flat.half, root=0)
+        path_to_optimizer = os.path.join(path_to_checkpoint, "optimizer.bin")
+        if os.path.exists(path_to_optimizer) and getattr(self, "optimizer", None) is not None:
+            with open(path_to_optimizer, "rb") as fh:
+                self.optimizer.load_state_dict(pickle.load(fh))
+        if self.mixed_precision:
+            path_to_mp = os.path.join(path_to_checkpoint, "mp_config.bin")
+            if os.path.exists(path_to_mp):
+                with open(path_to_mp, "rb") as fh:
+                    cfg = pickle.load(fh)
+                self.scaler.growth_factor = cfg["growth_factor"]
+                self.scaler.backoff_factor = cfg["backoff_factor"]
+                self.scaler.growth_interval = cfg["growth_interval"]
+                st = self.scaler.state.numpy()
+                st[0] = cfg["scale"]
+                st[1] = 1.0 / (cfg["scale"] * self.scaler.accum_steps)
+                st[2] = cfg["unskipped"]
+                self.scaler.state.set_from_numpy(st)
+            else:
+                warnings.warn("If you are resuming mixed precision training without its checkpointed config, "
+                              "you may have instability in training")

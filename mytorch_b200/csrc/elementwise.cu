@@ -199,7 +199,26 @@ __global__ void __launch_bounds__(256) rope_kernel(T* __restrict__ x, const floa
 
 using namespace mt;
 
+namespace mt {
+// Token ids as stored on disk (uint16) widened to the int32 the embedding kernels index with.
+__global__ void __launch_bounds__(256)
+widen_u16_kernel(const uint16_t* __restrict__ src, int32_t* __restrict__ dst, int64_t n) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+    dst[i] = (int32_t)src[i];
+}
+}  // namespace mt
+
 extern "C" {
+
+int mt_widen_u16_i32(const void* src, void* dst, int64_t n, void* stream) {
+  MT_REQUIRE(src && dst && n >= 0, "widen_u16_i32: bad arguments");
+  if (n == 0) return MT_OK;
+  int64_t blocks = (n + 255) / 256;
+  if (blocks > (int64_t)sm_count() * 8) blocks = (int64_t)sm_count() * 8;
+  mt::widen_u16_kernel<<<(unsigned)blocks, 256, 0, as_stream(stream)>>>((const uint16_t*)src, (int32_t*)dst, n);
+  MT_LAUNCH_CHECK();
+  return MT_OK;
+}
 
 int mt_cast(const void* src, int sd, void* dst, int dd, int64_t n, void* stream) {
   MT_REQUIRE(src && dst && n >= 0, "cast: bad arguments");

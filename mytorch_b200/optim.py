@@ -115,20 +115,42 @@ class AdamW(Optimizer):
                 p.grad = None
 
     def state_dict(self):
-        """Hyper-parameters and moments as NumPy arrays (optimizers.py:378-441)."""
-        return {"param_groups": [{k: (v if k not in ("params", "m", "v", "_tables") else None) for k, v in g.items()
-                                  if k not in ("params", "_tables")} | {
-                                      "m": [a.numpy() for a in g["m"]], "v": [a.numpy() for a in g["v"]]}
-                                 for g in self.param_groups]}
+        """Same layout as the reference's AdamW.state_dict (optimizers.py:378-407):
+        {"state": [per group {m, v, t, beta1_pow, beta2_pow}], "param_groups": [per group
+        {lr, beta1, beta2, eps, weight_decay, num_params}]}; the moments are host NumPy arrays."""
+        sd = {"state": [], "param_groups": []}
+        for g in self.param_groups:
+            sd["state"].append({"m": [a.numpy() for a in g["m"]], "v": [a.numpy() for a in g["v"]],
+                                "t": g["t"], "beta1_pow": g["beta1_pow"], "beta2_pow": g["beta2_pow"]})
+            sd["param_groups"].append({"lr": g["lr"], "beta1": g["beta1"], "beta2": g["beta2"], "eps": g["eps"],
+                                       "weight_decay": g["weight_decay"], "num_params": len(g["params"])})
+        return sd
 
     def load_state_dict(self, sd):
-        for g, s in zip(self.param_groups, sd["param_groups"]):
-            for k in ("lr", "beta1", "beta2", "eps", "weight_decay", "t", "beta1_pow", "beta2_pow"):
-                g[k] = s[k]
-            for a, h in zip(g["m"], s["m"]):
-                a.set_from_numpy(h)
-            for a, h in zip(g["v"], s["v"]):
-                a.set_from_numpy(h)
+        """Accepts the layout above (optimizers.py:410-441). Moments may be NumPy arrays or any
+        object that wraps one (`_array` attribute, `.get()` for device arrays, `__array__`)."""
+        if len(sd["state"]) != len(self.param_groups):
+            raise ValueError(f"Loaded state dict has {len(sd['state'])} parameter groups, "
+                             f"but optimizer has {len(self.param_groups)} parameter groups")
+
+        def host(a):
+            a = getattr(a, "_array", a)
+            if hasattr(a, "get") and not isinstance(a, np.ndarray):
+                a = a.get()
+            return np.asarray(a, dtype=np.float32)
+
+        for i, (g, st) in enumerate(zip(self.param_groups, sd["state"])):
+            if len(g["params"]) != len(st["m"]):
+                raise ValueError(f"Parameter group {i}: loaded state has {len(st['m'])} parameters, "
+                                 f"but optimizer has {len(g['params'])} parameters")
+            for a, h in zip(g["m"], st["m"]):
+                a.set_from_numpy(host(h).reshape(a.shape))
+            for a, h in zip(g["v"], st["v"]):
+                a.set_from_numpy(host(h).reshape(a.shape))
+            g["t"], g["beta1_pow"], g["beta2_pow"] = st["t"], st["beta1_pow"], st["beta2_pow"]
+            lg = sd["param_groups"][i]
+            for k in ("lr", "beta1", "beta2", "eps", "weight_decay"):
+                g[k] = lg[k]
 
 
 class CosineLRScheduler:

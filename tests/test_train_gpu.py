@@ -272,3 +272,99 @@ def test_chunked_lm_head_cross_entropy_matches_unfused(dtype, tol, softcap):
     for name, got, ref in (("dx", dxf, dl @ w), ("dw", dwf, dl.T @ x), ("dx unfused", dxu, dl @ w), ("dw unfused", dwu, dl.T @ x)):
         err = np.abs(got - ref).max() / np.abs(ref).max()
         assert err <= 2 * tol, (name, err)
+
+
+def test_checkpoint_files_match_reference_layout_and_resume(tmp_path):
+    """save_state writes the reference's three files (accelerate.py:916-975): model.safetensors
+    with the fp32 masters, optimizer.bin = pickled AdamW.state_dict() in the layout of
+    optimizers.py:378-407, mp_config.bin with the scaler fields; a fresh process-equivalent
+    (new model, optimizer, Accelerator) that loads them continues on the same losses."""
+    import pickle
+    from safetensors.numpy import load_file
+    cfg = og.GPT2Config(vocab_size=264, max_seq_len=64, embed_dim=128, mlp_ratio=4, num_blocks=2, num_heads=2)
+    params = og.init_params(cfg, seed=6)
+
+    def make():
+        mt, model = build(cfg, {k: v.copy() for k, v in params.items()})
+        acc = mt.Accelerator(num_gpus=1, rank=0, mixed_precision=True)
+        opt = mt.optim.AdamW(groups(model), lr=1e-3, beta1=0.9, beta2=0.95)
+        model, opt = acc.prepare(model, opt)
+        return mt, model, acc, opt
+
+    def run(mt, model, acc, opt, rng, steps):
+        out = []
+        for _ in range(steps):
+            x, y = og.synthetic_batch(rng, 4, 64, 264)
+            loss = mt.nn.CrossEntropyLoss()(model(mt.Tensor(x)), mt.Tensor(y))
+            acc.backward(loss)
+            acc.clip_grad_norm_(1.0)
+            opt.step()
+            opt.zero_grad()
+            out.append(loss.item())
+        return out
+
+    rng = np.random.default_rng(9)
+    mt, model, acc, opt = make()
+    run(mt, model, acc, opt, rng, 3)
+    ckpt = str(tmp_path / "ckpt")
+    acc.save_state(ckpt)
+    rng_state = rng.bit_generator.state
+    straight = run(mt, model, acc, opt, rng, 3)
+
+    weights = load_file(ckpt + "/model.safetensors")
+    names = [n for n, _ in model._named_parameters_no_dedup()]
+    assert sorted(weights) == sorted(names) and all(w.dtype == np.float32 for w in weights.values())
+    with open(ckpt + "/optimizer.bin", "rb") as fh:
+        osd = pickle.load(fh)
+    assert set(osd) == {"state", "param_groups"} and len(osd["state"]) == 2
+    assert set(osd["state"][0]) == {"m", "v", "t", "beta1_pow", "beta2_pow"} and osd["state"][0]["t"] == 3
+    assert set(osd["param_groups"][0]) == {"lr", "beta1", "beta2", "eps", "weight_decay", "num_params"}
+    with open(ckpt + "/mp_config.bin", "rb") as fh:
+        assert set(pickle.load(fh)) == {"scale", "growth_factor", "backoff_factor", "growth_interval", "unskipped"}
+
+    mt2, model2, acc2, opt2 = make()
+    acc2.load_state(ckpt)
+    rng2 = np.random.default_rng(0)
+    rng2.bit_generator.state = rng_state
+    resumed = run(mt2, model2, acc2, opt2, rng2, 3)
+    # split-K gradient accumulation adds in a scheduling-dependent order: equal to fp32 round-off
+    assert np.allclose(resumed, straight, rtol=2e-4, atol=0), (resumed, straight)
+
+
+def test_dataloader_device_staging_feeds_the_same_batches():
+    """The staged host -> device path (pinned buffers, copy stream, uint16 widened on the device)
+    hands out exactly the host batches, in order, across buffer reuse; a training loop fed by it
+    reaches the losses of the same loop fed with host arrays."""
+    import mytorch_b200 as mt
+    from mytorch_b200.utils.data import DataLoader, TokenLoader
+    toks = np.random.default_rng(2).integers(0, 264, 40000).astype(np.uint16)
+    ds = TokenLoader(toks, 64, virtual_length=40, seed=7)
+    host = [(x.copy(), y.copy()) for x, y in DataLoader(ds, batch_size=4, num_workers=2)]
+    dev = []
+    for x, y in DataLoader(ds, batch_size=4, num_workers=2, device=True, staging_depth=2):
+        assert x.data.dtype == "int32" and x.shape == (4, 64)
+        dev.append((x.numpy().copy(), y.numpy().copy()))
+    assert len(dev) == len(host) == 10
+    for (hx, hy), (dx, dy) in zip(host, dev):
+        assert np.array_equal(hx.astype(np.int32), dx) and np.array_equal(hy.astype(np.int32), dy)
+
+    cfg = og.GPT2Config(vocab_size=264, max_seq_len=64, embed_dim=128, mlp_ratio=4, num_blocks=2, num_heads=2)
+    params = og.init_params(cfg, seed=8)
+
+    def train(batches):
+        mt_, model = build(cfg, {k: v.copy() for k, v in params.items()})
+        opt = mt_.optim.AdamW(groups(model), lr=1e-3, beta1=0.9, beta2=0.95)
+        losses = []
+        for x, y in batches:
+            x = x if isinstance(x, mt_.Tensor) else mt_.Tensor(x.astype(np.int32))
+            y = y if isinstance(y, mt_.Tensor) else mt_.Tensor(y.astype(np.int32))
+            loss = mt_.nn.CrossEntropyLoss()(model(x), y)
+            loss.backward()
+            opt.step()
+            opt.zero_grad()
+            losses.append(loss.item())
+        return losses
+
+    a = train(host[:6])
+    b = train(DataLoader(TokenLoader(toks, 64, virtual_length=24, seed=7), batch_size=4, num_workers=2, device=True))
+    assert np.allclose(a, b, rtol=1e-5), (a, b)
