@@ -122,10 +122,20 @@ class GPT2(nn.Module):
             if "out_proj" in name:
                 nn.init.normal_(param, mean=0.0, std=0.02 / np.sqrt(2 * config.num_blocks))
         self.lm_head.weight = self.embeddings.char_embeddings.weight      # weight tying (:340-347)
+        self._gradient_checkpointing_enabled = False
+
+    def enable_gradient_checkpointing(self):
+        """Recompute every transformer block in the backward pass instead of keeping its
+        activations (gpt2.py:349-365)."""
+        self._gradient_checkpointing_enabled = True
 
     def forward(self, x):
+        from .utils.checkpoint import checkpoint
         x = self.embeddings(x)
         for block in self.blocks:
-            x = block(x)
+            if self._gradient_checkpointing_enabled and self.training and x.requires_grad:
+                x = checkpoint(block, x)
+            else:
+                x = block(x)
         x = self.final_layer_norm(x)
         return self.lm_head(x)

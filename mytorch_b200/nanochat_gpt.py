@@ -126,6 +126,11 @@ class GPT(nn.Module):
                 nn.init.zeros_(param)
         self.cos, self.sin = F.precompute_rotary_cos_sin(config.embed_dim // config.num_q_heads,
                                                          config.max_seq_len, config.rope_base)
+        self._gradient_checkpointing_enabled = False
+
+    def enable_gradient_checkpointing(self):
+        """Recompute each block in the backward pass (nanochat_gpt.py:318-322)."""
+        self._gradient_checkpointing_enabled = True
 
     def forward(self, input_ids, target_ids=None):
         B, T = input_ids.shape
@@ -134,7 +139,11 @@ class GPT(nn.Module):
         sin = DeviceArray(self.sin.ptr, (T, self.sin.shape[1]), "float32", base=self.sin)
         x = self.embeddings(input_ids)
         for block in self.blocks:
-            x = block(x, (cos, sin))
+            if self._gradient_checkpointing_enabled and self.training and x.requires_grad:
+                from .utils.checkpoint import checkpoint
+                x = checkpoint(block, x, (cos, sin))
+            else:
+                x = block(x, (cos, sin))
         x = norm(x)
         logits = self.lm_head(x)
         if target_ids is None:

@@ -368,3 +368,32 @@ def test_dataloader_device_staging_feeds_the_same_batches():
     a = train(host[:6])
     b = train(DataLoader(TokenLoader(toks, 64, virtual_length=24, seed=7), batch_size=4, num_workers=2, device=True))
     assert np.allclose(a, b, rtol=1e-5), (a, b)
+
+
+def test_gradient_checkpointing_gives_the_same_training_run():
+    """Blocks recomputed in the backward pass (utils/checkpoint.py, gpt2.py:349-365): same losses
+    and weights as the plain run (the recomputation repeats the same kernels on the same inputs)."""
+    cfg = og.GPT2Config(vocab_size=264, max_seq_len=128, embed_dim=128, mlp_ratio=4, num_blocks=4, num_heads=2)
+    params = og.init_params(cfg, seed=10)
+
+    def train(ckpt):
+        mt, model = build(cfg, {k: v.copy() for k, v in params.items()})
+        if ckpt:
+            model.enable_gradient_checkpointing()
+        opt = mt.optim.AdamW(groups(model), lr=1e-3, beta1=0.9, beta2=0.95)
+        rng = np.random.default_rng(11)
+        losses = []
+        for _ in range(3):
+            x, y = og.synthetic_batch(rng, 8, 128, 264)
+            loss = mt.nn.CrossEntropyLoss()(model(mt.Tensor(x)), mt.Tensor(y))
+            loss.backward()
+            opt.step()
+            opt.zero_grad()
+            losses.append(loss.item())
+        return losses, model.state_dict()
+
+    l0, w0 = train(False)
+    l1, w1 = train(True)
+    assert np.allclose(l0, l1, rtol=1e-6), (l0, l1)
+    for k in w0:
+        assert np.allclose(w0[k], w1[k], rtol=0, atol=1e-6), k
