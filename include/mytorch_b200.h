@@ -264,6 +264,24 @@ int mt_attn_bwd(const void* q, const void* k, const void* v, const void* o, cons
                 float scale, int causal, int dtype, void* stream);
 int mt_attn_force_simt(int on);
 
+/* The inference step: attention of q_len new query rows against a key/value cache, and the
+ * append of new rows to that cache (Cache.update and the cached branch of the attention module,
+ * gpt2_trainer/gpt2.py:29-86, :167-215; Sq != Skv as in fused_ops/flash_cross_attention.py).
+ * The cache is a ring [B, H, max_len, D] addressed with strides: row (pos0 + i) % max_len receives
+ * new row i, so once max_len rows are held the oldest is overwritten (the reference drops the
+ * oldest token by concatenating and slicing). mt_attn_decode attends to rows [0, kv_len) of the
+ * cache; causal_offset < 0 means every query sees every key (the reference's choice once the
+ * cache is non-empty), otherwise query i sees rows <= causal_offset + i (valid before the ring
+ * wraps). head_dim 64 or 128; cache rows 16-byte aligned. */
+int mt_attn_decode(const void* q, const void* k_cache, const void* v_cache, void* o,
+                   mt_strides3 sq, mt_strides3 skv, mt_strides3 so,
+                   int64_t batch, int64_t heads, int64_t q_len, int64_t kv_len, int64_t head_dim,
+                   float scale, int causal_offset, int dtype, void* stream);
+int mt_kv_append(const void* k_new, const void* v_new, void* k_cache, void* v_cache,
+                 mt_strides3 sk, mt_strides3 sv, mt_strides3 scache,
+                 int64_t batch, int64_t heads, int64_t n_new, int64_t pos0, int64_t max_len,
+                 int64_t head_dim, int dtype, void* stream);
+
 /* AdamW.step (mytorch/optim/optimizers.py:342-371), GradScaler.unscale_grads +
  * the inf/nan scan (mytorch/accelerate.py:71-89, 716-729), clip_grad_norm_
  * (mytorch/accelerate.py:799-856) and the master->half copy of

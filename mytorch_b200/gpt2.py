@@ -11,8 +11,10 @@ from dataclasses import dataclass
 
 import numpy as np
 
-from . import nn
+from . import _lib, nn
+from .array import DeviceArray, stream
 from .nn import functional as F
+from .tensor import Tensor
 
 
 @dataclass
@@ -31,6 +33,40 @@ class GPT2Config:          # gpt2_trainer/gpt2.py:12-27
     use_fused_ops: bool = True
 
 
+class Cache:
+    """Key/value cache of the inference step (gpt2_trainer/gpt2.py:29-86): per layer one
+    preallocated ring [B, H, max_seq_len, D] for keys and one for values. `update` appends the new
+    rows in place; when the ring is full the oldest row is overwritten, which is the reference's
+    drop-the-oldest policy without its concatenate and slice copies (attention does not depend on
+    the order in which the cached keys are stored)."""
+
+    def __init__(self, config):
+        self.max_seq_len = config.max_seq_len
+        self.key_cache = [None] * config.num_blocks
+        self.value_cache = [None] * config.num_blocks
+        self._appended = [0] * config.num_blocks
+
+    def __repr__(self):
+        return f"DynamicCache(Num_Layers: {len(self.key_cache)} | Cached Tokens: {self.get_seq_len()})"
+
+    def get_seq_len(self, layer_idx=0):
+        return min(self._appended[layer_idx], self.max_seq_len)
+
+    def update(self, k_ptr, v_ptr, strides, batch, heads, n_new, head_dim, dtype, layer_idx):
+        """Appends n_new rows read through (ptr, strides) and returns (keys, values, rows held)."""
+        if self.key_cache[layer_idx] is None:
+            shape = (batch, heads, self.max_seq_len, head_dim)
+            self.key_cache[layer_idx] = DeviceArray.empty(shape, dtype)
+            self.value_cache[layer_idx] = DeviceArray.empty(shape, dtype)
+        kc, vc = self.key_cache[layer_idx], self.value_cache[layer_idx]
+        assert kc.shape[0] == batch and kc.dtype == dtype, "cache was created for another batch size or dtype"
+        sc = _lib.Strides3(heads * self.max_seq_len * head_dim, self.max_seq_len * head_dim, head_dim)
+        _lib.kv_append(k_ptr, v_ptr, kc.ptr, vc.ptr, strides, strides, sc, batch, heads, n_new,
+                       self._appended[layer_idx] % self.max_seq_len, self.max_seq_len, head_dim, kc.code, stream())
+        self._appended[layer_idx] += n_new
+        return kc, vc, self.get_seq_len(layer_idx)
+
+
 class Embeddings(nn.Module):
     def __init__(self, config):
         super().__init__()
@@ -39,8 +75,16 @@ class Embeddings(nn.Module):
         self.position_embeddings = nn.Embedding(config.max_seq_len, config.embed_dim)
 
     def forward(self, input_ids, past_length=0):
-        assert past_length == 0, "the KV-cache path is outside the training step"
-        return F.token_position_embedding(input_ids, self.char_embeddings.weight, self.position_embeddings.weight)
+        if past_length == 0:
+            return F.token_position_embedding(input_ids, self.char_embeddings.weight, self.position_embeddings.weight)
+        # decoding: positions continue after the cached tokens (gpt2.py:115-117); inference only
+        B, T = input_ids.shape
+        E = self.config.embed_dim
+        assert past_length + T <= self.config.max_seq_len, "position table exhausted"
+        x = F.embedding(input_ids, self.char_embeddings.weight).data
+        pos = self.position_embeddings.weight.data.rows(past_length, past_length + T)
+        _lib.add_rowvec(x.ptr, pos.ptr, x.ptr, B, T * E, x.code, stream())
+        return Tensor(x)
 
 
 class Attention(nn.Module):
@@ -53,12 +97,35 @@ class Attention(nn.Module):
         self.out_proj = nn.Linear(self.embed_dim, self.embed_dim, bias=config.use_bias)
         self.proj_drop = nn.Dropout(config.attn_dropout_p)
 
-    def forward(self, x, residual=None):
+    def forward(self, x, residual=None, cache=None, layer_idx=None):
         qkv = self.qkv_proj(x)                                   # [B, T, 3E], per-head [q|k|v]
-        out = F.qkv_attention(qkv, self.num_heads, is_causal=True)  # [B, T, E]
+        if cache is not None and layer_idx is not None:
+            out = self._cached_attention(qkv, cache, layer_idx)
+        else:
+            out = F.qkv_attention(qkv, self.num_heads, is_causal=True)  # [B, T, E]
         # the block's skip connection is added in the projection's GEMM epilogue
         out = F.linear(out, self.out_proj.weight, self.out_proj.bias, residual=residual)
         return self.proj_drop(out)
+
+
+    def _cached_attention(self, qkv, cache, layer_idx):
+        """gpt2.py:179-215: the new keys/values join the cache; an empty cache means this call is
+        the prompt (causal attention among its tokens), otherwise the new queries see every cached
+        key. Inference only (no graph is recorded)."""
+        B, T, _ = qkv.shape
+        H, D, E = self.num_heads, self.head_dim, self.embed_dim
+        arr = qkv.data
+        sin = _lib.Strides3(T * 3 * E, 3 * D, 3 * E)               # q/k/v of head h start at h*3D (+0, +D, +2D)
+        past = cache.get_seq_len(layer_idx)
+        kc, vc, kv_len = cache.update(arr.ptr + D * arr.itemsize, arr.ptr + 2 * D * arr.itemsize, sin, B, H, T, D,
+                                      arr.dtype, layer_idx)
+        if past == 0:
+            return F.qkv_attention(qkv.detach(), H, is_causal=True)
+        out = DeviceArray.empty((B, T, E), arr.dtype)
+        sc = _lib.Strides3(H * cache.max_seq_len * D, cache.max_seq_len * D, D)
+        _lib.attn_decode(arr.ptr, kc.ptr, vc.ptr, out.ptr, sin, sc, _lib.Strides3(T * E, D, E), B, H, T, kv_len, D,
+                         float(D) ** -0.5, -1, arr.code, stream())
+        return Tensor(out)
 
 
 class FeedForward(nn.Module):
@@ -87,10 +154,10 @@ class TransformerBlock(nn.Module):
         self.feedforward = FeedForward(config)
         self.layernorm2 = nn.LayerNorm(config.embed_dim, weight=config.use_layernorm_weight, bias=config.use_bias)
 
-    def forward(self, x):
+    def forward(self, x, cache=None, layer_idx=None):
         # The skip connections stay separate adds: fusing them into the projection GEMM's
         # epilogue (residual=x) is supported but measured slower on B200 at these shapes.
-        x = x + self.attention(self.layernorm1(x))
+        x = x + self.attention(self.layernorm1(x), cache=cache, layer_idx=layer_idx)
         x = x + self.feedforward(self.layernorm2(x))
         return x
 
@@ -129,13 +196,46 @@ class GPT2(nn.Module):
         activations (gpt2.py:349-365)."""
         self._gradient_checkpointing_enabled = True
 
-    def forward(self, x):
+    def forward(self, x, cache=None):
+        """Logits; with a `Cache`, (logits, cache) as in gpt2.py:352-374."""
         from .utils.checkpoint import checkpoint
-        x = self.embeddings(x)
-        for block in self.blocks:
-            if self._gradient_checkpointing_enabled and self.training and x.requires_grad:
+        past_length = cache.get_seq_len() if cache is not None else 0
+        x = self.embeddings(x, past_length)
+        for layer_idx, block in enumerate(self.blocks):
+            if cache is not None:
+                x = block(x, cache=cache, layer_idx=layer_idx)
+            elif self._gradient_checkpointing_enabled and self.training and x.requires_grad:
                 x = checkpoint(block, x)
             else:
                 x = block(x)
         x = self.final_layer_norm(x)
-        return self.lm_head(x)
+        logits = self.lm_head(x)
+        return logits if cache is None else (logits, cache)
+
+    def generate(self, input_ids, max_new_tokens, temperature=1.0, top_k=None, use_cache=True, seed=None):
+        """Autoregressive sampling as in gpt2_trainer/inference_gpt2.py:137-174: the prompt fills
+        the cache, then one token per step; temperature-scaled softmax (optionally restricted to
+        the top_k logits), one draw per sequence on the host; temperature 0 takes the arg-max."""
+        from .tensor import no_grad
+        rng = np.random.default_rng(seed)
+        ids = np.asarray(input_ids.numpy() if isinstance(input_ids, Tensor) else input_ids, dtype=np.int32)
+        cache = Cache(self.config) if use_cache else None
+        feed = ids
+        with no_grad():
+            for _ in range(max_new_tokens):
+                out = self.forward(Tensor(feed), cache=cache)
+                logits = out[0] if use_cache else out
+                last = logits.numpy()[:, -1, :].astype(np.float64)
+                if temperature == 0:
+                    nxt = last.argmax(-1)
+                else:
+                    last = last / temperature
+                    if top_k is not None:
+                        kth = np.sort(last, -1)[:, -top_k][:, None]
+                        last = np.where(last < kth, -np.inf, last)
+                    p = np.exp(last - last.max(-1, keepdims=True))
+                    p /= p.sum(-1, keepdims=True)
+                    nxt = np.array([rng.choice(p.shape[-1], p=row) for row in p])
+                ids = np.concatenate([ids, nxt[:, None].astype(np.int32)], axis=1)
+                feed = ids[:, -1:] if use_cache else ids[:, -self.config.max_seq_len:]
+        return ids

@@ -413,3 +413,44 @@ def test_norm_backward_adds_into_existing_dx(mt, dtype, shape):
     _, RS2 = F.fused_rmsnorm_forward(X, None)
     F.fused_rmsnorm_backward(X, RS2, DY, None, dx_out=PREV2)
     close(PREV2.numpy(), want, 2 * TOL[dtype], "rmsnorm dx +=")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("D", [64, 128])
+def test_kv_cache_append_and_decode_attention(mt, dtype, D):
+    """mt_kv_append into a ring cache (including the wrap that overwrites the oldest rows) and
+    mt_attn_decode of a few query rows over it, against NumPy softmax attention."""
+    _lib = mt._lib
+    from mytorch_b200.array import stream
+    r = np.random.default_rng(15)
+    B, H, MAXL = 2, 3, 48
+    S3 = _lib.Strides3
+    kc = mt.DeviceArray.zeros((B, H, MAXL, D), dtype)
+    vc = mt.DeviceArray.zeros((B, H, MAXL, D), dtype)
+    sc = S3(H * MAXL * D, MAXL * D, D)
+    ring_k = np.zeros((B, H, MAXL, D)); ring_v = np.zeros((B, H, MAXL, D))
+    appended = 0
+    for n_new in (20, 1, 17, 1, 30):                 # 69 rows into a ring of 48
+        k = rnd(r.standard_normal((B, H, n_new, D)), dtype); v = rnd(r.standard_normal((B, H, n_new, D)), dtype)
+        K_, V_ = dev(mt, k, dtype), dev(mt, v, dtype)
+        sn = S3(H * n_new * D, n_new * D, D)
+        _lib.kv_append(K_.ptr, V_.ptr, kc.ptr, vc.ptr, sn, sn, sc, B, H, n_new, appended % MAXL, MAXL, D, kc.code, stream())
+        for i in range(n_new):
+            ring_k[:, :, (appended + i) % MAXL] = k[:, :, i]; ring_v[:, :, (appended + i) % MAXL] = v[:, :, i]
+        appended += n_new
+        kv_len = min(appended, MAXL)
+        close(kc.numpy(), ring_k, 1e-6, "ring k"); close(vc.numpy(), ring_v, 1e-6, "ring v")
+        for q_len, causal_offset in ((1, -1), (3, -1), (2, kv_len - 2)):
+            q = rnd(r.standard_normal((B, H, q_len, D)), dtype)
+            Q = dev(mt, q, dtype)
+            out = mt.DeviceArray.empty((B, H, q_len, D), dtype)
+            sq = S3(H * q_len * D, q_len * D, D)
+            _lib.attn_decode(Q.ptr, kc.ptr, vc.ptr, out.ptr, sq, sc, sq, B, H, q_len, kv_len, D, D ** -0.5,
+                             causal_offset, Q.code, stream())
+            s = np.einsum("bhqd,bhkd->bhqk", q, ring_k[:, :, :kv_len]) / np.sqrt(D)
+            if causal_offset >= 0:
+                for i in range(q_len):
+                    s[:, :, i, causal_offset + i + 1:] = -np.inf
+            p = np.exp(s - s.max(-1, keepdims=True)); p /= p.sum(-1, keepdims=True)
+            close(out.numpy(), np.einsum("bhqk,bhkd->bhqd", p, ring_v[:, :, :kv_len]), TOL[dtype], "decode attention")
+    no_device_flag(mt)

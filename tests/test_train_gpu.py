@@ -397,3 +397,32 @@ def test_gradient_checkpointing_gives_the_same_training_run():
     assert np.allclose(l0, l1, rtol=1e-6), (l0, l1)
     for k in w0:
         assert np.allclose(w0[k], w1[k], rtol=0, atol=1e-6), k
+
+
+def test_kv_cache_decoding_matches_the_full_forward():
+    """The inference step (gpt2.py:29-86, :167-215): prompt through the cache, then one token at
+    a time; at every step the last-position logits equal those of the oracle's full forward over
+    the whole prefix (fp32, 1e-4). Also two tokens in one step and greedy generate() with and
+    without the cache."""
+    import mytorch_b200 as mt
+    from mytorch_b200.gpt2 import Cache
+    cfg = og.GPT2Config(vocab_size=264, max_seq_len=64, embed_dim=128, mlp_ratio=4, num_blocks=2, num_heads=2)
+    params = og.init_params(cfg, seed=12)
+    _, model = build(cfg, params)
+    model.eval()
+    ids = np.random.default_rng(13).integers(0, 264, (3, 40)).astype(np.int32)
+    cache = Cache(model.config)
+    with mt.no_grad():
+        logits, cache = model(mt.Tensor(ids[:, :17]), cache=cache)
+        steps = [(17, logits.numpy()[:, -1])]
+        for n in range(17, 30):
+            logits, cache = model(mt.Tensor(ids[:, n:n + 1]), cache=cache)
+            steps.append((n + 1, logits.numpy()[:, -1]))
+        logits, cache = model(mt.Tensor(ids[:, 30:32]), cache=cache)     # two new tokens at once
+        assert cache.get_seq_len() == 32 and logits.shape == (3, 2, 264)
+    for n, got in steps:
+        want = og.forward(params, cfg, ids[:, :n])[1].reshape(3, n, -1)[:, -1]
+        assert np.abs(got.astype(np.float64) - want).max() <= 1e-4 * np.abs(want).max(), n
+    a = model.generate(ids[:, :8], 6, temperature=0, use_cache=True)
+    b = model.generate(ids[:, :8], 6, temperature=0, use_cache=False)
+    assert a.shape == (3, 14) and np.array_equal(a, b)
