@@ -250,14 +250,18 @@ def run_own(args):
             acc.comm.barrier()
         _lib.device_sync()
 
+    host_ms = [0.0]
+
     def timed(fn, steps):
         e0, e1 = C.c_void_p(), C.c_void_p()
         _lib.event_create(C.byref(e0)); _lib.event_create(C.byref(e1))
         barrier()
         _lib.event_record(e0, stream())
+        h0 = time.perf_counter()
         for _ in range(steps):
             fn()
         _lib.event_record(e1, stream())
+        host_ms[0] = (time.perf_counter() - h0) * 1e3 / steps    # time the host needs to queue one step
         _lib.event_sync(e1)
         barrier()
         ms = C.c_float()
@@ -275,6 +279,7 @@ def run_own(args):
     launches0 = _lib.launch_count()
     _lib.prof_begin(1)
     ms_total = timed(step_resident, args.steps)
+    host_queue_ms = host_ms[0]
     gemm_ms, gemm_n, gemm_flops = C.c_double(), C.c_int64(), C.c_double()
     _lib.prof_end(C.byref(gemm_ms), C.byref(gemm_n), C.byref(gemm_flops))
     launches = _lib.launch_count() - launches0
@@ -304,7 +309,7 @@ def run_own(args):
             "flops_per_token": ftok,
             "e2e": {"value": e2e_val, "unit": "tokens/s", "h2d_bytes_per_step": 2 * nbytes * accum,
                     "d2h_bytes_per_step": 4},
-            "gpu_launches": int(launches),
+            "gpu_launches": int(launches), "host_queue_ms_per_step": host_queue_ms,
             "roofline": {"kernel": "gemm_tc_kernel (tcgen05 GEMM, all launches of the timed region)", "bound": "tensor",
                          "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
                          "frac": (achieved / peaks["tflops"]) if achieved else None, "peak_source": peaks["source"],

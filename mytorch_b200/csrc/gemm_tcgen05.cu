@@ -177,10 +177,19 @@ __device__ __forceinline__ void stage_store(const CUtensorMap* map, const uint32
   ++sidx;
 }
 
+// Starts the copy of one 32-row x 128-byte slab of the aux operand into the warp's staging buffer
+// (one lane; the buffer's previous TMA store must have finished reading it).
+__device__ __forceinline__ void aux_slab_load(const CUtensorMap* tmAux, uint8_t* stage, uint32_t aux_bar, int x, int y) {
+  bulk_wait_read<0>();
+  mbar_expect_tx(aux_bar, 4096);
+  tma_load_2d(smem_u32(stage), tmAux, aux_bar, x, y);
+}
+
 template <int BN, typename TO>
-__device__ __forceinline__ void epilogue_staged(const GemmParams& P, const CUtensorMap* tmC, const CUtensorMap* tmPre,
-                                                uint32_t taddr, uint8_t* stage, int lane, int y0, int64_t n0,
-                                                bool add_bias, int& sidx, int col_begin) {
+__device__ __forceinline__ bool epilogue_staged(const GemmParams& P, const CUtensorMap* tmC, const CUtensorMap* tmPre,
+                                                const CUtensorMap* tmAux, uint32_t taddr, uint8_t* stage, int lane, int y0,
+                                                int64_t n0, bool add_bias, int& sidx, int col_begin, uint32_t aux_bar,
+                                                uint32_t& aux_phase, bool aux_prefetched, volatile int* abort_flag) {
   constexpr int CW = 128 / (int)sizeof(TO);   // accumulator columns per 128-byte staged row
   // This warp's half of the tile's columns is requested at once and waited for once.
   constexpr int GW = BN / 2;                  // columns per warp = per load group (128 or 64)
@@ -244,36 +253,37 @@ __device__ __forceinline__ void epilogue_staged(const GemmParams& P, const CUten
 #pragma unroll
         for (int e = 0; e < CW; ++e) rc[e] = __float_as_uint(act_apply_tc(__uint_as_float(rc[e]), act));
       }
-      if (P.aux_mode) {                       // uniform: combine with this thread's row of the aux operand
-        const int64_t row = (int64_t)y0 + lane;
-        if (row < P.M) {
-          const TO* arow = reinterpret_cast<const TO*>(P.aux) + row * P.ldc + col0;
-          constexpr int PER = 16 / (int)sizeof(TO);       // elements per 16-byte load
-#pragma unroll
-          for (int v = 0; v < CW / PER; ++v) {
-            if (col0 + v * PER >= P.N) break;
-            if (col0 + v * PER + PER <= P.N) {
-              Vec16<TO> a;
-              a.load(arow + v * PER);
-#pragma unroll
-              for (int u = 0; u < PER; ++u)
-                rc[v * PER + u] = __float_as_uint(aux_apply_tc(__uint_as_float(rc[v * PER + u]), a.get(u), P.aux_mode));
-            } else {
-              for (int u = 0; u < PER && col0 + v * PER + u < P.N; ++u)
-                rc[v * PER + u] = __float_as_uint(aux_apply_tc(__uint_as_float(rc[v * PER + u]), to_f(arow[v * PER + u]), P.aux_mode));
-            }
-          }
+      if (P.aux_mode) {
+        // uniform: combine with the matching slab of the aux operand. It comes through the
+        // staging buffer by TMA (coalesced, rows/columns past M/N read as zero); the first slab
+        // of a tile was requested before the accumulator wait, the others are requested here.
+        if (!(aux_prefetched && g0 == col_begin && cc == 0)) {
+          if (lane == 0) aux_slab_load(tmAux, stage, aux_bar, (int)col0, y0);
         }
+        if (!__all_sync(0xffffffffu, mbar_wait(aux_bar, aux_phase, abort_flag))) return false;
+        aux_phase ^= 1u;
+        constexpr int PER = 16 / (int)sizeof(TO);       // elements per 16-byte chunk
+#pragma unroll
+        for (int v = 0; v < 8; ++v) {
+          Vec16<TO> a;
+          a.load(reinterpret_cast<const TO*>(stage + lane * 128 + ((v ^ (lane & 7)) << 4)));
+#pragma unroll
+          for (int u = 0; u < PER; ++u)
+            rc[v * PER + u] = __float_as_uint(aux_apply_tc(__uint_as_float(rc[v * PER + u]), a.get(u), P.aux_mode));
+        }
+        __syncwarp();
       }
       stage_store<TO, CW>(tmC, rc, stage, lane, (int)col0, y0, P.accumulate != 0, sidx);
     }
   }
+  return true;
 }
 
 template <bool A_MN, bool B_MN, int BN, bool PAIR>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-               const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmPre, const GemmParams P) {
+               const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmPre,
+               const __grid_constant__ CUtensorMap tmAux, const GemmParams P) {
   using Cfg = GemmCfg<BN, PAIR>;
   // In a pair, rank 0 issues the MMAs and owns the operand-ready and
   // accumulator-free barriers; both CTAs walk the same list of 256 x BN tiles.
@@ -296,12 +306,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   auto acce_bar = [&](int b) { return bar0 + 8u * (2 * S + 2 + b); };
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  auto aux_bar = [&](int w) { return bar0 + 8u * (2 * S + 5 + w); };   // one per epilogue warp
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
     for (int b = 0; b < 2; ++b) { mbar_init(accf_bar(b), 1); mbar_init(acce_bar(b), PAIR ? 2 * kEpiWarps : kEpiWarps); }
+    for (int w = 0; w < kEpiWarps; ++w) mbar_init(aux_bar(w), 1);
     *abort_flag = 0;
     fence_barrier_init();
     fence_proxy_async();
@@ -420,6 +432,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int col_begin = ((warp - 2) >> 2) * (BN / 2);   // this warp's half of the tile's columns
     int it = 0;
     int sidx = 0;   // running count of staged stores of this warp (selects the staging buffer)
+    uint32_t aux_phase = 0;
+    const uint32_t my_aux_bar = aux_bar(warp - 2);
     bool ok = true;
     for (int t = worker; t < total_tiles && ok; t += workers, ++it) {
       const int mn = t % tiles_mn;
@@ -427,6 +441,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const int64_t m0 = (int64_t)(mn % P.tiles_m) * TM + (int64_t)rank * BM, n0 = (int64_t)(mn / P.tiles_m) * BN;
       const int buf = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
+      // the first aux slab of this tile travels while the accumulator is still being computed
+      const bool aux_pre = P.tma_store && P.aux_mode && !P.preact && (int)m0 + quarter * 32 < P.M && n0 + col_begin < P.N;
+      if (aux_pre && lane == 0)
+        aux_slab_load(&tmAux, epi_stage + (warp - 2) * 4096, my_aux_bar, (int)n0 + col_begin, (int)m0 + quarter * 32);
       // warp-uniform outcome: tcgen05.ld below needs all 32 lanes together
       if (!__all_sync(0xffffffffu, mbar_wait(accf_bar(buf), acc_phase, abort_flag))) { ok = false; break; }
       tc_fence_after();
@@ -436,9 +454,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         uint8_t* stage = epi_stage + (warp - 2) * 4096;
         const int y0 = (int)m0 + quarter * 32;
         if (y0 < P.M) {   // warp-uniform: a slab of 32 rows entirely past M has nothing to write
-          if (P.out_dtype == MT_F16) epilogue_staged<BN, __half>(P, &tmC, &tmPre, taddr, stage, lane, y0, n0, add_bias, sidx, col_begin);
-          else if (P.out_dtype == MT_BF16) epilogue_staged<BN, __nv_bfloat16>(P, &tmC, &tmPre, taddr, stage, lane, y0, n0, add_bias, sidx, col_begin);
-          else epilogue_staged<BN, float>(P, &tmC, &tmPre, taddr, stage, lane, y0, n0, add_bias, sidx, col_begin);
+          bool fine;
+          if (P.out_dtype == MT_F16) fine = epilogue_staged<BN, __half>(P, &tmC, &tmPre, &tmAux, taddr, stage, lane, y0, n0, add_bias, sidx, col_begin, my_aux_bar, aux_phase, aux_pre, abort_flag);
+          else if (P.out_dtype == MT_BF16) fine = epilogue_staged<BN, __nv_bfloat16>(P, &tmC, &tmPre, &tmAux, taddr, stage, lane, y0, n0, add_bias, sidx, col_begin, my_aux_bar, aux_phase, aux_pre, abort_flag);
+          else fine = epilogue_staged<BN, float>(P, &tmC, &tmPre, &tmAux, taddr, stage, lane, y0, n0, add_bias, sidx, col_begin, my_aux_bar, aux_phase, aux_pre, abort_flag);
+          if (!fine) { ok = false; break; }
         }
       } else
 #pragma unroll 1
@@ -592,7 +612,7 @@ bool gemm_tc_supported(const GemmArgs& g) {
 
 template <bool A_MN, bool B_MN, int BN>
 static int launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& tp,
-                     const GemmParams& P, int grid, cudaStream_t st) {
+                     const CUtensorMap& tx, const GemmParams& P, int grid, cudaStream_t st) {
   using Cfg = GemmCfg<BN, false>;
   static bool attr_set[16] = {false};
   int dev = 0;
@@ -602,7 +622,7 @@ static int launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const CUtenso
     MT_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
     attr_set[dev] = true;
   }
-  kern<<<grid, kGemmThreads, Cfg::kSmemBytes, st>>>(ta, tb, tc, tp, P);
+  kern<<<grid, kGemmThreads, Cfg::kSmemBytes, st>>>(ta, tb, tc, tp, tx, P);
   MT_LAUNCH_CHECK();
   return MT_OK;
 }
@@ -610,7 +630,7 @@ static int launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const CUtenso
 // CTA-pair variant: clusters of two CTAs; `pairs` = number of clusters to launch.
 template <bool A_MN, bool B_MN, int BN>
 static int launch_tc_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& tp,
-                          const GemmParams& P, int pairs, cudaStream_t st) {
+                          const CUtensorMap& tx, const GemmParams& P, int pairs, cudaStream_t st) {
   using Cfg = GemmCfg<BN, true>;
   static bool attr_set[16] = {false};
   int dev = 0;
@@ -633,7 +653,7 @@ static int launch_tc_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CU
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  MT_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, tp, P));
+  MT_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, tp, tx, P));
   return MT_OK;
 }
 
@@ -743,9 +763,10 @@ int gemm_tc(const GemmArgs& g, cudaStream_t st) {
 
   // Output through staged TMA stores when the tensor map can describe C (16-byte aligned base and
   // row pitch); read-modify-write of a half output keeps the direct path.
-  CUtensorMap tcm, tpm;
+  CUtensorMap tcm, tpm, txm;
   memset(&tcm, 0, sizeof(tcm));
   memset(&tpm, 0, sizeof(tpm));
+  memset(&txm, 0, sizeof(txm));
   const size_t osz = g.out_dtype == MT_F32 ? 4 : 2;
   P.tma_store = aligned16(g.C) && (g.ldc * osz) % 16 == 0 && (!g.preact || aligned16(g.preact)) &&
                 (!g.aux || aligned16(g.aux)) && !(g.accumulate && g.out_dtype != MT_F32);
@@ -757,14 +778,18 @@ int gemm_tc(const GemmArgs& g, cudaStream_t st) {
       rc = make_tmap_2d_typed(&tpm, g.preact, g.out_dtype, (uint64_t)g.N, (uint64_t)g.M, (uint64_t)g.ldc, cw, 32);
       if (rc) return rc;
     }
+    if (g.aux) {   // read slab by slab into the epilogue's staging buffers
+      rc = make_tmap_2d_typed(&txm, g.aux, g.out_dtype, (uint64_t)g.N, (uint64_t)g.M, (uint64_t)g.ldc, cw, 32);
+      if (rc) return rc;
+    }
   }
   ProfScope prof(PROF_GEMM, st, 2.0 * (double)g.M * (double)g.N * (double)g.K);
   const bool a_mn = g.trans_a != 0, b_mn = g.trans_b == 0;
 #define MT_TC(AM, BMN)                                                                                              \
-  (pair ? (bn == 256 ? launch_tc_pair<AM, BMN, 256>(ta, tb, tcm, tpm, P, grid, st)                                  \
-                     : launch_tc_pair<AM, BMN, 128>(ta, tb, tcm, tpm, P, grid, st))                                 \
-        : (bn == 256 ? launch_tc<AM, BMN, 256>(ta, tb, tcm, tpm, P, grid, st)                                       \
-                     : launch_tc<AM, BMN, 128>(ta, tb, tcm, tpm, P, grid, st)))
+  (pair ? (bn == 256 ? launch_tc_pair<AM, BMN, 256>(ta, tb, tcm, tpm, txm, P, grid, st)                                  \
+                     : launch_tc_pair<AM, BMN, 128>(ta, tb, tcm, tpm, txm, P, grid, st))                                 \
+        : (bn == 256 ? launch_tc<AM, BMN, 256>(ta, tb, tcm, tpm, txm, P, grid, st)                                       \
+                     : launch_tc<AM, BMN, 128>(ta, tb, tcm, tpm, txm, P, grid, st)))
   if (!a_mn && !b_mn) return MT_TC(false, false);
   if (!a_mn && b_mn) return MT_TC(false, true);
   if (a_mn && !b_mn) return MT_TC(true, false);

@@ -155,10 +155,9 @@ class TransformerBlock(nn.Module):
         self.layernorm2 = nn.LayerNorm(config.embed_dim, weight=config.use_layernorm_weight, bias=config.use_bias)
 
     def forward(self, x, cache=None, layer_idx=None):
-        # The skip connections stay separate adds: fusing them into the projection GEMM's
-        # epilogue (residual=x) is supported but measured slower on B200 at these shapes.
-        x = x + self.attention(self.layernorm1(x), cache=cache, layer_idx=layer_idx)
-        x = x + self.feedforward(self.layernorm2(x))
+        # The skip connections are added in the epilogue of each sublayer's last GEMM.
+        x = self.attention(self.layernorm1(x), residual=x, cache=cache, layer_idx=layer_idx)
+        x = self.feedforward(self.layernorm2(x), residual=x)
         return x
 
 
