@@ -31,6 +31,7 @@ typedef enum {
   MT_ERR_NCCL = 4, MT_ERR_TIMEOUT = 5, MT_ERR_UNSUPPORTED = 6, MT_ERR_DEVICE_FLAG = 7
 } mt_status;
 typedef enum { MT_ACT_NONE = 0, MT_ACT_GELU = 1, MT_ACT_RELU2 = 2, MT_ACT_RELU = 3 } mt_act;
+#define MT_ACT_STORE_GRAD 0x100   /* mt_gemm / mt_gemm_ex only, see there */
 
 /* ---- runtime: device arrays, copies, streams, events ----------------------
  * Replaces the CuPy allocator / cp.asarray / cp.asnumpy / cp.cuda.Event used
@@ -229,6 +230,11 @@ int mt_gemm(const void* A, const void* B, void* C, void* preact, const void* bia
  *               mytorch/nn/functional/layers/linear.py:193-221 + activations.py:182)
  *   aux_mode 3: C = result * 2*relu(aux)    (backward of relu_squared)
  *   aux_mode 4: C = result * (aux > 0)      (backward of relu)
+ *   aux_mode 5: C = result * aux            (aux already holds a derivative, see below)
+ * `act` may be OR'ed with MT_ACT_STORE_GRAD: the second output (`preact`) then receives the
+ * activation's derivative at the pre-activation, act'(A*B + bias), instead of the
+ * pre-activation itself - what the backward pass multiplies by (aux_mode 5), computed where the
+ * tanh of the forward activation is already at hand.
  * aux_mode 0 / aux NULL is mt_gemm. Not combinable with accumulate = 2. */
 int mt_gemm_ex(const void* A, const void* B, void* C, void* preact, const void* bias,
                const void* aux, int aux_mode, int64_t M, int64_t N, int64_t K,

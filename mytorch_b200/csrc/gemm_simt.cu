@@ -73,8 +73,8 @@ gemm_simt_kernel(const TI* __restrict__ A, const TI* __restrict__ B, TO* __restr
       if (gn >= N) continue;
       float v = alpha * acc[i][j];
       if (bias) v += to_f(bias[gn]);
-      if (preact) preact[gm * ldc + gn] = from_f<TO>(v);
-      v = act_apply(v, act);
+      if (preact) preact[gm * ldc + gn] = from_f<TO>((act & kActStoreGrad) ? act_grad(v, act) : v);
+      v = act_apply(v, act & 0xff);
       if (aux_mode) v = aux_apply(v, to_f(aux[gm * ldc + gn]), aux_mode);
       if (accumulate) v += to_f(C[gm * ldc + gn]);
       C[gm * ldc + gn] = from_f<TO>(v);

@@ -78,7 +78,54 @@ __device__ __forceinline__ float aux_apply_tc(float x, float a, int mode) {
     }
     case 3: return x * 2.f * fmaxf(a, 0.f);
     case 4: return a > 0.f ? x : 0.f;
+    case 5: return x * a;
     default: return x;
+  }
+}
+
+// tanh-GELU and its derivative on two values at once in half precision (fp16 outputs only: the
+// result is rounded to half anyway). The polynomial, the tanh (one MUFU op for the pair) and the
+// products run on packed half2 instructions, two to three times fewer issue slots than fp32.
+// The argument of the tanh path is clamped to [-16, 16], where tanh has long saturated, so x*x
+// cannot overflow and the derivative of a huge pre-activation is exactly 1 or 0, never NaN.
+__device__ __forceinline__ __half2 tanh_h2(__half2 x) {
+  uint32_t r, a = *reinterpret_cast<uint32_t*>(&x);
+  asm("tanh.approx.f16x2 %0, %1;" : "=r"(r) : "r"(a));
+  return *reinterpret_cast<__half2*>(&r);
+}
+template <bool WITH_GRAD>
+__device__ __forceinline__ void gelu_h2(float x0, float x1, uint32_t& y_bits, uint32_t& dy_bits) {
+  const __half2 one = __float2half2_rn(1.f), half = __float2half2_rn(0.5f);
+  const __half2 k = __float2half2_rn(0.7978845608f), kc = __float2half2_rn(0.7978845608f * 0.044715f);
+  const __half2 x = __floats2half2_rn(x0, x1);
+  const __half2 xc = __hmax2(__hmin2(x, __float2half2_rn(16.f)), __float2half2_rn(-16.f));
+  const __half2 x2 = __hmul2(xc, xc);
+  const __half2 t = tanh_h2(__hmul2(xc, __hfma2(kc, x2, k)));
+  const __half2 opt = __hadd2(one, t);
+  const __half2 y = __hmul2(__hmul2(half, x), opt);
+  y_bits = *reinterpret_cast<const uint32_t*>(&y);
+  if (WITH_GRAD) {
+    const __half2 k3c = __float2half2_rn(3.f * 0.7978845608f * 0.044715f);
+    const __half2 s = __hfma2(__hneg2(t), t, one);                    // 1 - t^2
+    const __half2 r = __hmul2(__hmul2(xc, __hfma2(k3c, x2, k)), s);   // x (k + 3kc x^2)(1 - t^2)
+    const __half2 dy = __hmul2(half, __hadd2(opt, r));
+    dy_bits = *reinterpret_cast<const uint32_t*>(&dy);
+  }
+}
+
+// Activation and its derivative of one pre-activation, sharing the tanh.
+__device__ __forceinline__ void act_both_tc(float x, int act, float& y, float& dy) {
+  switch (act) {
+    case MT_ACT_GELU: {
+      const float x2 = x * x;
+      const float t = tanh_fast(0.7978845608f * (x + 0.044715f * x2 * x));
+      y = 0.5f * x * (1.f + t);
+      dy = 0.5f * (1.f + t + x * (1.f - t * t) * 0.7978845608f * (1.f + 3.f * 0.044715f * x2));
+      return;
+    }
+    case MT_ACT_RELU2: { const float r = fmaxf(x, 0.f); y = r * r; dy = 2.f * r; return; }
+    case MT_ACT_RELU: y = fmaxf(x, 0.f); dy = x > 0.f ? 1.f : 0.f; return;
+    default: y = x; dy = 1.f; return;
   }
 }
 
@@ -194,7 +241,8 @@ __device__ __forceinline__ bool epilogue_staged(const GemmParams& P, const CUten
   // This warp's half of the tile's columns is requested at once and waited for once.
   constexpr int GW = BN / 2;                  // columns per warp = per load group (128 or 64)
   const float alpha = P.alpha;
-  const int act = P.act;
+  const int act = P.act & 0xff;
+  const bool store_grad = (P.act & kActStoreGrad) != 0;
 #pragma unroll 1
   for (int g0 = col_begin; g0 < col_begin + GW; g0 += GW) {
     if (n0 + g0 >= P.N) break;                // warp-uniform
@@ -248,10 +296,64 @@ __device__ __forceinline__ bool epilogue_staged(const GemmParams& P, const CUten
           for (int u = 0; u < 8; ++u) rc[e8 + u] = __float_as_uint(__uint_as_float(rc[e8 + u]) + bv[u]);
         }
       }
-      if (P.preact) stage_store<TO, CW>(tmPre, rc, stage, lane, (int)col0, y0, false, sidx);
-      if (act != MT_ACT_NONE) {
+      if (P.preact && store_grad) {
+        // the second output receives act'(x): computed together with act(x) (one tanh), packed
+        // into the staging rows eight columns at a time, while rc is overwritten with act(x)
+        if (lane == 0) bulk_wait_read<0>();
+        __syncwarp();
+        constexpr int PER = 16 / (int)sizeof(TO);
+        constexpr bool kHalfMath = std::is_same<TO, __half>::value;
 #pragma unroll
-        for (int e = 0; e < CW; ++e) rc[e] = __float_as_uint(act_apply_tc(__uint_as_float(rc[e]), act));
+        for (int v = 0; v < 8; ++v) {
+          if (kHalfMath && act == MT_ACT_GELU) {
+            // rc keeps gelu(x) as the exact float value of the half result: packing it again
+            // for the output store below is lossless
+            uint32_t yb[4], db[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              gelu_h2<true>(__uint_as_float(rc[v * 8 + 2 * u]), __uint_as_float(rc[v * 8 + 2 * u + 1]), yb[u], db[u]);
+              const __half2 yh = *reinterpret_cast<const __half2*>(&yb[u]);
+              rc[v * 8 + 2 * u] = __float_as_uint(__low2float(yh));
+              rc[v * 8 + 2 * u + 1] = __float_as_uint(__high2float(yh));
+            }
+            *reinterpret_cast<uint4*>(stage + lane * 128 + ((v ^ (lane & 7)) << 4)) = make_uint4(db[0], db[1], db[2], db[3]);
+            continue;
+          }
+          float d[PER];
+#pragma unroll
+          for (int u = 0; u < PER; ++u) {
+            float yv;
+            act_both_tc(__uint_as_float(rc[v * PER + u]), act, yv, d[u]);
+            rc[v * PER + u] = __float_as_uint(yv);
+          }
+          uint4 q;
+          if (sizeof(TO) == 4) {
+            q = make_uint4(__float_as_uint(d[0]), __float_as_uint(d[1]), __float_as_uint(d[2]), __float_as_uint(d[3]));
+          } else {
+            q.x = pack_pair<TO>(d[0], d[1]); q.y = pack_pair<TO>(d[2 % PER], d[3 % PER]);
+            q.z = pack_pair<TO>(d[4 % PER], d[5 % PER]); q.w = pack_pair<TO>(d[6 % PER], d[7 % PER]);
+          }
+          *reinterpret_cast<uint4*>(stage + lane * 128 + ((v ^ (lane & 7)) << 4)) = q;
+        }
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) { tma_store_2d(tmPre, smem_u32(stage), (int)col0, y0); bulk_commit(); }
+        ++sidx;
+      } else {
+        if (P.preact) stage_store<TO, CW>(tmPre, rc, stage, lane, (int)col0, y0, false, sidx);
+        if (std::is_same<TO, __half>::value && act == MT_ACT_GELU) {
+#pragma unroll
+          for (int e = 0; e < CW; e += 2) {
+            uint32_t yb, unused;
+            gelu_h2<false>(__uint_as_float(rc[e]), __uint_as_float(rc[e + 1]), yb, unused);
+            const __half2 yh = *reinterpret_cast<const __half2*>(&yb);
+            rc[e] = __float_as_uint(__low2float(yh));
+            rc[e + 1] = __float_as_uint(__high2float(yh));
+          }
+        } else if (act != MT_ACT_NONE) {
+#pragma unroll
+          for (int e = 0; e < CW; ++e) rc[e] = __float_as_uint(act_apply_tc(__uint_as_float(rc[e]), act));
+        }
       }
       if (P.aux_mode) {
         // uniform: combine with the matching slab of the aux operand. It comes through the
@@ -484,13 +586,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             }
             const int64_t off = row * P.ldc + col;
             if (P.preact) {
-              if (P.out_dtype == MT_F16) store8(reinterpret_cast<__half*>(P.preact) + off, v, n_valid, P.vec_store, 0);
-              else if (P.out_dtype == MT_BF16) store8(reinterpret_cast<__nv_bfloat16*>(P.preact) + off, v, n_valid, P.vec_store, 0);
-              else store8(reinterpret_cast<float*>(P.preact) + off, v, n_valid, P.vec_store, 0);
-            }
-            if (P.act != MT_ACT_NONE) {
+              float pv[8];
 #pragma unroll
-              for (int e = 0; e < 8; ++e) v[e] = act_apply_tc(v[e], P.act);
+              for (int e = 0; e < 8; ++e) pv[e] = (P.act & kActStoreGrad) ? act_grad(v[e], P.act) : v[e];
+              if (P.out_dtype == MT_F16) store8(reinterpret_cast<__half*>(P.preact) + off, pv, n_valid, P.vec_store, 0);
+              else if (P.out_dtype == MT_BF16) store8(reinterpret_cast<__nv_bfloat16*>(P.preact) + off, pv, n_valid, P.vec_store, 0);
+              else store8(reinterpret_cast<float*>(P.preact) + off, pv, n_valid, P.vec_store, 0);
+            }
+            if ((P.act & 0xff) != MT_ACT_NONE) {
+#pragma unroll
+              for (int e = 0; e < 8; ++e) v[e] = act_apply_tc(v[e], P.act & 0xff);
             }
             if (P.aux_mode) {
               for (int e = 0; e < n_valid; ++e) {
@@ -827,13 +932,15 @@ int mt_gemm(const void* A, const void* B, void* C, void* preact, const void* bia
 int mt_gemm_ex(const void* A, const void* B, void* C, void* preact, const void* bias, const void* aux, int aux_mode,
                int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int trans_a, int trans_b,
                int in_dtype, int out_dtype, int act, float alpha, int accumulate, void* stream) {
-  MT_REQUIRE((aux != nullptr) == (aux_mode != 0) && aux_mode >= 0 && aux_mode <= 4, "gemm: aux operand and aux_mode must be given together");
+  MT_REQUIRE((aux != nullptr) == (aux_mode != 0) && aux_mode >= 0 && aux_mode <= 5, "gemm: aux operand and aux_mode must be given together");
+  MT_REQUIRE((act & ~0x1ff) == 0 && (act & 0xff) <= MT_ACT_RELU, "gemm: unknown activation");
+  MT_REQUIRE(!(act & 0x100) || preact, "gemm: storing the activation's derivative needs the second output");
   MT_REQUIRE(!(aux_mode && accumulate == 2), "gemm: an aux operand cannot be combined with split-K accumulation");
   MT_REQUIRE(A && B && C && M >= 0 && N >= 0 && K >= 0, "gemm: bad arguments");
   MT_REQUIRE(lda >= (trans_a ? M : K) && ldb >= (trans_b ? K : N) && ldc >= N, "gemm: leading dimension too small");
   MT_REQUIRE(accumulate >= 0 && accumulate <= 2, "gemm: bad accumulate mode");
   MT_REQUIRE(accumulate != 2 || out_dtype == MT_F32, "gemm: atomic accumulation needs an fp32 output");
-  MT_REQUIRE(accumulate != 2 || (act == MT_ACT_NONE && !preact), "gemm: split-K accumulation cannot apply an activation");
+  MT_REQUIRE(accumulate != 2 || ((act & 0xff) == MT_ACT_NONE && !preact), "gemm: split-K accumulation cannot apply an activation");
   if (M == 0 || N == 0) return MT_OK;
   GemmArgs g{A, B, C, preact, bias, M, N, K, lda, ldb, ldc, trans_a, trans_b, in_dtype, out_dtype, act, alpha, accumulate};
   g.aux = aux;

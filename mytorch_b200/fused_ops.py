@@ -43,7 +43,9 @@ def _check_float(*arrs):
 def gemm(a, b, trans_a=False, trans_b=False, out=None, bias=None, act=None, preact=False,
          out_dtype=None, alpha=1.0, accumulate=0, aux=None, aux_mode=0):
     """out = combine(act(alpha * op(a) @ op(b) + bias), aux); see mt_gemm / mt_gemm_ex in
-    the C header (aux_mode 1 adds aux, 2/3/4 multiply by gelu'/relu2'/relu' of aux)."""
+    the C header (aux_mode 1 adds aux, 2/3/4 multiply by gelu'/relu2'/relu' of aux, 5 by aux).
+    preact=True also returns the pre-activation; preact="grad" returns the activation's
+    derivative at the pre-activation instead."""
     a, b = _A(a), _A(b)
     dt = _check_float(a, b, bias)
     assert a.ndim == 2 and b.ndim == 2
@@ -62,7 +64,7 @@ def gemm(a, b, trans_a=False, trans_b=False, out=None, bias=None, act=None, prea
         assert aux.size == M * N and aux.dtype == out.dtype, "aux must be [M,N] in the output dtype"
     _lib.gemm_ex(a.ptr, b.ptr, out.ptr, _ptr(pre), _ptr(bias), _ptr(aux), int(aux_mode if aux is not None else 0),
                  M, N, K, a.shape[1], b.shape[1], N, int(trans_a), int(trans_b), a.code, out.code,
-                 _lib.ACT[act], float(alpha), int(accumulate), stream())
+                 _lib.ACT[act] | (0x100 if preact == "grad" else 0), float(alpha), int(accumulate), stream())
     return (out, pre) if preact else out
 
 

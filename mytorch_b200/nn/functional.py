@@ -75,14 +75,15 @@ def linear(x, weight, bias=None, auto=False, fused=True, act_func=None, residual
 def mlp(x, w1, w2, act_func="gelu", residual=None):
     """act(x @ w1^T) @ w2^T (+ residual): the FeedForward of a block
     (gpt2_trainer/gpt2.py:237-283, bias-free form) as one autograd node. The
-    activation is applied in the first GEMM's epilogue; in the backward its
-    derivative is applied in the epilogue of the dY @ W2 GEMM (mt_gemm_ex aux_mode
-    2-4), which reads the saved pre-activation slab by slab through TMA: measured
-    on B200 at 16384x3072x768, 107 us against 64 + 64 us for the two kernels."""
+    activation is applied in the first GEMM's epilogue, which saves the
+    activation's derivative (same tanh) instead of the pre-activation; the backward
+    multiplies by it in the epilogue of the dY @ W2 GEMM (mt_gemm_ex aux_mode 5,
+    the saved tensor read slab by slab through TMA), so the backward of the
+    activation costs no kernel and no transcendental."""
     x2 = _flat2d(x.data)
     graph = _needs_graph(x, w1, w2, residual)
     if graph:
-        h, u = K.gemm(x2, w1.data, trans_b=True, act=act_func, preact=True)
+        h, u = K.gemm(x2, w1.data, trans_b=True, act=act_func, preact="grad")      # u = act'(x @ w1^T)
     else:
         h, u = K.gemm(x2, w1.data, trans_b=True, act=act_func), None
     y2 = K.gemm(h, w2.data, trans_b=True, aux=None if residual is None else _flat2d(residual.data), aux_mode=1)
@@ -94,7 +95,7 @@ def mlp(x, w1, w2, act_func="gelu", residual=None):
             g2 = _flat2d(g)
             if w2.requires_grad:
                 _param_grad_gemm(g2, h, w2)
-            du = K.gemm(g2, w2.data, aux=u, aux_mode=_lib.ACT_BWD_AUX[act_func])      # (dy @ w2) * act'(u), one kernel
+            du = K.gemm(g2, w2.data, aux=u, aux_mode=5)                                # (dy @ w2) * act'(.), one kernel
             if w1.requires_grad:
                 _param_grad_gemm(du, x2, w1)
             if x.requires_grad:

@@ -454,3 +454,32 @@ def test_kv_cache_append_and_decode_attention(mt, dtype, D):
             p = np.exp(s - s.max(-1, keepdims=True)); p /= p.sum(-1, keepdims=True)
             close(out.numpy(), np.einsum("bhqk,bhkd->bhqd", p, ring_v[:, :, :kv_len]), TOL[dtype], "decode attention")
     no_device_flag(mt)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("act,grad", [("gelu", lambda v: O.gelu_bwd(v, np.ones_like(v))),
+                                      ("relu_squared", lambda v: O.relu2_bwd(v, np.ones_like(v)))])
+@pytest.mark.parametrize("M,N,K", [(300, 264, 200), (513, 136, 72), (45, 50, 24)])
+def test_gemm_stores_activation_derivative_and_multiplies_by_it(mt, dtype, act, grad, M, N, K):
+    """MT_ACT_STORE_GRAD: the second output of the forward GEMM holds act'(x W^T + b); aux_mode 5
+    multiplies a later GEMM's result by it - together the backward of the activation."""
+    F = mt.fused_ops
+    r = np.random.default_rng(16)
+    x, w, b = rnd(r.standard_normal((M, K)), dtype), rnd(r.standard_normal((N, K)) * 0.2, dtype), rnd(r.standard_normal(N), dtype)
+    pre = x.astype(np.float64) @ w.T + b
+    X, W, B = dev(mt, x, dtype), dev(mt, w, dtype), dev(mt, b, dtype)
+    fwd = {"gelu": O.gelu_fwd, "relu_squared": O.relu2_fwd}[act]
+    t = TOL[dtype]
+    for policy in (1, 2):
+        mt._lib.gemm_tile_policy(policy)
+        try:
+            out, d = F.gemm(X, W, trans_b=True, bias=B, act=act, preact="grad")
+        finally:
+            mt._lib.gemm_tile_policy(0)
+        close(out.numpy(), fwd(pre), t, f"{act} (policy {policy})")
+        close(d.numpy(), grad(pre), 2 * t, f"{act}' (policy {policy})")
+    dy, w2 = rnd(r.standard_normal((M, 40)), dtype), rnd(r.standard_normal((40, N)) * 0.3, dtype)
+    dsaved = rnd(d.numpy(), dtype)
+    got = F.gemm(dev(mt, dy, dtype), dev(mt, w2, dtype), aux=dev(mt, dsaved, dtype), aux_mode=5)
+    close(got.numpy(), (dy.astype(np.float64) @ w2) * dsaved, t, "result * saved derivative")
+    no_device_flag(mt)
