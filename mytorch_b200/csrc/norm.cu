@@ -222,6 +222,98 @@ norm_bwd_warp(const T* __restrict__ x, const float* __restrict__ mean, const flo
   }
 }
 
+// Row-team variant for rows of exactly WPR*32 16-byte vectors (768 half columns = 3 warps, 1280 =
+// 5): a block is one team, a thread owns ONE vector (8 half columns) of every row the block
+// visits, so its dgamma/dbeta accumulators are 16 registers instead of the 48-64 of the
+// warp-per-row kernel and more warps fit an SM. Two rows are in flight per thread; the row
+// sums of the team's warps meet in shared memory (one __syncthreads per two rows, double
+// buffered). The block's column partials need no further reduction: thread t owns columns
+// [t*VN, t*VN+VN). Same partial layout as norm_bwd_warp.
+template <typename T, int WPR, bool RMS>
+__global__ void __launch_bounds__(WPR * 32, 768 / (WPR * 32))
+norm_bwd_team(const T* __restrict__ x, const float* __restrict__ mean, const float* __restrict__ rstd_in,
+              const T* __restrict__ dy, const T* __restrict__ gamma, T* __restrict__ dx,
+              float* __restrict__ partial, int64_t rows, bool want_dg, bool want_db, bool dx_acc) {
+  constexpr int VN = Vec16<T>::N;
+  constexpr int RB = 2;
+  constexpr int cols = WPR * 32 * VN;
+  __shared__ float part[2][RB][WPR][2];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int c0 = threadIdx.x * VN;
+  float dg[VN], db[VN];
+#pragma unroll
+  for (int e = 0; e < VN; ++e) { dg[e] = 0.f; db[e] = 0.f; }
+  Vec16<T> gv;
+  if (gamma) gv.load(gamma + c0);
+  const float inv_cols = 1.f / cols;
+  int it = 0;
+  for (int64_t r0 = (int64_t)blockIdx.x * RB; r0 < rows; r0 += (int64_t)gridDim.x * RB, ++it) {
+    Vec16<T> xv[RB], dv[RB];
+    float mu[RB], rs[RB];
+#pragma unroll
+    for (int j = 0; j < RB; ++j) {
+      const int64_t row = r0 + j < rows ? r0 + j : rows - 1;   // clamped: rows past the end are recomputed, not stored
+      xv[j].load(x + row * cols + c0);
+      dv[j].load(dy + row * cols + c0);
+      mu[j] = RMS ? 0.f : mean[row];
+      rs[j] = rstd_in[row];
+    }
+    float (*pp)[WPR][2] = part[it & 1];
+#pragma unroll
+    for (int j = 0; j < RB; ++j) {
+      float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+      for (int e = 0; e < VN; ++e) {
+        const float xh = (xv[j].get(e) - mu[j]) * rs[j];
+        const float d = dv[j].get(e);
+        const float dxh = gamma ? d * gv.get(e) : d;
+        s1 += dxh;
+        s2 += dxh * xh;
+        if (r0 + j < rows) { dg[e] += d * xh; db[e] += d; }
+      }
+      s1 = warp_sum(s1);
+      s2 = warp_sum(s2);
+      if (lane == 0) { pp[j][warp][0] = s1; pp[j][warp][1] = s2; }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < RB; ++j) {
+      if (r0 + j >= rows) break;
+      float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+      for (int w = 0; w < WPR; ++w) { s1 += pp[j][w][0]; s2 += pp[j][w][1]; }
+      s1 *= inv_cols;
+      s2 *= inv_cols;
+      if (RMS) s1 = 0.f;
+      Vec16<T> o;
+#pragma unroll
+      for (int e = 0; e < VN; ++e) {
+        const float xh = (xv[j].get(e) - mu[j]) * rs[j];
+        const float dxh = gamma ? dv[j].get(e) * gv.get(e) : dv[j].get(e);
+        o.set(e, rs[j] * (dxh - s1 - xh * s2));
+      }
+      T* dxr = dx + (r0 + j) * cols + c0;
+      if (dx_acc) {
+        Vec16<T> old;
+        old.load(dxr);
+#pragma unroll
+        for (int e = 0; e < VN; ++e) o.set(e, o.get(e) + old.get(e));
+      }
+      o.store(dxr);
+    }
+  }
+  if (want_dg) {
+    float* pg = partial + (size_t)blockIdx.x * 2 * cols + c0;
+#pragma unroll
+    for (int e = 0; e < VN; ++e) pg[e] = dg[e];
+  }
+  if (want_db) {
+    float* pb = partial + (size_t)blockIdx.x * 2 * cols + cols + c0;
+#pragma unroll
+    for (int e = 0; e < VN; ++e) pb[e] = db[e];
+  }
+}
+
 template <typename T, bool RMS>
 __global__ void __launch_bounds__(256)
 norm_bwd_block(const T* __restrict__ x, const float* __restrict__ mean, const float* __restrict__ rstd_in,
@@ -341,6 +433,27 @@ static int norm_bwd_launch(const void* x, const float* mean, const float* rstd, 
   if (rows == 0) return MT_OK;
   bool vec = cols % VN == 0 && aligned16(x) && aligned16(dy) && aligned16(dx) &&
              (!gamma || aligned16(gamma)) && cols / VN <= 32 * 4;
+  const int nvec_all = (int)(cols / VN);
+  if (vec && sizeof(T) == 2 && cols % (32 * VN) == 0 && nvec_all / 32 >= 2 && nvec_all / 32 <= 5) {
+    // rows of 2..5 warps of vectors (512..1280 half columns): one thread per vector
+    const int wpr = nvec_all / 32;
+    const int per_sm = 768 / (wpr * 32);      // resident blocks (the kernel is compiled for this occupancy)
+    int64_t want = (rows + 1) / 2;
+    int grid = (int)(want < (int64_t)sm_count() * per_sm ? want : (int64_t)sm_count() * per_sm);
+    bool wg = dgamma != nullptr, wb = dbeta != nullptr;
+    TempBuf part((wg || wb) ? (size_t)grid * 2 * cols * sizeof(float) : 0, st);
+    if (!part.ok()) return MT_ERR_CUDA;
+#define MT_TEAM(W) norm_bwd_team<T, W, RMS><<<grid, W * 32, 0, st>>>(xp, mean, rstd, dyp, gp, dxp, (float*)part.ptr, rows, wg, wb, (accumulate & 2) != 0)
+    if (wpr == 2) MT_TEAM(2); else if (wpr == 3) MT_TEAM(3); else if (wpr == 4) MT_TEAM(4); else MT_TEAM(5);
+#undef MT_TEAM
+    MT_LAUNCH_CHECK();
+    if (wg || wb) {
+      norm_bwd_finalize<<<(unsigned)((cols + 31) / 32), 32 * kFinalizeGroups, 0, st>>>((const float*)part.ptr, grid, (int)cols,
+                                                                                     dgamma, dbeta, accumulate & 1);
+      MT_LAUNCH_CHECK();
+    }
+    return MT_OK;
+  }
   if (vec) {
     int nvec = (int)(cols / VN);
     int64_t want = (rows + kWarpsPerBlock - 1) / kWarpsPerBlock;
