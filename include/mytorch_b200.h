@@ -154,6 +154,19 @@ int mt_ce_fwd(const void* logits, const int32_t* labels, float* loss, float* lse
 int mt_ce_bwd(const void* logits, const int32_t* labels, const float* lse, void* dlogits,
               float scale_host, const float* scale_dev, const float* count_dev,
               int64_t rows, int64_t classes, int64_t ld, float softcap, int dtype, void* stream);
+/* Forward and gradient of the mean cross entropy in one pass over the logits (no reference
+ * counterpart as one call; the math is fused_cross_entropy_forward followed by
+ * fused_cross_entropy_backward, fused_ops/cross_entropy.py:263,324): on return `logits` holds
+ * (softmax - onehot) * scale_host * scale_dev[0] / n_valid (0 on ignored rows), loss/lse/loss_sum/
+ * valid_count/loss_mean as mt_ce_fwd. The upstream gradient of the mean loss has to be known at
+ * this point (scale_dev, a device scalar; NULL = 1); mt_scale_ratio corrects the result if another
+ * value arrives later. Each block reads its row twice back to back, so DRAM sees one read and one
+ * write of the logits. */
+int mt_ce_fwd_grad(void* logits, const int32_t* labels, float* loss, float* lse, float* loss_sum,
+                   float* valid_count, float* loss_mean, float scale_host, const float* scale_dev,
+                   int64_t rows, int64_t classes, int64_t ld, float softcap, int dtype, void* stream);
+/* x[i] *= num[0] / den[0], both device scalars. */
+int mt_scale_ratio(void* x, int64_t n, const float* num, const float* den, int dtype, void* stream);
 
 /* Cross entropy over the vocabulary IN CHUNKS, for a fused lm_head + loss that
  * never holds the [rows, vocab] logits: the caller computes the logits of one

@@ -93,6 +93,8 @@ _SIG = {
     "mt_softmax_bwd": [_p, _p, _p, _i64, _i64, _i, _p],
     "mt_ce_fwd": [_p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _f, _i, _p],
     "mt_ce_bwd": [_p, _p, _p, _p, _f, _p, _p, _i64, _i64, _i64, _f, _i, _p],
+    "mt_ce_fwd_grad": [_p, _p, _p, _p, _p, _p, _p, _f, _p, _i64, _i64, _i64, _f, _i, _p],
+    "mt_scale_ratio": [_p, _i64, _p, _p, _i, _p],
     "mt_ce_chunk_fwd": [_p, _p, _p, _p, _i64, _i64, _i64, _i64, _f, _i, _p],
     "mt_ce_chunk_finish": [_p, _p, _p, _p, _p, _p, _p, _i64, _p],
     "mt_ce_chunk_bwd": [_p, _p, _p, _p, _f, _p, _p, _i64, _i64, _i64, _i64, _f, _i, _p],

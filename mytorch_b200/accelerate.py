@@ -161,6 +161,9 @@ class Accelerator:
         dynamic = bool(self.mixed_precision) and half_dtype == "float16"
         self.scaler = GradScaler(init_scale=2.0 ** 16 if dynamic else 1.0, dynamic=dynamic,
                                  accum_steps=gradient_accumulation_steps)
+        # backward() hands this device scalar to loss.backward(); a loss that computes its gradient
+        # in the forward pass (F.cross_entropy(..., fused_backward=True)) folds it in right there
+        Tensor.loss_grad_hint = self.scaler.scale_dev
         self._scalars = DeviceArray.zeros((4,), "float32")    # [sumsq, found_inf, -, -]
         self._sumsq = DeviceArray(self._scalars.ptr, (), "float32", base=self._scalars)
         self._found_inf = DeviceArray(self._scalars.ptr + 4, (), "float32", base=self._scalars)

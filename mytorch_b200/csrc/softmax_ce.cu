@@ -222,6 +222,126 @@ ce_finish_kernel(const float* __restrict__ lse, const float* __restrict__ tgt, c
   if (r < rows) loss[r] = labels[r] != -100 ? lse[r] - tgt[r] : 0.f;
 }
 
+// valid_count[0] = #labels != -100 (one block); runs before the fused forward+gradient kernel,
+// which needs the count for the 1/n of the mean.
+__global__ void __launch_bounds__(1024)
+ce_count_kernel(const int32_t* __restrict__ labels, int64_t rows, float* __restrict__ valid_count) {
+  __shared__ float sh[32];
+  float n = 0.f;
+  for (int64_t r = threadIdx.x; r < rows; r += blockDim.x) n += labels[r] != -100 ? 1.f : 0.f;
+  n = block_sum(n, sh);
+  if (threadIdx.x == 0) valid_count[0] = n;
+}
+
+// Forward and gradient in one kernel: a block reads its row once for the log-sum-exp and at once
+// a second time - while the row (100 KB at 50k classes) is still in L2 - to overwrite it with
+// (softmax - onehot) * scale / n_valid. DRAM sees one read and one write of the logits instead
+// of the two reads and one write of separate forward and backward kernels.
+template <typename T>
+__global__ void __launch_bounds__(kCeThreads)
+ce_fwd_grad_kernel(T* __restrict__ logits, const int32_t* __restrict__ labels, float* __restrict__ loss,
+                   float* __restrict__ lse_out, float scale_host, const float* __restrict__ scale_dev,
+                   const float* __restrict__ count_dev, int64_t classes, int64_t ld, float softcap, int vec_ok,
+                   int* __restrict__ flag) {
+  constexpr int VN = Vec16<T>::N;
+  __shared__ float shm[32], shs[32];
+  __shared__ float row_lse;
+  const int64_t row = blockIdx.x;
+  T* xr = logits + row * ld;
+  float m = -INFINITY, s = 0.f;
+  int64_t vec_end = 0;
+  if (vec_ok) {
+    const int64_t nvec = classes / VN;
+    vec_end = nvec * VN;
+    for (int64_t vi = threadIdx.x; vi < nvec; vi += kCeThreads) {
+      Vec16<T> v;
+      v.load(xr + vi * VN);
+      float f[VN];
+      float vm = -INFINITY;
+#pragma unroll
+      for (int e = 0; e < VN; ++e) { f[e] = softcap_f(v.get(e), softcap); vm = fmaxf(vm, f[e]); }
+      if (vm > m) { s *= exp2f((m - vm) * kLog2e); m = vm; }
+#pragma unroll
+      for (int e = 0; e < VN; ++e) s += exp2f((f[e] - m) * kLog2e);
+    }
+  }
+  for (int64_t c = vec_end + threadIdx.x; c < classes; c += kCeThreads) {
+    float f = softcap_f(to_f(xr[c]), softcap);
+    if (f > m) { s *= exp2f((m - f) * kLog2e); m = f; }
+    s += exp2f((f - m) * kLog2e);
+  }
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    float m2 = __shfl_xor_sync(0xffffffffu, m, o), s2 = __shfl_xor_sync(0xffffffffu, s, o);
+    float mm = fmaxf(m, m2);
+    s = (m == -INFINITY ? 0.f : s * exp2f((m - mm) * kLog2e)) + (m2 == -INFINITY ? 0.f : s2 * exp2f((m2 - mm) * kLog2e));
+    m = mm;
+  }
+  if (lane == 0) { shm[w] = m; shs[w] = s; }
+  __syncthreads();
+  const int32_t label = labels[row];
+  const bool valid = label >= 0 && label < classes;
+  if (w == 0) {
+    m = lane < kCeThreads / 32 ? shm[lane] : -INFINITY;
+    s = lane < kCeThreads / 32 ? shs[lane] : 0.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      float m2 = __shfl_xor_sync(0xffffffffu, m, o), s2 = __shfl_xor_sync(0xffffffffu, s, o);
+      float mm = fmaxf(m, m2);
+      s = (m == -INFINITY ? 0.f : s * exp2f((m - mm) * kLog2e)) + (m2 == -INFINITY ? 0.f : s2 * exp2f((m2 - mm) * kLog2e));
+      m = mm;
+    }
+    if (lane == 0) {
+      const float lse = m + logf(s);
+      lse_out[row] = lse;
+      row_lse = lse;
+      float l = 0.f;
+      if (valid) l = lse - softcap_f(to_f(xr[label]), softcap);
+      else if (label != -100 && flag) atomicMax(flag, 2);  // label out of range: recorded, row ignored
+      loss[row] = l;
+    }
+  }
+  __syncthreads();   // the loss read its target logit before anything below overwrites the row
+  const float l = row_lse;
+  float scale = scale_host;
+  if (scale_dev) scale *= scale_dev[0];
+  scale = valid ? scale / count_dev[0] : 0.f;
+  if (vec_ok) {
+    const int64_t nvec = classes / VN;
+    for (int64_t vi = threadIdx.x; vi < nvec; vi += kCeThreads) {
+      Vec16<T> v, o;
+      v.load(xr + vi * VN);
+#pragma unroll
+      for (int e = 0; e < VN; ++e) {
+        float x = v.get(e), f = x, dcap = 1.f;
+        if (softcap > 0.f) { float t = tanhf(x / softcap); f = softcap * t; dcap = 1.f - t * t; }
+        float p = valid ? exp2f((f - l) * kLog2e) : 0.f;
+        if (vi * VN + e == label) p -= 1.f;
+        o.set(e, p * scale * dcap);
+      }
+      o.store(xr + vi * VN);
+    }
+  }
+  for (int64_t c = vec_end + threadIdx.x; c < classes; c += kCeThreads) {
+    float x = to_f(xr[c]), f = x, dcap = 1.f;
+    if (softcap > 0.f) { float t = tanhf(x / softcap); f = softcap * t; dcap = 1.f - t * t; }
+    float p = valid ? exp2f((f - l) * kLog2e) : 0.f;
+    if (c == label) p -= 1.f;
+    xr[c] = from_f<T>(p * scale * dcap);
+  }
+}
+
+// x[i] *= num[0] / den[0] (device scalars): corrects a gradient that was scaled for another
+// upstream value than the one that finally arrived.
+template <typename T>
+__global__ void __launch_bounds__(256)
+scale_ratio_kernel(T* __restrict__ x, int64_t n, const float* __restrict__ num, const float* __restrict__ den) {
+  const float r = num[0] / den[0];
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+    x[i] = from_f<T>(to_f(x[i]) * r);
+}
+
 constexpr int kCeBwdChunk = 4096;  // elements of one row handled by one block
 
 template <typename T>
@@ -331,6 +451,40 @@ int mt_ce_fwd(const void* logits, const int32_t* labels, float* loss, float* lse
     ce_reduce_kernel<<<1, 1024, 0, st>>>(loss, labels, rows, loss_sum, valid_count, loss_mean);
     MT_LAUNCH_CHECK();
   }
+  return MT_OK;
+}
+
+int mt_ce_fwd_grad(void* logits, const int32_t* labels, float* loss, float* lse, float* loss_sum, float* valid_count,
+                   float* loss_mean, float scale_host, const float* scale_dev, int64_t rows, int64_t classes, int64_t ld,
+                   float softcap, int dtype, void* stream) {
+  MT_REQUIRE(logits && labels && loss && lse && valid_count && rows >= 0 && classes > 0 && ld >= classes,
+             "ce_fwd_grad: bad arguments");
+  cudaStream_t st = as_stream(stream);
+  ce_count_kernel<<<1, 1024, 0, st>>>(labels, rows, valid_count);
+  MT_LAUNCH_CHECK();
+  if (rows > 0) {
+    int* flag = device_flag_ptr();
+    MT_DISPATCH_FLOAT(dtype, T, {
+      int vec_ok = aligned16(logits) && (ld % Vec16<T>::N == 0);
+      ce_fwd_grad_kernel<T><<<(unsigned)rows, kCeThreads, 0, st>>>((T*)logits, labels, loss, lse, scale_host, scale_dev,
+                                                                 valid_count, classes, ld, softcap, vec_ok, flag);
+    });
+    MT_LAUNCH_CHECK();
+  }
+  if (loss_sum || loss_mean) {
+    ce_reduce_kernel<<<1, 1024, 0, st>>>(loss, labels, rows, loss_sum, valid_count, loss_mean);
+    MT_LAUNCH_CHECK();
+  }
+  return MT_OK;
+}
+
+int mt_scale_ratio(void* x, int64_t n, const float* num, const float* den, int dtype, void* stream) {
+  MT_REQUIRE(x && num && den && n >= 0, "scale_ratio: bad arguments");
+  if (n == 0) return MT_OK;
+  int64_t blocks = (n + 255) / 256;
+  if (blocks > (int64_t)sm_count() * 16) blocks = (int64_t)sm_count() * 16;
+  MT_DISPATCH_FLOAT(dtype, T, (scale_ratio_kernel<T><<<(unsigned)blocks, 256, 0, as_stream(stream)>>>((T*)x, n, num, den)));
+  MT_LAUNCH_CHECK();
   return MT_OK;
 }
 

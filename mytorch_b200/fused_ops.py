@@ -192,6 +192,23 @@ def fused_cross_entropy_forward(logits, labels, softcap=None, ld=None, reduce=Fa
     return loss, lse
 
 
+def fused_cross_entropy_forward_backward(logits, labels, softcap=None, ld=None, scale=1.0, scale_dev=None):
+    """Forward and gradient in one pass (mt_ce_fwd_grad): returns (loss[N], lse[N], tot) like
+    fused_cross_entropy_forward(reduce=True) and OVERWRITES logits with
+    (softmax - onehot) * scale * scale_dev / n_valid, the gradient of the mean loss for an
+    upstream gradient scale * scale_dev (device scalar, optional)."""
+    logits, labels = _A(logits), _A(labels)
+    n, c = logits.shape
+    ld = ld or c
+    assert labels.dtype == "int32"
+    loss = DeviceArray.empty((n,), "float32")
+    lse = DeviceArray.empty((n,), "float32")
+    tot = DeviceArray.empty((3,), "float32")
+    _lib.ce_fwd_grad(logits.ptr, labels.ptr, loss.ptr, lse.ptr, tot.ptr, tot.ptr + 4, tot.ptr + 8, float(scale),
+                     None if scale_dev is None else _A(scale_dev).ptr, n, c, ld, float(softcap or 0.0), logits.code, stream())
+    return loss, lse, tot
+
+
 def fused_cross_entropy_backward(logits, labels, logsumexp, softcap=None, scale=1.0, ld=None,
                                  scale_dev=None, count_dev=None):
     """(softmax - onehot) * scale written OVER logits, which is returned

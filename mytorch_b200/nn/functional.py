@@ -227,17 +227,41 @@ def softmax(x, dim=-1, auto=False, fused=True):
 
 
 # --------------------------------------------------------- cross entropy ----
-def cross_entropy(logits, targets, ignore_index=-100, softcap=None, auto=False, fused=True):
+def cross_entropy(logits, targets, ignore_index=-100, softcap=None, auto=False, fused=True, fused_backward=False):
     """Mean over valid rows of lse - logit[target]
     (mytorch/nn/functional/losses/cross_entropy.py:107-178). The valid count and
     the upstream gradient stay on the device (the reference reads both back to
     the host, :120 and :144); the backward overwrites the logits buffer, as the
     reference's fused kernel does. Unlike the reference's dispatcher (:178),
-    `softcap` is honoured when given."""
+    `softcap` is honoured when given.
+
+    fused_backward=True computes the gradient in the forward pass, while each row of logits is
+    still in cache (one read and one write of the logits instead of two reads and one write):
+    the logits buffer is overwritten ALREADY HERE, so it suits training loops that do not look at
+    the logits after the loss. The gradient is pre-multiplied by the upstream value that
+    backward() is expected to bring (`Tensor.loss_grad_hint`, the loss scale under mixed
+    precision, else 1); if something else arrives it is corrected by one more pass."""
     assert ignore_index == -100, "ignore_index is fixed to -100 like the reference's fused kernel"
     lg = _flat2d(logits.data)
     tg = targets.data if isinstance(targets, Tensor) else DeviceArray.from_numpy(targets, "int32")
     tg = tg.reshape(-1)
+    if fused_backward and _needs_graph(logits):
+        hint = Tensor.loss_grad_hint
+        loss_rows, lse, tot = K.fused_cross_entropy_forward_backward(lg, tg, softcap, scale_dev=hint)
+        out = Tensor(DeviceArray(tot.ptr + 8, (), "float32", base=tot))
+
+        def _bw_fused(g):
+            expected = hint.ptr if hint is not None else Tensor._unit_grad_ptr
+            if g.ptr != expected:      # another upstream gradient than announced: rescale by g / hint
+                one = None
+                if hint is None:
+                    one = DeviceArray.empty((1,), "float32").fill_(1.0)
+                _lib.scale_ratio(lg.ptr, lg.size, g.ptr, (hint if hint is not None else one).ptr, lg.code, stream())
+            logits._accumulate(lg.reshape(logits.shape))
+        out.requires_grad = True
+        out.grad_fn, out.grad_fn_name = _bw_fused, "<CrossEntropyFusedBackward>"
+        out._add_parents(logits)
+        return out
     loss_rows, lse, tot = K.fused_cross_entropy_forward(lg, tg, softcap, reduce=True)
     out = Tensor(DeviceArray(tot.ptr + 8, (), "float32", base=tot))   # the mean, a device scalar
     if _needs_graph(logits):

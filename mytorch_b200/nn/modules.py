@@ -238,12 +238,13 @@ class Dropout(Module):
 class CrossEntropyLoss(Module):
     """modules/losses/cross_entropy.py:4-12."""
 
-    def __init__(self, ignore_index=-100, softcap=None, auto=False, fused=True):
+    def __init__(self, ignore_index=-100, softcap=None, auto=False, fused=True, fused_backward=False):
         super().__init__()
         self.ignore_index, self.softcap = ignore_index, softcap
+        self.fused_backward = fused_backward     # see F.cross_entropy: the logits are overwritten in forward
 
     def forward(self, logits, targets):
-        return F.cross_entropy(logits, targets, self.ignore_index, self.softcap)
+        return F.cross_entropy(logits, targets, self.ignore_index, self.softcap, fused_backward=self.fused_backward)
 
 
 # initialisers (mytorch/nn/initializations.py:44-56), host RNG then upload

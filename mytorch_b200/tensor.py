@@ -47,6 +47,11 @@ class Tensor:
     # Optional callable(param) invoked during backward() as soon as the last closure contributing to
     # a parameter's gradient has run (set by Accelerator to start that gradient's all-reduce early).
     param_ready_hook = None
+    # Device scalar that loss.backward() will be called with (the loss scale of mixed-precision
+    # training), announced by the Accelerator so that a loss may fold it into a gradient it
+    # produces already in its forward pass. None = backward() is expected with its default of 1.
+    loss_grad_hint = None
+    _unit_grad_ptr = None
 
     def __init__(self, data, requires_grad=False, grad_fn=None, grad_fn_name=None, dtype=None, device=None):
         self.data = _to_device_array(data, dtype)
@@ -72,8 +77,10 @@ class Tensor:
             raise RuntimeError("backward() on a tensor that does not require grad")
         if grad is None:
             g = DeviceArray.empty(self.shape, self.dtype).fill_(1.0)
+            Tensor._unit_grad_ptr = g.ptr      # lets an op recognise "the upstream gradient is exactly 1"
         else:
             g = _to_device_array(grad, self.dtype)
+            Tensor._unit_grad_ptr = None
         order, seen = [], set()
         stack = [(self, False)]
         while stack:                      # iterative DFS post-order

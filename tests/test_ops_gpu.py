@@ -483,3 +483,36 @@ def test_gemm_stores_activation_derivative_and_multiplies_by_it(mt, dtype, act, 
     got = F.gemm(dev(mt, dy, dtype), dev(mt, w2, dtype), aux=dev(mt, dsaved, dtype), aux_mode=5)
     close(got.numpy(), (dy.astype(np.float64) @ w2) * dsaved, t, "result * saved derivative")
     no_device_flag(mt)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows,classes,ld,softcap", [(41, 131, 131, None), (64, 50257, 50264, None), (16, 50304, 50304, None),
+                                                     (3, 7, 16, None), (20, 1000, 1000, 15.0)])
+def test_cross_entropy_forward_and_gradient_in_one_pass(mt, dtype, rows, classes, ld, softcap):
+    """mt_ce_fwd_grad: same loss / lse / count as the forward kernel, and the logits buffer then
+    holds the gradient of the mean loss times the announced upstream value."""
+    F = mt.fused_ops
+    r = np.random.default_rng(17)
+    x = rnd(r.standard_normal((rows, classes)) * 2, dtype)
+    y = r.integers(0, classes, rows).astype(np.int32)
+    y[rows // 3] = -100
+    buf = np.zeros((rows, ld), np.float32)
+    buf[:, :classes] = x
+    L = dev(mt, buf, dtype)
+    Lv = mt.DeviceArray(L.ptr, (rows, classes), dtype, base=L)
+    Y = mt.DeviceArray.from_numpy(y)
+    up = mt.DeviceArray.from_numpy(np.array([3.0], np.float32))
+    loss, lse, tot = F.fused_cross_entropy_forward_backward(Lv, Y, softcap, ld=ld, scale_dev=up)
+    xs = x if softcap is None else softcap * np.tanh(x / softcap)
+    want_loss, want_lse = O.cross_entropy_rows(xs, y)
+    close(lse.numpy(), want_lse, 1e-5, "lse"); close(loss.numpy(), want_loss, 1e-4, "loss")
+    t = tot.numpy()
+    assert t[1] == rows - 1
+    close(t[2], want_loss.sum() / (rows - 1), 1e-5, "mean loss")
+    want = O.cross_entropy_bwd(xs, y, 3.0)
+    if softcap is not None:
+        want = want * (1.0 - np.tanh(x / softcap) ** 2)
+    got = L.numpy()[:, :classes]
+    close(got, want, 2e-2 if dtype != "float32" else 1e-4, "dlogits")
+    assert np.all(got[rows // 3] == 0)
+    no_device_flag(mt)

@@ -426,3 +426,50 @@ def test_kv_cache_decoding_matches_the_full_forward():
     a = model.generate(ids[:, :8], 6, temperature=0, use_cache=True)
     b = model.generate(ids[:, :8], 6, temperature=0, use_cache=False)
     assert a.shape == (3, 14) and np.array_equal(a, b)
+
+
+def test_fused_cross_entropy_backward_trains_like_the_two_pass_form():
+    """CrossEntropyLoss(fused_backward=True): the gradient is produced in the forward pass with the
+    loss scale announced by the Accelerator folded in; plain loss.backward() (upstream 1) and a
+    backward with an unannounced gradient (corrected by the extra pass) give the same results as
+    the two-pass form."""
+    import mytorch_b200 as mt
+    cfg = og.GPT2Config(vocab_size=264, max_seq_len=64, embed_dim=128, mlp_ratio=4, num_blocks=2, num_heads=2)
+    params = og.init_params(cfg, seed=14)
+
+    def amp_run(fused):
+        mt_, model = build(cfg, {k: v.copy() for k, v in params.items()})
+        acc = mt_.Accelerator(num_gpus=1, rank=0, mixed_precision=True)
+        opt = mt_.optim.AdamW(groups(model), lr=1e-3, beta1=0.9, beta2=0.95)
+        model, opt = acc.prepare(model, opt)
+        loss_fn = mt_.nn.CrossEntropyLoss(fused_backward=fused)
+        rng = np.random.default_rng(15)
+        out = []
+        for _ in range(4):
+            x, y = og.synthetic_batch(rng, 4, 64, 264)
+            loss = loss_fn(model(mt_.Tensor(x)), mt_.Tensor(y))
+            acc.backward(loss)
+            acc.clip_grad_norm_(1.0)
+            opt.step(); opt.zero_grad()
+            out.append(loss.item())
+        return out, acc._flat.master.numpy().copy()
+
+    (la, wa), (lb, wb) = amp_run(False), amp_run(True)
+    assert np.allclose(la, lb, rtol=2e-3), (la, lb)
+    assert np.abs(wa - wb).max() <= 2e-3
+
+    def fp32_grads(fused, upstream):
+        mt.Tensor.loss_grad_hint = None
+        mt_, model = build(cfg, {k: v.copy() for k, v in params.items()})
+        x, y = og.synthetic_batch(np.random.default_rng(16), 4, 64, 264)
+        loss = mt_.nn.CrossEntropyLoss(fused_backward=fused)(model(mt_.Tensor(x)), mt_.Tensor(y))
+        if upstream is None:
+            loss.backward()
+        else:
+            loss.backward(mt_.DeviceArray.from_numpy(np.array(upstream, np.float32)))
+        return {n: p.grad.numpy().copy() for n, p in model.named_parameters()}
+
+    for upstream in (None, 2.5):
+        ga, gb = fp32_grads(False, upstream), fp32_grads(True, upstream)
+        for n in ga:
+            assert np.abs(ga[n] - gb[n]).max() <= 1e-5 * max(1.0, np.abs(ga[n]).max()), (n, upstream)
