@@ -759,6 +759,7 @@ static int launch_tc_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CU
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   MT_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, tp, tx, P));
+  count_launch();
   return MT_OK;
 }
 
