@@ -78,6 +78,9 @@ int mt_cast(const void* src, int src_dtype, void* dst, int dst_dtype, int64_t n,
 /* uint16 token ids (the on-disk format of gpt2_trainer/train_gpt2.py:150) -> int32 indices,
  * so that batches cross PCIe at two bytes per token. */
 int mt_widen_u16_i32(const void* src_u16, void* dst_i32, int64_t n, void* stream);
+/* y = cap * tanh(x / cap), the logit soft cap of the nanochat model's inference branch
+ * (nanochat_trainer/core/nanochat_gpt.py:336). */
+int mt_softcap(const void* x, void* y, int64_t n, float cap, int dtype, void* stream);
 int mt_fill(void* dst, int dtype, float value, int64_t n, void* stream);
 int mt_add(const void* a, const void* b, void* out, int64_t n, int dtype, void* stream);          /* out = a + b */
 int mt_axpby(const void* x, float alpha, void* y, float beta, int64_t n, int x_dtype, int y_dtype, void* stream); /* y = alpha*x + beta*y */

@@ -75,6 +75,7 @@ _SIG = {
     "mt_prof_end": [C.POINTER(C.c_double), C.POINTER(_i64), C.POINTER(C.c_double)],
     "mt_cast": [_p, _i, _p, _i, _i64, _p],
     "mt_widen_u16_i32": [_p, _p, _i64, _p],
+    "mt_softcap": [_p, _p, _i64, _f, _i, _p],
     "mt_fill": [_p, _i, _f, _i64, _p],
     "mt_add": [_p, _p, _p, _i64, _i, _p],
     "mt_axpby": [_p, _f, _p, _f, _i64, _i, _i, _p],

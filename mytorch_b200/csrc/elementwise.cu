@@ -208,7 +208,28 @@ widen_u16_kernel(const uint16_t* __restrict__ src, int32_t* __restrict__ dst, in
 }
 }  // namespace mt
 
+namespace mt {
+// y = cap * tanh(x / cap): the soft cap nanochat puts on its logits.
+template <typename T>
+__global__ void __launch_bounds__(256)
+softcap_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t n, float cap) {
+  const float inv = 1.f / cap;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+    y[i] = from_f<T>(cap * tanhf(to_f(x[i]) * inv));
+}
+}  // namespace mt
+
 extern "C" {
+
+int mt_softcap(const void* x, void* y, int64_t n, float cap, int dtype, void* stream) {
+  MT_REQUIRE(x && y && n >= 0 && cap > 0.f, "softcap: bad arguments");
+  if (n == 0) return MT_OK;
+  int64_t blocks = (n + 255) / 256;
+  if (blocks > (int64_t)sm_count() * 16) blocks = (int64_t)sm_count() * 16;
+  MT_DISPATCH_FLOAT(dtype, T, (mt::softcap_kernel<T><<<(unsigned)blocks, 256, 0, as_stream(stream)>>>((const T*)x, (T*)y, n, cap)));
+  MT_LAUNCH_CHECK();
+  return MT_OK;
+}
 
 int mt_widen_u16_i32(const void* src, void* dst, int64_t n, void* stream) {
   MT_REQUIRE(src && dst && n >= 0, "widen_u16_i32: bad arguments");

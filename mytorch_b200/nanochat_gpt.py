@@ -6,7 +6,7 @@ q/k/v projections, rotary embedding THEN parameter-free RMSNorm on q and k
 lm_head (:287-288), loss = cross entropy of tanh-soft-capped logits.
 
 Same config fields, module names and state_dict keys as the reference. Training
-path only (no KV cache). Multi-head attention (num_kv_heads == num_q_heads, the
+path plus cached decoding (`KVCache`, nanochat_trainer/core/cache.py). Multi-head attention (num_kv_heads == num_q_heads, the
 560M "d20" configuration); grouped-query attention is not on this path.
 Unlike the reference's training dispatcher, which drops `softcap` before the
 loss is computed (mytorch/nn/functional/losses/cross_entropy.py:178), the cap
@@ -15,10 +15,44 @@ is applied, as the model definition intends.
 import math
 from dataclasses import dataclass
 
-from . import nn
-from .array import DeviceArray
+import numpy as np
+
+from . import _lib, nn
+from .array import DeviceArray, stream
 from .nn import functional as F
 from .tensor import Tensor
+
+
+class KVCache:
+    """Preallocated key/value cache [layers][B, H, seq_len, D] with a write position
+    (nanochat_trainer/core/cache.py:3-75): update() stores the new rows at [pos, pos+T) of its
+    layer, the position advances once per forward pass (after the last layer)."""
+
+    def __init__(self, batch_size, num_heads, seq_len, head_dim, num_layers):
+        self.cache_shape = (num_layers, batch_size, num_heads, seq_len, head_dim)
+        self.k_cache = self.v_cache = None
+        self._pos = 0
+
+    @property
+    def pos(self):
+        return self._pos
+
+    def reset(self):
+        self._pos = 0
+
+    def update(self, k_ptr, v_ptr, strides, n_new, dtype, layer_idx):
+        L, B, H, S, D = self.cache_shape
+        if self.k_cache is None:
+            self.k_cache = DeviceArray.empty(self.cache_shape, dtype)
+            self.v_cache = DeviceArray.empty(self.cache_shape, dtype)
+        assert self._pos + n_new <= S, "You have filled up your Cache!"
+        kc, vc = self.k_cache.rows(layer_idx, layer_idx + 1), self.v_cache.rows(layer_idx, layer_idx + 1)
+        sc = _lib.Strides3(H * S * D, S * D, D)
+        _lib.kv_append(k_ptr, v_ptr, kc.ptr, vc.ptr, strides, strides, sc, B, H, n_new, self._pos, S, D, kc.code, stream())
+        if layer_idx == L - 1:
+            self._pos += n_new
+            return kc, vc, self._pos
+        return kc, vc, self._pos + n_new
 
 
 @dataclass
@@ -63,7 +97,7 @@ class Attention(nn.Module):
         self.v_proj = nn.Linear(self.embed_dim, self.embed_dim, bias=config.use_bias)
         self.out_proj = nn.Linear(self.embed_dim, self.embed_dim, bias=config.use_bias)
 
-    def forward(self, x, cos_sin):
+    def forward(self, x, cos_sin, residual=None, cache=None, layer_idx=None):
         B, T, E = x.shape
         H, D = self.num_heads, self.head_dim
         q = self.q_proj(x).reshape(B, T, H, D)
@@ -73,8 +107,23 @@ class Attention(nn.Module):
         q, k = F.apply_rotary_pos_embed(q, k, cos, sin)          # rotary first ...
         q = norm(q.reshape(B * T * H, D)).reshape(B, T, H, D)     # ... then QK-norm over head_dim
         k = norm(k.reshape(B * T * H, D)).reshape(B, T, H, D)
-        out = F.bthd_attention(q, k, v, is_causal=True)           # [B, T, E], heads read in place
-        return self.out_proj(out)
+        if cache is not None:
+            # inference: new keys/values join the cache; the prompt (empty cache) attends causally
+            # among its own tokens, later tokens see everything cached (nanochat_gpt.py:126-160)
+            past = cache.pos
+            sin3 = _lib.Strides3(T * H * D, D, H * D)
+            kc, vc, kv_len = cache.update(k.data.ptr, v.data.ptr, sin3, T, k.data.dtype, layer_idx)
+            if past == 0:
+                out = F.bthd_attention(q, k, v, is_causal=True)
+            else:
+                S = cache.cache_shape[3]
+                o = DeviceArray.empty((B, T, E), q.data.dtype)
+                _lib.attn_decode(q.data.ptr, kc.ptr, vc.ptr, o.ptr, sin3, _lib.Strides3(H * S * D, S * D, D),
+                                 _lib.Strides3(T * E, D, E), B, H, T, kv_len, D, float(D) ** -0.5, past, q.data.code, stream())
+                out = Tensor(o)
+        else:
+            out = F.bthd_attention(q, k, v, is_causal=True)       # [B, T, E], heads read in place
+        return F.linear(out, self.out_proj.weight, self.out_proj.bias, residual=residual)
 
 
 class FeedForward(nn.Module):
@@ -84,10 +133,10 @@ class FeedForward(nn.Module):
         self.intermediate_dense = nn.Linear(config.embed_dim, hidden, bias=config.use_bias, act_func="relu_squared")
         self.out_proj = nn.Linear(hidden, config.embed_dim, bias=config.use_bias)
 
-    def forward(self, x):
+    def forward(self, x, residual=None):
         if self.intermediate_dense.bias is None and self.out_proj.bias is None:
-            return F.mlp(x, self.intermediate_dense.weight, self.out_proj.weight, "relu_squared")
-        return self.out_proj(self.intermediate_dense(x))
+            return F.mlp(x, self.intermediate_dense.weight, self.out_proj.weight, "relu_squared", residual=residual)
+        return F.linear(self.intermediate_dense(x), self.out_proj.weight, self.out_proj.bias, residual=residual)
 
 
 class TransformerBlock(nn.Module):
@@ -96,9 +145,10 @@ class TransformerBlock(nn.Module):
         self.attention = Attention(config, layer_idx)
         self.feedforward = FeedForward(config)
 
-    def forward(self, x, cos_sin):
-        x = x + self.attention(norm(x), cos_sin)
-        x = x + self.feedforward(norm(x))
+    def forward(self, x, cos_sin, cache=None, layer_idx=None):
+        # the skip connections are added in the epilogue of each sublayer's last GEMM
+        x = self.attention(norm(x), cos_sin, residual=x, cache=cache, layer_idx=layer_idx)
+        x = self.feedforward(norm(x), residual=x)
         return x
 
 
@@ -132,13 +182,16 @@ class GPT(nn.Module):
         """Recompute each block in the backward pass (nanochat_gpt.py:318-322)."""
         self._gradient_checkpointing_enabled = True
 
-    def forward(self, input_ids, target_ids=None):
+    def forward(self, input_ids, target_ids=None, cache=None):
         B, T = input_ids.shape
-        assert T <= self.config.max_seq_len, "sequence longer than the rotary table"
-        cos = DeviceArray(self.cos.ptr, (T, self.cos.shape[1]), "float32", base=self.cos)
-        sin = DeviceArray(self.sin.ptr, (T, self.sin.shape[1]), "float32", base=self.sin)
+        past = cache.pos if cache is not None else 0
+        assert past + T <= self.config.max_seq_len, "sequence longer than the rotary table"
+        cos, sin = self.cos.rows(past, past + T), self.sin.rows(past, past + T)   # positions continue after the cache
         x = self.embeddings(input_ids)
-        for block in self.blocks:
+        for layer_idx, block in enumerate(self.blocks):
+            if cache is not None:
+                x = block(x, (cos, sin), cache=cache, layer_idx=layer_idx)
+                continue
             if self._gradient_checkpointing_enabled and self.training and x.requires_grad:
                 from .utils.checkpoint import checkpoint
                 x = checkpoint(block, x, (cos, sin))
@@ -147,6 +200,41 @@ class GPT(nn.Module):
         x = norm(x)
         logits = self.lm_head(x)
         if target_ids is None:
-            return (logits,)
+            # inference branch (nanochat_gpt.py:334-340): soft-capped logits, plus the cache if one was given
+            if self.config.softcap and not self.training:
+                arr = logits.data
+                _lib.softcap(arr.ptr, arr.ptr, arr.size, float(self.config.softcap), arr.code, stream())
+            return (logits,) if cache is None else (logits, cache)
         loss = F.cross_entropy(logits, target_ids, softcap=self.config.softcap)
         return logits, loss
+
+    def generate(self, input_ids, max_new_tokens, temperature=1.0, top_k=None, seed=None):
+        """Cached autoregressive sampling for one batch of equally long prompts: the prompt fills a
+        KVCache, then one token per step (temperature 0 = arg-max)."""
+        from .tensor import no_grad
+        cfg = self.config
+        rng = np.random.default_rng(seed)
+        ids = np.asarray(input_ids.numpy() if isinstance(input_ids, Tensor) else input_ids, dtype=np.int32)
+        cache = KVCache(ids.shape[0], cfg.num_q_heads, cfg.max_seq_len, cfg.embed_dim // cfg.num_q_heads, cfg.num_blocks)
+        was_training = self.training
+        self.eval()
+        feed = ids
+        with no_grad():
+            for _ in range(max_new_tokens):
+                logits, cache = self.forward(Tensor(feed), None, cache=cache)
+                last = logits.numpy()[:, -1, :].astype(np.float64)
+                if temperature == 0:
+                    nxt = last.argmax(-1)
+                else:
+                    last = last / temperature
+                    if top_k is not None:
+                        kth = np.sort(last, -1)[:, -top_k][:, None]
+                        last = np.where(last < kth, -np.inf, last)
+                    p = np.exp(last - last.max(-1, keepdims=True))
+                    p /= p.sum(-1, keepdims=True)
+                    nxt = np.array([rng.choice(p.shape[-1], p=row) for row in p])
+                ids = np.concatenate([ids, nxt[:, None].astype(np.int32)], axis=1)
+                feed = ids[:, -1:]
+        if was_training:
+            self.train()
+        return ids

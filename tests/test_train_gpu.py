@@ -473,3 +473,37 @@ def test_fused_cross_entropy_backward_trains_like_the_two_pass_form():
         ga, gb = fp32_grads(False, upstream), fp32_grads(True, upstream)
         for n in ga:
             assert np.abs(ga[n] - gb[n]).max() <= 1e-5 * max(1.0, np.abs(ga[n]).max()), (n, upstream)
+
+
+def test_nanochat_kv_cache_decoding_matches_the_full_forward():
+    """nanochat inference branch (nanochat_gpt.py:301-340, core/cache.py): prompt then token by
+    token through the KVCache (rotary positions continue after the cache, head_dim 128 through the
+    decode-attention kernel) gives the soft-capped logits of the uncached forward, which the
+    training parity test pins to the reference."""
+    import mytorch_b200 as mt
+    from mytorch_b200.nanochat_gpt import GPT, GPTConfig, KVCache
+    cfg = GPTConfig(vocab_size=160, max_seq_len=48, embed_dim=256, mlp_ratio=4, num_blocks=2, num_q_heads=2, num_kv_heads=2)
+    np.random.seed(5)
+    model = GPT(cfg)
+    r = np.random.default_rng(6)
+    for n, p in model.named_parameters():          # out_proj / lm_head start at zero: give them values
+        if "out_proj" in n or "lm_head" in n:
+            p.data.set_from_numpy((r.standard_normal(p.shape) * 0.05).astype(np.float32))
+    model.eval()
+    ids = r.integers(0, 160, (2, 30)).astype(np.int32)
+    with mt.no_grad():
+        full = model(mt.Tensor(ids), None)[0].numpy()
+        assert np.abs(full).max() <= cfg.softcap
+        cache = KVCache(2, 2, 48, 128, 2)
+        out, cache = model(mt.Tensor(ids[:, :11]), None, cache=cache)
+        got = [out.numpy()]
+        for n in range(11, 26):
+            out, cache = model(mt.Tensor(ids[:, n:n + 1]), None, cache=cache)
+            got.append(out.numpy())
+        out, cache = model(mt.Tensor(ids[:, 26:30]), None, cache=cache)   # four tokens in one step, causal among them
+        got.append(out.numpy())
+        assert cache.pos == 30
+    got = np.concatenate(got, axis=1)
+    assert np.abs(got - full).max() <= 1e-4 * np.abs(full).max()
+    a = model.generate(ids[:, :5], 4, temperature=0)
+    assert a.shape == (2, 9) and np.array_equal(a[:, :5], ids[:, :5])
