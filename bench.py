@@ -319,9 +319,12 @@ def run_own(args):
                          "share_of_step": gemm_ms.value / ms_total,
                          # dram__bytes_read.sum + dram__bytes_write.sum of one captured launch of the
                          # qkv projection (16384x2304x768 fp16; profiles/gemm_tc_kernel_*.md): the
-                         # operands are read once (28.7 MB), 28.8 MB of the 75.5 MB output reaches
+                         # operands are read once (30.3 MB), 26.4 MB of the 75.5 MB output reaches
                          # DRAM before the kernel ends, the rest stays in L2.
-                         "traffic": 58.6e6, "traffic_unit": "bytes per launch (qkv projection, ncu)"},
+                         "traffic": 56.7e6, "traffic_unit": "bytes per launch (qkv projection, ncu)",
+                         # torch.matmul (cuBLAS) on the lm_head shape with random-normal operands,
+                         # same box type (profiles/gemm_vs_library_*.md): the same-data library figure
+                         "library_same_data_tflops": 1136.0},
             "clocks": clocks, "final_loss": final_loss, "device_flag": flag.value,
         }
         if world == 1 and not args.no_cpu_baseline:
