@@ -154,25 +154,47 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       const uint32_t idesc_mn = idesc_f16(P.is_bf16, 1, 1, 128, D);     // dQ: A M-major, B N-major
       const uint32_t sk = base + Cfg::kOffK, sv = base + Cfg::kOffV;
       const uint32_t spt = base + Cfg::kOffPT, sdst = base + Cfg::kOffDST;
+      // Descriptors that do not depend on the Q/dO stage are built once; the stage's own are built
+      // at the top of each step, BEFORE the barrier wait, so that after a wait this thread issues
+      // MMAs and nothing else (it shares a scheduler with busy warps and every extra instruction
+      // between wait and MMA costs 10-20 cycles of tensor-pipe idle time).
+      constexpr int NS = 4 * Cfg::kChunks;              // MMAs of one S^T or dP^T
+      uint64_t a_s[NS], a_dp[NS], a_dk[8], a_dq[8], b_dq[8], a_dv[8];
+#pragma unroll
+      for (int dc = 0; dc < Cfg::kChunks; ++dc)
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          a_s[dc * 4 + k] = smem_desc_sw128(sk + dc * 16384 + k * 32, 16, 1024);
+          a_dp[dc * 4 + k] = smem_desc_sw128(sv + dc * 16384 + k * 32, 16, 1024);
+        }
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        a_dk[ks] = smem_desc_sw128(sdst + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024);   // dS^T, K-major
+        a_dq[ks] = smem_desc_sw128(sdst + ks * 2048, 16384, 1024);                          // dS^T, M-major
+        b_dq[ks] = smem_desc_sw128(sk + ks * 2048, 16384, 1024);
+        a_dv[ks] = smem_desc_sw128(spt + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024);    // P^T in shared memory (head_dim 128)
+      }
+      auto issue_n = [&](uint32_t d, const uint64_t* a, const uint64_t* b, uint32_t idesc, uint32_t acc) {
+        if (NS == 4) umma_f16_x4(d, a, b, idesc, acc);
+        else umma_f16_x8(d, a, b, idesc, acc);
+      };
       bool ok = mbar_wait(bar_kv, 0, abort_flag);
       // S^T = K Q^T and dP^T = V dO^T of query block i into tensor memory
       auto issue_sdp = [&](int i) -> bool {
         const int s = i % ST;
         const uint32_t sq = base + Cfg::kOffQ + s * 2 * Cfg::kTile, sdo = sq + Cfg::kTile;
+        uint64_t b_s[NS], b_dp[NS];
+#pragma unroll
+        for (int dc = 0; dc < Cfg::kChunks; ++dc)
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            b_s[dc * 4 + k] = smem_desc_sw128(sq + dc * 16384 + k * 32, 16, 1024);
+            b_dp[dc * 4 + k] = smem_desc_sw128(sdo + dc * 16384 + k * 32, 16, 1024);
+          }
         if (!mbar_wait(bar_qfull0 + 8 * s, (i / ST) & 1, abort_flag)) return false;
         tc_fence_after();
-#pragma unroll
-        for (int dc = 0; dc < Cfg::kChunks; ++dc)
-#pragma unroll
-          for (int k = 0; k < 4; ++k)
-            umma_f16(tmem_base + Cfg::kColST, smem_desc_sw128(sk + dc * 16384 + k * 32, 16, 1024),
-                     smem_desc_sw128(sq + dc * 16384 + k * 32, 16, 1024), idesc_kk, (dc | k) ? 1u : 0u);
-#pragma unroll
-        for (int dc = 0; dc < Cfg::kChunks; ++dc)
-#pragma unroll
-          for (int k = 0; k < 4; ++k)
-            umma_f16(tmem_base + Cfg::kColDPT, smem_desc_sw128(sv + dc * 16384 + k * 32, 16, 1024),
-                     smem_desc_sw128(sdo + dc * 16384 + k * 32, 16, 1024), idesc_kk, (dc | k) ? 1u : 0u);
+        issue_n(tmem_base + Cfg::kColST, a_s, b_s, idesc_kk, 0u);
+        issue_n(tmem_base + Cfg::kColDPT, a_dp, b_dp, idesc_kk, 0u);
         umma_commit(bar_sdp);
         return true;
       };
@@ -192,30 +214,24 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           tc_fence_after();
           if (!issue_sdp(i + 1)) break;
         }
+        uint64_t b_dv[8], b_dk[8];
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          b_dv[ks] = smem_desc_sw128(sdo + ks * 2048, 16384, 1024);
+          b_dk[ks] = smem_desc_sw128(sq + ks * 2048, 16384, 1024);
+        }
         if (!mbar_wait(bar_pds, i & 1, abort_flag)) break;     // P^T, dS^T written
         tc_fence_after();
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {  // dV += P^T dO, reduction over the 128 queries
-          if (Cfg::kPTinTmem)
-            umma_f16_ts(tmem_base + Cfg::kColDV, tmem_base + Cfg::kColPT + ks * 8,
-                        smem_desc_sw128(sdo + ks * 2048, 16384, 1024), idesc_kn, (i > 0 || ks > 0) ? 1u : 0u);
-          else
-            umma_f16(tmem_base + Cfg::kColDV, smem_desc_sw128(spt + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024),
-                     smem_desc_sw128(sdo + ks * 2048, 16384, 1024), idesc_kn, (i > 0 || ks > 0) ? 1u : 0u);
-        }
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks)   // dK += dS^T Q
-          umma_f16(tmem_base + Cfg::kColDK, smem_desc_sw128(sdst + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024),
-                   smem_desc_sw128(sq + ks * 2048, 16384, 1024), idesc_kn, (i > 0 || ks > 0) ? 1u : 0u);
+        // dV += P^T dO (reduction over the 128 queries), dK += dS^T Q
+        if (Cfg::kPTinTmem) umma_f16_ts_x8(tmem_base + Cfg::kColDV, tmem_base + Cfg::kColPT, b_dv, idesc_kn, i > 0 ? 1u : 0u);
+        else umma_f16_x8(tmem_base + Cfg::kColDV, a_dv, b_dv, idesc_kn, i > 0 ? 1u : 0u);
+        umma_f16_x8(tmem_base + Cfg::kColDK, a_dk, b_dk, idesc_kn, i > 0 ? 1u : 0u);
         umma_commit(bar_qempty0 + 8 * s);   // Q and dO of this block are not read again (dQ needs neither)
         if (!Cfg::kAliasDQ) {
           if (i > 0 && !mbar_wait(bar_dqfree, (i - 1) & 1, abort_flag)) break;   // dQ columns read out
           tc_fence_after();
         }
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks)   // dQ = dS K, reduction over the 128 keys
-          umma_f16(tmem_base + Cfg::kColDQ, smem_desc_sw128(sdst + ks * 2048, 16384, 1024),
-                   smem_desc_sw128(sk + ks * 2048, 16384, 1024), idesc_mn, ks > 0 ? 1u : 0u);
+        umma_f16_x8(tmem_base + Cfg::kColDQ, a_dq, b_dq, idesc_mn, 0u);   // dQ = dS K, reduction over the 128 keys
         umma_commit(bar_dq);
       }
     }

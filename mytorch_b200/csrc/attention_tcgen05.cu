@@ -148,17 +148,34 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     if (lane == 0) {
       const uint32_t idesc_s = idesc_f16(P.is_bf16, 0, 0, 128, 128);
       const uint32_t idesc_o = idesc_f16(P.is_bf16, 0, 1, 128, D);
+      // every shared-memory descriptor is built once, ahead of the loop: after a barrier wait the
+      // thread issues MMAs and nothing else
+      uint64_t dq[4 * Cfg::kChunks], dk[2][4 * Cfg::kChunks], dv[2][8];
+#pragma unroll
+      for (int dc = 0; dc < Cfg::kChunks; ++dc)
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          dq[dc * 4 + k] = smem_desc_sw128(base + Cfg::kOffQ + dc * 16384 + k * 32, 16, 1024);
+#pragma unroll
+          for (int st = 0; st < 2; ++st)
+            dk[st][dc * 4 + k] = smem_desc_sw128(base + Cfg::kOffK + st * Cfg::kTile + dc * 16384 + k * 32, 16, 1024);
+        }
+#pragma unroll
+      for (int st = 0; st < 2; ++st)
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          dv[st][ks] = smem_desc_sw128(base + Cfg::kOffV + st * Cfg::kTile + ks * 2048, 16384, 1024);
       auto issue_s = [&](int j) -> bool {
         const int st = j & 1;
         if (!mbar_wait(bar_kfull0 + 8 * st, (j >> 1) & 1, abort_flag)) return false;
         tc_fence_after();
-        const uint32_t sq = base + Cfg::kOffQ, sk = base + Cfg::kOffK + st * Cfg::kTile;
-#pragma unroll
-        for (int dc = 0; dc < Cfg::kChunks; ++dc)
-#pragma unroll
-          for (int k = 0; k < 4; ++k)
-            umma_f16(tmem_s, smem_desc_sw128(sq + dc * 16384 + k * 32, 16, 1024),
-                     smem_desc_sw128(sk + dc * 16384 + k * 32, 16, 1024), idesc_s, (dc | k) ? 1u : 0u);
+        if (st == 0) {
+          umma_f16_x4(tmem_s, dq, dk[0], idesc_s, 0u);
+          if (Cfg::kChunks == 2) umma_f16_x4(tmem_s, dq + 4 * (Cfg::kChunks - 1), dk[0] + 4 * (Cfg::kChunks - 1), idesc_s, 1u);
+        } else {
+          umma_f16_x4(tmem_s, dq, dk[1], idesc_s, 0u);
+          if (Cfg::kChunks == 2) umma_f16_x4(tmem_s, dq + 4 * (Cfg::kChunks - 1), dk[1] + 4 * (Cfg::kChunks - 1), idesc_s, 1u);
+        }
         umma_commit(bar_kempty0 + 8 * st);
         umma_commit(bar_s);
         return true;
@@ -177,12 +194,9 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         tc_fence_after();
         if (!mbar_wait(bar_vfull0 + 8 * (j & 1), (j >> 1) & 1, abort_flag)) break;
         tc_fence_after();
-        const uint32_t sv = base + Cfg::kOffV + (j & 1) * Cfg::kTile;
         // A = P straight from tensor memory: 16 keys = 8 columns of packed half pairs per step
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks)
-          umma_f16_ts(tmem_o, tmem_p + ks * 8, smem_desc_sw128(sv + ks * 2048, 16384, 1024), idesc_o,
-                      (j > 0 || ks > 0) ? 1u : 0u);
+        if (j & 1) umma_f16_ts_x8(tmem_o, tmem_p, dv[1], idesc_o, j > 0 ? 1u : 0u);
+        else umma_f16_ts_x8(tmem_o, tmem_p, dv[0], idesc_o, j > 0 ? 1u : 0u);
         umma_commit(bar_vempty0 + 8 * (j & 1));
         umma_commit(bar_o);
       }

@@ -153,6 +153,73 @@ __device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, ui
       ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// Four / eight MMAs into one accumulator from one asm statement, all operands ready in
+// registers: after the barrier wait that precedes them the issuing thread executes nothing but
+// the MMAs themselves. (That thread shares a scheduler with busy warps and advances only every
+// 10-20 cycles, so every instruction between the wait and the last MMA delays the tensor pipe.)
+// The first MMA overwrites the accumulator unless acc_first != 0; the others accumulate.
+__device__ __forceinline__ void umma_f16_x4(uint32_t d, const uint64_t* a, const uint64_t* b, uint32_t idesc, uint32_t acc_first) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p, pt;\n"
+      "setp.ne.b32 p, %10, 0;\n"
+      "setp.eq.b32 pt, 0, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %9, p;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %3, %4, %9, pt;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %5, %6, %9, pt;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %7, %8, %9, pt;\n"
+      "}\n"
+      ::"r"(d), "l"(a[0]), "l"(b[0]), "l"(a[1]), "l"(b[1]), "l"(a[2]), "l"(b[2]), "l"(a[3]), "l"(b[3]), "r"(idesc), "r"(acc_first)
+      : "memory");
+}
+__device__ __forceinline__ void umma_f16_x8(uint32_t d, const uint64_t* a, const uint64_t* b, uint32_t idesc, uint32_t acc_first) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p, pt;\n"
+      "setp.ne.b32 p, %18, 0;\n"
+      "setp.eq.b32 pt, 0, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %17, p;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %3, %4, %17, pt;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %5, %6, %17, pt;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %7, %8, %17, pt;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %9, %10, %17, pt;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %11, %12, %17, pt;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %13, %14, %17, pt;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %15, %16, %17, pt;\n"
+      "}\n"
+      ::"r"(d), "l"(a[0]), "l"(b[0]), "l"(a[1]), "l"(b[1]), "l"(a[2]), "l"(b[2]), "l"(a[3]), "l"(b[3]),
+        "l"(a[4]), "l"(b[4]), "l"(a[5]), "l"(b[5]), "l"(a[6]), "l"(b[6]), "l"(a[7]), "l"(b[7]), "r"(idesc), "r"(acc_first)
+      : "memory");
+}
+// Eight MMAs with the A operand in tensor memory: columns a_tmem, a_tmem + 8, ... (16 half
+// elements of K per step).
+__device__ __forceinline__ void umma_f16_ts_x8(uint32_t d, uint32_t a_tmem, const uint64_t* b, uint32_t idesc, uint32_t acc_first) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p, pt;\n"
+      ".reg .b32 a1, a2, a3, a4, a5, a6, a7;\n"
+      "setp.ne.b32 p, %11, 0;\n"
+      "setp.eq.b32 pt, 0, 0;\n"
+      "add.u32 a1, %1, 8;\n"
+      "add.u32 a2, %1, 16;\n"
+      "add.u32 a3, %1, 24;\n"
+      "add.u32 a4, %1, 32;\n"
+      "add.u32 a5, %1, 40;\n"
+      "add.u32 a6, %1, 48;\n"
+      "add.u32 a7, %1, 56;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %10, p;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a1], %3, %10, pt;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a2], %4, %10, pt;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a3], %5, %10, pt;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a4], %6, %10, pt;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a5], %7, %10, pt;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a6], %8, %10, pt;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a7], %9, %10, pt;\n"
+      "}\n"
+      ::"r"(d), "r"(a_tmem), "l"(b[0]), "l"(b[1]), "l"(b[2]), "l"(b[3]), "l"(b[4]), "l"(b[5]), "l"(b[6]), "l"(b[7]),
+        "r"(idesc), "r"(acc_first)
+      : "memory");
+}
 // Makes `bar` complete once all MMAs issued so far by this thread have finished.
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");

@@ -51,7 +51,7 @@ def op_inputs(seed=1):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of the reference project (read only)")
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--skip-train", action="store_true")
     args = ap.parse_args()

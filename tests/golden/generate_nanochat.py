@@ -22,7 +22,7 @@ ROOT = os.path.dirname(os.path.dirname(HERE))
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of the reference project (read only)")
     args = ap.parse_args()
     sys.path[:0] = [os.path.join(HERE, "_cupy_standin"), args.reference,
                     os.path.join(args.reference, "nanochat_trainer", "core"), ROOT]
