@@ -516,3 +516,34 @@ def test_cross_entropy_forward_and_gradient_in_one_pass(mt, dtype, rows, classes
     close(got, want, 2e-2 if dtype != "float32" else 1e-4, "dlogits")
     assert np.all(got[rows // 3] == 0)
     no_device_flag(mt)
+
+
+def test_empty_inputs_are_accepted_everywhere(mt):
+    """Zero rows / zero batch: every entry point returns without launching on nothing and without
+    touching the device status word (the reference's wrappers get such shapes from a last, short
+    batch that a sharded loader can leave empty)."""
+    F = mt.fused_ops
+    Z = lambda *s, dt="float16": mt.DeviceArray.empty(s, dt)
+    g = mt.DeviceArray.from_numpy(np.ones(64, np.float32), "float16")
+    y, mu, rs = F.fused_layernorm_forward(Z(0, 64), g, None)
+    assert y.shape == (0, 64) and mu.shape == (0,)
+    dx, dg, _ = F.fused_layernorm_backward(Z(0, 64), mu, rs, Z(0, 64), g, None)
+    assert dx.shape == (0, 64) and np.all(dg.numpy() == 0)
+    y, rs = F.fused_rmsnorm_forward(Z(0, 64), None)
+    assert y.shape == (0, 64)
+    assert F.fused_softmax_forward(Z(0, 128)).shape == (0, 128)
+    assert F.fused_activation_forward(Z(0, 32), "gelu").shape == (0, 32)
+    assert F.gemm(Z(0, 64), Z(32, 64), trans_b=True).shape == (0, 32)
+    assert F.gemm(Z(16, 64), Z(0, 64), trans_b=True).shape == (16, 0)
+    w = mt.DeviceArray.from_numpy(np.ones((10, 8), np.float32), "float16")
+    idx = mt.DeviceArray.empty((0, 5), "int32")
+    assert F.fused_embedding_forward(w, idx).shape == (0, 5, 8)
+    assert np.all(F.fused_embedding_backward(Z(0, 5, 8), w, idx).numpy() == 0)
+    loss, lse = F.fused_cross_entropy_forward(Z(0, 100), mt.DeviceArray.empty((0,), "int32"))
+    assert loss.shape == (0,)
+    q = Z(0, 2, 128, 64)
+    _, _, _, o, m = F.fused_sdpa_forward(q, q, q, causal=True)
+    assert o.shape == (0, 2, 128, 64)
+    dq, dk, dv = F.fused_sdpa_backward(q, q, q, q, o, m, causal=True)
+    assert dq.shape == dk.shape == dv.shape == (0, 2, 128, 64)
+    no_device_flag(mt)
