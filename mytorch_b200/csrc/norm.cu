@@ -424,13 +424,22 @@ static int norm_fwd_launch(const void* x, const void* gamma, const void* beta, v
   return MT_OK;
 }
 
+// Column sums over no rows are zero: with nothing to launch the parameter gradients are
+// still defined (left alone when they accumulate into existing values).
+static int norm_bwd_no_rows(float* dgamma, float* dbeta, int64_t cols, int accumulate, cudaStream_t st) {
+  if (accumulate & 1) return MT_OK;
+  if (dgamma) MT_CHECK_CUDA(cudaMemsetAsync(dgamma, 0, (size_t)cols * sizeof(float), st));
+  if (dbeta) MT_CHECK_CUDA(cudaMemsetAsync(dbeta, 0, (size_t)cols * sizeof(float), st));
+  return MT_OK;
+}
+
 template <typename T, bool RMS>
 static int norm_bwd_launch(const void* x, const float* mean, const float* rstd, const void* dy,
                            const void* gamma, void* dx, float* dgamma, float* dbeta, int64_t rows,
                            int64_t cols, int accumulate, cudaStream_t st) {
   constexpr int VN = Vec16<T>::N;
   const T* xp = (const T*)x; const T* dyp = (const T*)dy; const T* gp = (const T*)gamma; T* dxp = (T*)dx;
-  if (rows == 0) return MT_OK;
+  if (rows == 0) return norm_bwd_no_rows(dgamma, dbeta, cols, accumulate, st);
   bool vec = cols % VN == 0 && aligned16(x) && aligned16(dy) && aligned16(dx) &&
              (!gamma || aligned16(gamma)) && cols / VN <= 32 * 4;
   const int nvec_all = (int)(cols / VN);
@@ -556,7 +565,7 @@ static int layernorm_bwd_noalloc_launch(const void* x, const float* mean, const 
   MT_REQUIRE(cols % VN == 0 && cols / VN <= 32 * 4 && aligned16(x) && aligned16(dy) && aligned16(dx) &&
              (!gamma || aligned16(gamma)),
              "layernorm_bwd_noalloc: needs 16-byte aligned tensors and cols a multiple of %d, at most %d", VN, 128 * VN);
-  if (rows == 0) return MT_OK;
+  if (rows == 0) return norm_bwd_no_rows(dgamma, dbeta, cols, accumulate, st);
   const int nvec = (int)(cols / VN);
   int64_t want = (rows + kWarpsPerBlock - 1) / kWarpsPerBlock;
   const int grid = (int)(want < kNoAllocMaxBlocks ? want : kNoAllocMaxBlocks);
