@@ -372,34 +372,35 @@ norm_bwd_colsum(const T* __restrict__ x, const float* __restrict__ mean, const f
   }
 }
 
-// Sums the per-block partial rows in a fixed order: block = 32 columns x 32 row
+// Sums the per-block partial rows in a fixed order: block = 8 columns x 32 row
 // groups (row group g adds rows g, g+32, ... in order; the groups are then added
-// in order), so the result does not depend on scheduling.
+// in order), so the result does not depend on scheduling. Grid (ceil(cols / 8), 2):
+// blockIdx.y = 0 reduces dgamma, 1 dbeta. Eight columns are one 32-byte sector of
+// a partial row (the partials are read from L2), and a 768-column norm spreads its
+// 1184 partial rows over 192 blocks.
 constexpr int kFinalizeGroups = 32;
-__global__ void __launch_bounds__(32 * kFinalizeGroups)
+constexpr int kFinalizeCols = 8;
+__global__ void __launch_bounds__(kFinalizeCols * kFinalizeGroups)
 norm_bwd_finalize(const float* __restrict__ partial, int nblocks, int cols,
                   float* __restrict__ dgamma, float* __restrict__ dbeta, int accumulate) {
-  __shared__ float sg[kFinalizeGroups][33], sb[kFinalizeGroups][33];
-  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
-  const int c = blockIdx.x * 32 + tx;
-  float g = 0.f, b = 0.f;
+  __shared__ float sm[kFinalizeGroups][kFinalizeCols + 1];
+  float* out = blockIdx.y ? dbeta : dgamma;
+  if (!out) return;
+  const int tx = threadIdx.x % kFinalizeCols, ty = threadIdx.x / kFinalizeCols;
+  const int c = blockIdx.x * kFinalizeCols + tx;
+  float v = 0.f;
   if (c < cols) {
-#pragma unroll 4
-    for (int i = ty; i < nblocks; i += kFinalizeGroups) {
-      const float* p = partial + (size_t)i * 2 * cols;
-      if (dgamma) g += p[c];
-      if (dbeta) b += p[cols + c];
-    }
+    const float* p = partial + (size_t)blockIdx.y * cols + c;
+#pragma unroll 8
+    for (int i = ty; i < nblocks; i += kFinalizeGroups) v += p[(size_t)i * 2 * cols];
   }
-  sg[ty][tx] = g;
-  sb[ty][tx] = b;
+  sm[ty][tx] = v;
   __syncthreads();
   if (ty == 0 && c < cols) {
-    float ag = 0.f, ab = 0.f;
+    float a = 0.f;
 #pragma unroll
-    for (int i = 0; i < kFinalizeGroups; ++i) { ag += sg[i][tx]; ab += sb[i][tx]; }
-    if (dgamma) dgamma[c] = accumulate ? dgamma[c] + ag : ag;
-    if (dbeta) dbeta[c] = accumulate ? dbeta[c] + ab : ab;
+    for (int i = 0; i < kFinalizeGroups; ++i) a += sm[i][tx];
+    out[c] = accumulate ? out[c] + a : a;
   }
 }
 
@@ -457,7 +458,7 @@ static int norm_bwd_launch(const void* x, const float* mean, const float* rstd, 
 #undef MT_TEAM
     MT_LAUNCH_CHECK();
     if (wg || wb) {
-      norm_bwd_finalize<<<(unsigned)((cols + 31) / 32), 32 * kFinalizeGroups, 0, st>>>((const float*)part.ptr, grid, (int)cols,
+      norm_bwd_finalize<<<dim3((unsigned)((cols + kFinalizeCols - 1) / kFinalizeCols), 2), kFinalizeCols * kFinalizeGroups, 0, st>>>((const float*)part.ptr, grid, (int)cols,
                                                                                      dgamma, dbeta, accumulate & 1);
       MT_LAUNCH_CHECK();
     }
@@ -479,7 +480,7 @@ static int norm_bwd_launch(const void* x, const float* mean, const float* rstd, 
 #undef MT_BWD
     MT_LAUNCH_CHECK();
     if (wg || wb) {
-      norm_bwd_finalize<<<(unsigned)((cols + 31) / 32), 32 * kFinalizeGroups, 0, st>>>((const float*)part.ptr, grid, (int)cols,
+      norm_bwd_finalize<<<dim3((unsigned)((cols + kFinalizeCols - 1) / kFinalizeCols), 2), kFinalizeCols * kFinalizeGroups, 0, st>>>((const float*)part.ptr, grid, (int)cols,
                                                                         dgamma, dbeta, accumulate & 1);
       MT_LAUNCH_CHECK();
     }
@@ -577,7 +578,7 @@ static int layernorm_bwd_noalloc_launch(const void* x, const float* mean, const 
 #undef MT_BWD
   MT_LAUNCH_CHECK();
   if (wg || wb) {
-    norm_bwd_finalize<<<(unsigned)((cols + 31) / 32), 32 * kFinalizeGroups, 0, st>>>(scratch, grid, (int)cols, dgamma, dbeta, accumulate);
+    norm_bwd_finalize<<<dim3((unsigned)((cols + kFinalizeCols - 1) / kFinalizeCols), 2), kFinalizeCols * kFinalizeGroups, 0, st>>>(scratch, grid, (int)cols, dgamma, dbeta, accumulate);
     MT_LAUNCH_CHECK();
   }
   return MT_OK;

@@ -5,6 +5,7 @@
 // Algorithmic traffic: softmax fwd 2*R*C*s, bwd 3*R*C*s; cross entropy fwd
 // R*C*s (one read), bwd 2*R*C*s (read + write).
 #include "common.cuh"
+#include "sm100.cuh"
 
 namespace mt {
 
@@ -332,6 +333,131 @@ ce_fwd_grad_kernel(T* __restrict__ logits, const int32_t* __restrict__ labels, f
   }
 }
 
+// ce_fwd_grad_kernel with the row staged in shared memory. One thread starts bulk copies of the
+// row (kCePieces pieces, one mbarrier each), so the whole row is in flight at once instead of one
+// 16-byte load per thread; the block folds max / sum piece by piece as they land, then computes
+// the gradient from shared memory and writes it straight over the row. Two blocks per SM: one
+// row's arithmetic overlaps the other's copy. Needs classes a multiple of the 16-byte vector,
+// 16-byte aligned rows and a row of at most kCeStagedMaxBytes.
+constexpr int kCePieces = 4;
+constexpr int kCeStagedMaxBytes = 110 * 1024;
+
+__device__ __forceinline__ float ex2_fast(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kCeThreads, 2)
+ce_fwd_grad_staged_kernel(T* __restrict__ logits, const int32_t* __restrict__ labels, float* __restrict__ loss,
+                          float* __restrict__ lse_out, float scale_host, const float* __restrict__ scale_dev,
+                          const float* __restrict__ count_dev, int classes, int64_t ld, float softcap,
+                          int* __restrict__ flag) {
+  constexpr int VN = Vec16<T>::N;
+  extern __shared__ __align__(128) uint8_t ce_row[];   // [nvec * 16 bytes of logits][kCePieces mbarriers][abort word]
+  __shared__ float shm[32], shs[32];
+  __shared__ float row_lse;
+  const int nvec = classes / VN;
+  const int per = (nvec + kCePieces - 1) / kCePieces;
+  const uint32_t sbase = sm100::smem_u32(ce_row);
+  const uint32_t bar0 = sbase + (uint32_t)nvec * 16u;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(ce_row + (size_t)nvec * 16 + 8 * kCePieces);
+  const int64_t row = blockIdx.x;
+  T* xr = logits + row * ld;
+  const T* sr = reinterpret_cast<const T*>(ce_row);
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int p = 0; p < kCePieces; ++p) sm100::mbar_init(bar0 + 8 * p, 1);
+    sm100::fence_barrier_init();
+    sm100::fence_proxy_async();
+    for (int p = 0; p < kCePieces; ++p) {
+      const int v0 = p * per, v1 = min(nvec, v0 + per);
+      if (v1 <= v0) break;
+      const uint32_t bytes = (uint32_t)(v1 - v0) * 16u;
+      sm100::mbar_expect_tx(bar0 + 8 * p, bytes);
+      sm100::bulk_load_1d(sbase + (uint32_t)v0 * 16u, xr + (int64_t)v0 * VN, bytes, bar0 + 8 * p);
+    }
+  }
+  __syncthreads();
+  float m = -INFINITY, s = 0.f;
+  for (int p = 0; p < kCePieces; ++p) {
+    const int v0 = p * per, v1 = min(nvec, v0 + per);
+    if (v1 <= v0) break;
+    if (!sm100::mbar_wait(bar0 + 8 * p, 0, abort_flag)) break;
+    for (int vi = v0 + threadIdx.x; vi < v1; vi += kCeThreads) {
+      Vec16<T> v;
+      v.load(sr + (int64_t)vi * VN);
+      float f[VN];
+      float vm = -INFINITY;
+#pragma unroll
+      for (int e = 0; e < VN; ++e) { f[e] = softcap_f(v.get(e), softcap); vm = fmaxf(vm, f[e]); }
+      if (vm > m) { s *= ex2_fast((m - vm) * kLog2e); m = vm; }
+      const float mb = m * kLog2e;
+#pragma unroll
+      for (int e = 0; e < VN; ++e) s += ex2_fast(fmaf(f[e], kLog2e, -mb));
+    }
+  }
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    float m2 = __shfl_xor_sync(0xffffffffu, m, o), s2 = __shfl_xor_sync(0xffffffffu, s, o);
+    float mm = fmaxf(m, m2);
+    s = (m == -INFINITY ? 0.f : s * exp2f((m - mm) * kLog2e)) + (m2 == -INFINITY ? 0.f : s2 * exp2f((m2 - mm) * kLog2e));
+    m = mm;
+  }
+  if (lane == 0) { shm[w] = m; shs[w] = s; }
+  __syncthreads();   // also: every wait above is over, so the abort word is final
+  if (*abort_flag) {
+    if (threadIdx.x == 0 && flag) atomicMax(flag, 103);   // a row copy did not arrive in time
+    return;
+  }
+  const int32_t label = labels[row];
+  const bool valid = label >= 0 && label < classes;
+  if (w == 0) {
+    m = lane < kCeThreads / 32 ? shm[lane] : -INFINITY;
+    s = lane < kCeThreads / 32 ? shs[lane] : 0.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      float m2 = __shfl_xor_sync(0xffffffffu, m, o), s2 = __shfl_xor_sync(0xffffffffu, s, o);
+      float mm = fmaxf(m, m2);
+      s = (m == -INFINITY ? 0.f : s * exp2f((m - mm) * kLog2e)) + (m2 == -INFINITY ? 0.f : s2 * exp2f((m2 - mm) * kLog2e));
+      m = mm;
+    }
+    if (lane == 0) {
+      const float lse = m + logf(s);
+      lse_out[row] = lse;
+      row_lse = lse;
+      float l = 0.f;
+      if (valid) l = lse - softcap_f(to_f(sr[label]), softcap);
+      else if (label != -100 && flag) atomicMax(flag, 2);  // label out of range: recorded, row ignored
+      loss[row] = l;
+    }
+  }
+  __syncthreads();
+  const float lb = row_lse * kLog2e;
+  float scale = scale_host;
+  if (scale_dev) scale *= scale_dev[0];
+  scale = valid ? scale / count_dev[0] : 0.f;
+  const int label_vec = valid ? label / VN : -1, label_e = valid ? label % VN : 0;
+  for (int vi = threadIdx.x; vi < nvec; vi += kCeThreads) {
+    Vec16<T> v, o;
+    v.load(sr + (int64_t)vi * VN);
+    float pe[VN];
+#pragma unroll
+    for (int e = 0; e < VN; ++e) {
+      float x = v.get(e), f = x, dcap = scale;
+      if (softcap > 0.f) { float t = tanhf(x / softcap); f = softcap * t; dcap = scale * (1.f - t * t); }
+      float pr = valid ? ex2_fast(fmaf(f, kLog2e, -lb)) : 0.f;
+      if (vi == label_vec && e == label_e) pr -= 1.f;
+      pe[e] = pr * dcap;
+    }
+#pragma unroll
+    for (int e = 0; e < VN; ++e) o.set(e, pe[e]);
+    o.store(xr + (int64_t)vi * VN);
+  }
+}
+
 // x[i] *= num[0] / den[0] (device scalars): corrects a gradient that was scaled for another
 // upstream value than the one that finally arrived.
 template <typename T>
@@ -465,9 +591,18 @@ int mt_ce_fwd_grad(void* logits, const int32_t* labels, float* loss, float* lse,
   if (rows > 0) {
     int* flag = device_flag_ptr();
     MT_DISPATCH_FLOAT(dtype, T, {
-      int vec_ok = aligned16(logits) && (ld % Vec16<T>::N == 0);
-      ce_fwd_grad_kernel<T><<<(unsigned)rows, kCeThreads, 0, st>>>((T*)logits, labels, loss, lse, scale_host, scale_dev,
-                                                                 valid_count, classes, ld, softcap, vec_ok, flag);
+      constexpr int VN = Vec16<T>::N;
+      int vec_ok = aligned16(logits) && (ld % VN == 0);
+      const int64_t row_bytes = classes * (int64_t)sizeof(T);
+      if (vec_ok && classes % VN == 0 && row_bytes <= kCeStagedMaxBytes) {
+        const int smem = (int)row_bytes + 8 * kCePieces + 16;
+        MT_CHECK_CUDA(cudaFuncSetAttribute(ce_fwd_grad_staged_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        ce_fwd_grad_staged_kernel<T><<<(unsigned)rows, kCeThreads, smem, st>>>((T*)logits, labels, loss, lse, scale_host, scale_dev,
+                                                                             valid_count, (int)classes, ld, softcap, flag);
+      } else {
+        ce_fwd_grad_kernel<T><<<(unsigned)rows, kCeThreads, 0, st>>>((T*)logits, labels, loss, lse, scale_host, scale_dev,
+                                                                   valid_count, classes, ld, softcap, vec_ok, flag);
+      }
     });
     MT_LAUNCH_CHECK();
   }
