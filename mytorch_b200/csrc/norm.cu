@@ -372,34 +372,46 @@ norm_bwd_colsum(const T* __restrict__ x, const float* __restrict__ mean, const f
   }
 }
 
-// Sums the per-block partial rows in a fixed order: block = 8 columns x 32 row
-// groups (row group g adds rows g, g+32, ... in order; the groups are then added
-// in order), so the result does not depend on scheduling. Grid (ceil(cols / 8), 2):
-// blockIdx.y = 0 reduces dgamma, 1 dbeta. Eight columns are one 32-byte sector of
-// a partial row (the partials are read from L2), and a 768-column norm spreads its
-// 1184 partial rows over 192 blocks.
-constexpr int kFinalizeGroups = 32;
+// Sums the per-block partial rows in a fixed order, so the result does not depend on
+// scheduling: block = 8 columns x 128 row groups; row group g adds rows g, g+128, ... in
+// order (about ten independent loads per thread, all in flight together), then the groups
+// are folded by a fixed tree (shuffles within a warp, shared memory across warps).
+// Grid (ceil(cols / 8), 2): blockIdx.y = 0 reduces dgamma, 1 dbeta. Eight columns are one
+// 32-byte sector of a partial row (the partials are read from L2), and a 768-column norm
+// spreads its 1184 partial rows over 192 blocks.
+constexpr int kFinalizeGroups = 128;
 constexpr int kFinalizeCols = 8;
 __global__ void __launch_bounds__(kFinalizeCols * kFinalizeGroups)
 norm_bwd_finalize(const float* __restrict__ partial, int nblocks, int cols,
                   float* __restrict__ dgamma, float* __restrict__ dbeta, int accumulate) {
-  __shared__ float sm[kFinalizeGroups][kFinalizeCols + 1];
+  constexpr int kWarps = kFinalizeCols * kFinalizeGroups / 32;     // 32: each warp holds 4 row groups x 8 columns
+  __shared__ float sm[kWarps][kFinalizeCols], sm2[kWarps / 4][kFinalizeCols];
   float* out = blockIdx.y ? dbeta : dgamma;
   if (!out) return;
   const int tx = threadIdx.x % kFinalizeCols, ty = threadIdx.x / kFinalizeCols;
   const int c = blockIdx.x * kFinalizeCols + tx;
+  const int w = threadIdx.x >> 5;
   float v = 0.f;
   if (c < cols) {
     const float* p = partial + (size_t)blockIdx.y * cols + c;
-#pragma unroll 8
+#pragma unroll 10
     for (int i = ty; i < nblocks; i += kFinalizeGroups) v += p[(size_t)i * 2 * cols];
   }
-  sm[ty][tx] = v;
+  v += __shfl_xor_sync(0xffffffffu, v, 8);
+  v += __shfl_xor_sync(0xffffffffu, v, 16);
+  if ((threadIdx.x & 31) < kFinalizeCols) sm[w][tx] = v;
   __syncthreads();
-  if (ty == 0 && c < cols) {
+  if (threadIdx.x < kWarps * kFinalizeCols) {       // 256 threads: thread = (warp row ty, column tx)
+    v = sm[ty][tx];
+    v += __shfl_xor_sync(0xffffffffu, v, 8);
+    v += __shfl_xor_sync(0xffffffffu, v, 16);
+    if ((threadIdx.x & 31) < kFinalizeCols) sm2[w][tx] = v;
+  }
+  __syncthreads();
+  if (threadIdx.x < kFinalizeCols && c < cols) {
     float a = 0.f;
 #pragma unroll
-    for (int i = 0; i < kFinalizeGroups; ++i) a += sm[i][tx];
+    for (int i = 0; i < kWarps / 4; ++i) a += sm2[i][tx];
     out[c] = accumulate ? out[c] + a : a;
   }
 }

@@ -2,7 +2,7 @@
 inputs larger than the 126 MB L2 where DRAM figures matter, under 2 GB held on
 the device, a handful of launches.
 
-    python -m mytorch_b200.kernel_cases {gemm|attn|mem|adamw}
+    python -m mytorch_b200.kernel_cases {gemm|attn|mem|adamw|gemm_vs_library|power}
 
 gemm : the GPT-2 124M qkv projection of one 16x1024-token micro-batch
        (16384x768 @ 768x2304, fp16), five launches
@@ -15,6 +15,9 @@ gemm_vs_library : the lm_head GEMM (16384x50304x768, fp16) timed for 300 back-to
        random-normal, small-integer and all-zero operands. Throughput on a power-capped B200
        depends on the operand values (bit toggling), so a roofline fraction only means
        something against a library number taken on the same data.
+power : board power (nvidia-smi, 20 ms samples) while one kernel at a time loops for ~1.5 s at the
+       GPT-2 124M shapes: time per launch x median power = energy per launch. On a 1 kW board the
+       training step runs at the power cap, so its floor is the sum of these energies / 1 kW.
 """
 import sys
 
@@ -52,6 +55,7 @@ def main(which):
             F.fused_layernorm_backward(x, mu, rs, dy, g, None)
             loss, lse = F.fused_cross_entropy_forward(lg, lab)
             F.fused_cross_entropy_backward(lg, lab, lse, scale=1.0)
+            F.fused_cross_entropy_forward_backward(lg, lab)      # what the training step runs
             F.fused_activation_backward(u, du, "gelu")
             F.fused_softmax_forward(randn((ROWS, 1024)))
     elif which == "adamw":
@@ -66,10 +70,93 @@ def main(which):
     elif which == "gemm_vs_library":
         gemm_vs_library(r)
         return
+    elif which == "power":
+        power_by_kernel(randn, r)
+        return
     else:
         raise SystemExit(__doc__)
     synchronize()
     print("done", which)
+
+
+def _time_own(fn, iters, warm=3):
+    import ctypes as C
+    from mytorch_b200 import _lib
+    from mytorch_b200.array import stream
+    for _ in range(warm):
+        fn()
+    e0, e1 = C.c_void_p(), C.c_void_p()
+    _lib.event_create(C.byref(e0)); _lib.event_create(C.byref(e1))
+    _lib.event_record(e0, stream())
+    for _ in range(iters):
+        fn()
+    _lib.event_record(e1, stream())
+    _lib.event_sync(e1)
+    ms = C.c_float()
+    _lib.event_elapsed_ms(e0, e1, C.byref(ms))
+    return ms.value / iters
+
+
+def power_by_kernel(randn, r, seconds=1.5):
+    import subprocess, threading, time
+    import mytorch_b200 as mt
+    samples = []
+
+    def sampler(stop):
+        p = subprocess.Popen(["nvidia-smi", "--query-gpu=clocks.sm,power.draw", "--format=csv,noheader,nounits",
+                              "-lms", "20"], stdout=subprocess.PIPE, text=True)
+        while not stop.is_set():
+            line = p.stdout.readline()
+            if "," in line:
+                samples.append([float(c) for c in line.split(",")])
+        p.terminate()      # the exact child started above
+
+    def sampled(body):
+        samples.clear()
+        stop = threading.Event()
+        th = threading.Thread(target=sampler, args=(stop,))
+        th.start()
+        time.sleep(0.05)
+        out = body()
+        stop.set()
+        th.join()
+        tail = samples[len(samples) // 3:] or [[0.0, 0.0]]     # skip the ramp
+        return out, float(np.median([s[0] for s in tail])), float(np.median([s[1] for s in tail]))
+
+    _, clk, watts = sampled(lambda: time.sleep(1.0))
+    print(f"{'idle (context up)':28s}: {'':10s}   clock {clk:5.0f} MHz | {watts:5.0f} W", flush=True)
+
+    def run(name, fn):
+        per = _time_own(fn, 10)
+        iters = max(10, int(seconds * 1e3 / per))
+        ms, clk, watts = sampled(lambda: _time_own(fn, iters))
+        print(f"{name:28s}: {ms * 1e3:8.1f} us | clock {clk:5.0f} MHz | {watts:5.0f} W | {ms * watts:7.2f} mJ per launch",
+              flush=True)
+
+    a, b = randn((ROWS, 768)), randn((2304, 768))
+    out = DeviceArray.empty((ROWS, 2304), "float16")
+    run("gemm 16384x2304x768", lambda: F.gemm(a, b, trans_b=True, out=out))
+    q, k, v, do = (randn((16, 12, 1024, 64)) for _ in range(4))
+    _, _, _, o, m = F.fused_sdpa_forward(q, k, v, causal=True)
+    run("attention fwd 16x12x1024x64", lambda: F.fused_sdpa_forward(q, k, v, causal=True))
+    run("attention bwd", lambda: F.fused_sdpa_backward(do, q, k, v, o, m, causal=True))
+    x, g, dy = randn((ROWS, 768)), randn((768,)), randn((ROWS, 768))
+    y, mu, rs = F.fused_layernorm_forward(x, g, None)
+    run("layernorm fwd 16384x768", lambda: F.fused_layernorm_forward(x, g, None))
+    run("layernorm bwd", lambda: F.fused_layernorm_backward(x, mu, rs, dy, g, None))
+    lg = randn((ROWS, 50304))
+    lab = DeviceArray.from_numpy(r.integers(0, 50257, ROWS).astype(np.int32))
+    run("cross entropy fwd+grad", lambda: F.fused_cross_entropy_forward_backward(lg, lab))
+    n = 124 * 1024 * 1024
+    p = mt.Tensor(DeviceArray.zeros((n,), "float32"), requires_grad=True)
+    p.is_param = True
+    opt = mt.optim.AdamW([{"params": [p], "weight_decay": 0.1}], lr=1e-3)
+    gz = DeviceArray.zeros((n,), "float32")
+
+    def step():
+        p.grad = gz
+        opt.step()
+    run("AdamW step, 130M fp32", step)
 
 
 def gemm_vs_library(r, m=16384, n=50304, k=768, iters=300):
