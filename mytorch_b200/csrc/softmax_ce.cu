@@ -119,7 +119,19 @@ softmax_bwd_block(const T* __restrict__ dy, const T* __restrict__ s, T* __restri
 }
 
 // ------------------------------------------------------- cross entropy ------
-__device__ __forceinline__ float softcap_f(float x, float cap) { return cap > 0.f ? cap * tanhf(x / cap) : x; }
+// tanh for the logit soft cap in a dozen instructions (tanhf costs several times that and the
+// capped cross entropy evaluates it twice per logit): 1 - 2 / (e^{2x} + 1) with the hardware
+// exp2 (relative error 2^-22), and the odd Taylor polynomial below |x| = 0.1 where that form
+// cancels. Relative error at most 1e-6 over the whole range; saturates to +-1 exactly.
+__device__ __forceinline__ float tanh_cap(float x) {
+  float e;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x * 2.8853900817779268f));   // e^{2x}
+  const float big = 1.f - __fdividef(2.f, e + 1.f);
+  const float x2 = x * x;
+  const float small = x * fmaf(x2, fmaf(x2, fmaf(x2, -17.f / 315.f, 2.f / 15.f), -1.f / 3.f), 1.f);
+  return fabsf(x) < 0.1f ? small : big;
+}
+__device__ __forceinline__ float softcap_f(float x, float cap) { return cap > 0.f ? cap * tanh_cap(__fdividef(x, cap)) : x; }
 
 constexpr int kCeThreads = 512;
 
@@ -316,7 +328,7 @@ ce_fwd_grad_kernel(T* __restrict__ logits, const int32_t* __restrict__ labels, f
 #pragma unroll
       for (int e = 0; e < VN; ++e) {
         float x = v.get(e), f = x, dcap = 1.f;
-        if (softcap > 0.f) { float t = tanhf(x / softcap); f = softcap * t; dcap = 1.f - t * t; }
+        if (softcap > 0.f) { float t = tanh_cap(__fdividef(x, softcap)); f = softcap * t; dcap = 1.f - t * t; }
         float p = valid ? exp2f((f - l) * kLog2e) : 0.f;
         if (vi * VN + e == label) p -= 1.f;
         o.set(e, p * scale * dcap);
@@ -326,7 +338,7 @@ ce_fwd_grad_kernel(T* __restrict__ logits, const int32_t* __restrict__ labels, f
   }
   for (int64_t c = vec_end + threadIdx.x; c < classes; c += kCeThreads) {
     float x = to_f(xr[c]), f = x, dcap = 1.f;
-    if (softcap > 0.f) { float t = tanhf(x / softcap); f = softcap * t; dcap = 1.f - t * t; }
+    if (softcap > 0.f) { float t = tanh_cap(__fdividef(x, softcap)); f = softcap * t; dcap = 1.f - t * t; }
     float p = valid ? exp2f((f - l) * kLog2e) : 0.f;
     if (c == label) p -= 1.f;
     xr[c] = from_f<T>(p * scale * dcap);
@@ -447,7 +459,7 @@ ce_fwd_grad_staged_kernel(T* __restrict__ logits, const int32_t* __restrict__ la
 #pragma unroll
     for (int e = 0; e < VN; ++e) {
       float x = v.get(e), f = x, dcap = scale;
-      if (softcap > 0.f) { float t = tanhf(x / softcap); f = softcap * t; dcap = scale * (1.f - t * t); }
+      if (softcap > 0.f) { float t = tanh_cap(__fdividef(x, softcap)); f = softcap * t; dcap = scale * (1.f - t * t); }
       float pr = valid ? ex2_fast(fmaf(f, kLog2e, -lb)) : 0.f;
       if (vi == label_vec && e == label_e) pr -= 1.f;
       pe[e] = pr * dcap;
@@ -499,7 +511,7 @@ ce_bwd_kernel(const T* __restrict__ logits, const int32_t* __restrict__ labels, 
 #pragma unroll
       for (int e = 0; e < VN; ++e) {
         float x = v.get(e), f = x, dcap = 1.f;
-        if (softcap > 0.f) { float t = tanhf(x / softcap); f = softcap * t; dcap = 1.f - t * t; }
+        if (softcap > 0.f) { float t = tanh_cap(__fdividef(x, softcap)); f = softcap * t; dcap = 1.f - t * t; }
         float p = ignored ? 0.f : exp2f((f - l) * kLog2e);
         if (cc + e == lab) p -= 1.f;
         o.set(e, p * scale * dcap);
@@ -510,7 +522,7 @@ ce_bwd_kernel(const T* __restrict__ logits, const int32_t* __restrict__ labels, 
   }
   for (int64_t cc = c + threadIdx.x; cc < c1; cc += 256) {
     float x = to_f(xr[cc]), f = x, dcap = 1.f;
-    if (softcap > 0.f) { float t = tanhf(x / softcap); f = softcap * t; dcap = 1.f - t * t; }
+    if (softcap > 0.f) { float t = tanh_cap(__fdividef(x, softcap)); f = softcap * t; dcap = 1.f - t * t; }
     float p = ignored ? 0.f : exp2f((f - l) * kLog2e);
     if (cc == lab) p -= 1.f;
     dr[cc] = from_f<T>(p * scale * dcap);
