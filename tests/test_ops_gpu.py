@@ -487,7 +487,8 @@ def test_gemm_stores_activation_derivative_and_multiplies_by_it(mt, dtype, act, 
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("rows,classes,ld,softcap", [(41, 131, 131, None), (64, 50257, 50264, None), (16, 50304, 50304, None),
-                                                     (3, 7, 16, None), (20, 1000, 1000, 15.0)])
+                                                     (3, 7, 16, None), (20, 1000, 1000, 15.0),
+                                                     (8, 4096, 4104, None), (5, 16, 16, None), (4, 24, 32, 15.0)])
 def test_cross_entropy_forward_and_gradient_in_one_pass(mt, dtype, rows, classes, ld, softcap):
     """mt_ce_fwd_grad: same loss / lse / count as the forward kernel, and the logits buffer then
     holds the gradient of the mean loss times the announced upstream value."""
