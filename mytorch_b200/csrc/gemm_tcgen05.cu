@@ -429,6 +429,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   if (PAIR) cluster_sync_all();   // the peer's barriers exist before anything signals them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // Everything above touched only this CTA's shared and tensor memory, so it may overlap the
+  // tail of the previous kernel in the stream; global memory is read and written from here on.
+  griddep_launch();
+  griddep_wait();
 
   const int tiles_mn = P.tiles_m * P.tiles_n;
   const int total_tiles = tiles_mn * P.splits;
@@ -715,6 +719,17 @@ bool gemm_tc_supported(const GemmArgs& g) {
   return true;
 }
 
+// Whether kernels are launched with programmatic stream serialization (their prologue then
+// overlaps the previous kernel's tail). MT_PDL=0 in the environment turns it off.
+static bool overlap_launches() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("MT_PDL");
+    on = (e && e[0] == '0') ? 0 : 1;
+  }
+  return on == 1;
+}
+
 template <bool A_MN, bool B_MN, int BN>
 static int launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& tp,
                      const CUtensorMap& tx, const GemmParams& P, int grid, cudaStream_t st) {
@@ -727,8 +742,19 @@ static int launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const CUtenso
     MT_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
     attr_set[dev] = true;
   }
-  kern<<<grid, kGemmThreads, Cfg::kSmemBytes, st>>>(ta, tb, tc, tp, tx, P);
-  MT_LAUNCH_CHECK();
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3(kGemmThreads);
+  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = overlap_launches() ? 1 : 0;
+  MT_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, tp, tx, P));
+  count_launch();
   return MT_OK;
 }
 
@@ -751,13 +777,15 @@ static int launch_tc_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CU
   cfg.blockDim = dim3(kGemmThreads);
   cfg.dynamicSmemBytes = Cfg::kSmemBytes;
   cfg.stream = st;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = overlap_launches() ? 2 : 1;
   MT_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, tp, tx, P));
   count_launch();
   return MT_OK;

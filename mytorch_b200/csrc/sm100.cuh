@@ -64,6 +64,15 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   return true;
 }
 
+// ---- programmatic dependent launch -------------------------------------------
+// A kernel launched with the programmatic-serialization attribute may start while
+// the kernel before it in the stream still runs; griddep_wait() returns once that
+// kernel has completed and its writes are visible, and must precede every access
+// to global memory. griddep_launch() lets the NEXT kernel in the stream start its
+// own prologue as soon as every CTA of this one has passed the call.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---- TMA: 2-D tiled load global -> shared, completion on an mbarrier ---------
 __device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const CUtensorMap* map, uint32_t bar, int x, int y) {
   asm volatile(
