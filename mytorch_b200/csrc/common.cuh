@@ -106,4 +106,29 @@ __device__ __forceinline__ float block_max(float v, float* sh) {
 
 int sm_count();
 
+// Programmatic dependent launch. A kernel launched through launch_overlapped() may start while
+// the kernel before it in the stream still runs; it must call grid_dependency_wait() before its
+// first access to global memory (the call returns at once in a kernel launched the plain way).
+// allow_dependents() lets the next kernel in the stream start as soon as every block of this one
+// has passed the call. MT_PDL=0 in the environment turns the overlap off (overlap_launches()).
+bool overlap_launches();
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void allow_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_overlapped(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                            Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = overlap_launches() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
 }  // namespace mt

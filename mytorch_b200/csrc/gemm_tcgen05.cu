@@ -719,17 +719,6 @@ bool gemm_tc_supported(const GemmArgs& g) {
   return true;
 }
 
-// Whether kernels are launched with programmatic stream serialization (their prologue then
-// overlaps the previous kernel's tail). MT_PDL=0 in the environment turns it off.
-static bool overlap_launches() {
-  static int on = -1;
-  if (on < 0) {
-    const char* e = getenv("MT_PDL");
-    on = (e && e[0] == '0') ? 0 : 1;
-  }
-  return on == 1;
-}
-
 template <bool A_MN, bool B_MN, int BN>
 static int launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& tp,
                      const CUtensorMap& tx, const GemmParams& P, int grid, cudaStream_t st) {

@@ -23,6 +23,8 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 norm_fwd_warp(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta,
               T* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out,
               int64_t rows, int cols, float eps) {
+  allow_dependents();
+  grid_dependency_wait();
   constexpr int VN = Vec16<T>::N;
   const int lane = threadIdx.x & 31;
   const int64_t row = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
@@ -234,6 +236,8 @@ __global__ void __launch_bounds__(WPR * 32, 768 / (WPR * 32))
 norm_bwd_team(const T* __restrict__ x, const float* __restrict__ mean, const float* __restrict__ rstd_in,
               const T* __restrict__ dy, const T* __restrict__ gamma, T* __restrict__ dx,
               float* __restrict__ partial, int64_t rows, bool want_dg, bool want_db, bool dx_acc) {
+  allow_dependents();
+  grid_dependency_wait();
   constexpr int VN = Vec16<T>::N;
   constexpr int RB = 2;
   constexpr int cols = WPR * 32 * VN;
@@ -384,6 +388,8 @@ constexpr int kFinalizeCols = 8;
 __global__ void __launch_bounds__(kFinalizeCols * kFinalizeGroups)
 norm_bwd_finalize(const float* __restrict__ partial, int nblocks, int cols,
                   float* __restrict__ dgamma, float* __restrict__ dbeta, int accumulate) {
+  allow_dependents();
+  grid_dependency_wait();
   constexpr int kWarps = kFinalizeCols * kFinalizeGroups / 32;     // 32: each warp holds 4 row groups x 8 columns
   __shared__ float sm[kWarps][kFinalizeCols], sm2[kWarps / 4][kFinalizeCols];
   float* out = blockIdx.y ? dbeta : dgamma;
@@ -427,7 +433,7 @@ static int norm_fwd_launch(const void* x, const void* gamma, const void* beta, v
   if (vec) {
     int nvec = (int)(cols / VN);
     dim3 grid((unsigned)((rows + kWarpsPerBlock - 1) / kWarpsPerBlock)), block(kWarpsPerBlock * 32);
-#define MT_FWD(MV) norm_fwd_warp<T, MV, RMS><<<grid, block, 0, st>>>(xp, gp, bp, yp, mean, rstd, rows, (int)cols, eps)
+#define MT_FWD(MV) MT_CHECK_CUDA(launch_overlapped(norm_fwd_warp<T, MV, RMS>, grid, block, 0, st, xp, gp, bp, yp, mean, rstd, rows, (int)cols, eps))
     if (nvec <= 32) MT_FWD(1); else if (nvec <= 64) MT_FWD(2); else if (nvec <= 128) MT_FWD(4); else MT_FWD(8);
 #undef MT_FWD
   } else {
@@ -465,13 +471,14 @@ static int norm_bwd_launch(const void* x, const float* mean, const float* rstd, 
     bool wg = dgamma != nullptr, wb = dbeta != nullptr;
     TempBuf part((wg || wb) ? (size_t)grid * 2 * cols * sizeof(float) : 0, st);
     if (!part.ok()) return MT_ERR_CUDA;
-#define MT_TEAM(W) norm_bwd_team<T, W, RMS><<<grid, W * 32, 0, st>>>(xp, mean, rstd, dyp, gp, dxp, (float*)part.ptr, rows, wg, wb, (accumulate & 2) != 0)
+#define MT_TEAM(W) MT_CHECK_CUDA(launch_overlapped(norm_bwd_team<T, W, RMS>, dim3(grid), dim3(W * 32), 0, st, xp, mean, rstd, dyp, gp, dxp, (float*)part.ptr, rows, wg, wb, (accumulate & 2) != 0))
     if (wpr == 2) MT_TEAM(2); else if (wpr == 3) MT_TEAM(3); else if (wpr == 4) MT_TEAM(4); else MT_TEAM(5);
 #undef MT_TEAM
     MT_LAUNCH_CHECK();
     if (wg || wb) {
-      norm_bwd_finalize<<<dim3((unsigned)((cols + kFinalizeCols - 1) / kFinalizeCols), 2), kFinalizeCols * kFinalizeGroups, 0, st>>>((const float*)part.ptr, grid, (int)cols,
-                                                                                     dgamma, dbeta, accumulate & 1);
+      MT_CHECK_CUDA(launch_overlapped(norm_bwd_finalize, dim3((unsigned)((cols + kFinalizeCols - 1) / kFinalizeCols), 2),
+                                      dim3(kFinalizeCols * kFinalizeGroups), 0, st, (const float*)part.ptr, grid, (int)cols,
+                                      dgamma, dbeta, accumulate & 1));
       MT_LAUNCH_CHECK();
     }
     return MT_OK;

@@ -1,6 +1,7 @@
 // Runtime part of the C ABI: error text, stream-ordered pooled allocation,
 // copies, streams, events, the device status word and per-kernel-class timing.
 #include "common.cuh"
+#include <cstdlib>
 #include "prof.cuh"
 #include <stdarg.h>
 #include <atomic>
@@ -21,6 +22,15 @@ void set_error(const char* fmt, ...) {
   g_err = buf;
 }
 void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+bool overlap_launches() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("MT_PDL");
+    on = (e && e[0] == '0') ? 0 : 1;
+  }
+  return on == 1;
+}
 
 static constexpr int kMaxDev = 16;
 static int* g_flag[kMaxDev] = {nullptr};
