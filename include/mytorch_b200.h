@@ -114,12 +114,13 @@ int mt_layernorm_bwd(const void* x, const float* mean, const float* rstd, const 
  * a host that has handed all device memory to its own arena, code running
  * where cudaMalloc/cudaFree would serialise or fail (for example inside a
  * region that forbids allocation), or a deployment with a fixed memory budget
- * that is audited up front. Same arguments and results as mt_layernorm_bwd; the
- * per-block partial sums of dgamma/dbeta go to a fixed 4 MiB device array inside
- * the library image (every GPU that loads the library holds it until exit).
- * Limits: cols <= 2048, cols a multiple of 8 (fp16/bf16) or 4 (fp32) and at most
- * 1024 (fp16/bf16) / 512 (fp32), tensors 16-byte aligned; anything else is
- * rejected with MT_ERR_INVALID and a message naming the limit. The first call on
+ * that is audited up front. Same arguments (the `accumulate` bit mask included)
+ * and results as mt_layernorm_bwd; the per-block partial sums of dgamma/dbeta go
+ * to a fixed 2 MiB device array inside the library image (every GPU that loads
+ * the library holds it until exit).
+ * Limits: cols at most 1024 (fp16/bf16) or 512 (fp32) and a multiple of 8
+ * (fp16/bf16) or 4 (fp32), tensors 16-byte aligned; anything else is rejected
+ * with MT_ERR_INVALID and a message naming the limit. The first call on
  * a device looks up the array's device address (cudaGetSymbolAddress) and caches
  * it, so make that first call before starting any stream capture. All calls
  * share the one array and it keeps the previous call's contents (each call
@@ -331,12 +332,20 @@ int mt_gradnorm_multi(const mt_tensor_list* L, int g_dtype, const float* inv_sca
  * clip_coef = min(1, max_norm / (sqrt(*sumsq) + 1e-6)) (max_norm <= 0: no clip);
  * skipped entirely when *found_inf != 0. Then the reference AdamW update
  * (decay applied after the Adam step, eps not bias-corrected) and, if p_half
- * is given, the low-precision copy. lr_t = lr*sqrt(1-beta2^t)/(1-beta1^t) is
- * computed on the host and passed in. zero_grad != 0 clears g afterwards. */
+ * is given, the low-precision copy. zero_grad != 0 clears g afterwards.
+ * The step count and the running powers of the betas stay on the device, so a
+ * step skipped because of *found_inf leaves them where they were, as the
+ * reference does by not calling optimizer.step() on an overflow
+ * (mytorch/accelerate.py:342-352): step_state is 8 doubles, two slots of
+ * {t, beta1^t, beta2^t, unused}. A call reads slot `slot` (state after the last
+ * applied step; initialise to {0, 1, 1, 0}) and writes the other one; the caller
+ * alternates `slot` on every call, applied or not. The kernel uses
+ * lr_t = lr * sqrt(1 - beta2^(t+1)) / (1 - beta1^(t+1)). */
 int mt_adamw_multi(const mt_tensor_list* L, int g_dtype, int half_dtype,
-                   float lr, float lr_t, float beta1, float beta2, float eps,
+                   float lr, double beta1, double beta2, float eps,
                    const float* inv_scale_dev, const float* sumsq_dev, float max_norm,
-                   const float* found_inf_dev, int zero_grad, void* stream);
+                   const float* found_inf_dev, int zero_grad, double* step_state, int slot,
+                   void* stream);
 
 /* GradScaler.update (mytorch/accelerate.py:91-121) on the device, so the step never
  * waits for the host: state = {scale, 1/(scale*accum_steps), clean-step counter,

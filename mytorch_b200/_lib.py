@@ -115,7 +115,7 @@ _SIG = {
     "mt_attn_decode": [_p, _p, _p, _p, _S, _S, _S, _i64, _i64, _i64, _i64, _i64, _f, _i, _i, _p],
     "mt_kv_append": [_p, _p, _p, _p, _S, _S, _S, _i64, _i64, _i64, _i64, _i64, _i64, _i, _p],
     "mt_gradnorm_multi": [C.POINTER(TensorList), _i, _p, _p, _p, _p],
-    "mt_adamw_multi": [C.POINTER(TensorList), _i, _i, _f, _f, _f, _f, _f, _p, _p, _f, _p, _i, _p],
+    "mt_adamw_multi": [C.POINTER(TensorList), _i, _i, _f, C.c_double, C.c_double, _f, _p, _p, _f, _p, _i, _p, _i, _p],
     "mt_scaler_update": [_p, _p, _f, _f, _i, _f, _i, _p],
     "mt_comm_unique_id": [_p],
     "mt_comm_init": [_pp, _p, _i, _i],

@@ -268,7 +268,12 @@ class Accelerator:
         """Shards an indexable dataset across ranks by interleaving
         (idx * world + rank, accelerate.py:455); other objects pass through."""
         if self.world_size > 1 and hasattr(loader, "shard"):
-            return loader.shard(self.rank, self.world_size)
+            loader = loader.shard(self.rank, self.world_size)
+        if hasattr(loader, "state_dict") and hasattr(loader, "load_state_dict"):
+            # prepared loaders are checkpointed with the rest of the state (accelerate.py:970-976)
+            if not hasattr(self, "dataloaders"):
+                self.dataloaders = []
+            self.dataloaders.append(loader)
         return loader
 
     def _fused_ctx(self):
@@ -342,18 +347,21 @@ class Accelerator:
     #   model.safetensors  fp32 master of every parameter, keyed by _named_parameters_no_dedup
     #   optimizer.bin      pickled AdamW.state_dict()
     #   mp_config.bin      pickled {scale, growth_factor, backoff_factor, growth_interval, unskipped}
+    #   dataloader_{i}.bin pickled state_dict() of the i-th prepared loader (epoch, batches consumed,
+    #                      shuffled order), so a resumed run continues on the next batch
     # so a run can move between the two implementations mid-training.
     def save_state(self, path_to_checkpoint, save_model_only=False):
         import pickle
         from safetensors.numpy import save_file
         if self.rank == 0:
             os.makedirs(path_to_checkpoint, exist_ok=True)
-            sd = {}
-            for name, p in self.model._named_parameters_no_dedup():
-                i = self._param_index.get(id(p))
-                a = self._flat.view(self._flat.master, i).numpy() if i is not None else p.numpy()
-                sd[name] = np.ascontiguousarray(a, dtype=np.float32)
-            save_file(sd, os.path.join(path_to_checkpoint, "model.safetensors"))
+            if self.model is not None:
+                sd = {}
+                for name, p in self.model._named_parameters_no_dedup():
+                    i = self._param_index.get(id(p))
+                    a = self._flat.view(self._flat.master, i).numpy() if i is not None else p.numpy()
+                    sd[name] = np.ascontiguousarray(a, dtype=np.float32)
+                save_file(sd, os.path.join(path_to_checkpoint, "model.safetensors"))
             if not save_model_only:
                 if getattr(self, "optimizer", None) is not None:
                     with open(os.path.join(path_to_checkpoint, "optimizer.bin"), "wb") as fh:
@@ -365,6 +373,9 @@ class Accelerator:
                            "unskipped": int(st[2])}
                     with open(os.path.join(path_to_checkpoint, "mp_config.bin"), "wb") as fh:
                         pickle.dump(cfg, fh)
+                for idx, loader in enumerate(getattr(self, "dataloaders", [])):
+                    with open(os.path.join(path_to_checkpoint, f"dataloader_{idx}.bin"), "wb") as fh:
+                        pickle.dump(loader.state_dict(), fh)
         self.wait_for_everyone()
 
     def load_state(self, path_to_checkpoint):
@@ -372,7 +383,7 @@ class Accelerator:
         import warnings
         from safetensors.numpy import load_file
         path_to_model = os.path.join(path_to_checkpoint, "model.safetensors")
-        if os.path.exists(path_to_model):
+        if os.path.exists(path_to_model) and self.model is not None:
             sd = load_file(path_to_model)
             for name, p in self.model._named_parameters_no_dedup():
                 i = self._param_index.get(id(p))
@@ -407,3 +418,10 @@ class Accelerator:
             else:
                 warnings.warn("If you are resuming mixed precision training without its checkpointed config, "
                               "you may have instability in training")
+        for idx, loader in enumerate(getattr(self, "dataloaders", [])):
+            path_to_loader = os.path.join(path_to_checkpoint, f"dataloader_{idx}.bin")
+            if os.path.exists(path_to_loader):
+                with open(path_to_loader, "rb") as fh:
+                    loader.load_state_dict(pickle.load(fh))
+            else:
+                warnings.warn(f"Couldn't find {path_to_loader}, cannot resume dataloader, starting from scratch!!")

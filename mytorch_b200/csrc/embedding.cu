@@ -143,9 +143,10 @@ int mt_embedding_bwd(const void* dy, const int32_t* idx, float* dweight, void* s
   size_t cub_bytes = cub_sort_bytes(n);
   iota_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(pos_in, n);
   MT_LAUNCH_CHECK();
-  int bits = 1;
-  while (bits < 32 && (1ll << bits) < vocab) ++bits;
-  MT_CHECK_CUDA(cub::DeviceRadixSort::SortPairs(cub_tmp, cub_bytes, idx, keys_out, pos_in, pos_out, (int)n, 0, bits, st));
+  // All 32 key bits take part: an out-of-range id (the forward pass flags those, the backward kernel
+  // skips them) then sorts before or after every valid id instead of landing, by its low bits,
+  // inside a run of equal valid ids and splitting it between two warps.
+  MT_CHECK_CUDA(cub::DeviceRadixSort::SortPairs(cub_tmp, cub_bytes, idx, keys_out, pos_in, pos_out, (int)n, 0, 32, st));
   count_launch(3);
   MT_DISPATCH_FLOAT(dtype, T, (embedding_bwd_kernel<T><<<(unsigned)((n + 3) / 4), 128, 0, st>>>((const T*)dy, keys_out, pos_out, dweight, n, dim, vocab)));
   MT_LAUNCH_CHECK();

@@ -10,6 +10,8 @@
 //
 // Algorithmic traffic (HBM roofline): forward 2*rows*cols*sizeof(T); backward
 // 3*rows*cols*sizeof(T) (+ negligible stats and partials).
+#include <atomic>
+
 #include "common.cuh"
 #include "tempbuf.cuh"
 
@@ -556,23 +558,27 @@ int mt_rmsnorm_bwd(const void* x, const float* rstd, const void* dy, const void*
 // library image, so the call itself never allocates or frees.
 namespace mt {
 constexpr int kNoAllocMaxBlocks = 256;   // partial rows (grid size cap)
-constexpr int kNoAllocMaxCols = 2048;    // widest row accepted
-static __device__ __align__(256) float g_ln_scratch[kNoAllocMaxBlocks * 2 * kNoAllocMaxCols];  // 4 MiB per GPU
+constexpr int kNoAllocMaxCols = 1024;    // widest row accepted (128 16-byte vectors of fp16/bf16; fp32 rows: 512)
+static __device__ __align__(256) float g_ln_scratch[kNoAllocMaxBlocks * 2 * kNoAllocMaxCols];  // 2 MiB per GPU
 
 // Device address of g_ln_scratch per device; in host code the symbol's name is
 // only a handle, so the address is looked up once per device and cached.
-static float* g_ln_scratch_ptr[16] = {nullptr};
+// Two host threads that race on the first call both look the address up and store the same
+// value, so an atomic slot per device is enough.
+static std::atomic<float*> g_ln_scratch_ptr[16];
 
 static int ln_scratch_address(float** out) {
   int dev = 0;
   MT_CHECK_CUDA(cudaGetDevice(&dev));
   MT_REQUIRE(dev >= 0 && dev < 16, "layernorm_bwd_noalloc: device index %d out of range", dev);
-  if (!g_ln_scratch_ptr[dev]) {
+  float* cached = g_ln_scratch_ptr[dev].load(std::memory_order_acquire);
+  if (!cached) {
     void* p = nullptr;
     MT_CHECK_CUDA(cudaGetSymbolAddress(&p, g_ln_scratch));
-    g_ln_scratch_ptr[dev] = static_cast<float*>(p);
+    cached = static_cast<float*>(p);
+    g_ln_scratch_ptr[dev].store(cached, std::memory_order_release);
   }
-  *out = g_ln_scratch_ptr[dev];
+  *out = cached;
   return MT_OK;
 }
 
@@ -592,12 +598,12 @@ static int layernorm_bwd_noalloc_launch(const void* x, const float* mean, const 
   const bool wg = dgamma != nullptr, wb = dbeta != nullptr;
   dim3 block(kWarpsPerBlock * 32);
   // every block writes its whole partial row, so nothing in the shared scratch has to start at zero
-#define MT_BWD(MV) norm_bwd_warp<T, MV, false><<<grid, block, 0, st>>>(xp, mean, rstd, dyp, gp, dxp, scratch, rows, (int)cols, wg, wb)
+#define MT_BWD(MV) norm_bwd_warp<T, MV, false><<<grid, block, 0, st>>>(xp, mean, rstd, dyp, gp, dxp, scratch, rows, (int)cols, wg, wb, (accumulate & 2) != 0)
   if (nvec <= 32) MT_BWD(1); else if (nvec <= 64) MT_BWD(2); else MT_BWD(4);
 #undef MT_BWD
   MT_LAUNCH_CHECK();
   if (wg || wb) {
-    norm_bwd_finalize<<<dim3((unsigned)((cols + kFinalizeCols - 1) / kFinalizeCols), 2), kFinalizeCols * kFinalizeGroups, 0, st>>>(scratch, grid, (int)cols, dgamma, dbeta, accumulate);
+    norm_bwd_finalize<<<dim3((unsigned)((cols + kFinalizeCols - 1) / kFinalizeCols), 2), kFinalizeCols * kFinalizeGroups, 0, st>>>(scratch, grid, (int)cols, dgamma, dbeta, accumulate & 1);
     MT_LAUNCH_CHECK();
   }
   return MT_OK;

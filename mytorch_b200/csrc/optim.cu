@@ -54,17 +54,29 @@ gradnorm_final_kernel(const float* __restrict__ partial_sq, const float* __restr
 
 template <typename TG, typename TH>
 __global__ void __launch_bounds__(kOptThreads)
-adamw_kernel(mt_tensor_list L, float lr, float lr_t, float beta1, float beta2, float eps,
+adamw_kernel(mt_tensor_list L, float lr, double beta1d, double beta2d, float eps,
              const float* __restrict__ inv_scale, const float* __restrict__ sumsq, float max_norm,
-             const float* __restrict__ found_inf, int zero_grad) {
+             const float* __restrict__ found_inf, int zero_grad, double* __restrict__ step_state, int slot) {
   const int64_t chunk = blockIdx.x;
+  const bool skip_step = found_inf && found_inf[0] != 0.f;
+  // Step counter and running beta powers live on the device and advance only when the update is
+  // applied. Every block reads slot `slot`; block 0 writes the other slot, which the next call reads.
+  const double* cur = step_state + 4 * slot;
+  const double b1p = cur[1] * beta1d, b2p = cur[2] * beta2d;
+  if (chunk == 0 && threadIdx.x == 0) {
+    double* nxt = step_state + 4 * (slot ^ 1);
+    nxt[0] = skip_step ? cur[0] : cur[0] + 1.0;
+    nxt[1] = skip_step ? cur[1] : b1p;
+    nxt[2] = skip_step ? cur[2] : b2p;
+  }
+  const float lr_t = (float)((double)lr * sqrt(1.0 - b2p) / (1.0 - b1p));
+  const float beta1 = (float)beta1d, beta2 = (float)beta2d;
   const int t = L.chunk_tensor[chunk];
   const int64_t off = L.chunk_offset[chunk];
   const int64_t size = L.size[t];
   const int64_t n = size - off < kChunk ? size - off : kChunk;
   TG* g = (TG*)L.g[t] + off;
-  const bool skip = found_inf && found_inf[0] != 0.f;
-  if (skip) {
+  if (skip_step) {
     if (zero_grad) for (int64_t i = threadIdx.x; i < n; i += kOptThreads) g[i] = from_f<TG>(0.f);
     return;
   }
@@ -147,18 +159,19 @@ int mt_gradnorm_multi(const mt_tensor_list* L, int g_dtype, const float* inv_sca
   return MT_OK;
 }
 
-int mt_adamw_multi(const mt_tensor_list* L, int g_dtype, int half_dtype, float lr, float lr_t, float beta1,
-                   float beta2, float eps, const float* inv_scale_dev, const float* sumsq_dev, float max_norm,
-                   const float* found_inf_dev, int zero_grad, void* stream) {
+int mt_adamw_multi(const mt_tensor_list* L, int g_dtype, int half_dtype, float lr, double beta1,
+                   double beta2, float eps, const float* inv_scale_dev, const float* sumsq_dev, float max_norm,
+                   const float* found_inf_dev, int zero_grad, double* step_state, int slot, void* stream) {
   MT_REQUIRE(L && L->n_chunks >= 0 && L->n_tensors >= 0, "adamw_multi: bad list");
+  MT_REQUIRE(step_state && (slot == 0 || slot == 1), "adamw_multi: step_state (8 doubles on the device) and slot 0/1 are required");
   if (L->n_chunks == 0) return MT_OK;
   cudaStream_t st = as_stream(stream);
   if (half_dtype != MT_F16 && half_dtype != MT_BF16) half_dtype = MT_F16;  // only used when p_half is given
   MT_DISPATCH_FLOAT(g_dtype, TG, {
     if (half_dtype == MT_F16)
-      adamw_kernel<TG, __half><<<(unsigned)L->n_chunks, kOptThreads, 0, st>>>(*L, lr, lr_t, beta1, beta2, eps, inv_scale_dev, sumsq_dev, max_norm, found_inf_dev, zero_grad);
+      adamw_kernel<TG, __half><<<(unsigned)L->n_chunks, kOptThreads, 0, st>>>(*L, lr, beta1, beta2, eps, inv_scale_dev, sumsq_dev, max_norm, found_inf_dev, zero_grad, step_state, slot);
     else
-      adamw_kernel<TG, __nv_bfloat16><<<(unsigned)L->n_chunks, kOptThreads, 0, st>>>(*L, lr, lr_t, beta1, beta2, eps, inv_scale_dev, sumsq_dev, max_norm, found_inf_dev, zero_grad);
+      adamw_kernel<TG, __nv_bfloat16><<<(unsigned)L->n_chunks, kOptThreads, 0, st>>>(*L, lr, beta1, beta2, eps, inv_scale_dev, sumsq_dev, max_norm, found_inf_dev, zero_grad, step_state, slot);
   });
   MT_LAUNCH_CHECK();
   return MT_OK;

@@ -254,6 +254,15 @@ def _bhsd_strides(a):
     return _lib.Strides3(H * S * D, S * D, D)
 
 
+def _check_self_attention_shapes(Q, K, V):
+    """The kernels index K and V with Q's batch, head and sequence counts, so anything but equal
+    logical shapes (fewer key/value heads, another key length) would read out of bounds."""
+    if Q.ndim != 4 or K.shape != Q.shape or V.shape != Q.shape:
+        raise NotImplementedError(
+            f"self-attention needs q, k, v of one shape [B,H,S,D]; got {Q.shape}, {K.shape}, {V.shape} "
+            "(grouped-query heads and cross attention are not part of this path)")
+
+
 def fused_sdpa_forward(Q, K, V, attn_mask=None, causal=False, softmax_scale=None, strides=None, out=None,
                        out_strides=None):
     """Q,K,V [B,H,S,D] -> (Q, K, V, O, M) with M the per-row log-sum-exp [B,H,S]
@@ -263,6 +272,7 @@ def fused_sdpa_forward(Q, K, V, attn_mask=None, causal=False, softmax_scale=None
         raise NotImplementedError("attn_mask is not on the GPT training path; use causal=True/False")
     Q, K, V = _A(Q), _A(K), _A(V)
     _check_float(Q, K, V)
+    _check_self_attention_shapes(Q, K, V)
     B, H, S, D = Q.shape
     scale = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(D)
     sq, sk, sv = strides or (_bhsd_strides(Q), _bhsd_strides(K), _bhsd_strides(V))
@@ -280,6 +290,8 @@ def fused_sdpa_backward(dO, Q, K, V, O, M, attn_mask=None, causal=False, softmax
     if attn_mask is not None:
         raise NotImplementedError("attn_mask is not on the GPT training path")
     dO, Q, K, V, O = _A(dO), _A(Q), _A(K), _A(V), _A(O)
+    _check_float(dO, Q, K, V, O)
+    _check_self_attention_shapes(Q, K, V)
     B, H, S, D = Q.shape
     scale = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(D)
     sq, sk, sv = strides or (_bhsd_strides(Q), _bhsd_strides(K), _bhsd_strides(V))

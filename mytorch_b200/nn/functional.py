@@ -333,6 +333,9 @@ def scaled_dot_product_attention(q, k, v, attn_mask=None, is_causal=False, softm
     """q,k,v [B,H,S,D] contiguous (mytorch/nn/functional/flash_attention/
     flash_attention.py:20-127). One backward launch (the reference runs its
     backward kernel twice, :73-91)."""
+    if enable_gqa or k.shape != q.shape or v.shape != q.shape:
+        raise NotImplementedError("grouped-query attention (fewer key/value heads than query heads) is not built; "
+                                  f"q, k, v must share one shape, got {q.shape}, {k.shape}, {v.shape}")
     _, _, _, o, m = K.fused_sdpa_forward(q.data, k.data, v.data, attn_mask, is_causal, softmax_scale)
     out = Tensor(o)
     if _needs_graph(q, k, v):
@@ -353,6 +356,8 @@ def bthd_attention(q, k, v, is_causal=True):
     addressed through strides, so the reference's transpose(1, 2) + contiguous
     copies are not made; the result is [B, T, H*D]."""
     B, T, H, D = q.shape
+    if k.shape != q.shape or v.shape != q.shape:
+        raise NotImplementedError(f"q, k, v must share one shape [B,T,H,D]; got {q.shape}, {k.shape}, {v.shape}")
     st = _lib.Strides3(T * H * D, D, H * D)
     as4 = lambda a: DeviceArray(a.ptr, (B, H, T, D), a.dtype, base=a)      # logical [B,H,T,D] over [B,T,H,D] memory
     qv, kv, vv = as4(q.data), as4(k.data), as4(v.data)

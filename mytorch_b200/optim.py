@@ -73,10 +73,23 @@ class AdamW(Optimizer):
         for group in self.param_groups:
             group["m"] = [DeviceArray.zeros(p.shape, "float32") for p in group["params"]]
             group["v"] = [DeviceArray.zeros(p.shape, "float32") for p in group["params"]]
-            group["t"] = 0
-            group["beta1_pow"] = 1.0
-            group["beta2_pow"] = 1.0
             group["_tables"] = None
+            self._set_step_state(group, 0, 1.0, 1.0)
+
+    # The step count and the running beta powers are device scalars (two slots of doubles, see
+    # mt_adamw_multi): a step that the loss-scale logic skips on the device must not advance them
+    # (the reference does not call optimizer.step() on an overflow, mytorch/accelerate.py:342-352),
+    # and the host never learns about a skip without a read-back.
+    @staticmethod
+    def _set_step_state(group, t, b1p, b2p):
+        host = np.array([t, b1p, b2p, 0.0] * 2, dtype=np.float64)
+        group["_step_state"] = DeviceArray.from_numpy(host.view(np.int64), "int64")
+        group["_slot"] = 0
+
+    @staticmethod
+    def _get_step_state(group):
+        host = group["_step_state"].numpy().view(np.float64).reshape(2, 4)[group["_slot"]]
+        return int(round(host[0])), float(host[1]), float(host[2])
 
     def _tables(self, group):
         ctx = self.fused_ctx or {}
@@ -96,18 +109,15 @@ class AdamW(Optimizer):
     def step(self):
         ctx = self.fused_ctx or {}
         for group in self.param_groups:
-            group["t"] += 1
-            group["beta1_pow"] *= group["beta1"]
-            group["beta2_pow"] *= group["beta2"]
-            lr_t = group["lr"] * (1 - group["beta2_pow"]) ** 0.5 / (1 - group["beta1_pow"])
             t = self._tables(group)
             if t.c.n_tensors == 0:
                 continue
             _lib.adamw_multi(C.byref(t.c), _lib.F32 if t.g_dtype == "float32" else (_lib.F16 if t.g_dtype == "float16" else _lib.BF16),
                              _lib.F16 if t.half_dtype == "float16" else _lib.BF16,
-                             float(group["lr"]), float(lr_t), float(group["beta1"]), float(group["beta2"]),
+                             float(group["lr"]), float(group["beta1"]), float(group["beta2"]),
                              float(group["eps"]), ctx.get("inv_scale"), ctx.get("sumsq"), float(ctx.get("max_norm", 0.0)),
-                             ctx.get("found_inf"), 0, stream())
+                             ctx.get("found_inf"), 0, group["_step_state"].ptr, group["_slot"], stream())
+            group["_slot"] ^= 1
 
     def zero_grad(self):
         for group in self.param_groups:
@@ -120,8 +130,9 @@ class AdamW(Optimizer):
         {lr, beta1, beta2, eps, weight_decay, num_params}]}; the moments are host NumPy arrays."""
         sd = {"state": [], "param_groups": []}
         for g in self.param_groups:
+            t, b1p, b2p = self._get_step_state(g)
             sd["state"].append({"m": [a.numpy() for a in g["m"]], "v": [a.numpy() for a in g["v"]],
-                                "t": g["t"], "beta1_pow": g["beta1_pow"], "beta2_pow": g["beta2_pow"]})
+                                "t": t, "beta1_pow": b1p, "beta2_pow": b2p})
             sd["param_groups"].append({"lr": g["lr"], "beta1": g["beta1"], "beta2": g["beta2"], "eps": g["eps"],
                                        "weight_decay": g["weight_decay"], "num_params": len(g["params"])})
         return sd
@@ -147,7 +158,7 @@ class AdamW(Optimizer):
                 a.set_from_numpy(host(h).reshape(a.shape))
             for a, h in zip(g["v"], st["v"]):
                 a.set_from_numpy(host(h).reshape(a.shape))
-            g["t"], g["beta1_pow"], g["beta2_pow"] = st["t"], st["beta1_pow"], st["beta2_pow"]
+            self._set_step_state(g, st["t"], st["beta1_pow"], st["beta2_pow"])
             lg = sd["param_groups"][i]
             for k in ("lr", "beta1", "beta2", "eps", "weight_decay"):
                 g[k] = lg[k]

@@ -339,6 +339,77 @@ def test_attention(mt, dtype, B, H, S, D, causal):
     no_device_flag(mt)
 
 
+@pytest.mark.parametrize("dtype", ["float16", "bfloat16"])
+@pytest.mark.parametrize("B,T,H,D", [(2, 257, 3, 64), (1, 1000, 2, 64), (2, 257, 2, 128), (1, 1000, 3, 128), (2, 1024, 12, 64)])
+def test_attention_on_strided_projection_layouts(mt, dtype, B, T, H, D):
+    """The tensor-core kernels reading q, k, v in place from the two layouts the models use — the
+    per-head interleaved [q|k|v] projection of GPT-2 (F.qkv_attention) and separate [B,T,H,D]
+    projections (F.bthd_attention) — at ragged and full sequence lengths, forward and backward."""
+    Fn = mt.nn.functional
+    r = np.random.default_rng(21)
+    E = H * D
+    qkv = rnd(r.standard_normal((B, T, H, 3 * D)), dtype)
+    do = rnd(r.standard_normal((B, T, E)), dtype)
+    q, k, v = (np.ascontiguousarray(qkv[..., i * D:(i + 1) * D].transpose(0, 2, 1, 3)) for i in range(3))   # [B,H,T,D]
+    o, p = O.attention_fwd(q, k, v, causal=True)
+    dq, dk, dv = O.attention_bwd(q, k, v, p, do.reshape(B, T, H, D).transpose(0, 2, 1, 3))
+    want_o = o.transpose(0, 2, 1, 3).reshape(B, T, E)
+    want_dqkv = np.concatenate([g.transpose(0, 2, 1, 3) for g in (dq, dk, dv)], axis=-1).reshape(B, T, 3 * E)
+    t = TOL[dtype]
+    # GPT-2 layout
+    x = mt.Tensor(dev(mt, qkv.reshape(B, T, 3 * E), dtype), requires_grad=True)
+    out = Fn.qkv_attention(x, H, is_causal=True)
+    close(out.numpy(), want_o, t, "qkv_attention o")
+    out.backward(dev(mt, do, dtype))
+    close(x.grad.numpy(), want_dqkv, 2 * t, "qkv_attention dqkv")
+    # separate projections, [B,T,H,D]
+    bthd = [mt.Tensor(dev(mt, np.ascontiguousarray(a.transpose(0, 2, 1, 3)), dtype), requires_grad=True) for a in (q, k, v)]
+    out2 = Fn.bthd_attention(*bthd, is_causal=True)
+    close(out2.numpy(), want_o, t, "bthd_attention o")
+    out2.backward(dev(mt, do, dtype))
+    for a, g, name in zip(bthd, (dq, dk, dv), "qkv"):
+        close(a.grad.numpy(), g.transpose(0, 2, 1, 3), 2 * t, f"bthd_attention d{name}")
+    no_device_flag(mt)
+
+
+def test_attention_rejects_mismatched_key_value_shapes(mt):
+    """Fewer key/value heads (grouped-query attention) or another key length are refused on the
+    host: the kernels index K and V with Q's extents."""
+    Fn = mt.nn.functional
+    q = mt.Tensor(mt.DeviceArray.zeros((1, 4, 64, 64), "float16"))
+    kv = mt.Tensor(mt.DeviceArray.zeros((1, 2, 64, 64), "float16"))
+    with pytest.raises(NotImplementedError):
+        Fn.scaled_dot_product_attention(q, kv, kv, is_causal=True)
+    with pytest.raises(NotImplementedError):
+        Fn.scaled_dot_product_attention(q, q, q, is_causal=True, enable_gqa=True)
+    with pytest.raises(NotImplementedError):
+        mt.fused_ops.fused_sdpa_forward(q.data, kv.data, kv.data, causal=True)
+    longer = mt.Tensor(mt.DeviceArray.zeros((1, 128, 4, 64), "float16"))
+    short = mt.Tensor(mt.DeviceArray.zeros((1, 64, 4, 64), "float16"))
+    with pytest.raises(NotImplementedError):
+        Fn.bthd_attention(short, longer, longer)
+
+
+def test_embedding_backward_with_out_of_range_ids_between_equal_ids(mt):
+    """Invalid ids (which the forward pass flags and the backward skips) must not split a run of
+    equal valid ids between two warps: the sums of the valid rows stay exact."""
+    F = mt.fused_ops
+    r = np.random.default_rng(5)
+    V, Dm, n = 300, 64, 4096
+    idx = r.integers(0, 8, n).astype(np.int32)          # long runs of a few ids
+    bad = r.choice(n, 200, replace=False)
+    idx[bad[:100]] = -1
+    idx[bad[100:150]] = V + 5
+    idx[bad[150:]] = (1 << 16) + 3                      # low bits look like a valid id
+    dy = r.standard_normal((n, Dm)).astype(np.float32)
+    w = mt.DeviceArray.zeros((V, Dm), "float32")
+    got = F.fused_embedding_backward(dev(mt, dy, "float32"), w, dev(mt, idx, "int32")).numpy()
+    ok = (idx >= 0) & (idx < V)
+    want = np.zeros((V, Dm), np.float64)
+    np.add.at(want, idx[ok], dy[ok].astype(np.float64))
+    close(got, want, 1e-5, "dW with invalid ids")
+
+
 def test_golden_small_vectors_fp32(mt, golden_ops, op_inputs):
     """The committed reference outputs, fp32, through the library."""
     F = mt.fused_ops

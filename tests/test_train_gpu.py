@@ -121,6 +121,39 @@ def test_mixed_precision_step_tracks_fp32_oracle(half):
         assert np.abs(m - ref).max() <= 6e-3 * max(1.0, np.abs(ref).max()), name   # 6 steps of lr 1e-3
 
 
+def test_gpt2_124m_fp16_amp_steps_track_fp32_oracle():
+    """The full GPT-2 124M (L12 H12 d768 ctx1024, vocabulary padded to 50304, tied head) under
+    fp16 mixed precision with dynamic loss scaling, AdamW lr 6e-4 wd 0.1, clip 1.0, on one
+    sequence of 1024 tokens: five steps on it, losses within 1e-2 of the fp32 oracle stepping the
+    same weights on the same batch (the oracle needs a few seconds per step at this size)."""
+    cfg = og.GPT2Config(vocab_size=50304, max_seq_len=1024, embed_dim=768, mlp_ratio=4, num_blocks=12, num_heads=12)
+    params = og.init_params(cfg, seed=0)
+    mt, model = build(cfg, params)
+    acc = mt.Accelerator(num_gpus=1, rank=0, mixed_precision=True)
+    opt = mt.optim.AdamW(groups(model), lr=6e-4, beta1=0.9, beta2=0.95)
+    model, opt = acc.prepare(model, opt)
+    loss_fn = mt.nn.CrossEntropyLoss(fused_backward=True)      # the loss path the benchmark uses
+    ref_opt = og.AdamW(params, 6e-4, 0.9, 0.95, 1e-8, 0.1)
+    x, y = og.synthetic_batch(np.random.default_rng(3), 1, 1024, 50257)    # one batch, revisited: the loss moves fast
+    got, want = [], []
+    for step in range(5):
+        loss = loss_fn(model(mt.Tensor(x)), mt.Tensor(y))
+        acc.backward(loss)
+        acc.clip_grad_norm_(1.0)
+        opt.step()
+        opt.zero_grad()
+        got.append(loss.item())
+        rl, _, cache = og.forward(params, cfg, x, y)
+        g = og.backward(params, cfg, cache)
+        O.clip_grad_norm(list(g.values()), 1.0)
+        ref_opt.step(params, g)
+        want.append(float(rl))
+    got, want = np.array(got), np.array(want)
+    assert acc.scaler.skipped_steps == 0
+    assert np.abs(got - want).max() <= 1e-2 * np.abs(want).max(), (got, want)
+    assert want[-1] < want[0] - 0.5, want        # the steps did move the loss, so the comparison means something
+
+
 def test_overflow_skips_the_step_and_halves_the_scale():
     """An inf planted in the gradient buffer (host-made input, no device fault):
     the fused update must leave weights and moments untouched, clear nothing it
@@ -147,12 +180,18 @@ def test_overflow_skips_the_step_and_halves_the_scale():
     assert np.array_equal(acc._flat.master.numpy(), before)
     assert not acc._flat.m.numpy().any()
     assert not acc._flat.grad.numpy().any()
-    # the next clean step proceeds
+    # the skipped step advanced neither the step count nor the beta powers (the reference does not
+    # call optimizer.step() on an overflow, mytorch/accelerate.py:342-352)
+    for st in opt.state_dict()["state"]:
+        assert (st["t"], st["beta1_pow"], st["beta2_pow"]) == (0, 1.0, 1.0), st
+    # the next clean step proceeds, with the bias correction of a FIRST step
     loss = mt.nn.CrossEntropyLoss()(model(mt.Tensor(x)), mt.Tensor(y))
     acc.backward(loss)
     opt.step()
     assert not np.array_equal(acc._flat.master.numpy(), before)
     assert acc.scaler.unskipped == 1
+    for st, grp in zip(opt.state_dict()["state"], opt.param_groups):
+        assert st["t"] == 1 and st["beta1_pow"] == grp["beta1"] and st["beta2_pow"] == grp["beta2"], st
 
 
 def test_adamw_multi_tensor_matches_reference_golden(golden_ops, op_inputs):
@@ -329,6 +368,56 @@ def test_checkpoint_files_match_reference_layout_and_resume(tmp_path):
     resumed = run(mt2, model2, acc2, opt2, rng2, 3)
     # split-K gradient accumulation adds in a scheduling-dependent order: equal to fp32 round-off
     assert np.allclose(resumed, straight, rtol=2e-4, atol=0), (resumed, straight)
+
+
+def test_checkpoint_carries_the_prepared_dataloader(tmp_path):
+    """A loader handed to Accelerator.prepare is written as dataloader_0.bin (accelerate.py:970-976)
+    and a resumed run continues on the batch after the last one consumed, in the same shuffled
+    order; a checkpoint without the file warns and starts the epoch over (accelerate.py:1036-1047)."""
+    import os
+    import pickle
+    import warnings
+    import mytorch_b200 as mt
+    from mytorch_b200.utils.data import DataLoader, Dataset
+
+    class Rows(Dataset):
+        def __len__(self):
+            return 37
+
+        def __getitem__(self, i):
+            return np.array([i, 2 * i], dtype=np.int32)
+
+    np.random.seed(11)
+    acc = mt.Accelerator(num_gpus=1, rank=0)
+    (dl,) = acc.prepare(DataLoader(Rows(), batch_size=4, shuffle=True))
+    it = iter(dl)
+    seen = [next(it)[:, 0].copy() for _ in range(3)]
+    ckpt = str(tmp_path / "ckpt")
+    acc.save_state(ckpt)
+    rest = []
+    while True:
+        try:
+            rest.append(next(it)[:, 0].copy())
+        except StopIteration:
+            break
+    with open(os.path.join(ckpt, "dataloader_0.bin"), "rb") as fh:
+        st = pickle.load(fh)
+    assert st["batches_consumed"] == 3 and st["epoch"] == 0 and len(st["shuffled_indices"]) == 37
+
+    acc2 = mt.Accelerator(num_gpus=1, rank=0)
+    (dl2,) = acc2.prepare(DataLoader(Rows(), batch_size=4, shuffle=True))
+    acc2.load_state(ckpt)
+    rest2 = [b[:, 0].copy() for b in dl2]
+    assert len(rest2) == len(rest) and all(np.array_equal(a, b) for a, b in zip(rest, rest2))
+    assert sorted(np.concatenate(seen + rest2).tolist()) == list(range(37))
+
+    os.remove(os.path.join(ckpt, "dataloader_0.bin"))
+    acc3 = mt.Accelerator(num_gpus=1, rank=0)
+    acc3.prepare(DataLoader(Rows(), batch_size=4, shuffle=True))
+    with warnings.catch_warnings(record=True) as w:
+        warnings.simplefilter("always")
+        acc3.load_state(ckpt)
+    assert any("cannot resume dataloader" in str(x.message) for x in w)
 
 
 def test_dataloader_device_staging_feeds_the_same_batches():
