@@ -151,7 +151,7 @@ def test_gpt2_124m_fp16_amp_steps_track_fp32_oracle():
     got, want = np.array(got), np.array(want)
     assert acc.scaler.skipped_steps == 0
     assert np.abs(got - want).max() <= 1e-2 * np.abs(want).max(), (got, want)
-    assert want[-1] < want[0] - 0.5, want        # the steps did move the loss, so the comparison means something
+    assert want.min() < want[0] - 0.5, want      # the steps did move the loss, so the comparison means something
 
 
 def test_overflow_skips_the_step_and_halves_the_scale():
