@@ -2,7 +2,7 @@
 inputs larger than the 126 MB L2 where DRAM figures matter, under 2 GB held on
 the device, a handful of launches.
 
-    python -m mytorch_b200.kernel_cases {gemm|attn|mem|adamw|gemm_vs_library|power}
+    python kernel_cases.py {gemm|attn|mem|adamw|gemm_vs_library|power|suite}
 
 gemm : the GPT-2 124M qkv projection of one 16x1024-token micro-batch
        (16384x768 @ 768x2304, fp16), five launches
@@ -18,7 +18,14 @@ gemm_vs_library : the lm_head GEMM (16384x50304x768, fp16) timed for 300 back-to
 power : board power (nvidia-smi, 20 ms samples) while one kernel at a time loops for ~1.5 s at the
        GPT-2 124M shapes: time per launch x median power = energy per launch. On a 1 kW board the
        training step runs at the power cap, so its floor is the sum of these energies / 1 kW.
+suite : the isolated fused-op suite at its stated shapes (attention 8x12x1024x64 causal, LayerNorm
+       16384x768, softmax 16384x1024, cross entropy 8192x50304, matmul 8192x768x3072), each op
+       forward and backward in fp16 and fp32, timed with CUDA events over inputs that rotate
+       through more than the 126 MB L2, with the achieved TFLOP/s or GB/s and its fraction of the
+       measured peak (MEASURED_PEAKS.json beside this file, else 6650 GB/s / 1590 TFLOP/s).
 """
+import json
+import os
 import sys
 
 import numpy as np
@@ -73,10 +80,109 @@ def main(which):
     elif which == "power":
         power_by_kernel(randn, r)
         return
+    elif which == "suite":
+        op_suite(r)
+        return
     else:
         raise SystemExit(__doc__)
     synchronize()
     print("done", which)
+
+
+def op_suite(r):
+    """Times every op of the isolated suite, forward and backward, fp16 and fp32."""
+    try:
+        with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")) as fh:
+            pk = json.load(fh)
+        hbm, tf, src = pk["hbm_gbs"], pk["bf16_tflops"], "of measured"
+    except Exception:
+        hbm, tf, src = 6650.0, 1590.0, "of fallback"
+    print(f"peaks: HBM {hbm:.0f} GB/s, tensor {tf:.0f} TFLOP/s (burst) - fractions are {src}")
+    print(f"{'op':34s} {'dtype':8s} {'us':>9s} {'achieved':>16s} {'frac':>6s}")
+
+    def report(name, dt, ms, flops=None, nbytes=None):
+        if flops is not None:
+            a = flops / ms / 1e9
+            # fp32 GEMM and attention run on the CUDA cores (full fp32 for the 1e-4 parity bar): no tensor roofline
+            frac = f"{a / tf:6.3f}" if dt == "float16" else "   n/a"
+            print(f"{name:34s} {dt:8s} {ms * 1e3:9.1f} {a:10.1f} TFLOP/s {frac}", flush=True)
+        else:
+            a = nbytes / ms / 1e6
+            print(f"{name:34s} {dt:8s} {ms * 1e3:9.1f} {a:10.0f} GB/s    {a / hbm:6.3f}", flush=True)
+
+    def rotating(make, min_bytes=300e6):
+        """Enough independent input sets that consecutive launches never find their data in L2."""
+        first = make()
+        per = sum(a.nbytes for a in first if isinstance(a, DeviceArray))
+        sets = [first] + [make() for _ in range(max(1, int(min_bytes / max(per, 1))))]
+        return sets
+
+    def timed(sets, fn, iters=None):
+        n = len(sets)
+        it = [0]
+
+        def one():
+            fn(*sets[it[0] % n])
+            it[0] += 1
+        per = _time_own(one, 3, warm=2)
+        return _time_own(one, iters or max(10, min(200, int(300.0 / max(per, 1e-3)))))
+
+    for dt in ("float16", "float32"):
+        sz = 2 if dt == "float16" else 4
+        rn = lambda shape: DeviceArray.from_numpy(r.standard_normal(shape, dtype=np.float32), dt)
+        # (a) attention
+        B, H, S, D = 8, 12, 1024, 64
+        sets = rotating(lambda: tuple(rn((B, H, S, D)) for _ in range(4)))
+        iters = 50 if dt == "float16" else 5
+        ms = timed(sets, lambda q, k, v, do: F.fused_sdpa_forward(q, k, v, causal=True), iters)
+        report("attention fwd 8x12x1024x64 causal", dt, ms, flops=2.0 * B * H * S * S * D)
+        saved = [F.fused_sdpa_forward(q, k, v, causal=True)[3:] for q, k, v, _ in sets]
+        full = [s_ + tuple(o) for s_, o in zip(sets, saved)]
+        ms = timed(full, lambda q, k, v, do, o, m: F.fused_sdpa_backward(do, q, k, v, o, m, causal=True), iters)
+        report("attention bwd", dt, ms, flops=5.0 * B * H * S * S * D)
+        del sets, saved, full
+        # (b) LayerNorm
+        N, E = 16384, 768
+        g, b = DeviceArray.from_numpy(np.ones(E, np.float32), dt), DeviceArray.from_numpy(np.zeros(E, np.float32), dt)
+        sets = rotating(lambda: (rn((N, E)), rn((N, E))))
+        ms = timed(sets, lambda x, dy: F.fused_layernorm_forward(x, g, b))
+        report("layernorm fwd 16384x768", dt, ms, nbytes=2.0 * N * E * sz)
+        full = [(x, dy) + tuple(F.fused_layernorm_forward(x, g, b)[1:]) for x, dy in sets]
+        ms = timed(full, lambda x, dy, mu, rs: F.fused_layernorm_backward(x, mu, rs, dy, g, b))
+        report("layernorm bwd", dt, ms, nbytes=3.0 * N * E * sz)
+        del sets, full
+        # (c) softmax
+        N, Cc = 16384, 1024
+        sets = rotating(lambda: (rn((N, Cc)), rn((N, Cc))))
+        ms = timed(sets, lambda x, dy: F.fused_softmax_forward(x))
+        report("softmax fwd 16384x1024", dt, ms, nbytes=2.0 * N * Cc * sz)
+        full = [(F.fused_softmax_forward(x), dy) for x, dy in sets]
+        ms = timed(full, lambda s_, dy: F.fused_softmax_backward(dy, s_))
+        report("softmax bwd", dt, ms, nbytes=3.0 * N * Cc * sz)
+        del sets, full
+        # (d) cross entropy: one set is already 0.8-1.6 GB
+        N, Cc = 8192, 50304
+        lab = DeviceArray.from_numpy(r.integers(0, 50257, N).astype(np.int32))
+        x = rn((N, Cc))
+        ms = _time_own(lambda: F.fused_cross_entropy_forward(x, lab), 20)
+        report("cross entropy fwd 8192x50304", dt, ms, nbytes=1.0 * N * Cc * sz)
+        _, lse = F.fused_cross_entropy_forward(x, lab)
+        ms = _time_own(lambda: F.fused_cross_entropy_backward(x, lab, lse, scale=1.0), 20)   # in place: values stay bounded
+        report("cross entropy bwd (in place)", dt, ms, nbytes=2.0 * N * Cc * sz)
+        ms = _time_own(lambda: F.fused_cross_entropy_forward_backward(x, lab, scale=float(N)), 20)
+        report("cross entropy fwd+grad, one pass", dt, ms, nbytes=2.0 * N * Cc * sz)
+        del x
+        # (e) matmul as Linear: X[8192,768], W[3072,768]
+        M, Kk, Nn = 8192, 768, 3072
+        sets = rotating(lambda: (rn((M, Kk)), rn((Nn, Kk)), rn((M, Nn))))
+        iters = 100 if dt == "float16" else 5
+        ms = timed(sets, lambda x, w, dy: F.gemm(x, w, trans_b=True), iters)
+        report("matmul fwd 8192x768x3072", dt, ms, flops=2.0 * M * Kk * Nn)
+        ms = timed(sets, lambda x, w, dy: F.gemm(dy, w), iters)
+        report("matmul dgrad", dt, ms, flops=2.0 * M * Kk * Nn)
+        ms = timed(sets, lambda x, w, dy: F.gemm(dy, x, trans_a=True, out_dtype="float32"), iters)
+        report("matmul wgrad (fp32 out)", dt, ms, flops=2.0 * M * Kk * Nn)
+        del sets
 
 
 def _time_own(fn, iters, warm=3):

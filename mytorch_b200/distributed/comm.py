@@ -113,6 +113,11 @@ class NCCLBackend:
         self._ev_done = self._new_event()
         self._bucket_events = []
         self._ov_active = False
+        # With record_exposed set, every gradient sync leaves a pair of events: the compute stream's
+        # position when it starts waiting, and the end of the last reduction on the comm stream.
+        # exposed_ms() turns the pairs into the time the compute stream actually waited.
+        self.record_exposed = False
+        self._exposed_pairs = []
 
     @staticmethod
     def _new_event():
@@ -186,9 +191,31 @@ class NCCLBackend:
         wait for all bucket reductions."""
         for b in range(len(self._ov_buckets)):
             self._launch_bucket(b)
-        _lib.event_record(self._ev_done, self.comm_stream)
-        _lib.stream_wait_event(stream(), self._ev_done)
+        self._join_compute_stream()
         self._ov_active = False
+
+    def _join_compute_stream(self):
+        done = self._ev_done
+        if self.record_exposed:
+            arrived, done = self._new_event(), self._new_event()
+            _lib.event_record(arrived, stream())
+            self._exposed_pairs.append((arrived, done))
+        _lib.event_record(done, self.comm_stream)
+        _lib.stream_wait_event(stream(), done)
+
+    def exposed_ms(self):
+        """Mean over the recorded gradient syncs of max(0, end of the last reduction - moment the
+        compute stream began to wait), in ms; clears the records. Call with the device idle."""
+        waits = []
+        for arrived, done in self._exposed_pairs:
+            _lib.event_sync(done)
+            ms = C.c_float()
+            _lib.event_elapsed_ms(arrived, done, C.byref(ms))
+            waits.append(max(0.0, ms.value))
+            _lib.event_destroy(arrived)
+            _lib.event_destroy(done)
+        self._exposed_pairs = []
+        return sum(waits) / len(waits) if waits else 0.0
 
     def allreduce_grads(self, grad_flat, bucket_elems):
         """In-place mean of the flat fp32 gradient buffer across ranks, bucket by
@@ -198,5 +225,4 @@ class NCCLBackend:
         for off, cnt in plan_buckets(grad_flat.size, bucket_elems):
             p = grad_flat.ptr + off * 4
             _lib.comm_allreduce(self.handle, p, p, cnt, _lib.F32, _OPS["avg"], self.comm_stream)
-        _lib.event_record(self._ev_done, self.comm_stream)
-        _lib.stream_wait_event(stream(), self._ev_done)
+        self._join_compute_stream()

@@ -177,6 +177,13 @@ class GPT(nn.Module):
         self.cos, self.sin = F.precompute_rotary_cos_sin(config.embed_dim // config.num_q_heads,
                                                          config.max_seq_len, config.rope_base)
         self._gradient_checkpointing_enabled = False
+        # How forward(input_ids, target_ids) produces the loss. "logits": (logits, loss) as the
+        # reference returns them. "fused": the loss writes the gradient of the logits over them in
+        # its forward pass (one read and one write of the [tokens, vocab] tensor) and None is
+        # returned in their place. "chunked": lm_head and loss walk the vocabulary in chunks and
+        # the logits are never held (F.lm_head_cross_entropy); None is returned in their place.
+        self.loss_mode = "logits"
+        self.loss_chunk = 8192
 
     def enable_gradient_checkpointing(self):
         """Recompute each block in the backward pass (nanochat_gpt.py:318-322)."""
@@ -198,6 +205,9 @@ class GPT(nn.Module):
             else:
                 x = block(x, (cos, sin))
         x = norm(x)
+        if target_ids is not None and self.loss_mode == "chunked" and self.lm_head.bias is None:
+            return None, F.lm_head_cross_entropy(x, self.lm_head.weight, target_ids, chunk=self.loss_chunk,
+                                                 softcap=self.config.softcap)
         logits = self.lm_head(x)
         if target_ids is None:
             # inference branch (nanochat_gpt.py:334-340): soft-capped logits, plus the cache if one was given
@@ -205,6 +215,8 @@ class GPT(nn.Module):
                 arr = logits.data
                 _lib.softcap(arr.ptr, arr.ptr, arr.size, float(self.config.softcap), arr.code, stream())
             return (logits,) if cache is None else (logits, cache)
+        if self.loss_mode == "fused":
+            return None, F.cross_entropy(logits, target_ids, softcap=self.config.softcap, fused_backward=True)
         loss = F.cross_entropy(logits, target_ids, softcap=self.config.softcap)
         return logits, loss
 

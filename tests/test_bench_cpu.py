@@ -36,3 +36,20 @@ def test_accumulation_keeps_the_global_batch():
     for n in (2, 4, 8):
         cfg = b.config_dict(n, b.accum_for(n))
         assert cfg["global_batch_tokens"] == 524288 and cfg["grad_accum"] * n == 32
+
+
+def test_d20_workload_arithmetic():
+    b = load_bench()
+    assert b.accum_for(1, "d20") == 1 and b.accum_for(8, "d20") == 1 and b.accum_for(2, "d20") == 4
+    for n in (2, 4, 8):
+        assert b.config_dict(n, b.accum_for(n, "d20"), "d20")["global_batch_tokens"] == 524288
+    # 6 * P_mm + 6 * L * T * d with P_mm = 477 102 080 matmul weights (untied head, no embedding)
+    assert b.flops_per_token(b.D20_CFG, 2048) == 6 * 477102080 + 6 * 20 * 2048 * 1280
+    assert b.flops_per_token() == 798031872
+
+
+def test_roofline_traffic_comes_from_the_capture_on_file():
+    b = load_bench()
+    cap = b.gemm_capture()
+    assert cap["traffic_bytes_per_launch"] == cap["dram_bytes_read"] + cap["dram_bytes_write"]
+    assert os.path.exists(os.path.join(ROOT, cap["summary"])) and os.path.exists(os.path.join(ROOT, cap["library_summary"]))
