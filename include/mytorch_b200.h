@@ -220,6 +220,26 @@ int mt_pos_embedding_bwd(const void* dy, float* dwpe, int64_t batch, int64_t seq
 int mt_rope(void* x, const float* cos, const float* sin, int64_t batch, int64_t seq,
             int64_t heads, int64_t head_dim, int backward, int dtype, void* stream);
 
+/* Rotary embedding THEN parameter-free RMSNorm over head_dim, on q and on k, in one pass over
+ * each tensor: the three statements of nanochat_trainer/core/nanochat_gpt.py:119-124
+ * (apply_rotary_pos_embed, norm(q), norm(k)), i.e. fused_rope_forward (fused_ops/rope.py:178)
+ * followed by fused_rmsnorm_forward with gamma = None (fused_ops/rmsnorm.py:159), and their
+ * backward passes in reverse order. Head h of token (b, t) starts at
+ * base + (b*seq + t) * ld + h * head_dim elements, so [B,T,H,D] tensors (ld = H*D) and column
+ * slices of a wider projection are read in place. xk/yk/rstd_k (dyk/...) may be NULL to process
+ * one tensor. rstd is fp32 [B*T*H]. The rotation happens in fp32 registers (the reference
+ * rounds the rotated values to the activation dtype before the norm).
+ * bwd takes the SAVED OUTPUT y (for a norm without gamma, x_hat = y) and rstd:
+ *   dr = rstd * (dy - y * mean(dy * y)),  dx = rotation of dr by the negative angle.
+ * head_dim must be 2, 4, 8, 16 or 32 16-byte vectors (64 or 128 for fp16/bf16). */
+int mt_rope_rmsnorm_fwd(const void* xq, const void* xk, void* yq, void* yk, float* rstd_q, float* rstd_k,
+                        const float* cos, const float* sin, int64_t batch, int64_t seq, int64_t heads,
+                        int64_t head_dim, int64_t ld_x, int64_t ld_y, float eps, int dtype, void* stream);
+int mt_rope_rmsnorm_bwd(const void* dyq, const void* dyk, const void* yq, const void* yk,
+                        const float* rstd_q, const float* rstd_k, void* dxq, void* dxk,
+                        const float* cos, const float* sin, int64_t batch, int64_t seq, int64_t heads,
+                        int64_t head_dim, int64_t ld_dy, int64_t ld_y, int64_t ld_dx, int dtype, void* stream);
+
 /* fused_linear_forward (mytorch/nn/functional/fused_ops/linear.py:118),
  * fused_grouped_matmul (mytorch/nn/functional/fused_ops/matmul.py:842) and
  * cupy.matmul reached from mytorch/nn/functional/layers/linear.py:86,104,123.

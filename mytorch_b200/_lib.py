@@ -104,6 +104,8 @@ _SIG = {
     "mt_embedding_pos_fwd": [_p, _p, _p, _p, _i64, _i64, _i64, _i64, _i, _p],
     "mt_pos_embedding_bwd": [_p, _p, _i64, _i64, _i64, _i, _p],
     "mt_rope": [_p, _p, _p, _i64, _i64, _i64, _i64, _i, _i, _p],
+    "mt_rope_rmsnorm_fwd": [_p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _f, _i, _p],
+    "mt_rope_rmsnorm_bwd": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i, _p],
     "mt_gemm": [_p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _i, _f, _i, _p],
     "mt_gemm_ex": [_p, _p, _p, _p, _p, _p, _i, _i64, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _i, _f, _i, _p],
     "mt_gemm_force_simt": [_i],

@@ -227,7 +227,7 @@ norm_bwd_warp(const T* __restrict__ x, const float* __restrict__ mean, const flo
 }
 
 // Row-team variant for rows of exactly WPR*32 16-byte vectors (768 half columns = 3 warps, 1280 =
-// 5): a block is one team, a thread owns ONE vector (8 half columns) of every row the block
+// 5, 768 fp32 columns = 6): a block is one team, a thread owns ONE vector (8 half columns) of every row the block
 // visits, so its dgamma/dbeta accumulators are 16 registers instead of the 48-64 of the
 // warp-per-row kernel and more warps fit an SM. Two rows are in flight per thread; the row
 // sums of the team's warps meet in shared memory (one __syncthreads per two rows, double
@@ -461,11 +461,12 @@ static int norm_bwd_launch(const void* x, const float* mean, const float* rstd, 
   constexpr int VN = Vec16<T>::N;
   const T* xp = (const T*)x; const T* dyp = (const T*)dy; const T* gp = (const T*)gamma; T* dxp = (T*)dx;
   if (rows == 0) return norm_bwd_no_rows(dgamma, dbeta, cols, accumulate, st);
-  bool vec = cols % VN == 0 && aligned16(x) && aligned16(dy) && aligned16(dx) &&
-             (!gamma || aligned16(gamma)) && cols / VN <= 32 * 4;
+  const bool al = cols % VN == 0 && aligned16(x) && aligned16(dy) && aligned16(dx) && (!gamma || aligned16(gamma));
+  const bool vec = al && cols / VN <= 32 * 4;
   const int nvec_all = (int)(cols / VN);
-  if (vec && sizeof(T) == 2 && cols % (32 * VN) == 0 && nvec_all / 32 >= 2 && nvec_all / 32 <= 5) {
-    // rows of 2..5 warps of vectors (512..1280 half columns): one thread per vector
+  if (al && cols % (32 * VN) == 0 && nvec_all / 32 >= 2 && (nvec_all / 32 <= 6 || nvec_all / 32 == 8)) {
+    // rows of 2..6 or 8 warps of vectors (512..1536 and 2048 half columns, 256..768 and 1024 fp32
+    // columns): one thread per vector
     const int wpr = nvec_all / 32;
     const int per_sm = 768 / (wpr * 32);      // resident blocks (the kernel is compiled for this occupancy)
     int64_t want = (rows + 1) / 2;
@@ -474,7 +475,8 @@ static int norm_bwd_launch(const void* x, const float* mean, const float* rstd, 
     TempBuf part((wg || wb) ? (size_t)grid * 2 * cols * sizeof(float) : 0, st);
     if (!part.ok()) return MT_ERR_CUDA;
 #define MT_TEAM(W) MT_CHECK_CUDA(launch_overlapped(norm_bwd_team<T, W, RMS>, dim3(grid), dim3(W * 32), 0, st, xp, mean, rstd, dyp, gp, dxp, (float*)part.ptr, rows, wg, wb, (accumulate & 2) != 0))
-    if (wpr == 2) MT_TEAM(2); else if (wpr == 3) MT_TEAM(3); else if (wpr == 4) MT_TEAM(4); else MT_TEAM(5);
+    if (wpr == 2) MT_TEAM(2); else if (wpr == 3) MT_TEAM(3); else if (wpr == 4) MT_TEAM(4); else if (wpr == 5) MT_TEAM(5);
+    else if (wpr == 6) MT_TEAM(6); else MT_TEAM(8);
 #undef MT_TEAM
     MT_LAUNCH_CHECK();
     if (wg || wb) {

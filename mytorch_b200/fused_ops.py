@@ -329,4 +329,30 @@ def fused_rope_backward(dx, cos, sin):
     return dx
 
 
+def fused_rope_rmsnorm_forward(q, k, cos, sin, eps=1e-5):
+    """q, k [B,L,H,D] -> (q', k', rstd_q, rstd_k) with x' = rmsnorm(rope(x)) over D, both tensors
+    in one launch (fused_rope_forward, fused_ops/rope.py:178, then fused_rmsnorm_forward with
+    gamma=None, fused_ops/rmsnorm.py:159, as nanochat_gpt.py:119-124 chains them). Out of place."""
+    q, k = _A(q), _A(k)
+    _check_float(q, k)
+    B, L, H, D = q.shape
+    assert k.shape == q.shape
+    yq, yk = DeviceArray.empty(q.shape, q.dtype), DeviceArray.empty(k.shape, k.dtype)
+    rq, rk = DeviceArray.empty((B * L * H,), "float32"), DeviceArray.empty((B * L * H,), "float32")
+    _lib.rope_rmsnorm_fwd(q.ptr, k.ptr, yq.ptr, yk.ptr, rq.ptr, rk.ptr, _A(cos).ptr, _A(sin).ptr, B, L, H, D,
+                          H * D, H * D, float(eps), q.code, stream())
+    return yq, yk, rq, rk
+
+
+def fused_rope_rmsnorm_backward(dyq, dyk, yq, yk, rstd_q, rstd_k, cos, sin):
+    """Gradients w.r.t. the un-rotated q and k from the gradients of the outputs, the saved outputs
+    and rstd (fused_rmsnorm_backward, fused_ops/rmsnorm.py:251, then fused_rope_backward, rope.py:265)."""
+    dyq, dyk, yq, yk = _A(dyq), _A(dyk), _A(yq), _A(yk)
+    B, L, H, D = yq.shape
+    dq, dk = DeviceArray.empty(yq.shape, yq.dtype), DeviceArray.empty(yk.shape, yk.dtype)
+    _lib.rope_rmsnorm_bwd(dyq.ptr, dyk.ptr, yq.ptr, yk.ptr, _A(rstd_q).ptr, _A(rstd_k).ptr, dq.ptr, dk.ptr,
+                          _A(cos).ptr, _A(sin).ptr, B, L, H, D, H * D, H * D, H * D, yq.code, stream())
+    return dq, dk
+
+
 __all__ = [n for n in dir() if n.startswith("fused_")] + ["gemm"]

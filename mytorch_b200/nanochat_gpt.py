@@ -104,9 +104,7 @@ class Attention(nn.Module):
         k = self.k_proj(x).reshape(B, T, H, D)
         v = self.v_proj(x).reshape(B, T, H, D)
         cos, sin = cos_sin
-        q, k = F.apply_rotary_pos_embed(q, k, cos, sin)          # rotary first ...
-        q = norm(q.reshape(B * T * H, D)).reshape(B, T, H, D)     # ... then QK-norm over head_dim
-        k = norm(k.reshape(B * T * H, D)).reshape(B, T, H, D)
+        q, k = F.rope_qk_norm(q, k, cos, sin)                    # rotary first, then QK-norm over head_dim: one kernel
         if cache is not None:
             # inference: new keys/values join the cache; the prompt (empty cache) attends causally
             # among its own tokens, later tokens see everything cached (nanochat_gpt.py:126-160)

@@ -39,6 +39,18 @@ def _existing_grad(t):
     return None
 
 
+def _input_grad_gemm(x, g2, w):
+    """x.grad (+)= g2 @ w. When another branch has already left its gradient in x.grad (the q, k
+    and v projections of one normalised input, say), the sum happens in the GEMM's epilogue
+    (C = result + C, read slab by slab) instead of a GEMM into a temporary plus an add pass."""
+    have = _existing_grad(x)
+    if have is not None and g2.dtype == have.dtype:
+        h2 = _flat2d(have)
+        K.gemm(g2, w, out=h2, aux=h2, aux_mode=1)
+    else:
+        x._accumulate(K.gemm(g2, w).reshape(x.shape))
+
+
 def linear(x, weight, bias=None, auto=False, fused=True, act_func=None, residual=None):
     """y = act(x @ weight^T + bias) (+ residual), weight [out, in]
     (mytorch/nn/functional/layers/linear.py:149-236). No transposed copy of the
@@ -65,7 +77,7 @@ def linear(x, weight, bias=None, auto=False, fused=True, act_func=None, residual
                 buf = bias.param_grad_buffer()
                 _lib.colsum(g2.ptr, buf.ptr, g2.shape[0], g2.shape[1], g2.code, buf.code, 1, stream())
             if x.requires_grad:
-                x._accumulate(K.gemm(g2, weight.data).reshape(x.shape))
+                _input_grad_gemm(x, g2, weight.data)
         out.requires_grad = True
         out.grad_fn, out.grad_fn_name = _bw, "<LinearBackward>"
         out._add_parents(x, weight, bias, residual)
@@ -99,7 +111,7 @@ def mlp(x, w1, w2, act_func="gelu", residual=None):
             if w1.requires_grad:
                 _param_grad_gemm(du, x2, w1)
             if x.requires_grad:
-                x._accumulate(K.gemm(du, w1.data).reshape(x.shape))
+                _input_grad_gemm(x, du, w1.data)
         out.requires_grad = True
         out.grad_fn, out.grad_fn_name = _bw, "<MLPBackward>"
         out._add_parents(x, w1, w2, residual)
@@ -448,6 +460,53 @@ def apply_rotary_pos_embed(q, k, cos, sin, unsqueeze_dim=2, auto=False, fused=Tr
             o._add_parents(x)
         outs.append(o)
     return outs[0], outs[1]
+
+
+def rope_qk_norm(q, k, cos, sin, eps=1e-5):
+    """norm(rope(q)), norm(rope(k)) for q, k [B,T,H,D]: rotary embedding followed by the
+    parameter-free RMSNorm over head_dim (nanochat_trainer/core/nanochat_gpt.py:119-124) as ONE
+    autograd node and one kernel per direction. Each tensor is read and written once (the
+    separate ops copy, rotate in place and normalise: three passes each way), and only the
+    outputs and one rstd per head vector are kept for the backward pass. Head sizes the fused
+    kernel does not take (anything but 2..32 16-byte vectors) go through the separate ops."""
+    D = q.shape[-1]
+    vec = 16 // q.data.itemsize
+    if D % vec or (D // vec) not in (2, 4, 8, 16, 32) or q.shape != k.shape:
+        q2, k2 = apply_rotary_pos_embed(q, k, cos, sin)
+        shp = q.shape
+        return (rmsnorm(q2.reshape(-1, D), eps=eps).reshape(shp), rmsnorm(k2.reshape(-1, D), eps=eps).reshape(shp))
+    yq, yk, rq, rk = K.fused_rope_rmsnorm_forward(q.data, k.data, cos, sin, eps)
+    oq, ok = Tensor(yq), Tensor(yk)
+    if _needs_graph(q, k):
+        # Two outputs, one backward kernel: each output's closure parks its gradient; a graph-only
+        # node between the outputs and (q, k) runs after both (it is their parent in the graph) and
+        # launches once. An output that received no gradient counts as zero.
+        slot = [None, None]
+
+        def _bw_pair(_):
+            gq = slot[0] if slot[0] is not None else DeviceArray.zeros(yq.shape, yq.dtype)
+            gk = slot[1] if slot[1] is not None else DeviceArray.zeros(yk.shape, yk.dtype)
+            dq, dk = K.fused_rope_rmsnorm_backward(gq, gk, yq, yk, rq, rk, cos, sin)
+            slot[0] = slot[1] = None
+            if q.requires_grad:
+                q._accumulate(dq)
+            if k.requires_grad:
+                k._accumulate(dk)
+
+        pair = Tensor(yq)
+        pair.requires_grad = True
+        pair.grad_fn, pair.grad_fn_name = _bw_pair, "<RopeQKNormBackward>"
+        pair._add_parents(q, k)
+
+        def _park(i):
+            def f(g):
+                slot[i] = g
+            return f
+        for i, o in enumerate((oq, ok)):
+            o.requires_grad = True
+            o.grad_fn, o.grad_fn_name = _park(i), "<RopeQKNormOutput>"
+            o._add_parents(pair)
+    return oq, ok
 
 
 def dropout(x, dropout_p=0.0, training=True):

@@ -372,6 +372,48 @@ def test_attention_on_strided_projection_layouts(mt, dtype, B, T, H, D):
     no_device_flag(mt)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("B,T,H,D", [(2, 19, 3, 32), (1, 33, 10, 128), (2, 64, 5, 64), (1, 7, 1, 128)])
+def test_rope_then_qk_rmsnorm_fused(mt, dtype, B, T, H, D):
+    """rotary embedding followed by the parameter-free RMSNorm over head_dim on q and k, one kernel
+    each way, against the oracle's separate ops chained the way the nanochat attention does; also
+    through autograd (F.rope_qk_norm) with only one of the two outputs used."""
+    F, Fn = mt.fused_ops, mt.nn.functional
+    r = np.random.default_rng(31)
+    q, k, dq_out, dk_out = (rnd(r.standard_normal((B, T, H, D)), dtype) for _ in range(4))
+    cos, sin = O.rope_cos_sin(D, T)
+    want, wgrad = [], []
+    for x, dy in ((q, dq_out), (k, dk_out)):
+        xr = O.rope_fwd(x, cos, sin).reshape(-1, D)
+        y, rstd = O.rmsnorm_fwd(xr)
+        dxr, _ = O.rmsnorm_bwd(xr, rstd, dy.reshape(-1, D))
+        want.append((y.reshape(B, T, H, D), rstd))
+        wgrad.append(O.rope_bwd(dxr.reshape(B, T, H, D), cos, sin))
+    C_, S_ = dev(mt, cos, "float32"), dev(mt, sin, "float32")
+    Q, Kk = dev(mt, q, dtype), dev(mt, k, dtype)
+    yq, yk, rq, rk = F.fused_rope_rmsnorm_forward(Q, Kk, C_, S_)
+    t = TOL[dtype]
+    close(yq.numpy(), want[0][0], t, "q'"); close(yk.numpy(), want[1][0], t, "k'")
+    close(rq.numpy(), want[0][1].reshape(-1), 1e-4 if dtype == "float32" else 5e-3, "rstd q")
+    close(rk.numpy(), want[1][1].reshape(-1), 1e-4 if dtype == "float32" else 5e-3, "rstd k")
+    gq, gk = F.fused_rope_rmsnorm_backward(dev(mt, dq_out, dtype), dev(mt, dk_out, dtype), yq, yk, rq, rk, C_, S_)
+    close(gq.numpy(), wgrad[0], 2 * t, "dq"); close(gk.numpy(), wgrad[1], 2 * t, "dk")
+    # autograd: both outputs used, then only the second
+    qt, kt = mt.Tensor(Q, requires_grad=True), mt.Tensor(Kk, requires_grad=True)
+    oq, ok = Fn.rope_qk_norm(qt, kt, C_, S_)
+    tot = oq + ok
+    tot.backward(dev(mt, dq_out, dtype))
+    ref_q = O.rope_bwd(O.rmsnorm_bwd(O.rope_fwd(q, cos, sin).reshape(-1, D), want[0][1], dq_out.reshape(-1, D))[0].reshape(B, T, H, D), cos, sin)
+    ref_k = O.rope_bwd(O.rmsnorm_bwd(O.rope_fwd(k, cos, sin).reshape(-1, D), want[1][1], dq_out.reshape(-1, D))[0].reshape(B, T, H, D), cos, sin)
+    close(qt.grad.numpy(), ref_q, 2 * t, "autograd dq"); close(kt.grad.numpy(), ref_k, 2 * t, "autograd dk")
+    qt2, kt2 = mt.Tensor(Q, requires_grad=True), mt.Tensor(Kk, requires_grad=True)
+    _, ok2 = Fn.rope_qk_norm(qt2, kt2, C_, S_)
+    ok2.backward(dev(mt, dk_out, dtype))
+    close(kt2.grad.numpy(), wgrad[1], 2 * t, "autograd dk alone")
+    assert not np.any(qt2.grad.numpy())
+    no_device_flag(mt)
+
+
 def test_attention_rejects_mismatched_key_value_shapes(mt):
     """Fewer key/value heads (grouped-query attention) or another key length are refused on the
     host: the kernels index K and V with Q's extents."""

@@ -270,6 +270,63 @@ def test_nanochat_half_precision_head_dim_128_runs_on_tensor_cores():
     assert f.value == 0
 
 
+def test_nanochat_d20_width_fp16_steps_track_fp32_oracle():
+    """A two-block stack at the d20 model's width (d1280, 10 heads of 128, vocabulary 65536,
+    ReLU^2 MLP of 5120, rotary + QK-norm, soft-capped loss) in fp16 mixed precision: three AdamW
+    steps on one batch, losses within 1e-2 of the fp32 oracle stepping the same weights; and the
+    three ways the model can produce its loss agree on the first step."""
+    import mytorch_b200 as mt
+    from mytorch_b200.nanochat_gpt import GPT, GPTConfig
+    from oracle import nanochat as on
+    cfg = on.GPTConfig(vocab_size=65536, max_seq_len=256, embed_dim=1280, mlp_ratio=4, num_blocks=2, num_heads=10)
+    params = on.init_params(cfg, seed=2)
+    params["embeddings.embeddings.weight"] *= 0.04      # token embeddings at the model's own scale (std 0.02)
+    x, y = og.synthetic_batch(np.random.default_rng(4), 2, 256, 65536)
+
+    def make(mode):
+        np.random.seed(0)
+        model = GPT(GPTConfig(vocab_size=65536, max_seq_len=256, embed_dim=1280, mlp_ratio=4, num_blocks=2,
+                              num_q_heads=10, num_kv_heads=10))
+        model.load_state_dict(params)
+        model.loss_mode = mode
+        acc = mt.Accelerator(num_gpus=1, rank=0, mixed_precision=True)
+        opt = mt.optim.AdamW([{"params": model.parameters(), "weight_decay": 0.1}], lr=3e-4, beta1=0.9, beta2=0.95)
+        model, opt = acc.prepare(model, opt)
+        return model, acc, opt
+
+    first = {}
+    for mode in ("logits", "chunked"):
+        model, acc, opt = make(mode)
+        _, loss = model(mt.Tensor(x), mt.Tensor(y))
+        first[mode] = loss.item()
+        del model, acc, opt
+    model, acc, opt = make("fused")
+    ref_opt = og.AdamW(params, 3e-4, 0.9, 0.95, 1e-8, 0.1)
+    got, want = [], []
+    for step in range(3):
+        logits, loss = model(mt.Tensor(x), mt.Tensor(y))
+        assert logits is None
+        acc.backward(loss)
+        acc.clip_grad_norm_(1.0)
+        opt.step()
+        opt.zero_grad()
+        got.append(loss.item())
+        rl, cache = on.forward(params, cfg, x, y)
+        g = on.backward(params, cfg, cache)
+        O.clip_grad_norm(list(g.values()), 1.0)
+        ref_opt.step(params, g)
+        want.append(float(rl))
+    got, want = np.array(got), np.array(want)
+    assert acc.scaler.skipped_steps == 0
+    assert np.abs(got - want).max() <= 1e-2 * np.abs(want).max(), (got, want)
+    for mode, v in first.items():
+        assert abs(v - want[0]) <= 1e-2 * want[0], (mode, v, want[0])
+    import ctypes
+    f = ctypes.c_int(0)
+    mt._lib.device_flag_read(ctypes.byref(f), mt.stream())
+    assert f.value == 0
+
+
 @pytest.mark.parametrize("dtype,tol", [("float32", 1e-4), ("float16", 1e-2)])
 @pytest.mark.parametrize("softcap", [None, 15.0])
 def test_chunked_lm_head_cross_entropy_matches_unfused(dtype, tol, softcap):
