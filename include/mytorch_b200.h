@@ -89,6 +89,19 @@ int mt_add_rowvec(const void* a, const void* v, void* out, int64_t rows, int64_t
 int mt_colsum(const void* a, void* out, int64_t rows, int64_t cols, int dtype, int out_dtype, int accumulate, void* stream); /* out[c] (+)= sum_r a[r,c] */
 int mt_sum_f32(const void* x, int dtype, int64_t n, float* out, void* stream);                    /* out[0] = sum x (fp32) */
 
+/* Layout ops of the autograd Tensor that copy: transpose (mytorch/tensor.py:1381), chunk (:1598),
+ * slicing in __getitem__ (:1314), concatenate / stack (mytorch/ops.py:62-160), the broadcast in the
+ * backward of sum / mean (mytorch/tensor.py:1734-1955); the elementwise product of
+ * Tensor.__mul__ (:596) and the reduction of sum / mean over the last axis.
+ * mt_copy_strided walks an index space of up to 6 dimensions (outermost first) and copies, or with
+ * accumulate_dtype >= 0 adds (dst += src in that mt_dtype), one element of elem_bytes (2 or 4) per
+ * index: dst[sum idx*dst_strides] = src[sum idx*src_strides], strides in elements, a source
+ * stride of 0 broadcasts. mt_rowsum: out[r] = alpha * sum_c a[r,c] (fp32 sum, fixed order). */
+int mt_copy_strided(const void* src, void* dst, int ndim, const int64_t* shape, const int64_t* src_strides,
+                    const int64_t* dst_strides, int elem_bytes, int accumulate_dtype, void* stream);
+int mt_mul(const void* a, const void* b, void* out, int64_t n, int dtype, void* stream);          /* out = a * b */
+int mt_rowsum(const void* a, void* out, int64_t rows, int64_t cols, float alpha, int dtype, void* stream);
+
 /* fused_activation_forward / fused_activation_backward
  * (mytorch/nn/functional/fused_ops/activations.py:212, :273) */
 int mt_act_fwd(const void* x, void* y, int64_t n, int act, int dtype, void* stream);

@@ -11,8 +11,9 @@ from . import fused_ops
 __all__ = ["DeviceArray", "as_device_array", "stream", "synchronize", "fused_ops", "MTError"]
 
 from .tensor import Tensor, no_grad, zeros, ones, zeros_like, randn, arange
-from . import nn, optim, utils
+from . import nn, optim, utils, ops
+from .ops import transpose, permute, chunk, concatenate, stack
 from .accelerate import Accelerator, GradScaler
 
-__all__ += ["Tensor", "no_grad", "zeros", "ones", "zeros_like", "randn", "arange", "nn", "optim",
-            "Accelerator", "GradScaler"]
+__all__ += ["Tensor", "no_grad", "zeros", "ones", "zeros_like", "randn", "arange", "nn", "optim", "ops",
+            "transpose", "permute", "chunk", "concatenate", "stack", "Accelerator", "GradScaler"]

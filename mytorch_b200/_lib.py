@@ -83,6 +83,9 @@ _SIG = {
     "mt_add_rowvec": [_p, _p, _p, _i64, _i64, _i, _p],
     "mt_colsum": [_p, _p, _i64, _i64, _i, _i, _i, _p],
     "mt_sum_f32": [_p, _i, _i64, _p, _p],
+    "mt_copy_strided": [_p, _p, _i, C.POINTER(_i64), C.POINTER(_i64), C.POINTER(_i64), _i, _i, _p],
+    "mt_mul": [_p, _p, _p, _i64, _i, _p],
+    "mt_rowsum": [_p, _p, _i64, _i64, _f, _i, _p],
     "mt_act_fwd": [_p, _p, _i64, _i, _i, _p],
     "mt_act_bwd": [_p, _p, _p, _i64, _i, _i, _p],
     "mt_layernorm_fwd": [_p, _p, _p, _p, _p, _p, _i64, _i64, _f, _i, _p],
