@@ -265,12 +265,15 @@ class Tensor:
         """Sums a gradient of a broadcast result back to this tensor's shape."""
         if g.shape == self.shape:
             return g
-        lead = len(g.shape) - self.ndim
-        if any(m != n for m, n in zip(self.shape, g.shape[lead:])):
-            raise NotImplementedError("gradient of a broadcast over inner dimensions is not built; broadcast over leading "
-                                      f"dimensions only ({self.shape} vs {g.shape})")
+        mine = (1,) * (len(g.shape) - self.ndim) + self.shape
+        j = 0
+        while j < len(mine) and mine[j:] != g.shape[j:]:
+            if mine[j] != 1:
+                raise NotImplementedError("gradient of a broadcast over inner dimensions is not built; broadcast over "
+                                          f"leading dimensions only ({self.shape} vs {g.shape})")
+            j += 1
         rows = 1
-        for n in g.shape[:lead]:
+        for n in g.shape[:j]:
             rows *= n
         out = DeviceArray.empty(self.shape or (1,), g.dtype)
         _lib.colsum(g.ptr, out.ptr, rows, max(1, self.data.size), g.code, out.code, 0, stream())
