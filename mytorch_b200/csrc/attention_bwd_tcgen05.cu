@@ -1,16 +1,22 @@
 // Tensor-core attention backward for sm_100a, fp16/bf16, head_dim 64 or 128.
 //
-// One CTA per (batch, head, block of 128 key/value rows); it walks the query
-// blocks that attend to it (all of them, or those at/after the diagonal when
-// causal). Per query block, five tcgen05 MMAs with accumulators in tensor memory:
+// A tile is one (batch, head, block of 128 key/value rows): the CTA that owns it walks the query
+// blocks that attend to it (all of them, or those at/after the diagonal when causal). The kernel
+// is persistent: one CTA per SM takes one tile per round of gridDim.x tiles (heaviest first,
+// dealt in alternating directions), tensor memory and barriers are set up once, and the roles
+// run ahead across tile boundaries - the producer loads the next tile's K/V as soon as the last
+// MMA reading the current ones has completed and keeps the Q/dO ring filled, the MMA warp issues
+// the next tile's first S^T/dP^T while the elementwise warps still flush dQ and drain dK/dV of
+// the current one.
+// Per query block, five tcgen05 MMAs with accumulators in tensor memory:
 //   S^T  = K Q^T            dP^T = V dO^T          (both 128x128xD, recomputed)
 //   dV  += P^T dO           dK  += dS^T Q          (128xDx128, accumulated)
 //   dQ   = dS K             (128xDx128, added to a fp32 buffer with TMA reduce-add,
 //                            since every key block contributes to every dQ row)
-// Warp roles: warp 8 TMA producer (K, V once; Q, dO and the block's row statistics per query
-// block, read in place through 4-D strided tensor maps, three stages at head_dim 64), warp 9
-// MMA issuer, warps 0-7 the elementwise stage: thread = key row = TMEM lane (two warps per lane
-// quarter, 64 query columns each). It copies S^T and dP^T to registers - which lets the MMA warp
+// Warp roles: one warp TMA producer (K, V once; Q, dO and the block's row statistics per query
+// block, read in place through 4-D strided tensor maps, three stages at head_dim 64), one warp
+// MMA issuer, the other warps the elementwise stage: thread = key row = TMEM lane (four warps per
+// lane quarter with 32 query columns each at head_dim 64, two with 64 each at head_dim 128). It copies S^T and dP^T to registers - which lets the MMA warp
 // start the next block's S^T / dP^T at once - forms P^T = exp2(S^T*scale*log2e - lse*log2e) and
 // dS^T = P^T (dP^T*scale - delta*scale), and writes dS^T as half into shared memory in the
 // swizzled layout that serves as K-major A operand for dK and, read the other way, as M-major A
@@ -31,10 +37,16 @@ namespace mt {
 
 using namespace sm100;
 
-constexpr int kBwdEwWarps = 8;                 // elementwise warps: two per TMEM lane quarter, 64 query columns each
-constexpr int kBwdThreads = 32 * (kBwdEwWarps + 2);
 
 template <int D> struct BwdCfg {
+  // Elementwise warps: kEwWarps / 4 per TMEM lane quarter, each taking kColsPerThread of the
+  // block's 128 query columns: sixteen warps with 32 columns per thread at head_dim 64, eight
+  // with 64 at head_dim 128, whose dQ staging lives inside the P^T buffer in slices that exactly
+  // one warp writes.
+  static constexpr int kEwWarps = D == 64 ? 16 : 8;
+  static constexpr int kColsPerThread = 128 / (kEwWarps / 4);
+  static constexpr int kThreads = 32 * (kEwWarps + 2);
+  static constexpr int kDrainWarps = 8;                     // column groups 0 and 1 write dK and dV
   static constexpr int kChunks = D / 64;
   static constexpr int kTile = 128 * D * 2;                 // one 128-row block of K/V/Q/dO
   // head_dim 64 has 64 spare TMEM columns: P^T lives there (A operand of the dV MMA read from
@@ -62,6 +74,17 @@ template <int D> struct BwdCfg {
   static constexpr int kColPT = 256 + 3 * D;                // packed half pairs, 64 columns (head_dim 64 only)
 };
 
+// Tiles are dealt to the persistent CTAs round by round, forwards in even rounds and backwards
+// in odd ones: with tiles sorted heaviest first, the CTA that got the heaviest tile of one round
+// gets the lightest of the next, which keeps the CTAs' totals within a few percent of each other.
+// Returns -1 when this CTA has no tile in the (last, partial) round.
+__device__ __forceinline__ int tile_of_round(int round, int n_tiles) {
+  const int G = (int)gridDim.x;
+  const int idx = (round & 1) ? G - 1 - (int)blockIdx.x : (int)blockIdx.x;
+  const int tile = round * G + idx;
+  return tile < n_tiles ? tile : -1;
+}
+
 struct AttnBwdParams {
   const float* stats;      // [2][B*H][nqb*128]: lse*log2e (+inf on padded rows), then delta*scale (0 on padded rows)
   float* dq_accum;
@@ -73,31 +96,33 @@ struct AttnBwdParams {
 };
 
 template <int D, typename T>
-__global__ void __launch_bounds__(kBwdThreads, 1)
+__global__ void __launch_bounds__(BwdCfg<D>::kThreads, 1)
 attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                    const __grid_constant__ CUtensorMap tmDQ, const __grid_constant__ CUtensorMap tmDK,
                    const __grid_constant__ CUtensorMap tmDV, const AttnBwdParams P) {
   using Cfg = BwdCfg<D>;
   constexpr int ST = Cfg::kStages;
+  constexpr int kBwdEwWarps = Cfg::kEwWarps;
+  constexpr int CPT = Cfg::kColsPerThread;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - raw);
   const uint32_t bar0 = base + Cfg::kOffBar;
   const uint32_t bar_kv = bar0, bar_qfull0 = bar0 + 8, bar_qempty0 = bar0 + 32, bar_sdp = bar0 + 56,
-                 bar_pds = bar0 + 64, bar_dq = bar0 + 72, bar_dqfree = bar0 + 80, bar_sdpfree = bar0 + 88;
+                 bar_pds = bar0 + 64, bar_dq = bar0 + 72, bar_dqfree = bar0 + 80, bar_sdpfree = bar0 + 88,
+                 bar_kvfree = bar0 + 96, bar_dkvfree = bar0 + 104;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + Cfg::kOffBar + 112);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + Cfg::kOffBar + 116);
   float* stat = reinterpret_cast<float*>(base_ptr + Cfg::kOffStat);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int bh_count = P.B * P.H;
-  const int jb = (int)(blockIdx.x / bh_count);     // key block; small j = most query blocks when causal, so heavy first
-  const int bh = blockIdx.x % bh_count;
-  const int b = bh / P.H, h = bh % P.H;
-  const int q_start = P.causal ? jb : 0;
-  const int n_q = P.nqb - q_start;
+  const int n_tiles = P.nqb * bh_count;
+  // Tile t: key block jb = t / bh_count (small jb = most query blocks when causal, so heavy tiles
+  // come first), (batch, head) = t % bh_count. Every role walks the same tile sequence and keeps a
+  // running count `g` of query blocks, from which ring stages and barrier parities follow.
 
   if (threadIdx.x == 0) {
     mbar_init(bar_kv, 1);
@@ -105,6 +130,8 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     mbar_init(bar_sdp, 1); mbar_init(bar_pds, 32 * kBwdEwWarps); mbar_init(bar_dq, 1);
     mbar_init(bar_dqfree, 32 * kBwdEwWarps);
     mbar_init(bar_sdpfree, kBwdEwWarps);
+    mbar_init(bar_kvfree, 1);
+    mbar_init(bar_dkvfree, Cfg::kDrainWarps);
     *abort_flag = 0;
     fence_barrier_init();
     fence_proxy_async();
@@ -122,27 +149,40 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     // ------------------------------------------------------------ producer --
     if (lane == 0) {
       prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV); prefetch_tmap(&tmDO);
-      mbar_expect_tx(bar_kv, 2 * Cfg::kTile);
-#pragma unroll
-      for (int dc = 0; dc < Cfg::kChunks; ++dc) {
-        load_rows(base + Cfg::kOffK + dc * 16384, &tmK, bar_kv, P.pk, dc * 64, jb * 128, h, b);
-        load_rows(base + Cfg::kOffV + dc * 16384, &tmV, bar_kv, P.pv, dc * 64, jb * 128, h, b);
-      }
-      for (int i = 0; i < n_q; ++i) {
-        const int s = i % ST;
-        if (!mbar_wait(bar_qempty0 + 8 * s, ((i / ST) & 1) ^ 1u, abort_flag)) break;
-        mbar_expect_tx(bar_qfull0 + 8 * s, 2 * Cfg::kTile + 1024);
-        const uint32_t sq = base + Cfg::kOffQ + s * 2 * Cfg::kTile, sdo = sq + Cfg::kTile;
-        {   // the block's row statistics travel with it
-          const int64_t spad = (int64_t)P.nqb * 128;
-          const float* src = P.stats + (int64_t)bh * spad + (int64_t)(q_start + i) * 128;
-          bulk_load_1d(base + Cfg::kOffStat + s * 1024, src, 512, bar_qfull0 + 8 * s);
-          bulk_load_1d(base + Cfg::kOffStat + s * 1024 + 512, src + (int64_t)bh_count * spad, 512, bar_qfull0 + 8 * s);
-        }
+      int g = 0;
+      bool ok = true;
+      for (int round = 0, tn = 0; round * (int)gridDim.x < n_tiles && ok; ++round) {
+        const int tile = tile_of_round(round, n_tiles);
+        if (tile < 0) continue;
+        const int tn_now = tn++;
+        const int jb = tile / bh_count, bh = tile % bh_count;
+        const int b = bh / P.H, h = bh % P.H;
+        const int q_start = P.causal ? jb : 0;
+        const int n_q = P.nqb - q_start;
+        // K and V of the previous tile are read until its last dQ MMA has completed
+        if (tn_now > 0 && !mbar_wait(bar_kvfree, (tn_now - 1) & 1, abort_flag)) break;
+        mbar_expect_tx(bar_kv, 2 * Cfg::kTile);
 #pragma unroll
         for (int dc = 0; dc < Cfg::kChunks; ++dc) {
-          load_rows(sq + dc * 16384, &tmQ, bar_qfull0 + 8 * s, P.pq, dc * 64, (q_start + i) * 128, h, b);
-          load_rows(sdo + dc * 16384, &tmDO, bar_qfull0 + 8 * s, P.pdo, dc * 64, (q_start + i) * 128, h, b);
+          load_rows(base + Cfg::kOffK + dc * 16384, &tmK, bar_kv, P.pk, dc * 64, jb * 128, h, b);
+          load_rows(base + Cfg::kOffV + dc * 16384, &tmV, bar_kv, P.pv, dc * 64, jb * 128, h, b);
+        }
+        for (int i = 0; i < n_q; ++i, ++g) {
+          const int s = g % ST;
+          if (!mbar_wait(bar_qempty0 + 8 * s, ((g / ST) & 1) ^ 1u, abort_flag)) { ok = false; break; }
+          mbar_expect_tx(bar_qfull0 + 8 * s, 2 * Cfg::kTile + 1024);
+          const uint32_t sq = base + Cfg::kOffQ + s * 2 * Cfg::kTile, sdo = sq + Cfg::kTile;
+          {   // the block's row statistics travel with it
+            const int64_t spad = (int64_t)P.nqb * 128;
+            const float* src = P.stats + (int64_t)bh * spad + (int64_t)(q_start + i) * 128;
+            bulk_load_1d(base + Cfg::kOffStat + s * 1024, src, 512, bar_qfull0 + 8 * s);
+            bulk_load_1d(base + Cfg::kOffStat + s * 1024 + 512, src + (int64_t)bh_count * spad, 512, bar_qfull0 + 8 * s);
+          }
+#pragma unroll
+          for (int dc = 0; dc < Cfg::kChunks; ++dc) {
+            load_rows(sq + dc * 16384, &tmQ, bar_qfull0 + 8 * s, P.pq, dc * 64, (q_start + i) * 128, h, b);
+            load_rows(sdo + dc * 16384, &tmDO, bar_qfull0 + 8 * s, P.pdo, dc * 64, (q_start + i) * 128, h, b);
+          }
         }
       }
     }
@@ -178,10 +218,9 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         if (NS == 4) umma_f16_x4(d, a, b, idesc, acc);
         else umma_f16_x8(d, a, b, idesc, acc);
       };
-      bool ok = mbar_wait(bar_kv, 0, abort_flag);
-      // S^T = K Q^T and dP^T = V dO^T of query block i into tensor memory
-      auto issue_sdp = [&](int i) -> bool {
-        const int s = i % ST;
+      // S^T = K Q^T and dP^T = V dO^T of query block g (running count) into tensor memory
+      auto issue_sdp = [&](int g) -> bool {
+        const int s = g % ST;
         const uint32_t sq = base + Cfg::kOffQ + s * 2 * Cfg::kTile, sdo = sq + Cfg::kTile;
         uint64_t b_s[NS], b_dp[NS];
 #pragma unroll
@@ -191,66 +230,95 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             b_s[dc * 4 + k] = smem_desc_sw128(sq + dc * 16384 + k * 32, 16, 1024);
             b_dp[dc * 4 + k] = smem_desc_sw128(sdo + dc * 16384 + k * 32, 16, 1024);
           }
-        if (!mbar_wait(bar_qfull0 + 8 * s, (i / ST) & 1, abort_flag)) return false;
+        if (!mbar_wait(bar_qfull0 + 8 * s, (g / ST) & 1, abort_flag)) return false;
         tc_fence_after();
         issue_n(tmem_base + Cfg::kColST, a_s, b_s, idesc_kk, 0u);
         issue_n(tmem_base + Cfg::kColDPT, a_dp, b_dp, idesc_kk, 0u);
         umma_commit(bar_sdp);
         return true;
       };
-      if (ok && !Cfg::kAliasDQ) ok = issue_sdp(0);
-      for (int i = 0; i < n_q && ok; ++i) {
-        const int s = i % ST;
-        const uint32_t sq = base + Cfg::kOffQ + s * 2 * Cfg::kTile, sdo = sq + Cfg::kTile;
-        if (Cfg::kAliasDQ) {
-          // dQ shares the S^T columns: the previous dQ must have been read out first
-          if (i > 0 && !mbar_wait(bar_dqfree, (i - 1) & 1, abort_flag)) break;
-          if (!issue_sdp(i)) break;
-        }
-        if (!Cfg::kAliasDQ && i + 1 < n_q) {
-          // The elementwise warps hold S^T / dP^T of block i in registers: the next block's are
-          // computed while they work, ahead of everything else of this block.
-          if (!mbar_wait(bar_sdpfree, i & 1, abort_flag)) break;
-          tc_fence_after();
-          if (!issue_sdp(i + 1)) break;
-        }
-        uint64_t b_dv[8], b_dk[8];
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          b_dv[ks] = smem_desc_sw128(sdo + ks * 2048, 16384, 1024);
-          b_dk[ks] = smem_desc_sw128(sq + ks * 2048, 16384, 1024);
-        }
-        if (!mbar_wait(bar_pds, i & 1, abort_flag)) break;     // P^T, dS^T written
+      int g0 = 0;                                       // running count of query blocks at the start of the tile
+      bool ok = true;
+      for (int round = 0, tcount = 0; round * (int)gridDim.x < n_tiles && ok; ++round) {
+        const int tile = tile_of_round(round, n_tiles);
+        if (tile < 0) continue;
+        const int tn = tcount++;
+        const int jb = tile / bh_count;
+        const int n_q = P.nqb - (P.causal ? jb : 0);
+        if (!mbar_wait(bar_kv, tn & 1, abort_flag)) break;
         tc_fence_after();
-        // dV += P^T dO (reduction over the 128 queries), dK += dS^T Q
-        if (Cfg::kPTinTmem) umma_f16_ts_x8(tmem_base + Cfg::kColDV, tmem_base + Cfg::kColPT, b_dv, idesc_kn, i > 0 ? 1u : 0u);
-        else umma_f16_x8(tmem_base + Cfg::kColDV, a_dv, b_dv, idesc_kn, i > 0 ? 1u : 0u);
-        umma_f16_x8(tmem_base + Cfg::kColDK, a_dk, b_dk, idesc_kn, i > 0 ? 1u : 0u);
-        umma_commit(bar_qempty0 + 8 * s);   // Q and dO of this block are not read again (dQ needs neither)
         if (!Cfg::kAliasDQ) {
-          if (i > 0 && !mbar_wait(bar_dqfree, (i - 1) & 1, abort_flag)) break;   // dQ columns read out
+          // the elementwise warps have copied the previous block's S^T / dP^T (last block of the
+          // previous tile) to registers
+          if (g0 > 0 && !mbar_wait(bar_sdpfree, (g0 - 1) & 1, abort_flag)) break;
           tc_fence_after();
+          if (!issue_sdp(g0)) break;
         }
-        umma_f16_x8(tmem_base + Cfg::kColDQ, a_dq, b_dq, idesc_mn, 0u);   // dQ = dS K, reduction over the 128 keys
-        umma_commit(bar_dq);
+        for (int i = 0; i < n_q; ++i) {
+          const int g = g0 + i;
+          const int s = g % ST;
+          const uint32_t sq = base + Cfg::kOffQ + s * 2 * Cfg::kTile, sdo = sq + Cfg::kTile;
+          if (Cfg::kAliasDQ) {
+            // dQ shares the S^T columns: the previous dQ must have been read out first
+            if (g > 0 && !mbar_wait(bar_dqfree, (g - 1) & 1, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            if (!issue_sdp(g)) { ok = false; break; }
+          }
+          if (!Cfg::kAliasDQ && i + 1 < n_q) {
+            // The elementwise warps hold S^T / dP^T of block g in registers: the next block's are
+            // computed while they work, ahead of everything else of this block.
+            if (!mbar_wait(bar_sdpfree, g & 1, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            if (!issue_sdp(g + 1)) { ok = false; break; }
+          }
+          uint64_t b_dv[8], b_dk[8];
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks) {
+            b_dv[ks] = smem_desc_sw128(sdo + ks * 2048, 16384, 1024);
+            b_dk[ks] = smem_desc_sw128(sq + ks * 2048, 16384, 1024);
+          }
+          if (!mbar_wait(bar_pds, g & 1, abort_flag)) { ok = false; break; }     // P^T, dS^T written
+          tc_fence_after();
+          if (i == 0 && tn > 0) {
+            // the first dV / dK MMA of a tile overwrites the accumulators: the previous tile's must
+            // have been read out (the elementwise warps drain them before this tile's first block)
+            if (!mbar_wait(bar_dkvfree, (tn - 1) & 1, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+          }
+          // dV += P^T dO (reduction over the 128 queries), dK += dS^T Q
+          if (Cfg::kPTinTmem) umma_f16_ts_x8(tmem_base + Cfg::kColDV, tmem_base + Cfg::kColPT, b_dv, idesc_kn, i > 0 ? 1u : 0u);
+          else umma_f16_x8(tmem_base + Cfg::kColDV, a_dv, b_dv, idesc_kn, i > 0 ? 1u : 0u);
+          umma_f16_x8(tmem_base + Cfg::kColDK, a_dk, b_dk, idesc_kn, i > 0 ? 1u : 0u);
+          umma_commit(bar_qempty0 + 8 * s);   // Q and dO of this block are not read again (dQ needs neither)
+          if (!Cfg::kAliasDQ) {
+            if (g > 0 && !mbar_wait(bar_dqfree, (g - 1) & 1, abort_flag)) { ok = false; break; }   // dQ columns read out
+            tc_fence_after();
+          }
+          umma_f16_x8(tmem_base + Cfg::kColDQ, a_dq, b_dq, idesc_mn, 0u);   // dQ = dS K, reduction over the 128 keys
+          umma_commit(bar_dq);
+        }
+        umma_commit(bar_kvfree);            // completes with the tile's last dQ: K and V may be replaced
+        g0 += n_q;
       }
     }
   } else {
     // ------------------------------------------------- elementwise stage --
     const int t = (warp & 3) * 32 + lane;             // key row within the block = TMEM lane
-    const int hh = warp >> 2;                         // which 64 of the block's 128 query columns this warp handles
-    const int kg = jb * 128 + t;                      // global key index
+    const int hh = warp >> 2;                         // which CPT of the block's 128 query columns this warp handles
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
     uint8_t* pt_row = base_ptr + Cfg::kOffPT + t * 128;
     uint8_t* dst_row = base_ptr + Cfg::kOffDST + t * 128;
     bool ok = true;
+    int bh = 0;
     // adds the finished dQ block (TMEM) into the fp32 accumulator [B*H, S, D]: each warp stages its
     // 32 rows x 32 columns in swizzled shared memory and one lane issues a TMA reduce-add (rows past
     // the sequence end are clipped by the tensor map)
     uint8_t* dq_stage = base_ptr + Cfg::kOffStage + warp * 4096;
+    constexpr int kDqChunks = D / 32;                                           // 32-column pieces of dQ
+    constexpr int kDqPer = kDqChunks >= kBwdEwWarps / 4 ? kDqChunks / (kBwdEwWarps / 4) : 1;   // pieces per column group
     auto flush_dq = [&](int qi) {
 #pragma unroll 1
-      for (int c = hh * (D / 64); c < (hh + 1) * (D / 64); ++c) {   // this warp's half of the dQ columns
+      for (int c = hh * kDqPer; c < (hh + 1) * kDqPer && c < kDqChunks; ++c) {   // this warp's share of the dQ columns
         uint32_t r[32];
         tmem_ld32(tmem_base + Cfg::kColDQ + lane_addr + c * 32, r);
         tmem_ld_wait();
@@ -268,137 +336,161 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         }
       }
     };
-    for (int i = 0; i < n_q && ok; ++i) {
-      const int qi = q_start + i;
-      // row statistics of this query block arrived with its Q/dO stage (bulk copy); the wait makes
-      // that copy visible to this thread and returns at once, since S^T needed the stage too
-      const float* lse2 = stat + (i % ST) * 256;
-      const float* dlt = lse2 + 128;
-      if (!__all_sync(0xffffffffu, mbar_wait(bar_sdp, i & 1, abort_flag))) { ok = false; break; }
-      if (!__all_sync(0xffffffffu, mbar_wait(bar_qfull0 + 8 * (i % ST), (i / ST) & 1, abort_flag))) { ok = false; break; }
-      tc_fence_after();
-      const bool diag = P.causal && qi == jb;
-      const bool dead = kg >= P.S;                    // padded key row: contributes nothing
-      {
-        uint32_t s_[64], d_[64];
-        tmem_ld32(tmem_base + Cfg::kColST + lane_addr + hh * 64, s_);
-        tmem_ld32(tmem_base + Cfg::kColST + lane_addr + hh * 64 + 32, s_ + 32);
-        tmem_ld32(tmem_base + Cfg::kColDPT + lane_addr + hh * 64, d_);
-        tmem_ld32(tmem_base + Cfg::kColDPT + lane_addr + hh * 64 + 32, d_ + 32);
-        tmem_ld_wait();
-        if (!Cfg::kAliasDQ) {
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar_sdpfree);   // S^T / dP^T columns may be overwritten
-        }
-        if (diag || __any_sync(0xffffffffu, dead)) {   // masked entries: score -inf -> p = 0, dS = 0
-#pragma unroll
-          for (int e = 0; e < 64; ++e)
-            if (dead || (diag && hh * 64 + e < t)) s_[e] = 0xff800000u;
-        }
-        if (!Cfg::kOwnStage) {   // staging aliases this warp's slice of P^T: let the last reduce finish reading it
-          if (lane == 0) bulk_wait_read<0>();
-          __syncwarp();
-        }
-        if (!Cfg::kAliasDQ && i > 0) {
-          // dS^T of the previous block is still an operand of its dQ MMA, which was issued after
-          // the S^T/dP^T MMAs of this block: it must have completed before dS^T is overwritten
-          if (!__all_sync(0xffffffffu, mbar_wait(bar_dq, (i - 1) & 1, abort_flag))) { ok = false; break; }
-        }
-        uint32_t ptp[Cfg::kPTinTmem ? 32 : 1];   // P^T of this thread as packed half pairs
-        const float4* lse4 = reinterpret_cast<const float4*>(lse2 + hh * 64);   // per query column, 16-byte loads
-        const float4* dlt4 = reinterpret_cast<const float4*>(dlt + hh * 64);
-#pragma unroll
-        for (int c16 = 0; c16 < 8; ++c16) {
-          uint32_t pp[4], dd[4];
-          const float4 la = lse4[c16 * 2], lb = lse4[c16 * 2 + 1], da = dlt4[c16 * 2], db = dlt4[c16 * 2 + 1];
-          const float lv[8] = {la.x, la.y, la.z, la.w, lb.x, lb.y, lb.z, lb.w};
-          const float dl8[8] = {da.x, da.y, da.z, da.w, db.x, db.y, db.z, db.w};
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            float pv[2], dv[2];
-#pragma unroll
-            for (int u = 0; u < 2; ++u) {
-              const int ce = c16 * 8 + 2 * e + u;              // this thread's column, of 64
-              const float p = ex2_approx(fmaf(__uint_as_float(s_[ce]), P.scale_log2, -lv[2 * e + u]));
-              pv[u] = p;
-              dv[u] = p * fmaf(__uint_as_float(d_[ce]), P.scale, -dl8[2 * e + u]);   // p (dP - delta) scale
-            }
-            pp[e] = pack2<T>(pv[0], pv[1]);
-            dd[e] = pack2<T>(dv[0], dv[1]);
-          }
-          const int off = hh * 16384 + ((c16 ^ (t & 7)) << 4);
-          if (Cfg::kPTinTmem) {
-#pragma unroll
-            for (int e = 0; e < 4; ++e) ptp[c16 * 4 + e] = pp[e];
-          } else {
-            *reinterpret_cast<uint4*>(pt_row + off) = make_uint4(pp[0], pp[1], pp[2], pp[3]);
-          }
-          *reinterpret_cast<uint4*>(dst_row + off) = make_uint4(dd[0], dd[1], dd[2], dd[3]);
-          if (Cfg::kPTinTmem && (c16 & 3) == 3)   // 32 finished columns = 16 packed words -> tensor memory
-            tmem_st16(tmem_base + Cfg::kColPT + lane_addr + hh * 32 + (c16 >> 2) * 16, ptp + (c16 >> 2) * 16);
-        }
-        if (Cfg::kPTinTmem) tmem_st_wait();
-      }
-      fence_proxy_async();
-      tc_fence_before();
-      mbar_arrive(bar_pds);
-      // dQ read-out. With its own TMEM columns the PREVIOUS block's dQ is flushed here, while the
-      // tensor core works on this block; when dQ aliases S^T it has to be this block's.
-      const int fi = Cfg::kAliasDQ ? i : i - 1;
-      if (fi >= 0) {
-        if (!__all_sync(0xffffffffu, mbar_wait(bar_dq, fi & 1, abort_flag))) { ok = false; break; }
+    int g0 = 0;                                       // running count of query blocks at the start of the tile
+    for (int round = 0; round * (int)gridDim.x < n_tiles && ok; ++round) {
+      const int tile = tile_of_round(round, n_tiles);
+      if (tile < 0) continue;
+      const int jb = tile / bh_count;
+      bh = tile % bh_count;
+      const int b = bh / P.H, h = bh % P.H;
+      const int q_start = P.causal ? jb : 0;
+      const int n_q = P.nqb - q_start;
+      const int kg = jb * 128 + t;                    // global key index
+      for (int i = 0; i < n_q && ok; ++i) {
+        const int g = g0 + i;
+        const int qi = q_start + i;
+        // row statistics of this query block arrived with its Q/dO stage (bulk copy); the wait makes
+        // that copy visible to this thread and returns at once, since S^T needed the stage too
+        const float* lse2 = stat + (g % ST) * 256;
+        const float* dlt = lse2 + 128;
+        if (!__all_sync(0xffffffffu, mbar_wait(bar_sdp, g & 1, abort_flag))) { ok = false; break; }
+        if (!__all_sync(0xffffffffu, mbar_wait(bar_qfull0 + 8 * (g % ST), (g / ST) & 1, abort_flag))) { ok = false; break; }
         tc_fence_after();
-        flush_dq(q_start + fi);
+        const bool diag = P.causal && qi == jb;
+        const bool dead = kg >= P.S;                    // padded key row: contributes nothing
+        {
+          uint32_t s_[CPT], d_[CPT];
+#pragma unroll
+          for (int c = 0; c < CPT; c += 32) {
+            tmem_ld32(tmem_base + Cfg::kColST + lane_addr + hh * CPT + c, s_ + c);
+            tmem_ld32(tmem_base + Cfg::kColDPT + lane_addr + hh * CPT + c, d_ + c);
+          }
+          tmem_ld_wait();
+          if (!Cfg::kAliasDQ) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_sdpfree);   // S^T / dP^T columns may be overwritten
+          }
+          if (diag || __any_sync(0xffffffffu, dead)) {   // masked entries: score -inf -> p = 0, dS = 0
+#pragma unroll
+            for (int e = 0; e < CPT; ++e)
+              if (dead || (diag && hh * CPT + e < t)) s_[e] = 0xff800000u;
+          }
+          if (!Cfg::kOwnStage) {   // staging aliases this warp's slice of P^T: let the last reduce / store finish reading it
+            if (lane == 0) bulk_wait_read<0>();
+            __syncwarp();
+          }
+          if (!Cfg::kAliasDQ && i > 0) {
+            // dS^T of the previous block is still an operand of its dQ MMA, which was issued after
+            // the S^T/dP^T MMAs of this block: it must have completed before dS^T is overwritten
+            // (at the first block of a tile the wait already happened before the previous tile's
+            // last dQ flush)
+            if (!__all_sync(0xffffffffu, mbar_wait(bar_dq, (g - 1) & 1, abort_flag))) { ok = false; break; }
+          }
+          uint32_t ptp[Cfg::kPTinTmem ? CPT / 2 : 1];   // P^T of this thread as packed half pairs
+          const float4* lse4 = reinterpret_cast<const float4*>(lse2 + hh * CPT);   // per query column, 16-byte loads
+          const float4* dlt4 = reinterpret_cast<const float4*>(dlt + hh * CPT);
+#pragma unroll
+          for (int c16 = 0; c16 < CPT / 8; ++c16) {
+            uint32_t pp[4], dd[4];
+            const float4 la = lse4[c16 * 2], lb = lse4[c16 * 2 + 1], da = dlt4[c16 * 2], db = dlt4[c16 * 2 + 1];
+            const float lv[8] = {la.x, la.y, la.z, la.w, lb.x, lb.y, lb.z, lb.w};
+            const float dl8[8] = {da.x, da.y, da.z, da.w, db.x, db.y, db.z, db.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              float pv[2], dv[2];
+#pragma unroll
+              for (int u = 0; u < 2; ++u) {
+                const int ce = c16 * 8 + 2 * e + u;              // this thread's column, of CPT
+                const float p = ex2_approx(fmaf(__uint_as_float(s_[ce]), P.scale_log2, -lv[2 * e + u]));
+                pv[u] = p;
+                dv[u] = p * fmaf(__uint_as_float(d_[ce]), P.scale, -dl8[2 * e + u]);   // p (dP - delta) scale
+              }
+              pp[e] = pack2<T>(pv[0], pv[1]);
+              dd[e] = pack2<T>(dv[0], dv[1]);
+            }
+            // byte offset of these 8 columns in the 128-row tile: 64-column chunk, then the swizzled 16-byte piece
+            const int col8 = hh * (CPT / 8) + c16;
+            const int off = (col8 >> 3) * 16384 + (((col8 & 7) ^ (t & 7)) << 4);
+            if (Cfg::kPTinTmem) {
+#pragma unroll
+              for (int e = 0; e < 4; ++e) ptp[c16 * 4 + e] = pp[e];
+            } else {
+              *reinterpret_cast<uint4*>(pt_row + off) = make_uint4(pp[0], pp[1], pp[2], pp[3]);
+            }
+            *reinterpret_cast<uint4*>(dst_row + off) = make_uint4(dd[0], dd[1], dd[2], dd[3]);
+            if (Cfg::kPTinTmem && (c16 & 3) == 3)   // 32 finished columns = 16 packed words -> tensor memory
+              tmem_st16(tmem_base + Cfg::kColPT + lane_addr + hh * (CPT / 2) + (c16 >> 2) * 16, ptp + (c16 >> 2) * 16);
+          }
+          if (Cfg::kPTinTmem) tmem_st_wait();
+        }
+        fence_proxy_async();
+        tc_fence_before();
+        mbar_arrive(bar_pds);
+        // dQ read-out. With its own TMEM columns the PREVIOUS block's dQ is flushed here, while the
+        // tensor core works on this block; when dQ aliases S^T it has to be this block's.
+        const int fi = Cfg::kAliasDQ ? i : i - 1;
+        if (fi >= 0) {
+          if (!__all_sync(0xffffffffu, mbar_wait(bar_dq, (g0 + fi) & 1, abort_flag))) { ok = false; break; }
+          tc_fence_after();
+          flush_dq(q_start + fi);
+          tc_fence_before();
+          mbar_arrive(bar_dqfree);
+        }
+      }
+      if (!ok) break;
+      if (!Cfg::kAliasDQ) {
+        // the tile's last dQ; its completion also means every MMA of the tile is complete
+        if (!__all_sync(0xffffffffu, mbar_wait(bar_dq, (g0 + n_q - 1) & 1, abort_flag))) { ok = false; break; }
+        tc_fence_after();
+        flush_dq(q_start + n_q - 1);
         tc_fence_before();
         mbar_arrive(bar_dqfree);
       }
-    }
-    if (ok && !Cfg::kAliasDQ) {
-      if (__all_sync(0xffffffffu, mbar_wait(bar_dq, (n_q - 1) & 1, abort_flag))) {
-        tc_fence_after();
-        flush_dq(q_start + n_q - 1);
-      } else {
-        ok = false;
-      }
-    }
-    if (lane == 0) bulk_wait_all<0>();   // reduces must be done with shared memory before the CTA exits
-    __syncwarp();
-    if (ok) {
-      // All MMAs are complete (the last bar_dq was waited above). The warps of column half 0 write
-      // dK, those of half 1 dV: 32 key rows x 64 columns at a time are staged (128-byte rows,
-      // swizzled) in the warp's buffer and stored by TMA, which clips rows past the sequence end.
-      const CUtensorMap* map = hh ? &tmDV : &tmDK;
-      const MapPos pos = hh ? P.pdv : P.pdk;
-      const int col0 = hh ? Cfg::kColDV : Cfg::kColDK;
-      uint8_t* stage = base_ptr + Cfg::kOffStage + warp * 4096;
+      // All MMAs of the tile are complete (its last bar_dq was waited above, in either variant).
+      // The warps of column group 0 write dK, those of group 1 dV: 32 key rows x 64 columns at a
+      // time are staged (128-byte rows, swizzled) in the warp's buffer and stored by TMA, which
+      // clips rows past the sequence end. Once the accumulators are in registers the MMA warp may
+      // start the next tile's dV / dK.
+      if (hh < 2) {
+        const CUtensorMap* map = hh ? &tmDV : &tmDK;
+        const MapPos pos = hh ? P.pdv : P.pdk;
+        const int col0 = hh ? Cfg::kColDV : Cfg::kColDK;
+        uint8_t* stage = base_ptr + Cfg::kOffStage + warp * 4096;
 #pragma unroll 1
-      for (int dc = 0; dc < Cfg::kChunks; ++dc) {
-        uint32_t r[64];
-        tmem_ld32(tmem_base + col0 + lane_addr + dc * 64, r);
-        tmem_ld32(tmem_base + col0 + lane_addr + dc * 64 + 32, r + 32);
-        tmem_ld_wait();
-        if (lane == 0) bulk_wait_read<0>();     // earlier reduce / store out of this buffer has been read
-        __syncwarp();
+        for (int dc = 0; dc < Cfg::kChunks; ++dc) {
+          uint32_t r[64];
+          tmem_ld32(tmem_base + col0 + lane_addr + dc * 64, r);
+          tmem_ld32(tmem_base + col0 + lane_addr + dc * 64 + 32, r + 32);
+          tmem_ld_wait();
+          if (dc == Cfg::kChunks - 1) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_dkvfree);
+          }
+          if (lane == 0) bulk_wait_read<0>();     // earlier reduce / store out of this buffer has been read
+          __syncwarp();
 #pragma unroll
-        for (int c16 = 0; c16 < 8; ++c16) {
-          uint4 v;
-          v.x = pack2<T>(__uint_as_float(r[c16 * 8 + 0]), __uint_as_float(r[c16 * 8 + 1]));
-          v.y = pack2<T>(__uint_as_float(r[c16 * 8 + 2]), __uint_as_float(r[c16 * 8 + 3]));
-          v.z = pack2<T>(__uint_as_float(r[c16 * 8 + 4]), __uint_as_float(r[c16 * 8 + 5]));
-          v.w = pack2<T>(__uint_as_float(r[c16 * 8 + 6]), __uint_as_float(r[c16 * 8 + 7]));
-          *reinterpret_cast<uint4*>(stage + lane * 128 + ((c16 ^ (lane & 7)) << 4)) = v;
-        }
-        fence_proxy_async();
-        __syncwarp();
-        if (lane == 0) {
-          store_rows(map, smem_u32(stage), pos, dc * 64, jb * 128 + (warp & 3) * 32, h, b);
-          bulk_commit();
+          for (int c16 = 0; c16 < 8; ++c16) {
+            uint4 v;
+            v.x = pack2<T>(__uint_as_float(r[c16 * 8 + 0]), __uint_as_float(r[c16 * 8 + 1]));
+            v.y = pack2<T>(__uint_as_float(r[c16 * 8 + 2]), __uint_as_float(r[c16 * 8 + 3]));
+            v.z = pack2<T>(__uint_as_float(r[c16 * 8 + 4]), __uint_as_float(r[c16 * 8 + 5]));
+            v.w = pack2<T>(__uint_as_float(r[c16 * 8 + 6]), __uint_as_float(r[c16 * 8 + 7]));
+            *reinterpret_cast<uint4*>(stage + lane * 128 + ((c16 ^ (lane & 7)) << 4)) = v;
+          }
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0) {
+            store_rows(map, smem_u32(stage), pos, dc * 64, jb * 128 + (warp & 3) * 32, h, b);
+            bulk_commit();
+          }
         }
       }
-      if (lane == 0) bulk_wait_all<0>();
-      __syncwarp();
+      g0 += n_q;
     }
+    if (lane == 0) bulk_wait_all<0>();   // reduces and stores must be done with shared memory before the CTA exits
+    __syncwarp();
   }
 
   tc_fence_before();
@@ -511,8 +603,9 @@ static int launch_bwd(const AttnArgs& a, cudaStream_t st) {
   P.causal = a.causal; P.is_bf16 = bf; P.scale = a.scale; P.scale_log2 = a.scale * kLog2eF; P.flag = device_flag_ptr();
   auto kern = attn_bwd_tc_kernel<D, T>;
   MT_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
-  const unsigned grid = (unsigned)(P.nqb * P.B * P.H);
-  kern<<<grid, kBwdThreads, Cfg::kSmem, st>>>(tq, tk, tv, tdo, tdq, tdk, tdv, P);
+  const int64_t n_tiles = (int64_t)P.nqb * P.B * P.H;
+  const unsigned grid = (unsigned)(n_tiles < sm_count() ? n_tiles : sm_count());   // persistent: one CTA per SM
+  kern<<<grid, Cfg::kThreads, Cfg::kSmem, st>>>(tq, tk, tv, tdo, tdq, tdk, tdv, P);
   MT_LAUNCH_CHECK();
   const int64_t n_vec = n_acc / 8;
   int64_t blocks = (n_vec + 255) / 256;
