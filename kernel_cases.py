@@ -2,7 +2,7 @@
 inputs larger than the 126 MB L2 where DRAM figures matter, under 2 GB held on
 the device, a handful of launches.
 
-    python kernel_cases.py {gemm|attn|mem|adamw|gemm_vs_library|power|suite}
+    python kernel_cases.py {gemm|attn|mem|adamw|gemm_vs_library|gemm_shapes|power|suite}
 
 gemm : the GPT-2 124M qkv projection of one 16x1024-token micro-batch
        (16384x768 @ 768x2304, fp16), five launches
@@ -15,6 +15,9 @@ gemm_vs_library : the lm_head GEMM (16384x50304x768, fp16) timed for 300 back-to
        random-normal, small-integer and all-zero operands. Throughput on a power-capped B200
        depends on the operand values (bit toggling), so a roofline fraction only means
        something against a library number taken on the same data.
+gemm_shapes : every GEMM of one GPT-2 124M micro-batch (16384 tokens: qkv, out-proj, fc1, fc2, lm_head;
+       forward, dgrad, wgrad, with the epilogues the model uses) timed back to back on random-normal
+       data, this library's kernel next to torch.matmul (cuBLAS) on the same operands.
 power : board power (nvidia-smi, 20 ms samples) while one kernel at a time loops for ~1.5 s at the
        GPT-2 124M shapes: time per launch x median power = energy per launch. On a 1 kW board the
        training step runs at the power cap, so its floor is the sum of these energies / 1 kW.
@@ -76,6 +79,9 @@ def main(which):
             opt.step()
     elif which == "gemm_vs_library":
         gemm_vs_library(r)
+        return
+    elif which == "gemm_shapes":
+        gemm_shapes(r)
         return
     elif which == "power":
         power_by_kernel(randn, r)
@@ -277,6 +283,66 @@ def power_by_kernel(randn, r, seconds=1.5):
         p.grad = gz
         opt.step()
     run("AdamW step, 130M fp32", step)
+
+
+def gemm_shapes(r, M=16384, iters=100):
+    """One line per GEMM of the GPT-2 124M step: this library (with the epilogue the model uses)
+    and torch.matmul on the same random-normal operands, microseconds and TFLOP/s."""
+    import torch
+    d, V = 768, 50304
+
+    def rn(shape, dt="float16"):
+        return DeviceArray.from_numpy(r.standard_normal(shape, dtype=np.float32), dt)
+
+    def tt(a):
+        return torch.from_numpy(a.numpy()).cuda()
+
+    def time_torch(fn):
+        for _ in range(3):
+            fn()
+        e0, e1 = torch.cuda.Event(True), torch.cuda.Event(True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / iters
+
+    print(f"{'GEMM (M=16384 tokens)':44s} {'N':>6s} {'K':>6s} | {'this library':>22s} | {'torch.matmul':>22s} | ratio")
+    total_own = total_lib = 0.0
+    for name, n_out, k_in, count in (("qkv", 3 * d, d, 12), ("out-proj", d, d, 12), ("fc1", 4 * d, d, 12),
+                                     ("fc2", d, 4 * d, 12), ("lm_head", V, d, 1)):
+        x, w, dy = rn((M, k_in)), rn((n_out, k_in)), rn((M, n_out))
+        res, aux = rn((M, n_out)), rn((M, k_in))
+        tx, tw, tdy = tt(x), tt(w), tt(dy)
+        y = DeviceArray.empty((M, n_out), "float16")
+        dx = DeviceArray.empty((M, k_in), "float16")
+        dw = DeviceArray.zeros((n_out, k_in), "float32")
+        variants = []
+        if name == "fc1":
+            variants.append(("fwd + GELU, derivative stored", lambda: F.gemm(x, w, trans_b=True, act="gelu", preact="grad"), M, n_out, k_in))
+        elif name in ("out-proj", "fc2"):
+            variants.append(("fwd + residual add", lambda: F.gemm(x, w, trans_b=True, out=y, aux=res, aux_mode=1), M, n_out, k_in))
+        else:
+            variants.append(("fwd", lambda: F.gemm(x, w, trans_b=True, out=y), M, n_out, k_in))
+        if name == "fc2":
+            variants.append(("dgrad * act'(.)", lambda: F.gemm(dy, w, out=dx, aux=aux, aux_mode=5), M, k_in, n_out))
+        else:
+            variants.append(("dgrad", lambda: F.gemm(dy, w, out=dx), M, k_in, n_out))
+        variants.append(("wgrad (fp32, split-K add)", lambda: F.gemm(dy, x, trans_a=True, out=dw, accumulate=2), n_out, k_in, M))
+        libs = [lambda: torch.matmul(tx, tw.t()), lambda: torch.matmul(tdy, tw), lambda: torch.matmul(tdy.t(), tx)]
+        for (label, fn, mm, nn, kk), lib in zip(variants, libs):
+            own = _time_own(fn, iters)
+            ref = time_torch(lib)
+            fl = 2.0 * mm * nn * kk
+            total_own += own * count
+            total_lib += ref * count
+            print(f"{name + ' ' + label:44s} {nn:6d} {kk:6d} | {own * 1e3:8.1f} us {fl / own / 1e9:6.0f} TF/s | "
+                  f"{ref * 1e3:8.1f} us {fl / ref / 1e9:6.0f} TF/s | {ref / own:5.2f}", flush=True)
+        del x, w, dy, res, aux, tx, tw, tdy, y, dx, dw
+    print(f"sum over one micro-batch (12 layers + head): this library {total_own:.2f} ms, torch.matmul {total_lib:.2f} ms "
+          "(the library side carries the fused epilogues; the torch side is the bare product)")
 
 
 def gemm_vs_library(r, m=16384, n=50304, k=768, iters=300):

@@ -57,6 +57,7 @@ struct GemmParams {
   int out_dtype, in_bf16, act, accumulate, vec_store, tma_store;
   float alpha;
   int tiles_m, tiles_n, splits, kb_per_split, kb_total;
+  int n_fast;   // order of the tile walk: 0 = neighbouring tiles share their columns (B panel), 1 = their rows (A panel)
   int* flag;
 };
 
@@ -448,8 +449,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       bool ok = true;
       for (int t = worker; t < total_tiles && ok; t += workers) {
         const int mn = t % tiles_mn, split = t / tiles_mn;
-        const int m0 = (mn % P.tiles_m) * TM + (int)rank * BM;
-        const int n0 = (mn / P.tiles_m) * BN + (int)rank * (PAIR ? BN / 2 : 0);   // this CTA's rows of the B tile
+        const int tm_i = P.n_fast ? mn / P.tiles_n : mn % P.tiles_m, tn_i = P.n_fast ? mn % P.tiles_n : mn / P.tiles_m;
+        const int m0 = tm_i * TM + (int)rank * BM;
+        const int n0 = tn_i * BN + (int)rank * (PAIR ? BN / 2 : 0);   // this CTA's rows of the B tile
         const int kb0 = split * P.kb_per_split;
         const int kb1 = min(kb0 + P.kb_per_split, P.kb_total);
         for (int kb = kb0; kb < kb1; ++kb) {
@@ -544,7 +546,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     for (int t = worker; t < total_tiles && ok; t += workers, ++it) {
       const int mn = t % tiles_mn;
       const bool add_bias = P.bias != nullptr && t / tiles_mn == 0;  // only the first K split adds it
-      const int64_t m0 = (int64_t)(mn % P.tiles_m) * TM + (int64_t)rank * BM, n0 = (int64_t)(mn / P.tiles_m) * BN;
+      const int tm_i = P.n_fast ? mn / P.tiles_n : mn % P.tiles_m, tn_i = P.n_fast ? mn % P.tiles_n : mn / P.tiles_m;
+      const int64_t m0 = (int64_t)tm_i * TM + (int64_t)rank * BM, n0 = (int64_t)tn_i * BN;
       const int buf = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       // the first aux slab of this tile travels while the accumulator is still being computed
@@ -871,6 +874,21 @@ int gemm_tc(const GemmArgs& g, cudaStream_t st) {
   P.kb_per_split = (kb_total + best_splits - 1) / best_splits;
   P.flag = device_flag_ptr();
   const long long total = (long long)P.tiles_m * P.tiles_n * P.splits;
+  {
+    // Which tiles run side by side decides what DRAM sees. Walking the rows first (the default),
+    // the tiles in flight share one B panel and each streams its own A panel, so A is read once
+    // per column tile; walking the columns first, the tiles of one row panel run together and
+    // share A, while B is read once per group of tiles in flight. An operand that fits the L2
+    // is read from DRAM once either way. The lm_head's dX and dW GEMMs (A = the 1.65 GB of
+    // dlogits, three column tiles) read 5 GB of DRAM the first way and 1.7 GB the second.
+    const double bytes_a = (double)g.M * (double)g.K * 2.0, bytes_b = (double)g.N * (double)g.K * 2.0;
+    const double l2 = 64e6;
+    const long long workers_now = pair ? pairs_avail : sms;
+    const double groups = (double)(((long long)P.tiles_m * P.tiles_n + workers_now - 1) / workers_now);
+    const double traffic_rows_first = bytes_b + bytes_a * (bytes_a > l2 ? P.tiles_n : 1);
+    const double traffic_cols_first = bytes_a + bytes_b * (bytes_b > l2 ? groups : 1);
+    P.n_fast = traffic_cols_first < traffic_rows_first ? 1 : 0;
+  }
   const int grid = pair ? (int)(total < pairs_avail ? total : pairs_avail)   // clusters
                         : (int)(total < sms ? total : sms);                  // CTAs
 
