@@ -281,6 +281,9 @@ int mt_gemm(const void* A, const void* B, void* C, void* preact, const void* bia
  *   aux_mode 3: C = result * 2*relu(aux)    (backward of relu_squared)
  *   aux_mode 4: C = result * (aux > 0)      (backward of relu)
  *   aux_mode 5: C = result * aux            (aux already holds a derivative, see below)
+ *   aux_mode 6: C = result * 2*sqrt(aux)    (backward of relu_squared from its OUTPUT: with
+ *               aux = relu(u)^2 the derivative 2*relu(u) is 2*sqrt(aux), so the forward pass
+ *               keeps nothing but the activation it needs anyway)
  * `act` may be OR'ed with MT_ACT_STORE_GRAD: the second output (`preact`) then receives the
  * activation's derivative at the pre-activation, act'(A*B + bias), instead of the
  * pre-activation itself - what the backward pass multiplies by (aux_mode 5), computed where the

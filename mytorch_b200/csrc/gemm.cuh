@@ -25,6 +25,7 @@ __device__ __forceinline__ float aux_apply(float x, float a, int mode) {
     case 3: return x * 2.f * fmaxf(a, 0.f);                 // x * d/da relu(a)^2
     case 4: return a > 0.f ? x : 0.f;                       // x * d/da relu(a)
     case 5: return x * a;                                   // x * aux (aux = a stored derivative)
+    case 6: return x * 2.f * sqrtf(fmaxf(a, 0.f));          // x * d/du relu(u)^2 with aux = relu(u)^2 itself
     default: return x;
   }
 }

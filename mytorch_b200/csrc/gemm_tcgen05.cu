@@ -80,6 +80,7 @@ __device__ __forceinline__ float aux_apply_tc(float x, float a, int mode) {
     case 3: return x * 2.f * fmaxf(a, 0.f);
     case 4: return a > 0.f ? x : 0.f;
     case 5: return x * a;
+    case 6: return x * 2.f * sqrtf(fmaxf(a, 0.f));
     default: return x;
   }
 }
@@ -968,7 +969,7 @@ int mt_gemm(const void* A, const void* B, void* C, void* preact, const void* bia
 int mt_gemm_ex(const void* A, const void* B, void* C, void* preact, const void* bias, const void* aux, int aux_mode,
                int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int trans_a, int trans_b,
                int in_dtype, int out_dtype, int act, float alpha, int accumulate, void* stream) {
-  MT_REQUIRE((aux != nullptr) == (aux_mode != 0) && aux_mode >= 0 && aux_mode <= 5, "gemm: aux operand and aux_mode must be given together");
+  MT_REQUIRE((aux != nullptr) == (aux_mode != 0) && aux_mode >= 0 && aux_mode <= 6, "gemm: aux operand and aux_mode must be given together");
   MT_REQUIRE((act & ~0x1ff) == 0 && (act & 0xff) <= MT_ACT_RELU, "gemm: unknown activation");
   MT_REQUIRE(!(act & 0x100) || preact, "gemm: storing the activation's derivative needs the second output");
   MT_REQUIRE(!(aux_mode && accumulate == 2), "gemm: an aux operand cannot be combined with split-K accumulation");

@@ -131,7 +131,17 @@ __device__ __forceinline__ float tanh_cap(float x) {
   const float small = x * fmaf(x2, fmaf(x2, fmaf(x2, -17.f / 315.f, 2.f / 15.f), -1.f / 3.f), 1.f);
   return fabsf(x) < 0.1f ? small : big;
 }
-__device__ __forceinline__ float softcap_f(float x, float cap) { return cap > 0.f ? cap * tanh_cap(__fdividef(x, cap)) : x; }
+// One MUFU instruction, relative error ~2^-11: at the level of the rounding that fp16 / bf16
+// logits already carry, so the half-precision kernels use it (FAST) and halve the special-function
+// work of the capped loss, which is bound by that unit (two passes x (tanh + exp) per logit).
+__device__ __forceinline__ float tanh_mufu(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+template <bool FAST> __device__ __forceinline__ float tanh_sel(float x) { return FAST ? tanh_mufu(x) : tanh_cap(x); }
+template <bool FAST = false>
+__device__ __forceinline__ float softcap_f(float x, float cap) { return cap > 0.f ? cap * tanh_sel<FAST>(__fdividef(x, cap)) : x; }
 
 constexpr int kCeThreads = 512;
 
@@ -155,14 +165,14 @@ ce_fwd_kernel(const T* __restrict__ logits, const int32_t* __restrict__ labels, 
       float f[VN];
       float vm = -INFINITY;
 #pragma unroll
-      for (int e = 0; e < VN; ++e) { f[e] = softcap_f(v.get(e), softcap); vm = fmaxf(vm, f[e]); }
+      for (int e = 0; e < VN; ++e) { f[e] = softcap_f<sizeof(T) == 2>(v.get(e), softcap); vm = fmaxf(vm, f[e]); }
       if (vm > m) { s *= exp2f((m - vm) * kLog2e); m = vm; }
 #pragma unroll
       for (int e = 0; e < VN; ++e) s += exp2f((f[e] - m) * kLog2e);
     }
   }
   for (int64_t c = vec_end + threadIdx.x; c < classes; c += kCeThreads) {
-    float f = softcap_f(to_f(xr[c]), softcap);
+    float f = softcap_f<sizeof(T) == 2>(to_f(xr[c]), softcap);
     if (f > m) { s *= exp2f((m - f) * kLog2e); m = f; }
     s += exp2f((f - m) * kLog2e);
   }
@@ -195,13 +205,13 @@ ce_fwd_kernel(const T* __restrict__ logits, const int32_t* __restrict__ labels, 
       const float mx = fmaxf(old, lse_c);
       lse_out[row] = mx == -INFINITY ? -INFINITY : mx + logf(__expf(old - mx) + __expf(lse_c - mx));
       const int64_t lab = (int64_t)labels[row] - col_offset;
-      if (lab >= 0 && lab < classes) tgt[row] = softcap_f(to_f(xr[lab]), softcap);
+      if (lab >= 0 && lab < classes) tgt[row] = softcap_f<sizeof(T) == 2>(to_f(xr[lab]), softcap);
     } else if (lane == 0) {
       float lse = m + logf(s);
       lse_out[row] = lse;
       int32_t lab = labels[row];
       float l = 0.f;
-      if (lab >= 0 && lab < classes) l = lse - softcap_f(to_f(xr[lab]), softcap);
+      if (lab >= 0 && lab < classes) l = lse - softcap_f<sizeof(T) == 2>(to_f(xr[lab]), softcap);
       else if (lab != -100 && flag) atomicMax(flag, 2);  // label out of range: recorded, row ignored
       loss[row] = l;
     }
@@ -272,14 +282,14 @@ ce_fwd_grad_kernel(T* __restrict__ logits, const int32_t* __restrict__ labels, f
       float f[VN];
       float vm = -INFINITY;
 #pragma unroll
-      for (int e = 0; e < VN; ++e) { f[e] = softcap_f(v.get(e), softcap); vm = fmaxf(vm, f[e]); }
+      for (int e = 0; e < VN; ++e) { f[e] = softcap_f<sizeof(T) == 2>(v.get(e), softcap); vm = fmaxf(vm, f[e]); }
       if (vm > m) { s *= exp2f((m - vm) * kLog2e); m = vm; }
 #pragma unroll
       for (int e = 0; e < VN; ++e) s += exp2f((f[e] - m) * kLog2e);
     }
   }
   for (int64_t c = vec_end + threadIdx.x; c < classes; c += kCeThreads) {
-    float f = softcap_f(to_f(xr[c]), softcap);
+    float f = softcap_f<sizeof(T) == 2>(to_f(xr[c]), softcap);
     if (f > m) { s *= exp2f((m - f) * kLog2e); m = f; }
     s += exp2f((f - m) * kLog2e);
   }
@@ -310,7 +320,7 @@ ce_fwd_grad_kernel(T* __restrict__ logits, const int32_t* __restrict__ labels, f
       lse_out[row] = lse;
       row_lse = lse;
       float l = 0.f;
-      if (valid) l = lse - softcap_f(to_f(xr[label]), softcap);
+      if (valid) l = lse - softcap_f<sizeof(T) == 2>(to_f(xr[label]), softcap);
       else if (label != -100 && flag) atomicMax(flag, 2);  // label out of range: recorded, row ignored
       loss[row] = l;
     }
@@ -328,7 +338,7 @@ ce_fwd_grad_kernel(T* __restrict__ logits, const int32_t* __restrict__ labels, f
 #pragma unroll
       for (int e = 0; e < VN; ++e) {
         float x = v.get(e), f = x, dcap = 1.f;
-        if (softcap > 0.f) { float t = tanh_cap(__fdividef(x, softcap)); f = softcap * t; dcap = 1.f - t * t; }
+        if (softcap > 0.f) { float t = tanh_sel<sizeof(T) == 2>(__fdividef(x, softcap)); f = softcap * t; dcap = 1.f - t * t; }
         float p = valid ? exp2f((f - l) * kLog2e) : 0.f;
         if (vi * VN + e == label) p -= 1.f;
         o.set(e, p * scale * dcap);
@@ -338,7 +348,7 @@ ce_fwd_grad_kernel(T* __restrict__ logits, const int32_t* __restrict__ labels, f
   }
   for (int64_t c = vec_end + threadIdx.x; c < classes; c += kCeThreads) {
     float x = to_f(xr[c]), f = x, dcap = 1.f;
-    if (softcap > 0.f) { float t = tanh_cap(__fdividef(x, softcap)); f = softcap * t; dcap = 1.f - t * t; }
+    if (softcap > 0.f) { float t = tanh_sel<sizeof(T) == 2>(__fdividef(x, softcap)); f = softcap * t; dcap = 1.f - t * t; }
     float p = valid ? exp2f((f - l) * kLog2e) : 0.f;
     if (c == label) p -= 1.f;
     xr[c] = from_f<T>(p * scale * dcap);
@@ -403,7 +413,7 @@ ce_fwd_grad_staged_kernel(T* __restrict__ logits, const int32_t* __restrict__ la
       float f[VN];
       float vm = -INFINITY;
 #pragma unroll
-      for (int e = 0; e < VN; ++e) { f[e] = softcap_f(v.get(e), softcap); vm = fmaxf(vm, f[e]); }
+      for (int e = 0; e < VN; ++e) { f[e] = softcap_f<sizeof(T) == 2>(v.get(e), softcap); vm = fmaxf(vm, f[e]); }
       if (vm > m) { s *= ex2_fast((m - vm) * kLog2e); m = vm; }
       const float mb = m * kLog2e;
 #pragma unroll
@@ -441,7 +451,7 @@ ce_fwd_grad_staged_kernel(T* __restrict__ logits, const int32_t* __restrict__ la
       lse_out[row] = lse;
       row_lse = lse;
       float l = 0.f;
-      if (valid) l = lse - softcap_f(to_f(sr[label]), softcap);
+      if (valid) l = lse - softcap_f<sizeof(T) == 2>(to_f(sr[label]), softcap);
       else if (label != -100 && flag) atomicMax(flag, 2);  // label out of range: recorded, row ignored
       loss[row] = l;
     }
@@ -459,7 +469,7 @@ ce_fwd_grad_staged_kernel(T* __restrict__ logits, const int32_t* __restrict__ la
 #pragma unroll
     for (int e = 0; e < VN; ++e) {
       float x = v.get(e), f = x, dcap = scale;
-      if (softcap > 0.f) { float t = tanh_cap(__fdividef(x, softcap)); f = softcap * t; dcap = scale * (1.f - t * t); }
+      if (softcap > 0.f) { float t = tanh_sel<sizeof(T) == 2>(__fdividef(x, softcap)); f = softcap * t; dcap = scale * (1.f - t * t); }
       float pr = valid ? ex2_fast(fmaf(f, kLog2e, -lb)) : 0.f;
       if (vi == label_vec && e == label_e) pr -= 1.f;
       pe[e] = pr * dcap;
@@ -511,7 +521,7 @@ ce_bwd_kernel(const T* __restrict__ logits, const int32_t* __restrict__ labels, 
 #pragma unroll
       for (int e = 0; e < VN; ++e) {
         float x = v.get(e), f = x, dcap = 1.f;
-        if (softcap > 0.f) { float t = tanh_cap(__fdividef(x, softcap)); f = softcap * t; dcap = 1.f - t * t; }
+        if (softcap > 0.f) { float t = tanh_sel<sizeof(T) == 2>(__fdividef(x, softcap)); f = softcap * t; dcap = 1.f - t * t; }
         float p = ignored ? 0.f : exp2f((f - l) * kLog2e);
         if (cc + e == lab) p -= 1.f;
         o.set(e, p * scale * dcap);
@@ -522,7 +532,7 @@ ce_bwd_kernel(const T* __restrict__ logits, const int32_t* __restrict__ labels, 
   }
   for (int64_t cc = c + threadIdx.x; cc < c1; cc += 256) {
     float x = to_f(xr[cc]), f = x, dcap = 1.f;
-    if (softcap > 0.f) { float t = tanh_cap(__fdividef(x, softcap)); f = softcap * t; dcap = 1.f - t * t; }
+    if (softcap > 0.f) { float t = tanh_sel<sizeof(T) == 2>(__fdividef(x, softcap)); f = softcap * t; dcap = 1.f - t * t; }
     float p = ignored ? 0.f : exp2f((f - l) * kLog2e);
     if (cc == lab) p -= 1.f;
     dr[cc] = from_f<T>(p * scale * dcap);

@@ -94,7 +94,10 @@ def mlp(x, w1, w2, act_func="gelu", residual=None):
     activation costs no kernel and no transcendental."""
     x2 = _flat2d(x.data)
     graph = _needs_graph(x, w1, w2, residual)
-    if graph:
+    # relu(u)^2 carries its own derivative: 2*relu(u) = 2*sqrt(h). Nothing extra is stored and the
+    # backward GEMM takes the square root of h in its epilogue (aux_mode 6).
+    from_output = act_func in ("relu_squared", "relu2")
+    if graph and not from_output:
         h, u = K.gemm(x2, w1.data, trans_b=True, act=act_func, preact="grad")      # u = act'(x @ w1^T)
     else:
         h, u = K.gemm(x2, w1.data, trans_b=True, act=act_func), None
@@ -107,7 +110,8 @@ def mlp(x, w1, w2, act_func="gelu", residual=None):
             g2 = _flat2d(g)
             if w2.requires_grad:
                 _param_grad_gemm(g2, h, w2)
-            du = K.gemm(g2, w2.data, aux=u, aux_mode=5)                                # (dy @ w2) * act'(.), one kernel
+            du = (K.gemm(g2, w2.data, aux=h, aux_mode=6) if from_output                # (dy @ w2) * act'(.), one kernel
+                  else K.gemm(g2, w2.data, aux=u, aux_mode=5))
             if w1.requires_grad:
                 _param_grad_gemm(du, x2, w1)
             if x.requires_grad:

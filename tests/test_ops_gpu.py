@@ -502,6 +502,10 @@ def test_gemm_aux_operand_residual_and_activation_backward(mt, dtype):
     close(F.gemm(A, B, trans_b=True, aux=AUX, aux_mode=2).numpy(), O.gelu_bwd(aux.astype(np.float64), base), 2 * t, "gelu'")
     close(F.gemm(A, B, trans_b=True, aux=AUX, aux_mode=3).numpy(), O.relu2_bwd(aux.astype(np.float64), base), 2 * t, "relu2'")
     close(F.gemm(A, B, trans_b=True, aux=AUX, aux_mode=4).numpy(), (aux > 0) * base, 2 * t, "relu'")
+    # relu_squared's derivative recovered from its OUTPUT: aux = relu(u)^2, factor 2*sqrt(aux) = 2*relu(u)
+    h = rnd(np.maximum(aux, 0.0) ** 2, dtype)
+    close(F.gemm(A, B, trans_b=True, aux=dev(mt, h, dtype), aux_mode=6).numpy(), base * 2.0 * np.sqrt(h.astype(np.float64)),
+          2 * t, "relu2' from its output")
     # activation first, then the residual
     close(F.gemm(A, B, trans_b=True, act="gelu", aux=AUX, aux_mode=1).numpy(), O.gelu_fwd(base) + aux, t, "gelu + residual")
     no_device_flag(mt)
