@@ -48,7 +48,10 @@ template <int BN, bool PAIR = false> struct GemmCfg {
   static constexpr int kStages = PAIR ? 6 : (BN == 256 ? 4 : 6);
   static constexpr int kTmemCols = 2 * BN;  // two accumulator buffers
   static constexpr int kEpiBytes = kEpiWarps * 4096;  // per epilogue warp: one 32-row x 128-byte staging buffer
-  static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024 /*align*/ + 512 /*barriers*/;
+  // Epilogues that move a second [M,N] tensor (an aux operand read, or a second output) can run
+  // with one pipeline stage less and use its shared memory as a second staging buffer per warp.
+  static constexpr bool kCanDoubleStage = kStageBytes >= kEpiBytes;
 };
 
 struct GemmParams {
@@ -57,6 +60,7 @@ struct GemmParams {
   int out_dtype, in_bf16, act, accumulate, vec_store, tma_store;
   float alpha;
   int tiles_m, tiles_n, splits, kb_per_split, kb_total;
+  int stages;   // pipeline stages in use: Cfg::kStages, or one less with the last stage's memory as second staging buffers
   int n_fast;   // order of the tile walk: 0 = neighbouring tiles share their columns (B panel), 1 = their rows (A panel)
   int* flag;
 };
@@ -198,9 +202,11 @@ template <> __device__ __forceinline__ uint32_t pack_pair<float>(float a, float)
 // rows/columns past M/N clipped by the tensor map, optional fp32 reduce-add.
 template <typename TO, int CW>
 __device__ __forceinline__ void stage_store(const CUtensorMap* map, const uint32_t* r, uint8_t* stage, int lane, int x,
-                                            int y, bool reduce, int& sidx) {
+                                            int y, bool reduce, int& sidx, bool keep_one = false) {
   uint8_t* buf = stage;
-  if (lane == 0) bulk_wait_read<0>();   // the previous store of this warp has finished reading the buffer
+  // the last store out of this buffer has finished reading it: with two buffers used in turn that
+  // is the store before the latest one, which may still be in flight
+  if (lane == 0) { if (keep_one) bulk_wait_read<1>(); else bulk_wait_read<0>(); }
   __syncwarp();
   uint8_t* rowp = buf + lane * 128;
 #pragma unroll
@@ -238,8 +244,15 @@ template <int BN, typename TO>
 __device__ __forceinline__ bool epilogue_staged(const GemmParams& P, const CUtensorMap* tmC, const CUtensorMap* tmPre,
                                                 const CUtensorMap* tmAux, uint32_t taddr, uint8_t* stage, int lane, int y0,
                                                 int64_t n0, bool add_bias, int& sidx, int col_begin, uint32_t aux_bar,
-                                                uint32_t& aux_phase, bool aux_prefetched, volatile int* abort_flag) {
+                                                uint32_t& aux_phase, bool aux_prefetched, volatile int* abort_flag,
+                                                uint8_t* stage2 = nullptr, uint32_t aux_bar2 = 0, uint32_t* aux_phase2 = nullptr,
+                                                bool aux_prefetched2 = false) {
   constexpr int CW = 128 / (int)sizeof(TO);   // accumulator columns per 128-byte staged row
+  // Two staging buffers (half outputs: two slabs per warp and tile): slab 0 lives in `stage`,
+  // slab 1 in `stage2` - the aux slabs of both are in flight before the accumulator is ready,
+  // and one slab's TMA store reads its buffer while the next slab is computed into the other.
+  // A second output goes through `stage2`, the first through `stage`.
+  const bool dbl = stage2 != nullptr && BN / 2 / CW == 2;
   // This warp's half of the tile's columns is requested at once and waited for once.
   constexpr int GW = BN / 2;                  // columns per warp = per load group (128 or 64)
   const float alpha = P.alpha;
@@ -301,7 +314,8 @@ __device__ __forceinline__ bool epilogue_staged(const GemmParams& P, const CUten
       if (P.preact && store_grad) {
         // the second output receives act'(x): computed together with act(x) (one tanh), packed
         // into the staging rows eight columns at a time, while rc is overwritten with act(x)
-        if (lane == 0) bulk_wait_read<0>();
+        uint8_t* const gstage = dbl ? stage2 : stage;
+        if (lane == 0) { if (dbl) bulk_wait_read<1>(); else bulk_wait_read<0>(); }
         __syncwarp();
         constexpr int PER = 16 / (int)sizeof(TO);
         constexpr bool kHalfMath = std::is_same<TO, __half>::value;
@@ -318,7 +332,7 @@ __device__ __forceinline__ bool epilogue_staged(const GemmParams& P, const CUten
               rc[v * 8 + 2 * u] = __float_as_uint(__low2float(yh));
               rc[v * 8 + 2 * u + 1] = __float_as_uint(__high2float(yh));
             }
-            *reinterpret_cast<uint4*>(stage + lane * 128 + ((v ^ (lane & 7)) << 4)) = make_uint4(db[0], db[1], db[2], db[3]);
+            *reinterpret_cast<uint4*>(gstage + lane * 128 + ((v ^ (lane & 7)) << 4)) = make_uint4(db[0], db[1], db[2], db[3]);
             continue;
           }
           float d[PER];
@@ -335,14 +349,14 @@ __device__ __forceinline__ bool epilogue_staged(const GemmParams& P, const CUten
             q.x = pack_pair<TO>(d[0], d[1]); q.y = pack_pair<TO>(d[2 % PER], d[3 % PER]);
             q.z = pack_pair<TO>(d[4 % PER], d[5 % PER]); q.w = pack_pair<TO>(d[6 % PER], d[7 % PER]);
           }
-          *reinterpret_cast<uint4*>(stage + lane * 128 + ((v ^ (lane & 7)) << 4)) = q;
+          *reinterpret_cast<uint4*>(gstage + lane * 128 + ((v ^ (lane & 7)) << 4)) = q;
         }
         fence_proxy_async();
         __syncwarp();
-        if (lane == 0) { tma_store_2d(tmPre, smem_u32(stage), (int)col0, y0); bulk_commit(); }
+        if (lane == 0) { tma_store_2d(tmPre, smem_u32(gstage), (int)col0, y0); bulk_commit(); }
         ++sidx;
       } else {
-        if (P.preact) stage_store<TO, CW>(tmPre, rc, stage, lane, (int)col0, y0, false, sidx);
+        if (P.preact) stage_store<TO, CW>(tmPre, rc, dbl ? stage2 : stage, lane, (int)col0, y0, false, sidx, dbl);
         if (std::is_same<TO, __half>::value && act == MT_ACT_GELU) {
 #pragma unroll
           for (int e = 0; e < CW; e += 2) {
@@ -361,23 +375,31 @@ __device__ __forceinline__ bool epilogue_staged(const GemmParams& P, const CUten
         // uniform: combine with the matching slab of the aux operand. It comes through the
         // staging buffer by TMA (coalesced, rows/columns past M/N read as zero); the first slab
         // of a tile was requested before the accumulator wait, the others are requested here.
-        if (!(aux_prefetched && g0 == col_begin && cc == 0)) {
-          if (lane == 0) aux_slab_load(tmAux, stage, aux_bar, (int)col0, y0);
+        const bool second = dbl && !P.preact && cc == 1;          // slab 1 of a double-staged tile
+        uint8_t* const astage = second ? stage2 : stage;
+        if (!((second ? aux_prefetched2 : aux_prefetched) && g0 == col_begin && cc == (second ? 1 : 0))) {
+          if (lane == 0) aux_slab_load(tmAux, astage, second ? aux_bar2 : aux_bar, (int)col0, y0);
         }
-        if (!__all_sync(0xffffffffu, mbar_wait(aux_bar, aux_phase, abort_flag))) return false;
-        aux_phase ^= 1u;
+        if (second) {
+          if (!__all_sync(0xffffffffu, mbar_wait(aux_bar2, *aux_phase2, abort_flag))) return false;
+          *aux_phase2 ^= 1u;
+        } else {
+          if (!__all_sync(0xffffffffu, mbar_wait(aux_bar, aux_phase, abort_flag))) return false;
+          aux_phase ^= 1u;
+        }
         constexpr int PER = 16 / (int)sizeof(TO);       // elements per 16-byte chunk
 #pragma unroll
         for (int v = 0; v < 8; ++v) {
           Vec16<TO> a;
-          a.load(reinterpret_cast<const TO*>(stage + lane * 128 + ((v ^ (lane & 7)) << 4)));
+          a.load(reinterpret_cast<const TO*>(astage + lane * 128 + ((v ^ (lane & 7)) << 4)));
 #pragma unroll
           for (int u = 0; u < PER; ++u)
             rc[v * PER + u] = __float_as_uint(aux_apply_tc(__uint_as_float(rc[v * PER + u]), a.get(u), P.aux_mode));
         }
         __syncwarp();
       }
-      stage_store<TO, CW>(tmC, rc, stage, lane, (int)col0, y0, P.accumulate != 0, sidx);
+      // first output: with two buffers and no second output, slab 1 goes through `stage2`
+      stage_store<TO, CW>(tmC, rc, (dbl && !P.preact && cc == 1) ? stage2 : stage, lane, (int)col0, y0, P.accumulate != 0, sidx, dbl);
     }
   }
   return true;
@@ -395,29 +417,31 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const int worker = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
   const int workers = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
   constexpr int TM = PAIR ? 2 * BM : BM;                  // rows of one scheduled tile
-  constexpr int S = Cfg::kStages;
+  constexpr int SMAX = Cfg::kStages;          // the shared-memory layout is that of the full pipeline
+  const int S = P.stages;                     // stages in use (SMAX, or SMAX - 1 with a second staging buffer per warp)
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;  // 1024-byte alignment for the 128B swizzle
   uint8_t* base_ptr = smem_raw + (base - raw);
-  uint8_t* epi_stage = base_ptr + S * Cfg::kStageBytes;   // 1024-byte aligned (stage sizes are multiples of 1 KB)
+  uint8_t* epi_stage = base_ptr + SMAX * Cfg::kStageBytes;   // 1024-byte aligned (stage sizes are multiples of 1 KB)
+  uint8_t* epi_stage2 = S < SMAX ? base_ptr + (SMAX - 1) * Cfg::kStageBytes : nullptr;   // the unused last stage
   uint64_t* bars = reinterpret_cast<uint64_t*>(epi_stage + Cfg::kEpiBytes);
   // barrier slots: full[S], empty[S], acc_full[2], acc_empty[2]
-  const uint32_t bar0 = base + S * Cfg::kStageBytes + Cfg::kEpiBytes;
+  const uint32_t bar0 = base + SMAX * Cfg::kStageBytes + Cfg::kEpiBytes;
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
-  auto empty_bar = [&](int s) { return bar0 + 8u * (S + s); };
-  auto accf_bar = [&](int b) { return bar0 + 8u * (2 * S + b); };
-  auto acce_bar = [&](int b) { return bar0 + 8u * (2 * S + 2 + b); };
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 4);
+  auto empty_bar = [&](int s) { return bar0 + 8u * (SMAX + s); };
+  auto accf_bar = [&](int b) { return bar0 + 8u * (2 * SMAX + b); };
+  auto acce_bar = [&](int b) { return bar0 + 8u * (2 * SMAX + 2 + b); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * SMAX + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  auto aux_bar = [&](int w) { return bar0 + 8u * (2 * S + 5 + w); };   // one per epilogue warp
+  auto aux_bar = [&](int w) { return bar0 + 8u * (2 * SMAX + 5 + w); };   // two per epilogue warp: slab 0, slab 1
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < S; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    for (int s = 0; s < SMAX; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
     for (int b = 0; b < 2; ++b) { mbar_init(accf_bar(b), 1); mbar_init(acce_bar(b), PAIR ? 2 * kEpiWarps : kEpiWarps); }
-    for (int w = 0; w < kEpiWarps; ++w) mbar_init(aux_bar(w), 1);
+    for (int w = 0; w < 2 * kEpiWarps; ++w) mbar_init(aux_bar(w), 1);
     *abort_flag = 0;
     fence_barrier_init();
     fence_proxy_async();
@@ -541,8 +565,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int col_begin = ((warp - 2) >> 2) * (BN / 2);   // this warp's half of the tile's columns
     int it = 0;
     int sidx = 0;   // running count of staged stores of this warp (selects the staging buffer)
-    uint32_t aux_phase = 0;
-    const uint32_t my_aux_bar = aux_bar(warp - 2);
+    uint32_t aux_phase = 0, aux_phase2 = 0;
+    const uint32_t my_aux_bar = aux_bar(warp - 2), my_aux_bar2 = aux_bar(kEpiWarps + warp - 2);
+    uint8_t* const stage2 = epi_stage2 ? epi_stage2 + (warp - 2) * 4096 : nullptr;
+    const int slab_cols = P.out_dtype == MT_F32 ? 32 : 64;     // accumulator columns of one staged slab
     bool ok = true;
     for (int t = worker; t < total_tiles && ok; t += workers, ++it) {
       const int mn = t % tiles_mn;
@@ -555,6 +581,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const bool aux_pre = P.tma_store && P.aux_mode && !P.preact && (int)m0 + quarter * 32 < P.M && n0 + col_begin < P.N;
       if (aux_pre && lane == 0)
         aux_slab_load(&tmAux, epi_stage + (warp - 2) * 4096, my_aux_bar, (int)n0 + col_begin, (int)m0 + quarter * 32);
+      // with a second staging buffer (half outputs, two slabs per warp) the second slab travels too
+      const bool aux_pre2 = aux_pre && stage2 != nullptr && slab_cols == 64 && BN / 2 == 128 && n0 + col_begin + 64 < P.N;
+      if (aux_pre2 && lane == 0)
+        aux_slab_load(&tmAux, stage2, my_aux_bar2, (int)n0 + col_begin + 64, (int)m0 + quarter * 32);
       // warp-uniform outcome: tcgen05.ld below needs all 32 lanes together
       if (!__all_sync(0xffffffffu, mbar_wait(accf_bar(buf), acc_phase, abort_flag))) { ok = false; break; }
       tc_fence_after();
@@ -565,9 +595,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const int y0 = (int)m0 + quarter * 32;
         if (y0 < P.M) {   // warp-uniform: a slab of 32 rows entirely past M has nothing to write
           bool fine;
-          if (P.out_dtype == MT_F16) fine = epilogue_staged<BN, __half>(P, &tmC, &tmPre, &tmAux, taddr, stage, lane, y0, n0, add_bias, sidx, col_begin, my_aux_bar, aux_phase, aux_pre, abort_flag);
-          else if (P.out_dtype == MT_BF16) fine = epilogue_staged<BN, __nv_bfloat16>(P, &tmC, &tmPre, &tmAux, taddr, stage, lane, y0, n0, add_bias, sidx, col_begin, my_aux_bar, aux_phase, aux_pre, abort_flag);
-          else fine = epilogue_staged<BN, float>(P, &tmC, &tmPre, &tmAux, taddr, stage, lane, y0, n0, add_bias, sidx, col_begin, my_aux_bar, aux_phase, aux_pre, abort_flag);
+          if (P.out_dtype == MT_F16) fine = epilogue_staged<BN, __half>(P, &tmC, &tmPre, &tmAux, taddr, stage, lane, y0, n0, add_bias, sidx, col_begin, my_aux_bar, aux_phase, aux_pre, abort_flag, stage2, my_aux_bar2, &aux_phase2, aux_pre2);
+          else if (P.out_dtype == MT_BF16) fine = epilogue_staged<BN, __nv_bfloat16>(P, &tmC, &tmPre, &tmAux, taddr, stage, lane, y0, n0, add_bias, sidx, col_begin, my_aux_bar, aux_phase, aux_pre, abort_flag, stage2, my_aux_bar2, &aux_phase2, aux_pre2);
+          else fine = epilogue_staged<BN, float>(P, &tmC, &tmPre, &tmAux, taddr, stage, lane, y0, n0, add_bias, sidx, col_begin, my_aux_bar, aux_phase, aux_pre, abort_flag, stage2, my_aux_bar2, &aux_phase2, aux_pre2);
           if (!fine) { ok = false; break; }
         }
       } else
@@ -924,6 +954,18 @@ int gemm_tc(const GemmArgs& g, cudaStream_t st) {
       rc = make_tmap_2d_typed(&txm, g.aux, g.out_dtype, (uint64_t)g.N, (uint64_t)g.M, (uint64_t)g.ldc, cw, 32);
       if (rc) return rc;
     }
+  }
+  // An aux operand combined into a half-precision output: one pipeline stage less, its shared
+  // memory becomes a second staging buffer per warp, so both aux slabs of a tile are in flight
+  // before its accumulator is ready (fc2 forward + residual: 75 -> 70 us). A second OUTPUT gains
+  // nothing from it and loses the stage (fc1 forward with the stored derivative: 84 -> 98 us), so
+  // that variant keeps the full pipeline.
+  {
+    const bool second_tensor = g.aux != nullptr && g.preact == nullptr && P.tma_store && g.out_dtype != MT_F32;
+    const int smax = pair ? GemmCfg<256, true>::kStages : (bn == 256 ? GemmCfg<256, false>::kStages : GemmCfg<128, false>::kStages);
+    const bool can = pair ? (bn == 256 ? GemmCfg<256, true>::kCanDoubleStage : GemmCfg<128, true>::kCanDoubleStage)
+                          : (bn == 256 ? GemmCfg<256, false>::kCanDoubleStage : GemmCfg<128, false>::kCanDoubleStage);
+    P.stages = (second_tensor && can && bn == 256) ? smax - 1 : smax;
   }
   ProfScope prof(PROF_GEMM, st, 2.0 * (double)g.M * (double)g.N * (double)g.K);
   const bool a_mn = g.trans_a != 0, b_mn = g.trans_b == 0;
