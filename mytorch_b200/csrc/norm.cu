@@ -229,10 +229,11 @@ norm_bwd_warp(const T* __restrict__ x, const float* __restrict__ mean, const flo
 // Row-team variant for rows of exactly WPR*32 16-byte vectors (768 half columns = 3 warps, 1280 =
 // 5, 768 fp32 columns = 6): a block is one team, a thread owns ONE vector (8 half columns) of every row the block
 // visits, so its dgamma/dbeta accumulators are 16 registers instead of the 48-64 of the
-// warp-per-row kernel and more warps fit an SM. Two rows are in flight per thread; the row
-// sums of the team's warps meet in shared memory (one __syncthreads per two rows, double
+// warp-per-row kernel and more warps fit an SM. kTeamRows rows are in flight per thread; the row
+// sums of the team's warps meet in shared memory (one __syncthreads per kTeamRows rows, double
 // buffered). The block's column partials need no further reduction: thread t owns columns
 // [t*VN, t*VN+VN). Same partial layout as norm_bwd_warp.
+constexpr int kTeamRows = 2;     // rows in flight per thread (x and dy: 2 x 16 bytes each); three measured the same, four spill
 template <typename T, int WPR, bool RMS>
 __global__ void __launch_bounds__(WPR * 32, 768 / (WPR * 32))
 norm_bwd_team(const T* __restrict__ x, const float* __restrict__ mean, const float* __restrict__ rstd_in,
@@ -241,7 +242,7 @@ norm_bwd_team(const T* __restrict__ x, const float* __restrict__ mean, const flo
   allow_dependents();
   grid_dependency_wait();
   constexpr int VN = Vec16<T>::N;
-  constexpr int RB = 2;
+  constexpr int RB = kTeamRows;
   constexpr int cols = WPR * 32 * VN;
   __shared__ float part[2][RB][WPR][2];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -469,7 +470,7 @@ static int norm_bwd_launch(const void* x, const float* mean, const float* rstd, 
     // columns): one thread per vector
     const int wpr = nvec_all / 32;
     const int per_sm = 768 / (wpr * 32);      // resident blocks (the kernel is compiled for this occupancy)
-    int64_t want = (rows + 1) / 2;
+    int64_t want = (rows + kTeamRows - 1) / kTeamRows;
     int grid = (int)(want < (int64_t)sm_count() * per_sm ? want : (int64_t)sm_count() * per_sm);
     bool wg = dgamma != nullptr, wb = dbeta != nullptr;
     TempBuf part((wg || wb) ? (size_t)grid * 2 * cols * sizeof(float) : 0, st);
