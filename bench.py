@@ -13,8 +13,10 @@ optimizer step: forward + backward of `accum` micro-batches, gradient all-reduce
       batch 524288 tokens at N = 8 (accum = 8 / N for N > 1, 1 at N = 1).
 Timing: CUDA events on the compute stream around exactly K steps, bracketed by barrier +
 synchronize, max over ranks. `value` has the token ids resident in HBM; `e2e` repeats the K
-steps with host batches (pinned -> device copy of ids and labels and a device -> host read of
-the loss inside every step).
+steps with host batches: every step copies its ids and labels from pinned host memory to the
+device and its loss from the device to pinned host memory, and the host reads every loss inside
+the timed region - one step late (it waits for step n - 1's copy after queueing step n), the
+last one before the closing event.
 
 Reference arm (`--impl reference`): the reference's algorithm for the same step on the host
 cores (the NumPy oracle, which is pinned to the reference by the golden vectors), with every
@@ -304,6 +306,11 @@ def run_own(args):
     stage_y = DeviceArray.empty((micro_b, ctx), "int32")
     loss_pin = C.c_void_p()
     _lib.host_alloc(C.byref(loss_pin), 64)
+    loss_host = np.ctypeslib.as_array((C.c_float * 16).from_address(loss_pin.value))
+    loss_events = [C.c_void_p(), C.c_void_p()]
+    for ev in loss_events:
+        _lib.event_create(C.byref(ev))
+    e2e_state = {"n": 0, "last": None}
 
     counter = [0]
 
@@ -323,6 +330,10 @@ def run_own(args):
         return loss
 
     def step_e2e():
+        """One optimizer step fed from pinned host memory, its loss copied back to pinned host
+        memory. The host reads each step's loss one step late - it waits for the copy of step n - 1
+        after it has queued step n - the way a training loop logs its loss without draining the
+        GPU; e2e_drain() reads the last one. Every step's loss is read inside the timed region."""
         for _ in range(acc.gradient_accumulation_steps):
             i = counter[0] % n_batches
             counter[0] += 1
@@ -330,9 +341,21 @@ def run_own(args):
             _lib.memcpy_h2d(stage_x.ptr, base, nbytes, stream())
             _lib.memcpy_h2d(stage_y.ptr, base + nbytes, nbytes, stream())
             loss = micro(stage_x, stage_y)
-        _lib.memcpy_d2h(loss_pin.value, loss.data.ptr, 4, stream())
-        _lib.stream_sync(stream())
+        n = e2e_state["n"]
+        _lib.memcpy_d2h(loss_pin.value + 4 * (n & 1), loss.data.ptr, 4, stream())
+        _lib.event_record(loss_events[n & 1], stream())
+        if n > 0:
+            _lib.event_sync(loss_events[(n - 1) & 1])
+            e2e_state["last"] = float(loss_host[(n - 1) & 1])
+        e2e_state["n"] = n + 1
         return loss
+
+    def e2e_drain():
+        n = e2e_state["n"]
+        if n > 0:
+            _lib.event_sync(loss_events[(n - 1) & 1])
+            e2e_state["last"] = float(loss_host[(n - 1) & 1])
+        e2e_state["n"] = 0
 
     def barrier():
         if acc.comm is not None:
@@ -342,7 +365,7 @@ def run_own(args):
     host_ms = [0.0]
     window = [0.0, 0.0]      # host time of the last timed region, for the clock samples
 
-    def timed(fn, steps):
+    def timed(fn, steps, after=None):
         e0, e1 = C.c_void_p(), C.c_void_p()
         _lib.event_create(C.byref(e0)); _lib.event_create(C.byref(e1))
         barrier()
@@ -351,6 +374,8 @@ def run_own(args):
         window[0] = h0
         for _ in range(steps):
             fn()
+        if after is not None:
+            after()
         _lib.event_record(e1, stream())
         host_ms[0] = (time.perf_counter() - h0) * 1e3 / steps    # time the host needs to queue one step
         _lib.event_sync(e1)
@@ -373,8 +398,15 @@ def run_own(args):
         acc.comm.exposed_ms()                      # drop the warm-up's records
     launches0 = _lib.launch_count()
     ms_total = timed(step_resident, args.steps)
-    host_queue_ms = host_ms[0]
     launches = _lib.launch_count() - launches0
+    # Host time to queue ONE step into an empty stream. (Averaged over the K timed steps the host
+    # figure includes the time it is blocked on a full launch queue, two to three steps ahead of
+    # the device.)
+    _lib.device_sync()
+    h0 = time.perf_counter()
+    step_resident()
+    host_queue_ms = (time.perf_counter() - h0) * 1e3
+    _lib.device_sync()
     exposed = acc.comm.exposed_ms() if acc.comm is not None else None
     clocks = sampler.summary(tuple(window)) if rank == 0 else None
     # The roofline of the dominant kernel comes from a second pass over the same K steps with a
@@ -389,11 +421,11 @@ def run_own(args):
     ms_prof2 = timed(step_resident, args.steps)
     attn_ms, attn_n, attn_flops = C.c_double(), C.c_int64(), C.c_double()
     _lib.prof_end(C.byref(attn_ms), C.byref(attn_n), C.byref(attn_flops))
-    final_loss = None
     for _ in range(2):
         step_e2e()
-    ms_e2e = timed(step_e2e, args.steps)
-    final_loss = float(np.ctypeslib.as_array((C.c_float * 1).from_address(loss_pin.value))[0])
+    e2e_drain()
+    ms_e2e = timed(step_e2e, args.steps, after=e2e_drain)
+    final_loss = e2e_state["last"]
     flag = C.c_int(0)
     _lib.device_flag_read(C.byref(flag), stream())
     free_b, total_b = C.c_size_t(), C.c_size_t()

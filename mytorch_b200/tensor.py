@@ -104,6 +104,7 @@ class Tensor:
     # produces already in its forward pass. None = backward() is expected with its default of 1.
     loss_grad_hint = None
     _unit_grad_ptr = None
+    last_backward_timings = None
 
     def __init__(self, data, requires_grad=False, grad_fn=None, grad_fn_name=None, dtype=None, device=None):
         self.data = _to_device_array(data, dtype)
@@ -122,9 +123,17 @@ class Tensor:
     def _add_parents(self, *parents):
         self._parents = tuple(p for p in parents if isinstance(p, Tensor) and p.requires_grad)
 
-    def backward(self, grad=None):
+    def backward(self, grad=None, retain_graph=False, time_backward=False, num_ops_to_show=-1):
         """Topological sort from this tensor, closures run in reverse order;
-        the graph is released afterwards (mytorch/tensor.py:182-261)."""
+        the graph is released afterwards (mytorch/tensor.py:182-261).
+
+        time_backward=True brackets every closure with a pair of CUDA events on the compute stream
+        and prints, after one synchronisation at the end, the device time per `grad_fn_name`
+        (summed over its occurrences) - the reference's per-closure timer (:221-261), which
+        synchronises after every closure and keeps only the last occurrence's time. The table is
+        also left in `Tensor.last_backward_timings` ({name: [milliseconds, calls]})."""
+        if retain_graph:
+            raise NotImplementedError("retain_graph is not built: closures release their buffers as they run")
         if not self.requires_grad:
             raise RuntimeError("backward() on a tensor that does not require grad")
         if grad is None:
@@ -159,9 +168,18 @@ class Tensor:
             ready_at = {}
             for k, p in last_use.values():
                 ready_at.setdefault(k, []).append(p)
+        marks = [] if time_backward else None
         for k, node in enumerate(exec_order):
             if node.grad_fn is not None:
+                if marks is not None:
+                    import ctypes as C
+                    e0, e1 = C.c_void_p(), C.c_void_p()
+                    _lib.event_create(C.byref(e0)); _lib.event_create(C.byref(e1))
+                    _lib.event_record(e0, stream())
                 node.grad_fn(node.grad)
+                if marks is not None:
+                    _lib.event_record(e1, stream())
+                    marks.append((node.grad_fn_name or "<unnamed>", e0, e1))
                 node.grad_fn = None
                 node._parents = ()
                 if not node.is_param:
@@ -169,6 +187,24 @@ class Tensor:
             if hook is not None:
                 for p in ready_at.get(k, ()):
                     hook(p)               # every kernel writing p.grad has been queued
+        if marks is not None:
+            import ctypes as C
+            table = {}
+            for name, e0, e1 in marks:
+                _lib.event_sync(e1)
+                ms = C.c_float()
+                _lib.event_elapsed_ms(e0, e1, C.byref(ms))
+                row = table.setdefault(name, [0.0, 0])
+                row[0] += ms.value
+                row[1] += 1
+                _lib.event_destroy(e0); _lib.event_destroy(e1)
+            Tensor.last_backward_timings = table
+            rows = sorted(table.items(), key=lambda kv: -kv[1][0])
+            if num_ops_to_show is not None and num_ops_to_show >= 0:
+                rows = rows[:num_ops_to_show]
+            print(f"\nTop {num_ops_to_show} most time-consuming backward functions:")
+            for name, (ms, n) in rows:
+                print(f"{name:<34s} {ms:9.3f} ms total over {n} call(s)")
 
     def _accumulate(self, g):
         """grad += g. Takes ownership of g when there is no gradient yet."""

@@ -63,6 +63,26 @@ def test_tiny_gpt2_fp32_50_steps_match_reference_losses():
         assert abs(got - want) <= 1e-3 * want, (k, got, want)
 
 
+def test_backward_timing_table(capsys):
+    """loss.backward(time_backward=True) reports the device time of every backward closure by name
+    (mytorch/tensor.py:221-261) and leaves the gradients unchanged."""
+    cfg = og.GPT2Config(65, 64, 64, 4, 2, 2)
+    params = og.init_params(cfg, seed=0)
+    x, y = og.synthetic_batch(np.random.default_rng(0), 4, 64, 65)
+    grads = []
+    for timed in (False, True):
+        mt, model = build(cfg, params)
+        loss = mt.nn.CrossEntropyLoss()(model(mt.Tensor(x)), mt.Tensor(y))
+        loss.backward(time_backward=timed, num_ops_to_show=5)
+        grads.append({n: p.grad.numpy() for n, p in model.named_parameters()})
+    out = capsys.readouterr().out
+    assert "most time-consuming backward functions" in out and "<LinearBackward>" in out
+    table = mt.Tensor.last_backward_timings
+    assert table["<MLPBackward>"][1] == 2 and all(ms >= 0 for ms, _ in table.values())
+    for k in grads[0]:
+        assert np.array_equal(grads[0][k], grads[1][k]) or np.allclose(grads[0][k], grads[1][k], rtol=1e-5, atol=1e-7), k
+
+
 def test_first_step_gradients_match_reference():
     cfg = og.GPT2Config(65, 256, 256, 4, 4, 4)
     mt, model = build(cfg, og.init_params(cfg, seed=0))
