@@ -321,6 +321,21 @@ int mt_attn_bwd(const void* q, const void* k, const void* v, const void* o, cons
                 mt_strides3 sdq, mt_strides3 sdk, mt_strides3 sdv,
                 int64_t batch, int64_t heads, int64_t seq, int64_t head_dim,
                 float scale, int causal, int dtype, void* stream);
+/* The same with grouped-query heads (fused_ops/flash_attention.py:445-455, 1014-1018,
+ * 1171-1176; the nanochat model's num_kv_heads, nanochat_trainer/core/nanochat_gpt.py:31-32,
+ * 78-90): k, v, dk and dv have kv_heads heads, query head h reads key/value head
+ * h / (heads / kv_heads), and dk / dv sum the contributions of the query heads of their group.
+ * heads must be a multiple of kv_heads; kv_heads = heads is mt_attn_fwd / mt_attn_bwd. */
+int mt_attn_fwd_gqa(const void* q, const void* k, const void* v, void* o, float* lse,
+                    mt_strides3 sq, mt_strides3 sk, mt_strides3 sv, mt_strides3 so,
+                    int64_t batch, int64_t heads, int64_t kv_heads, int64_t seq, int64_t head_dim,
+                    float scale, int causal, int dtype, void* stream);
+int mt_attn_bwd_gqa(const void* q, const void* k, const void* v, const void* o, const void* d_o,
+                    const float* lse, void* dq, void* dk, void* dv, float* delta, float* dq_accum,
+                    mt_strides3 sq, mt_strides3 sk, mt_strides3 sv, mt_strides3 so, mt_strides3 sdo,
+                    mt_strides3 sdq, mt_strides3 sdk, mt_strides3 sdv,
+                    int64_t batch, int64_t heads, int64_t kv_heads, int64_t seq, int64_t head_dim,
+                    float scale, int causal, int dtype, void* stream);
 int mt_attn_force_simt(int on);
 
 /* The inference step: attention of q_len new query rows against a key/value cache, and the

@@ -116,6 +116,9 @@ _SIG = {
     "mt_attn_fwd": [_p, _p, _p, _p, _p, _S, _S, _S, _S, _i64, _i64, _i64, _i64, _f, _i, _i, _p],
     "mt_attn_bwd": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _S, _S, _S, _S, _S, _S, _S, _S,
                     _i64, _i64, _i64, _i64, _f, _i, _i, _p],
+    "mt_attn_fwd_gqa": [_p, _p, _p, _p, _p, _S, _S, _S, _S, _i64, _i64, _i64, _i64, _i64, _f, _i, _i, _p],
+    "mt_attn_bwd_gqa": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _S, _S, _S, _S, _S, _S, _S, _S,
+                        _i64, _i64, _i64, _i64, _i64, _f, _i, _i, _p],
     "mt_attn_force_simt": [_i],
     "mt_attn_decode": [_p, _p, _p, _p, _S, _S, _S, _i64, _i64, _i64, _i64, _i64, _f, _i, _i, _p],
     "mt_kv_append": [_p, _p, _p, _p, _S, _S, _S, _i64, _i64, _i64, _i64, _i64, _i64, _i, _p],

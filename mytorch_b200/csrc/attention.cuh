@@ -12,6 +12,7 @@ struct AttnArgs {
   float* dq_accum;
   mt_strides3 sq, sk, sv, so, sdo, sdq, sdk, sdv;
   int64_t batch, heads, seq, head_dim;
+  int64_t kv_heads;   // heads of k, v, dk, dv; query head h reads key/value head h / (heads / kv_heads)
   float scale;
   int causal, dtype;
 };

@@ -91,6 +91,7 @@ struct AttnBwdParams {
   void* dk; void* dv;
   MapPos pq, pk, pv, pdo, pdk, pdv;
   int B, H, S, nqb, causal, is_bf16;
+  int Hkv, group;       // key/value heads; query heads per key/value head (H = Hkv * group)
   float scale, scale_log2;
   int* flag;
 };
@@ -118,11 +119,14 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   float* stat = reinterpret_cast<float*>(base_ptr + Cfg::kOffStat);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int bh_count = P.B * P.H;
+  const int bh_count = P.B * P.Hkv;           // (batch, key/value head) pairs
   const int n_tiles = P.nqb * bh_count;
   // Tile t: key block jb = t / bh_count (small jb = most query blocks when causal, so heavy tiles
-  // come first), (batch, head) = t % bh_count. Every role walks the same tile sequence and keeps a
-  // running count `g` of query blocks, from which ring stages and barrier parities follow.
+  // come first), (batch, key/value head) = t % bh_count. The tile's steps are the query blocks of
+  // every query head that reads this key/value head: step i = (query head hk*group + i / n_qb,
+  // query block q_start + i % n_qb); dK and dV accumulate over all of them. Every role walks the
+  // same tile sequence and keeps a running count `g` of steps, from which ring stages and barrier
+  // parities follow.
 
   if (threadIdx.x == 0) {
     mbar_init(bar_kv, 1);
@@ -155,10 +159,11 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         const int tile = tile_of_round(round, n_tiles);
         if (tile < 0) continue;
         const int tn_now = tn++;
-        const int jb = tile / bh_count, bh = tile % bh_count;
-        const int b = bh / P.H, h = bh % P.H;
+        const int jb = tile / bh_count, bkv = tile % bh_count;
+        const int b = bkv / P.Hkv, h = bkv % P.Hkv;          // h: key/value head
         const int q_start = P.causal ? jb : 0;
-        const int n_q = P.nqb - q_start;
+        const int n_qb = P.nqb - q_start;
+        const int n_q = n_qb * P.group;
         // K and V of the previous tile are read until its last dQ MMA has completed
         if (tn_now > 0 && !mbar_wait(bar_kvfree, (tn_now - 1) & 1, abort_flag)) break;
         mbar_expect_tx(bar_kv, 2 * Cfg::kTile);
@@ -172,16 +177,17 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           if (!mbar_wait(bar_qempty0 + 8 * s, ((g / ST) & 1) ^ 1u, abort_flag)) { ok = false; break; }
           mbar_expect_tx(bar_qfull0 + 8 * s, 2 * Cfg::kTile + 1024);
           const uint32_t sq = base + Cfg::kOffQ + s * 2 * Cfg::kTile, sdo = sq + Cfg::kTile;
+          const int hq = h * P.group + i / n_qb, qi = q_start + i % n_qb;   // query head and block of this step
           {   // the block's row statistics travel with it
             const int64_t spad = (int64_t)P.nqb * 128;
-            const float* src = P.stats + (int64_t)bh * spad + (int64_t)(q_start + i) * 128;
+            const float* src = P.stats + ((int64_t)b * P.H + hq) * spad + (int64_t)qi * 128;
             bulk_load_1d(base + Cfg::kOffStat + s * 1024, src, 512, bar_qfull0 + 8 * s);
-            bulk_load_1d(base + Cfg::kOffStat + s * 1024 + 512, src + (int64_t)bh_count * spad, 512, bar_qfull0 + 8 * s);
+            bulk_load_1d(base + Cfg::kOffStat + s * 1024 + 512, src + (int64_t)P.B * P.H * spad, 512, bar_qfull0 + 8 * s);
           }
 #pragma unroll
           for (int dc = 0; dc < Cfg::kChunks; ++dc) {
-            load_rows(sq + dc * 16384, &tmQ, bar_qfull0 + 8 * s, P.pq, dc * 64, (q_start + i) * 128, h, b);
-            load_rows(sdo + dc * 16384, &tmDO, bar_qfull0 + 8 * s, P.pdo, dc * 64, (q_start + i) * 128, h, b);
+            load_rows(sq + dc * 16384, &tmQ, bar_qfull0 + 8 * s, P.pq, dc * 64, qi * 128, hq, b);
+            load_rows(sdo + dc * 16384, &tmDO, bar_qfull0 + 8 * s, P.pdo, dc * 64, qi * 128, hq, b);
           }
         }
       }
@@ -244,7 +250,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         if (tile < 0) continue;
         const int tn = tcount++;
         const int jb = tile / bh_count;
-        const int n_q = P.nqb - (P.causal ? jb : 0);
+        const int n_q = (P.nqb - (P.causal ? jb : 0)) * P.group;
         if (!mbar_wait(bar_kv, tn & 1, abort_flag)) break;
         tc_fence_after();
         if (!Cfg::kAliasDQ) {
@@ -309,14 +315,13 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     uint8_t* pt_row = base_ptr + Cfg::kOffPT + t * 128;
     uint8_t* dst_row = base_ptr + Cfg::kOffDST + t * 128;
     bool ok = true;
-    int bh = 0;
     // adds the finished dQ block (TMEM) into the fp32 accumulator [B*H, S, D]: each warp stages its
     // 32 rows x 32 columns in swizzled shared memory and one lane issues a TMA reduce-add (rows past
     // the sequence end are clipped by the tensor map)
     uint8_t* dq_stage = base_ptr + Cfg::kOffStage + warp * 4096;
     constexpr int kDqChunks = D / 32;                                           // 32-column pieces of dQ
     constexpr int kDqPer = kDqChunks >= kBwdEwWarps / 4 ? kDqChunks / (kBwdEwWarps / 4) : 1;   // pieces per column group
-    auto flush_dq = [&](int qi) {
+    auto flush_dq = [&](int qi, int bh) {        // bh: (batch, query head) index of the block
 #pragma unroll 1
       for (int c = hh * kDqPer; c < (hh + 1) * kDqPer && c < kDqChunks; ++c) {   // this warp's share of the dQ columns
         uint32_t r[32];
@@ -341,14 +346,18 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       const int tile = tile_of_round(round, n_tiles);
       if (tile < 0) continue;
       const int jb = tile / bh_count;
-      bh = tile % bh_count;
-      const int b = bh / P.H, h = bh % P.H;
+      const int bkv = tile % bh_count;
+      const int b = bkv / P.Hkv, h = bkv % P.Hkv;     // h: key/value head
       const int q_start = P.causal ? jb : 0;
-      const int n_q = P.nqb - q_start;
+      const int n_qb = P.nqb - q_start;
+      const int n_q = n_qb * P.group;
       const int kg = jb * 128 + t;                    // global key index
+      // step i of the tile -> (batch, query head) index and query block
+      auto bh_of = [&](int i) { return b * P.H + h * P.group + i / n_qb; };
+      auto qi_of = [&](int i) { return q_start + i % n_qb; };
       for (int i = 0; i < n_q && ok; ++i) {
         const int g = g0 + i;
-        const int qi = q_start + i;
+        const int qi = qi_of(i);
         // row statistics of this query block arrived with its Q/dO stage (bulk copy); the wait makes
         // that copy visible to this thread and returns at once, since S^T needed the stage too
         const float* lse2 = stat + (g % ST) * 256;
@@ -433,7 +442,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         if (fi >= 0) {
           if (!__all_sync(0xffffffffu, mbar_wait(bar_dq, (g0 + fi) & 1, abort_flag))) { ok = false; break; }
           tc_fence_after();
-          flush_dq(q_start + fi);
+          flush_dq(qi_of(fi), bh_of(fi));
           tc_fence_before();
           mbar_arrive(bar_dqfree);
         }
@@ -443,7 +452,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         // the tile's last dQ; its completion also means every MMA of the tile is complete
         if (!__all_sync(0xffffffffu, mbar_wait(bar_dq, (g0 + n_q - 1) & 1, abort_flag))) { ok = false; break; }
         tc_fence_after();
-        flush_dq(q_start + n_q - 1);
+        flush_dq(qi_of(n_q - 1), bh_of(n_q - 1));
         tc_fence_before();
         mbar_arrive(bar_dqfree);
       }
@@ -585,12 +594,12 @@ static int launch_bwd(const AttnArgs& a, cudaStream_t st) {
   CUtensorMap tq, tk, tv, tdo;
   AttnBwdParams P;
   if ((rc = make_qkv_map(&tq, &P.pq, a.q, bf, a.sq, a.batch, a.heads, a.seq, D))) return rc;
-  if ((rc = make_qkv_map(&tk, &P.pk, a.k, bf, a.sk, a.batch, a.heads, a.seq, D))) return rc;
-  if ((rc = make_qkv_map(&tv, &P.pv, a.v, bf, a.sv, a.batch, a.heads, a.seq, D))) return rc;
+  if ((rc = make_qkv_map(&tk, &P.pk, a.k, bf, a.sk, a.batch, a.kv_heads, a.seq, D))) return rc;
+  if ((rc = make_qkv_map(&tv, &P.pv, a.v, bf, a.sv, a.batch, a.kv_heads, a.seq, D))) return rc;
   if ((rc = make_qkv_map(&tdo, &P.pdo, a.d_o, bf, a.sdo, a.batch, a.heads, a.seq, D))) return rc;
   CUtensorMap tdk, tdv;
-  if ((rc = make_qkv_map(&tdk, &P.pdk, a.dk, bf, a.sdk, a.batch, a.heads, a.seq, D, 32))) return rc;
-  if ((rc = make_qkv_map(&tdv, &P.pdv, a.dv, bf, a.sdv, a.batch, a.heads, a.seq, D, 32))) return rc;
+  if ((rc = make_qkv_map(&tdk, &P.pdk, a.dk, bf, a.sdk, a.batch, a.kv_heads, a.seq, D, 32))) return rc;
+  if ((rc = make_qkv_map(&tdv, &P.pdv, a.dv, bf, a.sdv, a.batch, a.kv_heads, a.seq, D, 32))) return rc;
   CUtensorMap tdq;
   {
     uint64_t dims[3] = {(uint64_t)D, (uint64_t)a.seq, (uint64_t)(a.batch * a.heads)};
@@ -600,10 +609,11 @@ static int launch_bwd(const AttnArgs& a, cudaStream_t st) {
   }
   P.stats = (const float*)stats.ptr; P.dq_accum = a.dq_accum; P.dk = a.dk; P.dv = a.dv;
   P.B = (int)a.batch; P.H = (int)a.heads; P.S = (int)a.seq; P.nqb = (int)((a.seq + 127) / 128);
+  P.Hkv = (int)a.kv_heads; P.group = (int)(a.heads / a.kv_heads);
   P.causal = a.causal; P.is_bf16 = bf; P.scale = a.scale; P.scale_log2 = a.scale * kLog2eF; P.flag = device_flag_ptr();
   auto kern = attn_bwd_tc_kernel<D, T>;
   MT_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
-  const int64_t n_tiles = (int64_t)P.nqb * P.B * P.H;
+  const int64_t n_tiles = (int64_t)P.nqb * P.B * P.Hkv;
   const unsigned grid = (unsigned)(n_tiles < sm_count() ? n_tiles : sm_count());   // persistent: one CTA per SM
   kern<<<grid, Cfg::kThreads, Cfg::kSmem, st>>>(tq, tk, tv, tdo, tdq, tdk, tdv, P);
   MT_LAUNCH_CHECK();

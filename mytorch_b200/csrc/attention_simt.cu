@@ -34,7 +34,7 @@ template <typename T>
 __global__ void __launch_bounds__(kWarps * 32)
 attn_fwd_simt(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, T* __restrict__ o,
               float* __restrict__ lse, mt_strides3 sq, mt_strides3 sk, mt_strides3 sv, mt_strides3 so,
-              int heads, int S, int D, float scale, int causal) {
+              int heads, int group, int S, int D, float scale, int causal) {
   extern __shared__ float sm[];
   const int ld = D + 1;
   float* Ks = sm;                       // [32][ld]
@@ -44,8 +44,8 @@ attn_fwd_simt(const T* __restrict__ q, const T* __restrict__ k, const T* __restr
   const int bh = blockIdx.y, b = bh / heads, h = bh % heads;
   const int row_base = blockIdx.x * kRowsPerBlock;
   const T* qb = q + (int64_t)b * sq.b + (int64_t)h * sq.h;
-  const T* kb = k + (int64_t)b * sk.b + (int64_t)h * sk.h;
-  const T* vb = v + (int64_t)b * sv.b + (int64_t)h * sv.h;
+  const T* kb = k + (int64_t)b * sk.b + (int64_t)(h / group) * sk.h;      // query head h reads key/value head h / group
+  const T* vb = v + (int64_t)b * sv.b + (int64_t)(h / group) * sv.h;
   T* ob = o + (int64_t)b * so.b + (int64_t)h * so.h;
   for (int i = threadIdx.x; i < kRowsPerBlock * D; i += blockDim.x) {
     int r = i / D, d = i - r * D;
@@ -148,7 +148,7 @@ template <typename T>
 __global__ void __launch_bounds__(kWarps * 32)
 attn_bwd_dq_simt(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, const T* __restrict__ d_o,
                  const float* __restrict__ lse, const float* __restrict__ delta, T* __restrict__ dq, mt_strides3 sq,
-                 mt_strides3 sk, mt_strides3 sv, mt_strides3 sdo, mt_strides3 sdq, int heads, int S, int D,
+                 mt_strides3 sk, mt_strides3 sv, mt_strides3 sdo, mt_strides3 sdq, int heads, int group, int S, int D,
                  float scale, int causal) {
   extern __shared__ float sm[];
   const int ld = D + 1;
@@ -160,8 +160,8 @@ attn_bwd_dq_simt(const T* __restrict__ q, const T* __restrict__ k, const T* __re
   const int bh = blockIdx.y, b = bh / heads, h = bh % heads;
   const int row_base = blockIdx.x * kRowsPerBlock;
   const T* qb = q + (int64_t)b * sq.b + (int64_t)h * sq.h;
-  const T* kb = k + (int64_t)b * sk.b + (int64_t)h * sk.h;
-  const T* vb = v + (int64_t)b * sv.b + (int64_t)h * sv.h;
+  const T* kb = k + (int64_t)b * sk.b + (int64_t)(h / group) * sk.h;      // query head h reads key/value head h / group
+  const T* vb = v + (int64_t)b * sv.b + (int64_t)(h / group) * sv.h;
   const T* gb = d_o + (int64_t)b * sdo.b + (int64_t)h * sdo.h;
   T* dqb = dq + (int64_t)b * sdq.b + (int64_t)h * sdq.h;
   for (int i = threadIdx.x; i < kRowsPerBlock * D; i += blockDim.x) {
@@ -228,7 +228,7 @@ __global__ void __launch_bounds__(kWarps * 32)
 attn_bwd_dkv_simt(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, const T* __restrict__ d_o,
                   const float* __restrict__ lse, const float* __restrict__ delta, T* __restrict__ dk,
                   T* __restrict__ dv, mt_strides3 sq, mt_strides3 sk, mt_strides3 sv, mt_strides3 sdo,
-                  mt_strides3 sdk, mt_strides3 sdv, int heads, int S, int D, float scale, int causal) {
+                  mt_strides3 sdk, mt_strides3 sdv, int heads, int group, int S, int D, float scale, int causal) {
   extern __shared__ float sm[];
   const int ld = D + 1;
   float* Qs = sm;                               // [32][ld] query tile (unscaled)
@@ -238,12 +238,12 @@ attn_bwd_dkv_simt(const T* __restrict__ q, const T* __restrict__ k, const T* __r
   float* Ls = Vs + kRowsPerBlock * D;           // [32] lse of the query tile
   float* Ds = Ls + kTile;                       // [32] delta of the query tile
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // `heads` counts key/value heads here: the block owns rows of one key/value head and sums the
+  // contributions of the `group` query heads that read it
   const int bh = blockIdx.y, b = bh / heads, h = bh % heads;
   const int row_base = blockIdx.x * kRowsPerBlock;
-  const T* qb = q + (int64_t)b * sq.b + (int64_t)h * sq.h;
   const T* kb = k + (int64_t)b * sk.b + (int64_t)h * sk.h;
   const T* vb = v + (int64_t)b * sv.b + (int64_t)h * sv.h;
-  const T* gb = d_o + (int64_t)b * sdo.b + (int64_t)h * sdo.h;
   for (int i = threadIdx.x; i < kRowsPerBlock * D; i += blockDim.x) {
     int r = i / D, d = i - r * D;
     int gr = row_base + r;
@@ -257,14 +257,19 @@ attn_bwd_dkv_simt(const T* __restrict__ q, const T* __restrict__ k, const T* __r
     for (int c = 0; c < kMaxD / 32; ++c) { acck[r][c] = 0.f; accv[r][c] = 0.f; }
   // causal: only queries i >= j contribute; start at the tile holding row_base
   const int q_begin = causal ? (row_base / kTile) * kTile : 0;
+  for (int gq = 0; gq < group; ++gq) {
+  const int hq = h * group + gq;
+  const int64_t bhq = (int64_t)b * heads * group + hq;       // index of the query head in [B, H] (lse, delta)
+  const T* qb = q + (int64_t)b * sq.b + (int64_t)hq * sq.h;
+  const T* gb = d_o + (int64_t)b * sdo.b + (int64_t)hq * sdo.h;
   for (int t0 = q_begin; t0 < S; t0 += kTile) {
     __syncthreads();
     load_tile(Qs, ld, qb, sq.s, t0, S, D);
     load_tile(Gs, ld, gb, sdo.s, t0, S, D);
     if (threadIdx.x < kTile) {
       int gi = t0 + threadIdx.x;
-      Ls[threadIdx.x] = gi < S ? lse[(int64_t)bh * S + gi] : 0.f;
-      Ds[threadIdx.x] = gi < S ? delta[(int64_t)bh * S + gi] : 0.f;
+      Ls[threadIdx.x] = gi < S ? lse[bhq * S + gi] : 0.f;
+      Ds[threadIdx.x] = gi < S ? delta[bhq * S + gi] : 0.f;
     }
     __syncthreads();
 #pragma unroll
@@ -294,6 +299,7 @@ attn_bwd_dkv_simt(const T* __restrict__ q, const T* __restrict__ k, const T* __r
         }
       }
     }
+  }
   }
   T* dkb = dk + (int64_t)b * sdk.b + (int64_t)h * sdk.h;
   T* dvb = dv + (int64_t)b * sdv.b + (int64_t)h * sdv.h;
@@ -335,7 +341,7 @@ int attn_fwd_simt_launch(const AttnArgs& a, cudaStream_t st) {
   size_t smem = (size_t)(2 * kTile * (D + 1) + kRowsPerBlock * D) * sizeof(float);
   MT_DISPATCH_FLOAT(a.dtype, T, MT_CHECK_CUDA(cudaFuncSetAttribute(attn_fwd_simt<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536)));
   MT_DISPATCH_FLOAT(a.dtype, T, (attn_fwd_simt<T><<<grid, kWarps * 32, smem, st>>>(
-      (const T*)a.q, (const T*)a.k, (const T*)a.v, (T*)a.o_out, a.lse, a.sq, a.sk, a.sv, a.so, (int)a.heads, S, D, a.scale, a.causal)));
+      (const T*)a.q, (const T*)a.k, (const T*)a.v, (T*)a.o_out, a.lse, a.sq, a.sk, a.sv, a.so, (int)a.heads, (int)(a.heads / a.kv_heads), S, D, a.scale, a.causal)));
   MT_LAUNCH_CHECK();
   return MT_OK;
 }
@@ -354,9 +360,11 @@ int attn_bwd_simt_launch(const AttnArgs& a, cudaStream_t st) {
     MT_CHECK_CUDA(cudaFuncSetAttribute(attn_bwd_dq_simt<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536));
     MT_CHECK_CUDA(cudaFuncSetAttribute(attn_bwd_dkv_simt<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536));
     attn_bwd_dq_simt<T><<<grid, kWarps * 32, smem_dq, st>>>((const T*)a.q, (const T*)a.k, (const T*)a.v, (const T*)a.d_o,
-        a.lse, a.delta, (T*)a.dq, a.sq, a.sk, a.sv, a.sdo, a.sdq, (int)a.heads, S, D, a.scale, a.causal);
-    attn_bwd_dkv_simt<T><<<grid, kWarps * 32, smem_dkv, st>>>((const T*)a.q, (const T*)a.k, (const T*)a.v, (const T*)a.d_o,
-        a.lse, a.delta, (T*)a.dk, (T*)a.dv, a.sq, a.sk, a.sv, a.sdo, a.sdk, a.sdv, (int)a.heads, S, D, a.scale, a.causal);
+        a.lse, a.delta, (T*)a.dq, a.sq, a.sk, a.sv, a.sdo, a.sdq, (int)a.heads, (int)(a.heads / a.kv_heads), S, D, a.scale, a.causal);
+    dim3 grid_kv((S + kRowsPerBlock - 1) / kRowsPerBlock, (unsigned)(a.batch * a.kv_heads));
+    attn_bwd_dkv_simt<T><<<grid_kv, kWarps * 32, smem_dkv, st>>>((const T*)a.q, (const T*)a.k, (const T*)a.v, (const T*)a.d_o,
+        a.lse, a.delta, (T*)a.dk, (T*)a.dv, a.sq, a.sk, a.sv, a.sdo, a.sdk, a.sdv, (int)a.kv_heads, (int)(a.heads / a.kv_heads),
+        S, D, a.scale, a.causal);
   });
   MT_LAUNCH_CHECK();
   count_launch(1);

@@ -56,6 +56,7 @@ struct AttnFwdParams {
   float* lse;
   MapPos pq, pk, pv, po;
   int B, H, S, nqb, causal, is_bf16;
+  int group;            // query heads per key/value head
   float scale_log2;
   int* flag;
 };
@@ -88,6 +89,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   const int qb = P.nqb - 1 - (int)(blockIdx.x / bh_count);   // heaviest (last) query blocks first
   const int bh = blockIdx.x % bh_count;
   const int b = bh / P.H, h = bh % P.H;
+  const int hk = h / P.group;                            // key/value head of this query head
   const int n_kv_total = (P.S + 127) / 128;
   const int n_kv = P.causal ? min(qb + 1, n_kv_total) : n_kv_total;
 
@@ -129,7 +131,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         mbar_expect_tx(bar_kfull0 + 8 * st, Cfg::kTile);
 #pragma unroll
         for (int dc = 0; dc < Cfg::kChunks; ++dc)
-          load_rows(base + Cfg::kOffK + st * Cfg::kTile + dc * 16384, &tmK, bar_kfull0 + 8 * st, P.pk, dc * 64, j * 128, h, b);
+          load_rows(base + Cfg::kOffK + st * Cfg::kTile + dc * 16384, &tmK, bar_kfull0 + 8 * st, P.pk, dc * 64, j * 128, hk, b);
         return true;
       };
       bool okp = load_k(0);
@@ -140,7 +142,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         mbar_expect_tx(bar_vfull0 + 8 * st, Cfg::kTile);
 #pragma unroll
         for (int dc = 0; dc < Cfg::kChunks; ++dc)
-          load_rows(base + Cfg::kOffV + st * Cfg::kTile + dc * 16384, &tmV, bar_vfull0 + 8 * st, P.pv, dc * 64, j * 128, h, b);
+          load_rows(base + Cfg::kOffV + st * Cfg::kTile + dc * 16384, &tmV, bar_vfull0 + 8 * st, P.pv, dc * 64, j * 128, hk, b);
       }
     }
   } else if (warp == kSoftmaxWarps + 1) {
@@ -381,9 +383,10 @@ static int launch_fwd(const AttnArgs& a, cudaStream_t st) {
   AttnFwdParams P;
   if ((rc = make_qkv_map(&to, &P.po, a.o_out, bf, a.so, a.batch, a.heads, a.seq, D, 32))) return rc;
   if ((rc = make_qkv_map(&tq, &P.pq, a.q, bf, a.sq, a.batch, a.heads, a.seq, D))) return rc;
-  if ((rc = make_qkv_map(&tk, &P.pk, a.k, bf, a.sk, a.batch, a.heads, a.seq, D))) return rc;
-  if ((rc = make_qkv_map(&tv, &P.pv, a.v, bf, a.sv, a.batch, a.heads, a.seq, D))) return rc;
+  if ((rc = make_qkv_map(&tk, &P.pk, a.k, bf, a.sk, a.batch, a.kv_heads, a.seq, D))) return rc;
+  if ((rc = make_qkv_map(&tv, &P.pv, a.v, bf, a.sv, a.batch, a.kv_heads, a.seq, D))) return rc;
   P.lse = a.lse;
+  P.group = (int)(a.heads / a.kv_heads);
   P.B = (int)a.batch; P.H = (int)a.heads; P.S = (int)a.seq; P.nqb = (int)((a.seq + 127) / 128);
   P.causal = a.causal; P.is_bf16 = bf; P.scale_log2 = a.scale * kLog2eF; P.flag = device_flag_ptr();
   auto kern = attn_fwd_tc_kernel<D, T>;

@@ -255,32 +255,35 @@ def _bhsd_strides(a):
 
 
 def _check_self_attention_shapes(Q, K, V):
-    """The kernels index K and V with Q's batch, head and sequence counts, so anything but equal
-    logical shapes (fewer key/value heads, another key length) would read out of bounds."""
-    if Q.ndim != 4 or K.shape != Q.shape or V.shape != Q.shape:
+    """The kernels index K and V with Q's batch and sequence counts and with head h / group, so the
+    shapes are checked on the host: q [B,H,S,D], k and v [B,Hkv,S,D] with H a multiple of Hkv
+    (Hkv < H is grouped-query attention). Another key length would read out of bounds. Returns Hkv."""
+    ok = Q.ndim == 4 and K.ndim == 4 and K.shape == V.shape and K.shape[0] == Q.shape[0] and K.shape[2:] == Q.shape[2:]
+    if not ok or K.shape[1] < 1 or Q.shape[1] % K.shape[1] != 0:
         raise NotImplementedError(
-            f"self-attention needs q, k, v of one shape [B,H,S,D]; got {Q.shape}, {K.shape}, {V.shape} "
-            "(grouped-query heads and cross attention are not part of this path)")
+            f"self-attention needs q [B,H,S,D] and k, v [B,Hkv,S,D] with H a multiple of Hkv; got {Q.shape}, "
+            f"{K.shape}, {V.shape} (another key length, i.e. cross attention, is not part of this path)")
+    return K.shape[1]
 
 
 def fused_sdpa_forward(Q, K, V, attn_mask=None, causal=False, softmax_scale=None, strides=None, out=None,
                        out_strides=None):
-    """Q,K,V [B,H,S,D] -> (Q, K, V, O, M) with M the per-row log-sum-exp [B,H,S]
-    (fused_ops/flash_attention.py:1269). `strides` (three Strides3) lets callers
-    pass views such as the interleaved qkv projection."""
+    """Q [B,H,S,D], K, V [B,Hkv,S,D] -> (Q, K, V, O, M) with M the per-row log-sum-exp [B,H,S]
+    (fused_ops/flash_attention.py:1269; Hkv < H is grouped-query attention, :445-455). `strides`
+    (three Strides3) lets callers pass views such as the interleaved qkv projection."""
     if attn_mask is not None:
         raise NotImplementedError("attn_mask is not on the GPT training path; use causal=True/False")
     Q, K, V = _A(Q), _A(K), _A(V)
     _check_float(Q, K, V)
-    _check_self_attention_shapes(Q, K, V)
+    Hkv = _check_self_attention_shapes(Q, K, V)
     B, H, S, D = Q.shape
     scale = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(D)
     sq, sk, sv = strides or (_bhsd_strides(Q), _bhsd_strides(K), _bhsd_strides(V))
     O = out if out is not None else DeviceArray.empty((B, H, S, D), Q.dtype)
     so = out_strides or _bhsd_strides(O)
     M = DeviceArray.empty((B, H, S), "float32")
-    _lib.attn_fwd(Q.ptr, K.ptr, V.ptr, O.ptr, M.ptr, sq, sk, sv, so, B, H, S, D, scale, int(bool(causal)),
-                  Q.code, stream())
+    _lib.attn_fwd_gqa(Q.ptr, K.ptr, V.ptr, O.ptr, M.ptr, sq, sk, sv, so, B, H, Hkv, S, D, scale, int(bool(causal)),
+                      Q.code, stream())
     return Q, K, V, O, M
 
 
@@ -291,13 +294,14 @@ def fused_sdpa_backward(dO, Q, K, V, O, M, attn_mask=None, causal=False, softmax
         raise NotImplementedError("attn_mask is not on the GPT training path")
     dO, Q, K, V, O = _A(dO), _A(Q), _A(K), _A(V), _A(O)
     _check_float(dO, Q, K, V, O)
-    _check_self_attention_shapes(Q, K, V)
+    Hkv = _check_self_attention_shapes(Q, K, V)
     B, H, S, D = Q.shape
     scale = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(D)
     sq, sk, sv = strides or (_bhsd_strides(Q), _bhsd_strides(K), _bhsd_strides(V))
     if out is None:
-        dQ, dK, dV = (DeviceArray.empty((B, H, S, D), Q.dtype) for _ in range(3))
-        sdq = sdk = sdv = _bhsd_strides(dQ)
+        dQ = DeviceArray.empty((B, H, S, D), Q.dtype)
+        dK, dV = (DeviceArray.empty((B, Hkv, S, D), Q.dtype) for _ in range(2))
+        sdq, sdk, sdv = _bhsd_strides(dQ), _bhsd_strides(dK), _bhsd_strides(dV)
     else:
         dQ, dK, dV = out
         sdq, sdk, sdv = out_strides
@@ -305,9 +309,9 @@ def fused_sdpa_backward(dO, Q, K, V, O, M, attn_mask=None, causal=False, softmax
     sdo = do_strides or _bhsd_strides(dO)
     delta = DeviceArray.empty((B, H, S), "float32")
     dq_acc = DeviceArray.empty((B * H * S * D,), "float32") if Q.dtype != "float32" else None
-    _lib.attn_bwd(Q.ptr, K.ptr, V.ptr, O.ptr, dO.ptr, _A(M).ptr, dQ.ptr, dK.ptr, dV.ptr, delta.ptr,
-                  _ptr(dq_acc), sq, sk, sv, so, sdo, sdq, sdk, sdv, B, H, S, D, scale, int(bool(causal)),
-                  Q.code, stream())
+    _lib.attn_bwd_gqa(Q.ptr, K.ptr, V.ptr, O.ptr, dO.ptr, _A(M).ptr, dQ.ptr, dK.ptr, dV.ptr, delta.ptr,
+                      _ptr(dq_acc), sq, sk, sv, so, sdo, sdq, sdk, sdv, B, H, Hkv, S, D, scale, int(bool(causal)),
+                      Q.code, stream())
     return dQ, dK, dV
 
 
@@ -336,11 +340,17 @@ def fused_rope_rmsnorm_forward(q, k, cos, sin, eps=1e-5):
     q, k = _A(q), _A(k)
     _check_float(q, k)
     B, L, H, D = q.shape
-    assert k.shape == q.shape
+    Hk = k.shape[2]
+    assert k.shape == (B, L, Hk, D)
     yq, yk = DeviceArray.empty(q.shape, q.dtype), DeviceArray.empty(k.shape, k.dtype)
-    rq, rk = DeviceArray.empty((B * L * H,), "float32"), DeviceArray.empty((B * L * H,), "float32")
-    _lib.rope_rmsnorm_fwd(q.ptr, k.ptr, yq.ptr, yk.ptr, rq.ptr, rk.ptr, _A(cos).ptr, _A(sin).ptr, B, L, H, D,
-                          H * D, H * D, float(eps), q.code, stream())
+    rq, rk = DeviceArray.empty((B * L * H,), "float32"), DeviceArray.empty((B * L * Hk,), "float32")
+    c, s_ = _A(cos).ptr, _A(sin).ptr
+    if Hk == H:      # one launch for both tensors
+        _lib.rope_rmsnorm_fwd(q.ptr, k.ptr, yq.ptr, yk.ptr, rq.ptr, rk.ptr, c, s_, B, L, H, D, H * D, H * D, float(eps),
+                              q.code, stream())
+    else:            # grouped-query heads: k has fewer heads per token
+        _lib.rope_rmsnorm_fwd(q.ptr, None, yq.ptr, None, rq.ptr, None, c, s_, B, L, H, D, H * D, H * D, float(eps), q.code, stream())
+        _lib.rope_rmsnorm_fwd(k.ptr, None, yk.ptr, None, rk.ptr, None, c, s_, B, L, Hk, D, Hk * D, Hk * D, float(eps), k.code, stream())
     return yq, yk, rq, rk
 
 
@@ -349,9 +359,17 @@ def fused_rope_rmsnorm_backward(dyq, dyk, yq, yk, rstd_q, rstd_k, cos, sin):
     and rstd (fused_rmsnorm_backward, fused_ops/rmsnorm.py:251, then fused_rope_backward, rope.py:265)."""
     dyq, dyk, yq, yk = _A(dyq), _A(dyk), _A(yq), _A(yk)
     B, L, H, D = yq.shape
+    Hk = yk.shape[2]
     dq, dk = DeviceArray.empty(yq.shape, yq.dtype), DeviceArray.empty(yk.shape, yk.dtype)
-    _lib.rope_rmsnorm_bwd(dyq.ptr, dyk.ptr, yq.ptr, yk.ptr, _A(rstd_q).ptr, _A(rstd_k).ptr, dq.ptr, dk.ptr,
-                          _A(cos).ptr, _A(sin).ptr, B, L, H, D, H * D, H * D, H * D, yq.code, stream())
+    c, s_ = _A(cos).ptr, _A(sin).ptr
+    if Hk == H:
+        _lib.rope_rmsnorm_bwd(dyq.ptr, dyk.ptr, yq.ptr, yk.ptr, _A(rstd_q).ptr, _A(rstd_k).ptr, dq.ptr, dk.ptr,
+                              c, s_, B, L, H, D, H * D, H * D, H * D, yq.code, stream())
+    else:
+        _lib.rope_rmsnorm_bwd(dyq.ptr, None, yq.ptr, None, _A(rstd_q).ptr, None, dq.ptr, None, c, s_, B, L, H, D,
+                              H * D, H * D, H * D, yq.code, stream())
+        _lib.rope_rmsnorm_bwd(dyk.ptr, None, yk.ptr, None, _A(rstd_k).ptr, None, dk.ptr, None, c, s_, B, L, Hk, D,
+                              Hk * D, Hk * D, Hk * D, yk.code, stream())
     return dq, dk
 
 

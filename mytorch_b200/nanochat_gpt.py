@@ -6,8 +6,10 @@ q/k/v projections, rotary embedding THEN parameter-free RMSNorm on q and k
 lm_head (:287-288), loss = cross entropy of tanh-soft-capped logits.
 
 Same config fields, module names and state_dict keys as the reference. Training
-path plus cached decoding (`KVCache`, nanochat_trainer/core/cache.py). Multi-head attention (num_kv_heads == num_q_heads, the
-560M "d20" configuration); grouped-query attention is not on this path.
+path plus cached decoding (`KVCache`, nanochat_trainer/core/cache.py). num_kv_heads may be a
+divisor of num_q_heads (grouped-query attention: query head h reads key/value head
+h // (num_q_heads // num_kv_heads), nanochat_gpt.py:78-90); the 560M "d20" configuration is
+multi-head (10 of each). Cached decoding is built for the multi-head form only.
 Unlike the reference's training dispatcher, which drops `softcap` before the
 loss is computed (mytorch/nn/functional/losses/cross_entropy.py:178), the cap
 is applied, as the model definition intends.
@@ -88,23 +90,28 @@ class Embeddings(nn.Module):
 class Attention(nn.Module):
     def __init__(self, config, layer_idx):
         super().__init__()
-        if config.num_kv_heads != config.num_q_heads:
-            raise NotImplementedError("grouped-query attention is outside the training path built here")
+        assert config.num_kv_heads <= config.num_q_heads and config.num_q_heads % config.num_kv_heads == 0, \
+            "Q Heads must be divisible by KV Heads"
         self.embed_dim, self.num_heads = config.embed_dim, config.num_q_heads
+        self.num_kv_heads = config.num_kv_heads
         self.head_dim = config.embed_dim // config.num_q_heads
-        self.q_proj = nn.Linear(self.embed_dim, self.embed_dim, bias=config.use_bias)
-        self.k_proj = nn.Linear(self.embed_dim, self.embed_dim, bias=config.use_bias)
-        self.v_proj = nn.Linear(self.embed_dim, self.embed_dim, bias=config.use_bias)
+        # fewer key/value heads than query heads = grouped-query attention (nanochat_gpt.py:78-90)
+        self.q_proj = nn.Linear(self.embed_dim, self.num_heads * self.head_dim, bias=config.use_bias)
+        self.k_proj = nn.Linear(self.embed_dim, self.num_kv_heads * self.head_dim, bias=config.use_bias)
+        self.v_proj = nn.Linear(self.embed_dim, self.num_kv_heads * self.head_dim, bias=config.use_bias)
         self.out_proj = nn.Linear(self.embed_dim, self.embed_dim, bias=config.use_bias)
 
     def forward(self, x, cos_sin, residual=None, cache=None, layer_idx=None):
         B, T, E = x.shape
-        H, D = self.num_heads, self.head_dim
+        H, Hk, D = self.num_heads, self.num_kv_heads, self.head_dim
         q = self.q_proj(x).reshape(B, T, H, D)
-        k = self.k_proj(x).reshape(B, T, H, D)
-        v = self.v_proj(x).reshape(B, T, H, D)
+        k = self.k_proj(x).reshape(B, T, Hk, D)
+        v = self.v_proj(x).reshape(B, T, Hk, D)
         cos, sin = cos_sin
         q, k = F.rope_qk_norm(q, k, cos, sin)                    # rotary first, then QK-norm over head_dim: one kernel
+        if cache is not None and Hk != H:
+            raise NotImplementedError("cached decoding with grouped-query heads is not built (training and uncached "
+                                      "inference are)")
         if cache is not None:
             # inference: new keys/values join the cache; the prompt (empty cache) attends causally
             # among its own tokens, later tokens see everything cached (nanochat_gpt.py:126-160)

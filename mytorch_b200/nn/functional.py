@@ -346,12 +346,13 @@ def lm_head_cross_entropy(x, weight, targets, chunk=8192, softcap=None):
 
 # -------------------------------------------------------------- attention ----
 def scaled_dot_product_attention(q, k, v, attn_mask=None, is_causal=False, softmax_scale=None, enable_gqa=False):
-    """q,k,v [B,H,S,D] contiguous (mytorch/nn/functional/flash_attention/
-    flash_attention.py:20-127). One backward launch (the reference runs its
+    """q [B,H,S,D], k, v [B,Hkv,S,D] contiguous (mytorch/nn/functional/flash_attention/
+    flash_attention.py:20-127); with enable_gqa=True Hkv may divide H and query head h
+    attends to key/value head h // (H // Hkv). One backward launch (the reference runs its
     backward kernel twice, :73-91)."""
-    if enable_gqa or k.shape != q.shape or v.shape != q.shape:
-        raise NotImplementedError("grouped-query attention (fewer key/value heads than query heads) is not built; "
-                                  f"q, k, v must share one shape, got {q.shape}, {k.shape}, {v.shape}")
+    if k.shape[1] != q.shape[1] and not enable_gqa:
+        # the reference's check (flash_attention.py:43-44): fewer key/value heads need the flag
+        raise ValueError(f"q has {q.shape[1]} heads and k has {k.shape[1]}: pass enable_gqa=True for grouped-query attention")
     _, _, _, o, m = K.fused_sdpa_forward(q.data, k.data, v.data, attn_mask, is_causal, softmax_scale)
     out = Tensor(o)
     if _needs_graph(q, k, v):
@@ -372,20 +373,23 @@ def bthd_attention(q, k, v, is_causal=True):
     addressed through strides, so the reference's transpose(1, 2) + contiguous
     copies are not made; the result is [B, T, H*D]."""
     B, T, H, D = q.shape
-    if k.shape != q.shape or v.shape != q.shape:
-        raise NotImplementedError(f"q, k, v must share one shape [B,T,H,D]; got {q.shape}, {k.shape}, {v.shape}")
+    Hk = k.shape[2]
+    if k.shape != (B, T, Hk, D) or v.shape != k.shape or H % Hk:
+        raise NotImplementedError(f"q [B,T,H,D] and k, v [B,T,Hkv,D] with H a multiple of Hkv; got {q.shape}, {k.shape}, {v.shape}")
     st = _lib.Strides3(T * H * D, D, H * D)
-    as4 = lambda a: DeviceArray(a.ptr, (B, H, T, D), a.dtype, base=a)      # logical [B,H,T,D] over [B,T,H,D] memory
-    qv, kv, vv = as4(q.data), as4(k.data), as4(v.data)
+    sk_ = _lib.Strides3(T * Hk * D, D, Hk * D)                              # fewer key/value heads per token
+    as4 = lambda a, h=H: DeviceArray(a.ptr, (B, h, T, D), a.dtype, base=a)  # logical [B,h,T,D] over [B,T,h,D] memory
+    qv, kv, vv = as4(q.data), as4(k.data, Hk), as4(v.data, Hk)
     o_arr = DeviceArray.empty((B, T, H * D), q.dtype)
     ov = as4(o_arr)
-    _, _, _, _, m = K.fused_sdpa_forward(qv, kv, vv, None, is_causal, None, strides=(st, st, st), out=ov, out_strides=st)
+    _, _, _, _, m = K.fused_sdpa_forward(qv, kv, vv, None, is_causal, None, strides=(st, sk_, sk_), out=ov, out_strides=st)
     out = Tensor(o_arr)
     if _needs_graph(q, k, v):
         def _bw(g):
-            dq, dk, dv = (DeviceArray.empty((B, T, H, D), q.dtype) for _ in range(3))
-            K.fused_sdpa_backward(as4(g), qv, kv, vv, ov, m, None, is_causal, None, strides=(st, st, st),
-                                  out=(as4(dq), as4(dk), as4(dv)), out_strides=(st, st, st), o_strides=st, do_strides=st)
+            dq = DeviceArray.empty((B, T, H, D), q.dtype)
+            dk, dv = (DeviceArray.empty((B, T, Hk, D), q.dtype) for _ in range(2))
+            K.fused_sdpa_backward(as4(g), qv, kv, vv, ov, m, None, is_causal, None, strides=(st, sk_, sk_),
+                                  out=(as4(dq), as4(dk, Hk), as4(dv, Hk)), out_strides=(st, sk_, sk_), o_strides=st, do_strides=st)
             for t, d in ((q, dq), (k, dk), (v, dv)):
                 if t.requires_grad:
                     t._accumulate(d)
@@ -475,10 +479,9 @@ def rope_qk_norm(q, k, cos, sin, eps=1e-5):
     kernel does not take (anything but 2..32 16-byte vectors) go through the separate ops."""
     D = q.shape[-1]
     vec = 16 // q.data.itemsize
-    if D % vec or (D // vec) not in (2, 4, 8, 16, 32) or q.shape != k.shape:
+    if D % vec or (D // vec) not in (2, 4, 8, 16, 32) or q.shape[:2] != k.shape[:2] or k.shape[-1] != D:
         q2, k2 = apply_rotary_pos_embed(q, k, cos, sin)
-        shp = q.shape
-        return (rmsnorm(q2.reshape(-1, D), eps=eps).reshape(shp), rmsnorm(k2.reshape(-1, D), eps=eps).reshape(shp))
+        return (rmsnorm(q2.reshape(-1, D), eps=eps).reshape(q.shape), rmsnorm(k2.reshape(-1, D), eps=eps).reshape(k.shape))
     yq, yk, rq, rk = K.fused_rope_rmsnorm_forward(q.data, k.data, cos, sin, eps)
     oq, ok = Tensor(yq), Tensor(yk)
     if _needs_graph(q, k):

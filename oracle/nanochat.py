@@ -3,8 +3,9 @@
 INFRASTRUCTURE: see oracle/__init__.py.
 
 Per block: x + attn(norm(x)), x + mlp(norm(x)) with norm = parameter-free
-RMSNorm (:39-43); attention = q/k/v projections, rotary embedding then RMSNorm
-on q and k (:121-124), causal softmax attention, out_proj; mlp = ReLU^2 (4x).
+RMSNorm (:39-43); attention = q/k/v projections (k and v with num_kv_heads heads, :88-90),
+rotary embedding then RMSNorm on q and k (:121-124), key/value heads repeated over their
+group (:139-141), causal softmax attention, out_proj; mlp = ReLU^2 (4x).
 Loss = cross entropy of softcap * tanh(logits / softcap) (:334-349, the
 model's stated intent; the reference's CPU dispatcher cannot take a softcap, so
 the reference run that pins this file caps the logits with the model's own
@@ -25,6 +26,7 @@ class GPTConfig:
     mlp_ratio: int = 4
     num_blocks: int = 20
     num_heads: int = 10
+    num_kv_heads: int = 0          # 0 = as many as query heads; a divisor of num_heads = grouped-query attention
     rope_base: float = 10000.0
     softcap: float = 15.0
 
@@ -35,12 +37,13 @@ def init_params(cfg, seed=0, dtype=np.float32):
     to most of the network)."""
     rng = np.random.default_rng(seed)
     E, Hd = cfg.embed_dim, cfg.embed_dim * cfg.mlp_ratio
+    Ekv = (cfg.num_kv_heads or cfg.num_heads) * (E // cfg.num_heads)     # k/v projection width (nanochat_gpt.py:88-90)
     p = {"embeddings.embeddings.weight": rng.normal(0, 0.5, (cfg.vocab_size, E))}
     s = 1.0 / np.sqrt(E)
     for i in range(cfg.num_blocks):
         b = f"blocks.{i}."
         for n in ("q_proj", "k_proj", "v_proj", "out_proj"):
-            p[b + f"attention.{n}.weight"] = rng.normal(0, s, (E, E))
+            p[b + f"attention.{n}.weight"] = rng.normal(0, s, (Ekv if n in ("k_proj", "v_proj") else E, E))
         p[b + "feedforward.intermediate_dense.weight"] = rng.normal(0, s, (Hd, E))
         p[b + "feedforward.out_proj.weight"] = rng.normal(0, 1.0 / np.sqrt(Hd), (E, Hd))
     p["lm_head.weight"] = rng.normal(0, s, (cfg.vocab_size, E))
@@ -51,6 +54,8 @@ def forward(params, cfg, ids, targets):
     B, T = ids.shape
     E, H = cfg.embed_dim, cfg.num_heads
     D = E // H
+    Hk = cfg.num_kv_heads or H
+    G = H // Hk                                 # query heads per key/value head
     cos, sin = ops.rope_cos_sin(D, T, cfg.rope_base)
     x = params["embeddings.embeddings.weight"][ids].reshape(B * T, E)
     cache = {"ids": ids, "blocks": [], "cos": cos, "sin": sin}
@@ -60,15 +65,17 @@ def forward(params, cfg, ids, targets):
         h1, c["rs1"] = ops.rmsnorm_fwd(x)
         c["h1"] = h1
         q = ops.linear_fwd(h1, params[b + "attention.q_proj.weight"]).reshape(B, T, H, D)
-        k = ops.linear_fwd(h1, params[b + "attention.k_proj.weight"]).reshape(B, T, H, D)
-        v = ops.linear_fwd(h1, params[b + "attention.v_proj.weight"]).reshape(B, T, H, D)
+        k = ops.linear_fwd(h1, params[b + "attention.k_proj.weight"]).reshape(B, T, Hk, D)
+        v = ops.linear_fwd(h1, params[b + "attention.v_proj.weight"]).reshape(B, T, Hk, D)
         qr, kr = ops.rope_fwd(q, cos, sin), ops.rope_fwd(k, cos, sin)
         c["qr"], c["kr"] = qr.reshape(-1, D), kr.reshape(-1, D)
         qn, c["rsq"] = ops.rmsnorm_fwd(c["qr"])
         kn, c["rsk"] = ops.rmsnorm_fwd(c["kr"])
         qh = qn.reshape(B, T, H, D).transpose(0, 2, 1, 3)
-        kh = kn.reshape(B, T, H, D).transpose(0, 2, 1, 3)
+        kh = kn.reshape(B, T, Hk, D).transpose(0, 2, 1, 3)
         vh = v.transpose(0, 2, 1, 3)
+        if G > 1:                               # repeat_interleave over the head axis (nanochat_gpt.py:139-141)
+            kh, vh = np.repeat(kh, G, axis=1), np.repeat(vh, G, axis=1)
         o, pr = ops.attention_fwd(qh, kh, vh, causal=True)
         c["qh"], c["kh"], c["vh"], c["p"] = qh, kh, vh, pr
         a = o.transpose(0, 2, 1, 3).reshape(B * T, E)
@@ -99,6 +106,8 @@ def backward(params, cfg, cache):
     B, T = ids.shape
     E, H = cfg.embed_dim, cfg.num_heads
     D = E // H
+    Hk = cfg.num_kv_heads or H
+    G = H // Hk
     cos, sin = cache["cos"], cache["sin"]
     grads = {}
     dcap = ops.cross_entropy_bwd(cache["capped"], cache["targets"])
@@ -117,13 +126,16 @@ def backward(params, cfg, cache):
         da, grads[b + "attention.out_proj.weight"], _ = ops.linear_bwd(c["a"], params[b + "attention.out_proj.weight"], dx)
         do = da.reshape(B, T, H, D).transpose(0, 2, 1, 3)
         dqh, dkh, dvh = ops.attention_bwd(c["qh"], c["kh"], c["vh"], c["p"], do)
+        if G > 1:                               # a key/value head collects the gradients of its group
+            dkh = dkh.reshape(B, Hk, G, T, D).sum(axis=2)
+            dvh = dvh.reshape(B, Hk, G, T, D).sum(axis=2)
         dqn = dqh.transpose(0, 2, 1, 3).reshape(-1, D)
         dkn = dkh.transpose(0, 2, 1, 3).reshape(-1, D)
         dqr = ops.rmsnorm_bwd(c["qr"], c["rsq"], dqn)[0].reshape(B, T, H, D)
-        dkr = ops.rmsnorm_bwd(c["kr"], c["rsk"], dkn)[0].reshape(B, T, H, D)
+        dkr = ops.rmsnorm_bwd(c["kr"], c["rsk"], dkn)[0].reshape(B, T, Hk, D)
         dq = ops.rope_bwd(dqr, cos, sin).reshape(B * T, E)
-        dk = ops.rope_bwd(dkr, cos, sin).reshape(B * T, E)
-        dv = dvh.transpose(0, 2, 1, 3).reshape(B * T, E)
+        dk = ops.rope_bwd(dkr, cos, sin).reshape(B * T, Hk * D)
+        dv = dvh.transpose(0, 2, 1, 3).reshape(B * T, Hk * D)
         dh1 = 0
         for n, d in (("q_proj", dq), ("k_proj", dk), ("v_proj", dv)):
             dh, grads[b + f"attention.{n}.weight"], _ = ops.linear_bwd(c["h1"], params[b + f"attention.{n}.weight"], d)

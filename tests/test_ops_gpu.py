@@ -414,18 +414,53 @@ def test_rope_then_qk_rmsnorm_fused(mt, dtype, B, T, H, D):
     no_device_flag(mt)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("B,H,Hkv,S,D,causal", [(2, 4, 2, 70, 32, True), (1, 6, 2, 257, 64, True), (2, 4, 1, 128, 64, False),
+                                                (1, 10, 5, 300, 128, True), (2, 8, 2, 1024, 64, True)])
+def test_grouped_query_attention(mt, dtype, B, H, Hkv, S, D, causal):
+    """Fewer key/value heads than query heads (fused_ops/flash_attention.py:445-455): query head h
+    attends to key/value head h // (H // Hkv); dK and dV sum over the query heads of their group.
+    Against the oracle with the key/value heads repeated, contiguous [B,H,S,D] and the models'
+    [B,T,H,D] layout."""
+    F, Fn = mt.fused_ops, mt.nn.functional
+    r = np.random.default_rng(17)
+    G = H // Hkv
+    q, do = (rnd(r.standard_normal((B, H, S, D)), dtype) for _ in range(2))
+    k, v = (rnd(r.standard_normal((B, Hkv, S, D)), dtype) for _ in range(2))
+    o, p = O.attention_fwd(q, np.repeat(k, G, axis=1), np.repeat(v, G, axis=1), causal=causal)
+    dq, dk, dv = O.attention_bwd(q, np.repeat(k, G, axis=1), np.repeat(v, G, axis=1), p, do)
+    dk, dv = (g.reshape(B, Hkv, G, S, D).sum(axis=2) for g in (dk, dv))
+    t = TOL[dtype]
+    Q, K, V, DO = (dev(mt, a, dtype) for a in (q, k, v, do))
+    _, _, _, Ou, M = F.fused_sdpa_forward(Q, K, V, causal=causal)
+    close(Ou.numpy(), o, t, "o")
+    DQ, DK, DV = F.fused_sdpa_backward(DO, Q, K, V, Ou, M, causal=causal)
+    assert DK.shape == (B, Hkv, S, D) and DV.shape == (B, Hkv, S, D)
+    close(DQ.numpy(), dq, 2 * t, "dq"); close(DK.numpy(), dk, 2 * t, "dk"); close(DV.numpy(), dv, 2 * t, "dv")
+    if causal:   # the [B,T,H,D] form the nanochat model uses, through autograd
+        ts = [mt.Tensor(dev(mt, np.ascontiguousarray(a.transpose(0, 2, 1, 3)), dtype), requires_grad=True) for a in (q, k, v)]
+        out = Fn.bthd_attention(*ts, is_causal=True)
+        close(out.numpy(), o.transpose(0, 2, 1, 3).reshape(B, S, H * D), t, "bthd o")
+        out.backward(dev(mt, np.ascontiguousarray(do.transpose(0, 2, 1, 3)).reshape(B, S, H * D), dtype))
+        for a, g, name in zip(ts, (dq, dk, dv), "qkv"):
+            close(a.grad.numpy(), g.transpose(0, 2, 1, 3), 2 * t, f"bthd d{name}")
+    no_device_flag(mt)
+
+
 def test_attention_rejects_mismatched_key_value_shapes(mt):
-    """Fewer key/value heads (grouped-query attention) or another key length are refused on the
-    host: the kernels index K and V with Q's extents."""
+    """Key/value heads that do not divide the query heads, fewer of them without enable_gqa, or
+    another key length are refused on the host: the kernels index K and V with Q's extents."""
     Fn = mt.nn.functional
     q = mt.Tensor(mt.DeviceArray.zeros((1, 4, 64, 64), "float16"))
     kv = mt.Tensor(mt.DeviceArray.zeros((1, 2, 64, 64), "float16"))
+    kv3 = mt.Tensor(mt.DeviceArray.zeros((1, 3, 64, 64), "float16"))
+    with pytest.raises(ValueError):
+        Fn.scaled_dot_product_attention(q, kv, kv, is_causal=True)          # needs enable_gqa=True
+    assert Fn.scaled_dot_product_attention(q, kv, kv, is_causal=True, enable_gqa=True).shape == (1, 4, 64, 64)
     with pytest.raises(NotImplementedError):
-        Fn.scaled_dot_product_attention(q, kv, kv, is_causal=True)
+        Fn.scaled_dot_product_attention(q, kv3, kv3, is_causal=True, enable_gqa=True)
     with pytest.raises(NotImplementedError):
-        Fn.scaled_dot_product_attention(q, q, q, is_causal=True, enable_gqa=True)
-    with pytest.raises(NotImplementedError):
-        mt.fused_ops.fused_sdpa_forward(q.data, kv.data, kv.data, causal=True)
+        mt.fused_ops.fused_sdpa_forward(q.data, kv3.data, kv3.data, causal=True)
     longer = mt.Tensor(mt.DeviceArray.zeros((1, 128, 4, 64), "float16"))
     short = mt.Tensor(mt.DeviceArray.zeros((1, 64, 4, 64), "float16"))
     with pytest.raises(NotImplementedError):

@@ -155,13 +155,16 @@ def test_tiny_gpt2_loss_trajectory(tiny_golden):
         assert abs(a - b) <= 1e-4 * abs(b), (losses, ref)
 
 
-def test_nanochat_tiny_matches_reference():
-    """nanochat-style GPT oracle against the reference run (6 AdamW steps)."""
+@pytest.mark.parametrize("fname,heads,seed", [("nanochat_tiny.json", dict(num_heads=2), 4),
+                                              ("nanochat_tiny_gqa.json", dict(num_heads=4, num_kv_heads=2), 5)])
+def test_nanochat_tiny_matches_reference(fname, heads, seed):
+    """nanochat-style GPT oracle against the reference run (6 AdamW steps), multi-head and
+    grouped-query (4 query heads on 2 key/value heads)."""
     from oracle import nanochat as on
-    with open(os.path.join(GOLDEN, "nanochat_tiny.json")) as fh:
+    with open(os.path.join(GOLDEN, fname)) as fh:
         gold = json.load(fh)
-    cfg = on.GPTConfig(vocab_size=96, max_seq_len=32, embed_dim=64, mlp_ratio=4, num_blocks=2, num_heads=2)
-    params = on.init_params(cfg, seed=4)
+    cfg = on.GPTConfig(vocab_size=96, max_seq_len=32, embed_dim=64, mlp_ratio=4, num_blocks=2, **heads)
+    params = on.init_params(cfg, seed=seed)
     m = {k: np.zeros_like(v) for k, v in params.items()}
     v = {k: np.zeros_like(p) for k, p in params.items()}
     rng = np.random.default_rng(8)

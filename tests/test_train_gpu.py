@@ -228,20 +228,23 @@ def test_adamw_multi_tensor_matches_reference_golden(golden_ops, op_inputs):
     assert np.abs(opt.param_groups[0]["v"][0].numpy() - g["adam_v"]).max() <= 1e-6
 
 
-def test_nanochat_tiny_fp32_matches_reference_losses():
+@pytest.mark.parametrize("fname,hq,hkv,seed", [("nanochat_tiny.json", 2, 2, 4), ("nanochat_tiny_gqa.json", 4, 2, 5)])
+def test_nanochat_tiny_fp32_matches_reference_losses(fname, hq, hkv, seed):
     """nanochat-style GPT (RoPE then QK-norm, parameter-free RMSNorm, ReLU^2,
     untied head, soft-capped loss) through the CUDA library against the
-    reference run in tests/golden/nanochat_tiny.json."""
+    reference runs in tests/golden/: multi-head, and grouped-query with 4 query heads on 2
+    key/value heads."""
     import mytorch_b200 as mt
     from mytorch_b200.nanochat_gpt import GPT, GPTConfig
     from oracle import nanochat as on
-    with open(os.path.join(GOLDEN, "nanochat_tiny.json")) as fh:
+    with open(os.path.join(GOLDEN, fname)) as fh:
         gold = json.load(fh)
-    cfg = on.GPTConfig(vocab_size=96, max_seq_len=32, embed_dim=64, mlp_ratio=4, num_blocks=2, num_heads=2)
+    cfg = on.GPTConfig(vocab_size=96, max_seq_len=32, embed_dim=64, mlp_ratio=4, num_blocks=2, num_heads=hq,
+                       num_kv_heads=hkv)
     np.random.seed(0)
     model = GPT(GPTConfig(vocab_size=96, max_seq_len=32, embed_dim=64, mlp_ratio=4, num_blocks=2,
-                          num_q_heads=2, num_kv_heads=2))
-    model.load_state_dict(on.init_params(cfg, seed=4))
+                          num_q_heads=hq, num_kv_heads=hkv))
+    model.load_state_dict(on.init_params(cfg, seed=seed))
     opt = mt.optim.AdamW([{"params": model.parameters(), "weight_decay": 0.1}], lr=1e-3, beta1=0.9, beta2=0.95)
     rng = np.random.default_rng(8)
     for step in range(6):
