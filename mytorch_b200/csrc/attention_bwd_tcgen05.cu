@@ -13,16 +13,26 @@
 //   dV  += P^T dO           dK  += dS^T Q          (128xDx128, accumulated)
 //   dQ   = dS K             (128xDx128, added to a fp32 buffer with TMA reduce-add,
 //                            since every key block contributes to every dQ row)
-// Warp roles: one warp TMA producer (K, V once; Q, dO and the block's row statistics per query
-// block, read in place through 4-D strided tensor maps, three stages at head_dim 64), one warp
-// MMA issuer, the other warps the elementwise stage: thread = key row = TMEM lane (four warps per
-// lane quarter with 32 query columns each at head_dim 64, two with 64 each at head_dim 128). It copies S^T and dP^T to registers - which lets the MMA warp
-// start the next block's S^T / dP^T at once - forms P^T = exp2(S^T*scale*log2e - lse*log2e) and
-// dS^T = P^T (dP^T*scale - delta*scale), and writes dS^T as half into shared memory in the
-// swizzled layout that serves as K-major A operand for dK and, read the other way, as M-major A
-// operand for dQ. P^T goes to tensor memory (head_dim 64: A operand of the dV MMA read from
-// TMEM) or to shared memory (head_dim 128, where tensor memory is full). No transposes are
-// materialised anywhere. dK and dV leave through staged TMA stores.
+// Warp roles: one warp TMA producer (K, V once per tile; Q, dO and the block's row statistics per
+// query block, read in place through 4-D strided tensor maps), one warp MMA issuer, sixteen warps
+// the elementwise stage: thread = key row = TMEM lane, four warps per lane quarter with 32 query
+// columns each. It copies S^T and dP^T to registers, forms P^T = exp2(S^T*scale*log2e - lse*log2e)
+// and dS^T = P^T (dP^T*scale - delta*scale), writes P^T to tensor memory as packed half pairs (the
+// A operand of the dV MMA) and dS^T as half into shared memory in the swizzled layout that serves
+// as K-major A operand for dK and, read the other way, as M-major A operand for dQ. No transposes
+// are materialised anywhere. dK and dV leave through staged TMA stores.
+//   head_dim 64: every accumulator has tensor-memory columns of its own and Q/dO come through a
+// ring of three stages, so the next block's S^T/dP^T are issued as soon as the elementwise warps
+// hold the current ones in registers, and a block's dQ is read out during the next block's MMAs.
+//   head_dim 128: S^T, dP^T, dV and dK fill the 512 columns. P^T is written over S^T (after a
+// barrier among the four warps of a lane quarter) and dQ is computed over dP^T; there is one
+// buffer each for Q and dO. Per block the MMA order is dV, dK, dQ, S^T(next), dP^T(next): dV and dK
+// free dO and Q, whose reloads (already in L2 by a prefetch) enter the TMA queue ahead of the dQ
+// reduce-adds, S^T(next) only needs P^T consumed, dP^T(next) waits until dQ is in registers.
+// The dQ reduce-add is the scarce resource at head_dim 128: reductions leave an SM at ~25 bytes
+// per clock (measured; ~15 when all SMs send them), i.e. 2600-4300 cycles for the 64 KB of one
+// block against 2520 cycles of MMA; it runs asynchronously out of staging buffers that nothing
+// else uses.
 // A small kernel run first writes the row statistics lse*log2e and delta*scale =
 // scale*rowsum(O*dO), padded to whole blocks.
 //
@@ -32,6 +42,11 @@
 #include "sm100.cuh"
 #include "attention_tc.cuh"
 #include "tempbuf.cuh"
+#include <algorithm>
+#include <array>
+#include <map>
+#include <mutex>
+#include <vector>
 
 namespace mt {
 
@@ -39,39 +54,48 @@ using namespace sm100;
 
 
 template <int D> struct BwdCfg {
-  // Elementwise warps: kEwWarps / 4 per TMEM lane quarter, each taking kColsPerThread of the
-  // block's 128 query columns: sixteen warps with 32 columns per thread at head_dim 64, eight
-  // with 64 at head_dim 128, whose dQ staging lives inside the P^T buffer in slices that exactly
-  // one warp writes.
-  static constexpr int kEwWarps = D == 64 ? 16 : 8;
+  // Elementwise warps: four per TMEM lane quarter, each taking 32 of the block's 128 query columns.
+  static constexpr int kEwWarps = 16;
   static constexpr int kColsPerThread = 128 / (kEwWarps / 4);
   static constexpr int kThreads = 32 * (kEwWarps + 2);
-  static constexpr int kDrainWarps = 8;                     // column groups 0 and 1 write dK and dV
   static constexpr int kChunks = D / 64;
   static constexpr int kTile = 128 * D * 2;                 // one 128-row block of K/V/Q/dO
-  // head_dim 64 has 64 spare TMEM columns: P^T lives there (A operand of the dV MMA read from
-  // tensor memory) and the 32 KB it would take in shared memory buy a third Q/dO stage.
-  static constexpr bool kPTinTmem = D == 64;
-  static constexpr int kStages = D == 64 ? 3 : 1;           // Q+dO ring
+  // head_dim 64: a ring of three Q+dO stages behind one barrier pair per stage. head_dim 128 has
+  // room for one Q and one dO buffer, each with barriers of its own: Q is reloaded as soon as the
+  // dK MMA (issued first) has read it, dO after the dV MMA; both were brought into L2 a block ahead.
+  static constexpr bool kSplit = D == 128;
+  static constexpr int kQStages = D == 64 ? 3 : 1;
+  static constexpr int kDOStages = D == 64 ? 3 : 1;
   static constexpr int kOffK = 0;
   static constexpr int kOffV = kTile;
-  static constexpr int kOffQ = 2 * kTile;                   // stage s: Q at +s*2*kTile, dO right after it
-  static constexpr int kOffPT = kOffQ + kStages * 2 * kTile;
-  static constexpr int kOffDST = kOffPT + (kPTinTmem ? 0 : 32768);
-  static constexpr int kOffStat = kOffDST + 32768;          // per Q/dO stage: lse*log2e [128], delta*scale [128] floats
-  // dQ staging for TMA reduce-add: one 32-row x 128-byte buffer per elementwise warp. With its own
-  // TMEM columns (head_dim 64) dQ is flushed while P^T is live, so it gets its own 32 KB; when dQ
-  // aliases S^T (head_dim 128) the flush happens while P^T is dead and each warp stages in the
-  // part of the P^T buffer that only it writes.
-  static constexpr bool kOwnStage = D == 64;
-  static constexpr int kOffStage = kOwnStage ? kOffStat + 4096 : kOffPT;
-  static constexpr int kOffBar = kOffStat + 4096 + (kOwnStage ? 32768 : 0);
-  static constexpr int kSmem = kOffBar + 256 + 1024;
+  static constexpr int kOffQ = 2 * kTile;
+  static constexpr int kOffDO = kOffQ + kQStages * kTile;
+  static constexpr int kOffDST = kOffDO + kDOStages * kTile;
+  // Staging for the TMA reduce-add of dQ and the TMA stores of dK/dV: a buffer of 32 rows x 128
+  // bytes of its own for every warp that flushes (the eight warps of column groups 0 and 1 at
+  // head_dim 64, all sixteen at head_dim 128). Reduce-adds leave an SM at about 25 bytes per clock
+  // (15 when every SM sends them), so a block's dQ - 32 KB / 64 KB of fp32 - is on its way for
+  // thousands of cycles: the buffers are not shared with anything, and a warp meets its buffer
+  // again only a whole block later, when the reduce-add has long read it.
+  static constexpr int kFlushWarps = D == 64 ? 8 : 16;
+  static constexpr int kStageRows = 32;
+  static constexpr int kStageBytes = kStageRows * 128;
+  static constexpr int kOffStage = kOffDST + 32768;
+  static constexpr int kOffStat = kOffStage + kFlushWarps * kStageBytes;   // per Q stage: lse*log2e [128], delta*scale [128] floats
+  static constexpr int kOffBar = kOffStat + kQStages * 1024;
+  // No slack for aligning the base: the dynamic shared-memory window of a kernel without static
+  // shared memory starts 1024-byte aligned (checked at entry).
+  static constexpr int kSmem = kOffBar + 256;
+  static_assert(kSmem <= 232448, "shared memory of one CTA");
+  // Tensor memory, 512 columns. head_dim 64: S^T, dP^T, dV, dK, dQ and P^T (packed half pairs)
+  // each have their own. head_dim 128 fills all 512 with S^T, dP^T, dV and dK: P^T is written over
+  // the first 64 columns of S^T once every warp of the lane quarter has read its scores, and dQ
+  // is computed over dP^T, which the elementwise warps have read by then.
   static constexpr int kTmemCols = 512;
   static constexpr int kColST = 0, kColDPT = 128, kColDV = 256, kColDK = 256 + D;
-  static constexpr bool kAliasDQ = D == 128;                // dQ shares the S^T columns when TMEM is full
-  static constexpr int kColDQ = kAliasDQ ? 0 : 256 + 2 * D;
-  static constexpr int kColPT = 256 + 3 * D;                // packed half pairs, 64 columns (head_dim 64 only)
+  static constexpr bool kAliasDQ = D == 128;
+  static constexpr int kColDQ = kAliasDQ ? kColDPT : 256 + 2 * D;
+  static constexpr int kColPT = kAliasDQ ? kColST : 256 + 3 * D;
 };
 
 // Tiles are dealt to the persistent CTAs round by round, forwards in even rounds and backwards
@@ -92,6 +116,7 @@ struct AttnBwdParams {
   MapPos pq, pk, pv, pdo, pdk, pdv;
   int B, H, S, nqb, causal, is_bf16;
   int Hkv, group;       // key/value heads; query heads per key/value head (H = Hkv * group)
+  int gh;               // (batch, key/value head) pairs per group of the tile order
   float scale, scale_log2;
   int* flag;
 };
@@ -103,17 +128,21 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                    const __grid_constant__ CUtensorMap tmDQ, const __grid_constant__ CUtensorMap tmDK,
                    const __grid_constant__ CUtensorMap tmDV, const AttnBwdParams P) {
   using Cfg = BwdCfg<D>;
-  constexpr int ST = Cfg::kStages;
+  constexpr int ST = Cfg::kQStages;             // Q ring (at head_dim 64 dO travels with it)
   constexpr int kBwdEwWarps = Cfg::kEwWarps;
   constexpr int CPT = Cfg::kColsPerThread;
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t raw = smem_u32(smem_raw);
-  const uint32_t base = (raw + 1023u) & ~1023u;
-  uint8_t* base_ptr = smem_raw + (base - raw);
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t base = smem_u32(smem_raw);
+  if (base & 1023u) {   // the 128-byte swizzle needs 1024-byte aligned tiles
+    if (threadIdx.x == 0 && P.flag) atomicMax(P.flag, 102);
+    return;
+  }
+  uint8_t* base_ptr = smem_raw;
   const uint32_t bar0 = base + Cfg::kOffBar;
   const uint32_t bar_kv = bar0, bar_qfull0 = bar0 + 8, bar_qempty0 = bar0 + 32, bar_sdp = bar0 + 56,
                  bar_pds = bar0 + 64, bar_dq = bar0 + 72, bar_dqfree = bar0 + 80, bar_sdpfree = bar0 + 88,
-                 bar_kvfree = bar0 + 96, bar_dkvfree = bar0 + 104;
+                 bar_kvfree = bar0 + 96, bar_dkvfree = bar0 + 104, bar_quarter0 = bar0 + 128,   // four quarter barriers: +128 .. +159
+                 bar_dofull = bar0 + 160, bar_doempty = bar0 + 168;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + Cfg::kOffBar + 112);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + Cfg::kOffBar + 116);
   float* stat = reinterpret_cast<float*>(base_ptr + Cfg::kOffStat);
@@ -121,8 +150,10 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int bh_count = P.B * P.Hkv;           // (batch, key/value head) pairs
   const int n_tiles = P.nqb * bh_count;
-  // Tile t: key block jb = t / bh_count (small jb = most query blocks when causal, so heavy tiles
-  // come first), (batch, key/value head) = t % bh_count. The tile's steps are the query blocks of
+  // Tile t -> (key block jb, (batch, key/value head)) by decode_tile: heads in groups of P.gh,
+  // within a group small jb first (= most query blocks when causal, so heavy tiles come first; a
+  // group is two rounds of gridDim.x tiles, dealt forwards then backwards, so every CTA gets a heavy
+  // and a light tile of it). The tile's steps are the query blocks of
   // every query head that reads this key/value head: step i = (query head hk*group + i / n_qb,
   // query block q_start + i % n_qb); dK and dV accumulate over all of them. Every role walks the
   // same tile sequence and keeps a running count `g` of steps, from which ring stages and barrier
@@ -135,7 +166,9 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     mbar_init(bar_dqfree, 32 * kBwdEwWarps);
     mbar_init(bar_sdpfree, kBwdEwWarps);
     mbar_init(bar_kvfree, 1);
-    mbar_init(bar_dkvfree, Cfg::kDrainWarps);
+    for (int i = 0; i < 4; ++i) mbar_init(bar_quarter0 + 8 * i, 4);   // one arrival per warp of a lane quarter
+    mbar_init(bar_dkvfree, 8 * Cfg::kChunks);       // one arrival per warp that drains a 64-column piece of dK or dV
+    mbar_init(bar_dofull, 1); mbar_init(bar_doempty, 1);
     *abort_flag = 0;
     fence_barrier_init();
     fence_proxy_async();
@@ -153,42 +186,98 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     // ------------------------------------------------------------ producer --
     if (lane == 0) {
       prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV); prefetch_tmap(&tmDO);
-      int g = 0;
-      bool ok = true;
-      for (int round = 0, tn = 0; round * (int)gridDim.x < n_tiles && ok; ++round) {
-        const int tile = tile_of_round(round, n_tiles);
-        if (tile < 0) continue;
-        const int tn_now = tn++;
-        const int jb = tile / bh_count, bkv = tile % bh_count;
-        const int b = bkv / P.Hkv, h = bkv % P.Hkv;          // h: key/value head
-        const int q_start = P.causal ? jb : 0;
-        const int n_qb = P.nqb - q_start;
-        const int n_q = n_qb * P.group;
+      // One step of this CTA's work: a query block of a tile. Steps are numbered g = 0, 1, ... across
+      // tiles; `tn` counts the tiles.
+      struct Step { int round, tn, i, n_q, n_qb, q_start, jb, b, h; bool valid; };
+      auto enter_round = [&](Step& st) {      // finds the tile of st.round (or a later one); i = 0
+        st.valid = false;
+        for (; st.round * (int)gridDim.x < n_tiles; ++st.round) {
+          const int tile = tile_of_round(st.round, n_tiles);
+          if (tile < 0) continue;
+          int bkv;
+          decode_tile(tile, P.nqb, bh_count, P.gh, st.jb, bkv);
+          st.b = bkv / P.Hkv; st.h = bkv % P.Hkv;            // h: key/value head
+          st.q_start = P.causal ? st.jb : 0;
+          st.n_qb = P.nqb - st.q_start;
+          st.n_q = st.n_qb * P.group;
+          st.i = 0;
+          st.valid = true;
+          return;
+        }
+      };
+      auto advance = [&](Step& st) {
+        if (++st.i < st.n_q) return;
+        ++st.round; ++st.tn;
+        enter_round(st);
+      };
+      auto load_kv = [&](const Step& st) -> bool {
         // K and V of the previous tile are read until its last dQ MMA has completed
-        if (tn_now > 0 && !mbar_wait(bar_kvfree, (tn_now - 1) & 1, abort_flag)) break;
+        if (st.tn > 0 && !mbar_wait(bar_kvfree, (st.tn - 1) & 1, abort_flag)) return false;
         mbar_expect_tx(bar_kv, 2 * Cfg::kTile);
 #pragma unroll
         for (int dc = 0; dc < Cfg::kChunks; ++dc) {
-          load_rows(base + Cfg::kOffK + dc * 16384, &tmK, bar_kv, P.pk, dc * 64, jb * 128, h, b);
-          load_rows(base + Cfg::kOffV + dc * 16384, &tmV, bar_kv, P.pv, dc * 64, jb * 128, h, b);
+          load_rows(base + Cfg::kOffK + dc * 16384, &tmK, bar_kv, P.pk, dc * 64, st.jb * 128, st.h, st.b);
+          load_rows(base + Cfg::kOffV + dc * 16384, &tmV, bar_kv, P.pv, dc * 64, st.jb * 128, st.h, st.b);
         }
-        for (int i = 0; i < n_q; ++i, ++g) {
-          const int s = g % ST;
-          if (!mbar_wait(bar_qempty0 + 8 * s, ((g / ST) & 1) ^ 1u, abort_flag)) { ok = false; break; }
-          mbar_expect_tx(bar_qfull0 + 8 * s, 2 * Cfg::kTile + 1024);
-          const uint32_t sq = base + Cfg::kOffQ + s * 2 * Cfg::kTile, sdo = sq + Cfg::kTile;
-          const int hq = h * P.group + i / n_qb, qi = q_start + i % n_qb;   // query head and block of this step
-          {   // the block's row statistics travel with it
-            const int64_t spad = (int64_t)P.nqb * 128;
-            const float* src = P.stats + ((int64_t)b * P.H + hq) * spad + (int64_t)qi * 128;
-            bulk_load_1d(base + Cfg::kOffStat + s * 1024, src, 512, bar_qfull0 + 8 * s);
-            bulk_load_1d(base + Cfg::kOffStat + s * 1024 + 512, src + (int64_t)P.B * P.H * spad, 512, bar_qfull0 + 8 * s);
-          }
+        return true;
+      };
+      // Q of step g (and, at head_dim 64, its dO) with the block's row statistics
+      auto load_q = [&](const Step& st, int g) -> bool {
+        const int s = g % ST;
+        if (!mbar_wait(bar_qempty0 + 8 * s, ((g / ST) & 1) ^ 1u, abort_flag)) return false;
+        mbar_expect_tx(bar_qfull0 + 8 * s, (Cfg::kSplit ? 1 : 2) * Cfg::kTile + 1024);
+        const int hq = st.h * P.group + st.i / st.n_qb, qi = st.q_start + st.i % st.n_qb;   // query head and block of this step
+        const int64_t spad = (int64_t)P.nqb * 128;
+        const float* src = P.stats + ((int64_t)st.b * P.H + hq) * spad + (int64_t)qi * 128;
+        bulk_load_1d(base + Cfg::kOffStat + s * 1024, src, 512, bar_qfull0 + 8 * s);
+        bulk_load_1d(base + Cfg::kOffStat + s * 1024 + 512, src + (int64_t)P.B * P.H * spad, 512, bar_qfull0 + 8 * s);
 #pragma unroll
-          for (int dc = 0; dc < Cfg::kChunks; ++dc) {
-            load_rows(sq + dc * 16384, &tmQ, bar_qfull0 + 8 * s, P.pq, dc * 64, qi * 128, hq, b);
-            load_rows(sdo + dc * 16384, &tmDO, bar_qfull0 + 8 * s, P.pdo, dc * 64, qi * 128, hq, b);
+        for (int dc = 0; dc < Cfg::kChunks; ++dc) {
+          load_rows(base + Cfg::kOffQ + s * Cfg::kTile + dc * 16384, &tmQ, bar_qfull0 + 8 * s, P.pq, dc * 64, qi * 128, hq, st.b);
+          if (!Cfg::kSplit)
+            load_rows(base + Cfg::kOffDO + s * Cfg::kTile + dc * 16384, &tmDO, bar_qfull0 + 8 * s, P.pdo, dc * 64, qi * 128, hq, st.b);
+        }
+        return true;
+      };
+      Step cur;
+      cur.round = 0; cur.tn = 0;
+      enter_round(cur);
+      if (!Cfg::kSplit) {
+        for (int g = 0; cur.valid; ++g, advance(cur)) {
+          if (cur.i == 0 && !load_kv(cur)) break;
+          if (!load_q(cur, g)) break;
+        }
+      } else {
+        // One buffer each for Q and dO: while step g is worked on, step g+1's Q and dO are brought
+        // into L2; its dO is loaded as soon as the dV MMA of step g has completed, its Q after the
+        // dK MMA (issued in that order) and, where step g+1 opens a tile, that tile's K and V follow.
+        auto load_do = [&](const Step& st) {
+          mbar_expect_tx(bar_dofull, Cfg::kTile);
+          const int hq = st.h * P.group + st.i / st.n_qb, qi = st.q_start + st.i % st.n_qb;
+#pragma unroll
+          for (int dc = 0; dc < Cfg::kChunks; ++dc)
+            load_rows(base + Cfg::kOffDO + dc * 16384, &tmDO, bar_dofull, P.pdo, dc * 64, qi * 128, hq, st.b);
+        };
+        bool ok = cur.valid;
+        if (ok) ok = load_kv(cur);
+        if (ok) ok = load_q(cur, 0);
+        if (ok) load_do(cur);
+        Step nxt = cur;
+        if (ok) advance(nxt);
+        for (int g = 0; ok && nxt.valid; ++g) {
+          {
+            const int hq = nxt.h * P.group + nxt.i / nxt.n_qb, qi = nxt.q_start + nxt.i % nxt.n_qb;
+#pragma unroll
+            for (int dc = 0; dc < Cfg::kChunks; ++dc) {
+              prefetch_rows(&tmDO, P.pdo, dc * 64, qi * 128, hq, nxt.b);
+              prefetch_rows(&tmQ, P.pq, dc * 64, qi * 128, hq, nxt.b);
+            }
           }
+          if (!mbar_wait(bar_doempty, g & 1, abort_flag)) break;      // dV of step g has read dO
+          load_do(nxt);
+          if (!load_q(nxt, g + 1)) break;                              // waits for dK of step g
+          if (nxt.i == 0 && !load_kv(nxt)) break;
+          advance(nxt);
         }
       }
     }
@@ -199,13 +288,13 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       const uint32_t idesc_kn = idesc_f16(P.is_bf16, 0, 1, 128, D);     // dV, dK: A K-major, B N-major
       const uint32_t idesc_mn = idesc_f16(P.is_bf16, 1, 1, 128, D);     // dQ: A M-major, B N-major
       const uint32_t sk = base + Cfg::kOffK, sv = base + Cfg::kOffV;
-      const uint32_t spt = base + Cfg::kOffPT, sdst = base + Cfg::kOffDST;
+      const uint32_t sdst = base + Cfg::kOffDST;
       // Descriptors that do not depend on the Q/dO stage are built once; the stage's own are built
       // at the top of each step, BEFORE the barrier wait, so that after a wait this thread issues
       // MMAs and nothing else (it shares a scheduler with busy warps and every extra instruction
       // between wait and MMA costs 10-20 cycles of tensor-pipe idle time).
       constexpr int NS = 4 * Cfg::kChunks;              // MMAs of one S^T or dP^T
-      uint64_t a_s[NS], a_dp[NS], a_dk[8], a_dq[8], b_dq[8], a_dv[8];
+      uint64_t a_s[NS], a_dp[NS], a_dk[8], a_dq[8], b_dq[8];
 #pragma unroll
       for (int dc = 0; dc < Cfg::kChunks; ++dc)
 #pragma unroll
@@ -218,27 +307,39 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         a_dk[ks] = smem_desc_sw128(sdst + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024);   // dS^T, K-major
         a_dq[ks] = smem_desc_sw128(sdst + ks * 2048, 16384, 1024);                          // dS^T, M-major
         b_dq[ks] = smem_desc_sw128(sk + ks * 2048, 16384, 1024);
-        a_dv[ks] = smem_desc_sw128(spt + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024);    // P^T in shared memory (head_dim 128)
       }
       auto issue_n = [&](uint32_t d, const uint64_t* a, const uint64_t* b, uint32_t idesc, uint32_t acc) {
         if (NS == 4) umma_f16_x4(d, a, b, idesc, acc);
         else umma_f16_x8(d, a, b, idesc, acc);
       };
-      // S^T = K Q^T and dP^T = V dO^T of query block g (running count) into tensor memory
-      auto issue_sdp = [&](int g) -> bool {
+      // S^T = K Q^T of query block g (running count) into tensor memory
+      auto issue_s = [&](int g) -> bool {
         const int s = g % ST;
-        const uint32_t sq = base + Cfg::kOffQ + s * 2 * Cfg::kTile, sdo = sq + Cfg::kTile;
-        uint64_t b_s[NS], b_dp[NS];
+        const uint32_t sq = base + Cfg::kOffQ + s * Cfg::kTile;
+        uint64_t b_s[NS];
 #pragma unroll
         for (int dc = 0; dc < Cfg::kChunks; ++dc)
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            b_s[dc * 4 + k] = smem_desc_sw128(sq + dc * 16384 + k * 32, 16, 1024);
-            b_dp[dc * 4 + k] = smem_desc_sw128(sdo + dc * 16384 + k * 32, 16, 1024);
-          }
+          for (int k = 0; k < 4; ++k) b_s[dc * 4 + k] = smem_desc_sw128(sq + dc * 16384 + k * 32, 16, 1024);
         if (!mbar_wait(bar_qfull0 + 8 * s, (g / ST) & 1, abort_flag)) return false;
         tc_fence_after();
         issue_n(tmem_base + Cfg::kColST, a_s, b_s, idesc_kk, 0u);
+        return true;
+      };
+      // dP^T = V dO^T of query block g; completes bar_sdp together with the S^T issued before it
+      auto issue_dp = [&](int g) -> bool {
+        const uint32_t sdo = base + Cfg::kOffDO + (g % Cfg::kDOStages) * Cfg::kTile;
+        uint64_t b_dp[NS];
+#pragma unroll
+        for (int dc = 0; dc < Cfg::kChunks; ++dc)
+#pragma unroll
+          for (int k = 0; k < 4; ++k) b_dp[dc * 4 + k] = smem_desc_sw128(sdo + dc * 16384 + k * 32, 16, 1024);
+        if (Cfg::kSplit) {
+          if (!mbar_wait(bar_dofull, g & 1, abort_flag)) return false;
+          // dQ of the previous block sits in these columns until the elementwise warps have read it
+          if (g > 0 && !mbar_wait(bar_dqfree, (g - 1) & 1, abort_flag)) return false;
+          tc_fence_after();
+        }
         issue_n(tmem_base + Cfg::kColDPT, a_dp, b_dp, idesc_kk, 0u);
         umma_commit(bar_sdp);
         return true;
@@ -249,7 +350,8 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         const int tile = tile_of_round(round, n_tiles);
         if (tile < 0) continue;
         const int tn = tcount++;
-        const int jb = tile / bh_count;
+        int jb, bkv_unused;
+        decode_tile(tile, P.nqb, bh_count, P.gh, jb, bkv_unused);
         const int n_q = (P.nqb - (P.causal ? jb : 0)) * P.group;
         if (!mbar_wait(bar_kv, tn & 1, abort_flag)) break;
         tc_fence_after();
@@ -258,24 +360,21 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           // previous tile) to registers
           if (g0 > 0 && !mbar_wait(bar_sdpfree, (g0 - 1) & 1, abort_flag)) break;
           tc_fence_after();
-          if (!issue_sdp(g0)) break;
         }
+        // (head_dim 128: every MMA of the previous tile has completed - K and V were only replaced
+        // after that - so P^T in the S^T columns is dead; issue_dp waits for the last dQ's read-out)
+        if (!issue_s(g0) || !issue_dp(g0)) break;
         for (int i = 0; i < n_q; ++i) {
           const int g = g0 + i;
           const int s = g % ST;
-          const uint32_t sq = base + Cfg::kOffQ + s * 2 * Cfg::kTile, sdo = sq + Cfg::kTile;
-          if (Cfg::kAliasDQ) {
-            // dQ shares the S^T columns: the previous dQ must have been read out first
-            if (g > 0 && !mbar_wait(bar_dqfree, (g - 1) & 1, abort_flag)) { ok = false; break; }
-            tc_fence_after();
-            if (!issue_sdp(g)) { ok = false; break; }
-          }
+          const uint32_t sq = base + Cfg::kOffQ + s * Cfg::kTile;
+          const uint32_t sdo = base + Cfg::kOffDO + (g % Cfg::kDOStages) * Cfg::kTile;
           if (!Cfg::kAliasDQ && i + 1 < n_q) {
             // The elementwise warps hold S^T / dP^T of block g in registers: the next block's are
             // computed while they work, ahead of everything else of this block.
             if (!mbar_wait(bar_sdpfree, g & 1, abort_flag)) { ok = false; break; }
             tc_fence_after();
-            if (!issue_sdp(g + 1)) { ok = false; break; }
+            if (!issue_s(g + 1) || !issue_dp(g + 1)) { ok = false; break; }
           }
           uint64_t b_dv[8], b_dk[8];
 #pragma unroll
@@ -291,17 +390,32 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             if (!mbar_wait(bar_dkvfree, (tn - 1) & 1, abort_flag)) { ok = false; break; }
             tc_fence_after();
           }
-          // dV += P^T dO (reduction over the 128 queries), dK += dS^T Q
-          if (Cfg::kPTinTmem) umma_f16_ts_x8(tmem_base + Cfg::kColDV, tmem_base + Cfg::kColPT, b_dv, idesc_kn, i > 0 ? 1u : 0u);
-          else umma_f16_x8(tmem_base + Cfg::kColDV, a_dv, b_dv, idesc_kn, i > 0 ? 1u : 0u);
-          umma_f16_x8(tmem_base + Cfg::kColDK, a_dk, b_dk, idesc_kn, i > 0 ? 1u : 0u);
-          umma_commit(bar_qempty0 + 8 * s);   // Q and dO of this block are not read again (dQ needs neither)
+          // dV += P^T dO (reduction over the 128 queries, A = P^T from tensor memory), dK += dS^T Q,
+          // dQ = dS K (reduction over the 128 keys)
           if (!Cfg::kAliasDQ) {
+            umma_f16_ts_x8(tmem_base + Cfg::kColDV, tmem_base + Cfg::kColPT, b_dv, idesc_kn, i > 0 ? 1u : 0u);
+            umma_f16_x8(tmem_base + Cfg::kColDK, a_dk, b_dk, idesc_kn, i > 0 ? 1u : 0u);
+            umma_commit(bar_qempty0 + 8 * s);   // Q and dO of this block are not read again (dQ needs neither)
             if (g > 0 && !mbar_wait(bar_dqfree, (g - 1) & 1, abort_flag)) { ok = false; break; }   // dQ columns read out
             tc_fence_after();
+            umma_f16_x8(tmem_base + Cfg::kColDQ, a_dq, b_dq, idesc_mn, 0u);
+            umma_commit(bar_dq);
+          } else {
+            // dV and dK first: they free the dO and Q buffers, and the loads of the next block must
+            // enter the TMA queue before the 64 KB of dQ reduce-adds that follow the dQ MMA - a load
+            // queued behind those waits a couple of thousand cycles.
+            umma_f16_ts_x8(tmem_base + Cfg::kColDV, tmem_base + Cfg::kColPT, b_dv, idesc_kn, i > 0 ? 1u : 0u);
+            umma_commit(bar_doempty);           // dO of this block is not read again
+            umma_f16_x8(tmem_base + Cfg::kColDK, a_dk, b_dk, idesc_kn, i > 0 ? 1u : 0u);
+            umma_commit(bar_qempty0 + 8 * s);   // Q of this block is not read again
+            umma_f16_x8(tmem_base + Cfg::kColDQ, a_dq, b_dq, idesc_mn, 0u);
+            umma_commit(bar_dq);
           }
-          umma_f16_x8(tmem_base + Cfg::kColDQ, a_dq, b_dq, idesc_mn, 0u);   // dQ = dS K, reduction over the 128 keys
-          umma_commit(bar_dq);
+          if (Cfg::kAliasDQ && i + 1 < n_q) {
+            // The next block's S^T goes over P^T, which the dV MMA above (earlier in the pipe) was the
+            // last to read; its dP^T goes over dQ and waits for the read-out inside issue_dp.
+            if (!issue_s(g + 1) || !issue_dp(g + 1)) { ok = false; break; }
+          }
         }
         umma_commit(bar_kvfree);            // completes with the tile's last dQ: K and V may be replaced
         g0 += n_q;
@@ -312,41 +426,58 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const int t = (warp & 3) * 32 + lane;             // key row within the block = TMEM lane
     const int hh = warp >> 2;                         // which CPT of the block's 128 query columns this warp handles
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
-    uint8_t* pt_row = base_ptr + Cfg::kOffPT + t * 128;
     uint8_t* dst_row = base_ptr + Cfg::kOffDST + t * 128;
     bool ok = true;
     // adds the finished dQ block (TMEM) into the fp32 accumulator [B*H, S, D]: each warp stages its
     // 32 rows x 32 columns in swizzled shared memory and one lane issues a TMA reduce-add (rows past
     // the sequence end are clipped by the tensor map)
-    uint8_t* dq_stage = base_ptr + Cfg::kOffStage + warp * 4096;
-    constexpr int kDqChunks = D / 32;                                           // 32-column pieces of dQ
-    constexpr int kDqPer = kDqChunks >= kBwdEwWarps / 4 ? kDqChunks / (kBwdEwWarps / 4) : 1;   // pieces per column group
-    auto flush_dq = [&](int qi, int bh) {        // bh: (batch, query head) index of the block
-#pragma unroll 1
-      for (int c = hh * kDqPer; c < (hh + 1) * kDqPer && c < kDqChunks; ++c) {   // this warp's share of the dQ columns
-        uint32_t r[32];
-        tmem_ld32(tmem_base + Cfg::kColDQ + lane_addr + c * 32, r);
-        tmem_ld_wait();
-        if (lane == 0) bulk_wait_read<0>();     // the previous reduce has finished reading the buffer
-        __syncwarp();
+    // This warp's staging buffer (only warps that flush or drain have one)
+    uint8_t* stage_buf = base_ptr + Cfg::kOffStage + (warp % Cfg::kFlushWarps) * Cfg::kStageBytes;
+    constexpr int kPieces = 32 / Cfg::kStageRows;     // a warp's 32 rows leave in this many TMA operations
+    constexpr int kDqChunks = D / 32;                 // 32-column pieces of dQ: column group hh flushes piece hh
+    // Writes 128 bytes per row (`w`: this lane's row as 32 words) of rows
+    // [piece * kStageRows, (piece + 1) * kStageRows) into the staging buffer, swizzled.
+    auto stage_rows = [&](int piece, const uint32_t (&w)[32]) -> uint32_t {
+      uint8_t* buf = stage_buf;
+      if (lane == 0) bulk_wait_read<0>();             // the previous operation has finished reading the buffer
+      __syncwarp();
+      if (lane / Cfg::kStageRows == piece) {
+        const int rr = lane % Cfg::kStageRows;
 #pragma unroll
         for (int c16 = 0; c16 < 8; ++c16)
-          *reinterpret_cast<uint4*>(dq_stage + lane * 128 + ((c16 ^ (lane & 7)) << 4)) =
-              make_uint4(r[c16 * 4], r[c16 * 4 + 1], r[c16 * 4 + 2], r[c16 * 4 + 3]);
-        fence_proxy_async();
-        __syncwarp();
-        if (lane == 0) {
-          tma_reduce_add_3d(&tmDQ, smem_u32(dq_stage), c * 32, qi * 128 + (warp & 3) * 32, bh);
-          bulk_commit();
+          *reinterpret_cast<uint4*>(buf + rr * 128 + ((c16 ^ (rr & 7)) << 4)) =
+              make_uint4(w[c16 * 4], w[c16 * 4 + 1], w[c16 * 4 + 2], w[c16 * 4 + 3]);
+      }
+      fence_proxy_async();
+      __syncwarp();
+      return smem_u32(buf);
+    };
+    auto flush_dq = [&](int qi, int bh) {             // bh: (batch, query head) index of the block
+      if (hh < kDqChunks) {
+        uint32_t r[32];
+        tmem_ld32(tmem_base + Cfg::kColDQ + lane_addr + hh * 32, r);
+        tmem_ld_wait();
+        tc_fence_before();
+        mbar_arrive(bar_dqfree);                      // the dQ columns may be overwritten: the rest works from registers
+#pragma unroll
+        for (int piece = 0; piece < kPieces; ++piece) {
+          const uint32_t src = stage_rows(piece, r);
+          if (lane == 0) {
+            tma_reduce_add_3d(&tmDQ, src, hh * 32, qi * 128 + (warp & 3) * 32 + piece * Cfg::kStageRows, bh);
+            bulk_commit();
+          }
         }
+      } else {
+        mbar_arrive(bar_dqfree);
       }
     };
     int g0 = 0;                                       // running count of query blocks at the start of the tile
-    for (int round = 0; round * (int)gridDim.x < n_tiles && ok; ++round) {
+    for (int round = 0, tcount_ew = 0; round * (int)gridDim.x < n_tiles && ok; ++round) {
       const int tile = tile_of_round(round, n_tiles);
       if (tile < 0) continue;
-      const int jb = tile / bh_count;
-      const int bkv = tile % bh_count;
+      const int tn_ew = tcount_ew++;
+      int jb, bkv;
+      decode_tile(tile, P.nqb, bh_count, P.gh, jb, bkv);
       const int b = bkv / P.Hkv, h = bkv % P.Hkv;     // h: key/value head
       const int q_start = P.causal ? jb : 0;
       const int n_qb = P.nqb - q_start;
@@ -385,9 +516,14 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             for (int e = 0; e < CPT; ++e)
               if (dead || (diag && hh * CPT + e < t)) s_[e] = 0xff800000u;
           }
-          if (!Cfg::kOwnStage) {   // staging aliases this warp's slice of P^T: let the last reduce / store finish reading it
-            if (lane == 0) bulk_wait_read<0>();
+          if (Cfg::kAliasDQ) {
+            // P^T goes over the first S^T columns: every warp of this lane quarter must hold its
+            // scores in registers first
+            tc_fence_before();
             __syncwarp();
+            if (lane == 0) mbar_arrive(bar_quarter0 + 8 * (warp & 3));
+            if (!__all_sync(0xffffffffu, mbar_wait(bar_quarter0 + 8 * (warp & 3), g & 1, abort_flag))) { ok = false; break; }
+            tc_fence_after();
           }
           if (!Cfg::kAliasDQ && i > 0) {
             // dS^T of the previous block is still an operand of its dQ MMA, which was issued after
@@ -396,7 +532,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             // last dQ flush)
             if (!__all_sync(0xffffffffu, mbar_wait(bar_dq, (g - 1) & 1, abort_flag))) { ok = false; break; }
           }
-          uint32_t ptp[Cfg::kPTinTmem ? CPT / 2 : 1];   // P^T of this thread as packed half pairs
+          uint32_t ptp[CPT / 2];                        // P^T of this thread as packed half pairs
           const float4* lse4 = reinterpret_cast<const float4*>(lse2 + hh * CPT);   // per query column, 16-byte loads
           const float4* dlt4 = reinterpret_cast<const float4*>(dlt + hh * CPT);
 #pragma unroll
@@ -421,17 +557,13 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             // byte offset of these 8 columns in the 128-row tile: 64-column chunk, then the swizzled 16-byte piece
             const int col8 = hh * (CPT / 8) + c16;
             const int off = (col8 >> 3) * 16384 + (((col8 & 7) ^ (t & 7)) << 4);
-            if (Cfg::kPTinTmem) {
 #pragma unroll
-              for (int e = 0; e < 4; ++e) ptp[c16 * 4 + e] = pp[e];
-            } else {
-              *reinterpret_cast<uint4*>(pt_row + off) = make_uint4(pp[0], pp[1], pp[2], pp[3]);
-            }
+            for (int e = 0; e < 4; ++e) ptp[c16 * 4 + e] = pp[e];
             *reinterpret_cast<uint4*>(dst_row + off) = make_uint4(dd[0], dd[1], dd[2], dd[3]);
-            if (Cfg::kPTinTmem && (c16 & 3) == 3)   // 32 finished columns = 16 packed words -> tensor memory
+            if ((c16 & 3) == 3)   // 32 finished columns = 16 packed words -> tensor memory
               tmem_st16(tmem_base + Cfg::kColPT + lane_addr + hh * (CPT / 2) + (c16 >> 2) * 16, ptp + (c16 >> 2) * 16);
           }
-          if (Cfg::kPTinTmem) tmem_st_wait();
+          tmem_st_wait();
         }
         fence_proxy_async();
         tc_fence_before();
@@ -443,8 +575,6 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           if (!__all_sync(0xffffffffu, mbar_wait(bar_dq, (g0 + fi) & 1, abort_flag))) { ok = false; break; }
           tc_fence_after();
           flush_dq(qi_of(fi), bh_of(fi));
-          tc_fence_before();
-          mbar_arrive(bar_dqfree);
         }
       }
       if (!ok) break;
@@ -453,45 +583,38 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         if (!__all_sync(0xffffffffu, mbar_wait(bar_dq, (g0 + n_q - 1) & 1, abort_flag))) { ok = false; break; }
         tc_fence_after();
         flush_dq(qi_of(n_q - 1), bh_of(n_q - 1));
-        tc_fence_before();
-        mbar_arrive(bar_dqfree);
       }
       // All MMAs of the tile are complete (its last bar_dq was waited above, in either variant).
-      // The warps of column group 0 write dK, those of group 1 dV: 32 key rows x 64 columns at a
-      // time are staged (128-byte rows, swizzled) in the warp's buffer and stored by TMA, which
-      // clips rows past the sequence end. Once the accumulators are in registers the MMA warp may
-      // start the next tile's dV / dK.
-      if (hh < 2) {
-        const CUtensorMap* map = hh ? &tmDV : &tmDK;
-        const MapPos pos = hh ? P.pdv : P.pdk;
-        const int col0 = hh ? Cfg::kColDV : Cfg::kColDK;
-        uint8_t* stage = base_ptr + Cfg::kOffStage + warp * 4096;
-#pragma unroll 1
-        for (int dc = 0; dc < Cfg::kChunks; ++dc) {
-          uint32_t r[64];
-          tmem_ld32(tmem_base + col0 + lane_addr + dc * 64, r);
-          tmem_ld32(tmem_base + col0 + lane_addr + dc * 64 + 32, r + 32);
-          tmem_ld_wait();
-          if (dc == Cfg::kChunks - 1) {
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_dkvfree);
-          }
-          if (lane == 0) bulk_wait_read<0>();     // earlier reduce / store out of this buffer has been read
-          __syncwarp();
+      // Each 64-column piece of dK and of dV is drained by one column group: 32 key rows at a time
+      // are staged (128-byte rows, swizzled) in the warp's buffer and stored by TMA, which clips
+      // rows past the sequence end. Once the accumulators are in registers the MMA warp may start
+      // the next tile's dV / dK.
+      if (Cfg::kAliasDQ) {
+        // here the dQ MMA is not the block's last: wait for the commit that follows the tile's last MMA
+        if (!__all_sync(0xffffffffu, mbar_wait(bar_kvfree, tn_ew & 1, abort_flag))) { ok = false; break; }
+        tc_fence_after();
+      }
+      if ((hh >> 1) < Cfg::kChunks) {
+        // column group hh drains the 64-column piece hh >> 1 of dK (even hh) or dV (odd hh)
+        const CUtensorMap* map = (hh & 1) ? &tmDV : &tmDK;
+        const MapPos pos = (hh & 1) ? P.pdv : P.pdk;
+        const int col0 = (hh & 1) ? Cfg::kColDV : Cfg::kColDK;
+        const int dc = hh >> 1;
+        uint32_t r[64];
+        tmem_ld32(tmem_base + col0 + lane_addr + dc * 64, r);
+        tmem_ld32(tmem_base + col0 + lane_addr + dc * 64 + 32, r + 32);
+        tmem_ld_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_dkvfree);
+        uint32_t w[32];
 #pragma unroll
-          for (int c16 = 0; c16 < 8; ++c16) {
-            uint4 v;
-            v.x = pack2<T>(__uint_as_float(r[c16 * 8 + 0]), __uint_as_float(r[c16 * 8 + 1]));
-            v.y = pack2<T>(__uint_as_float(r[c16 * 8 + 2]), __uint_as_float(r[c16 * 8 + 3]));
-            v.z = pack2<T>(__uint_as_float(r[c16 * 8 + 4]), __uint_as_float(r[c16 * 8 + 5]));
-            v.w = pack2<T>(__uint_as_float(r[c16 * 8 + 6]), __uint_as_float(r[c16 * 8 + 7]));
-            *reinterpret_cast<uint4*>(stage + lane * 128 + ((c16 ^ (lane & 7)) << 4)) = v;
-          }
-          fence_proxy_async();
-          __syncwarp();
+        for (int e = 0; e < 32; ++e) w[e] = pack2<T>(__uint_as_float(r[2 * e]), __uint_as_float(r[2 * e + 1]));
+#pragma unroll
+        for (int piece = 0; piece < kPieces; ++piece) {
+          const uint32_t src = stage_rows(piece, w);
           if (lane == 0) {
-            store_rows(map, smem_u32(stage), pos, dc * 64, jb * 128 + (warp & 3) * 32, h, b);
+            store_rows(map, src, pos, dc * 64, jb * 128 + (warp & 3) * 32 + piece * Cfg::kStageRows, h, b);
             bulk_commit();
           }
         }
@@ -577,6 +700,36 @@ bool attn_bwd_tc_supported(const AttnArgs& a) {
   return true;
 }
 
+// Heaviest CTA's share of query blocks over the ideal share (all of the work / SMs) when causal tiles
+// in the order of decode_tile (heads in groups of gh) are dealt to `grid` CTAs round by round,
+// forwards in even rounds and backwards in odd ones.
+static double dealing_imbalance(int bh_count, int nqb, int gh, int grid, int sms) {
+  // the same few shapes come back every step: remember the answers
+  static std::mutex mu;
+  static std::map<std::array<int, 5>, double> memo;
+  const std::array<int, 5> key = {bh_count, nqb, gh, grid, sms};
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = memo.find(key);
+    if (it != memo.end()) return it->second;
+  }
+  std::vector<int64_t> load((size_t)grid, 0);
+  const int64_t n_tiles = (int64_t)bh_count * nqb;
+  for (int64_t t = 0; t < n_tiles; ++t) {
+    const int64_t per = (int64_t)gh * nqb, gi = t / per, r = t - gi * per;
+    const int64_t gh_cur = std::min<int64_t>(gh, bh_count - gi * gh);
+    const int jb = (int)(r / gh_cur);
+    const int64_t round = t / grid, idx = t - round * grid;
+    load[(size_t)((round & 1) ? grid - 1 - idx : idx)] += nqb - jb;
+  }
+  int64_t mx = 0, sum = 0;
+  for (int64_t v : load) { mx = std::max(mx, v); sum += v; }
+  const double res = sum ? (double)mx * sms / (double)sum : 1.0;
+  std::lock_guard<std::mutex> lock(mu);
+  if (memo.size() < 256) memo[key] = res;
+  return res;
+}
+
 template <int D, typename T>
 static int launch_bwd(const AttnArgs& a, cudaStream_t st) {
   using Cfg = BwdCfg<D>;
@@ -598,13 +751,13 @@ static int launch_bwd(const AttnArgs& a, cudaStream_t st) {
   if ((rc = make_qkv_map(&tv, &P.pv, a.v, bf, a.sv, a.batch, a.kv_heads, a.seq, D))) return rc;
   if ((rc = make_qkv_map(&tdo, &P.pdo, a.d_o, bf, a.sdo, a.batch, a.heads, a.seq, D))) return rc;
   CUtensorMap tdk, tdv;
-  if ((rc = make_qkv_map(&tdk, &P.pdk, a.dk, bf, a.sdk, a.batch, a.kv_heads, a.seq, D, 32))) return rc;
-  if ((rc = make_qkv_map(&tdv, &P.pdv, a.dv, bf, a.sdv, a.batch, a.kv_heads, a.seq, D, 32))) return rc;
+  if ((rc = make_qkv_map(&tdk, &P.pdk, a.dk, bf, a.sdk, a.batch, a.kv_heads, a.seq, D, Cfg::kStageRows))) return rc;
+  if ((rc = make_qkv_map(&tdv, &P.pdv, a.dv, bf, a.sdv, a.batch, a.kv_heads, a.seq, D, Cfg::kStageRows))) return rc;
   CUtensorMap tdq;
   {
     uint64_t dims[3] = {(uint64_t)D, (uint64_t)a.seq, (uint64_t)(a.batch * a.heads)};
     uint64_t str[2] = {(uint64_t)D, (uint64_t)(a.seq * D)};
-    uint32_t box[3] = {32, 32, 1};
+    uint32_t box[3] = {32, (uint32_t)Cfg::kStageRows, 1};
     if ((rc = make_tmap_nd_typed(&tdq, a.dq_accum, MT_F32, 3, dims, str, box))) return rc;
   }
   P.stats = (const float*)stats.ptr; P.dq_accum = a.dq_accum; P.dk = a.dk; P.dv = a.dv;
@@ -614,7 +767,28 @@ static int launch_bwd(const AttnArgs& a, cudaStream_t st) {
   auto kern = attn_bwd_tc_kernel<D, T>;
   MT_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
   const int64_t n_tiles = (int64_t)P.nqb * P.B * P.Hkv;
-  const unsigned grid = (unsigned)(n_tiles < sm_count() ? n_tiles : sm_count());   // persistent: one CTA per SM
+  // Persistent, one CTA per SM. Tile order: with every head in one group the CTAs that run at the
+  // same time each stream a different head's Q, dO and dQ, which together no longer fit in L2 once
+  // there are many long heads. Then heads are taken in groups of about 2 * SMs / blocks-per-head -
+  // a group is two rounds of the grid, and its footprint in L2 stays near 30 MB (head_dim 64) or
+  // 60 MB (128) whatever the sequence length - provided the fixed dealing of tiles to CTAs stays
+  // balanced (the last group is smaller, which can leave CTAs idle at the end).
+  int grid_i = (int)(n_tiles < sm_count() ? n_tiles : sm_count());
+  P.gh = (int)(P.B * P.Hkv);
+  const double footprint = (double)a.batch * a.heads * a.seq * D * 12.0;   // Q, dO, K, V (2 bytes each) + fp32 dQ
+  if (a.causal && P.nqb > 1 && n_tiles > 2 * (int64_t)sm_count() && footprint > 96e6) {
+    const int gh = 2 * sm_count() / P.nqb > 1 ? 2 * sm_count() / P.nqb : 1;
+    if (gh < P.B * P.Hkv) {
+      int grid_g = grid_i;
+      if ((gh * P.nqb) % 2 == 0 && gh * P.nqb / 2 >= sm_count() * 7 / 8) grid_g = gh * P.nqb / 2;   // rounds line up with groups
+      if (dealing_imbalance(P.B * P.Hkv, P.nqb, gh, grid_g, sm_count()) <=
+          dealing_imbalance(P.B * P.Hkv, P.nqb, P.gh, grid_i, sm_count()) + 0.03) {
+        P.gh = gh;
+        grid_i = grid_g;
+      }
+    }
+  }
+  const unsigned grid = (unsigned)grid_i;
   kern<<<grid, Cfg::kThreads, Cfg::kSmem, st>>>(tq, tk, tv, tdo, tdq, tdk, tdv, P);
   MT_LAUNCH_CHECK();
   const int64_t n_vec = n_acc / 8;

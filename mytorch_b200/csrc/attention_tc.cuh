@@ -13,11 +13,32 @@ constexpr float kLn2F = 0.6931471805599453f;
 // the outer dimensions are ordered by ascending stride when the map is built.
 struct MapPos { int s, h, b; };
 
+// Tile order shared by the forward and backward kernels. Tiles are (block index along the
+// sequence, (batch, head) pair). Heads are taken in groups of `gh`: within a group the order is
+// block-major (all heads' heaviest block first), and a group is finished before the next begins.
+// The CTAs that run at the same time therefore work on a few heads only, whose K/V (forward) or
+// Q/dO/dQ (backward) stay in L2 while every block of the head is visited; with all heads in one
+// group the concurrent CTAs would each stream a different head and the re-reads would come from
+// DRAM. `slot` runs over the blocks in the order they should be taken (0 first).
+__device__ __forceinline__ void decode_tile(int tile, int n_blocks, int bh_count, int gh, int& slot, int& bh) {
+  const int per_group = gh * n_blocks;
+  const int gi = tile / per_group, r = tile - gi * per_group;
+  const int gh_cur = min(gh, bh_count - gi * gh);      // the last group may be smaller
+  slot = r / gh_cur;
+  bh = gi * gh + (r - slot * gh_cur);
+}
+
 __device__ __forceinline__ void load_rows(uint32_t dst, const CUtensorMap* map, uint32_t bar, MapPos pos, int d0, int row0,
                                           int h, int b) {
   int c[4];
   c[0] = d0; c[pos.s] = row0; c[pos.h] = h; c[pos.b] = b;
   sm100::tma_load_4d(dst, map, bar, c[0], c[1], c[2], c[3]);
+}
+
+__device__ __forceinline__ void prefetch_rows(const CUtensorMap* map, MapPos pos, int d0, int row0, int h, int b) {
+  int c[4];
+  c[0] = d0; c[pos.s] = row0; c[pos.h] = h; c[pos.b] = b;
+  sm100::tma_prefetch_4d(map, c[0], c[1], c[2], c[3]);
 }
 
 // Store of a staged tile (64 of head_dim x `box rows` of seq) through the same kind of map.

@@ -57,6 +57,7 @@ struct AttnFwdParams {
   MapPos pq, pk, pv, po;
   int B, H, S, nqb, causal, is_bf16;
   int group;            // query heads per key/value head
+  int gh;               // (batch, head) pairs per group of the CTA order
   float scale_log2;
   int* flag;
 };
@@ -86,8 +87,11 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int bh_count = P.B * P.H;
-  const int qb = P.nqb - 1 - (int)(blockIdx.x / bh_count);   // heaviest (last) query blocks first
-  const int bh = blockIdx.x % bh_count;
+  // CTAs start in blockIdx order: heads in groups of P.gh, within a group the heaviest (last) query
+  // blocks first, so that the CTAs resident at one time read the K and V of a few heads only
+  int slot, bh;
+  decode_tile((int)blockIdx.x, P.nqb, bh_count, P.gh, slot, bh);
+  const int qb = P.nqb - 1 - slot;
   const int b = bh / P.H, h = bh % P.H;
   const int hk = h / P.group;                            // key/value head of this query head
   const int n_kv_total = (P.S + 127) / 128;
@@ -389,6 +393,14 @@ static int launch_fwd(const AttnArgs& a, cudaStream_t st) {
   P.group = (int)(a.heads / a.kv_heads);
   P.B = (int)a.batch; P.H = (int)a.heads; P.S = (int)a.seq; P.nqb = (int)((a.seq + 127) / 128);
   P.causal = a.causal; P.is_bf16 = bf; P.scale_log2 = a.scale * kLog2eF; P.flag = device_flag_ptr();
+  // Heads per group of the CTA order: all of them while every head's K and V fit in L2 together,
+  // else about as many as give each resident CTA (two per SM at head_dim 64, one at 128) two tiles.
+  P.gh = (int)(a.batch * a.heads);
+  if ((double)a.batch * a.kv_heads * a.seq * D * 4.0 > 64e6 && P.nqb > 1) {
+    const int resident = sm_count() * (D == 64 ? 2 : 1);
+    const int gh = 2 * resident / P.nqb > 1 ? 2 * resident / P.nqb : 1;
+    if (gh < P.gh) P.gh = gh;
+  }
   auto kern = attn_fwd_tc_kernel<D, T>;
   MT_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
   const unsigned grid = (unsigned)(P.nqb * P.B * P.H);

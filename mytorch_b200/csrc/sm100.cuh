@@ -92,6 +92,12 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst_smem, const CUtensorMap
       ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y), "r"(z), "r"(w)
       : "memory");
 }
+// Brings the box into L2 without a destination in shared memory: a later tma_load_4d of the same
+// box finds it there.
+__device__ __forceinline__ void tma_prefetch_4d(const CUtensorMap* map, int x, int y, int z, int w) {
+  asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global [%0, {%1, %2, %3, %4}];"
+               ::"l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
+}
 // Untiled bulk copy global -> shared (both 16-byte aligned, size a multiple of 16 bytes).
 __device__ __forceinline__ void bulk_load_1d(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
