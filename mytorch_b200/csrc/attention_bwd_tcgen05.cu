@@ -24,9 +24,9 @@
 //   head_dim 64: every accumulator has tensor-memory columns of its own and Q/dO come through a
 // ring of three stages, so the next block's S^T/dP^T are issued as soon as the elementwise warps
 // hold the current ones in registers, and a block's dQ is read out during the next block's MMAs.
-//   head_dim 128: S^T, dP^T, dV and dK fill the 512 columns. P^T is written over S^T (after a
-// barrier among the four warps of a lane quarter) and dQ is computed over dP^T; there is one
-// buffer each for Q and dO. Per block the MMA order is dV, dK, dQ, S^T(next), dP^T(next): dV and dK
+//   head_dim 128: S^T, dP^T, dV and dK fill the 512 columns. Each warp writes its P^T over S^T
+// columns that only it has read, and dQ is computed over dP^T; there is one buffer each for Q
+// and dO. Per block the MMA order is dV, dK, dQ, S^T(next), dP^T(next): dV and dK
 // free dO and Q, whose reloads (already in L2 by a prefetch) enter the TMA queue ahead of the dQ
 // reduce-adds, S^T(next) only needs P^T consumed, dP^T(next) waits until dQ is in registers.
 // The dQ reduce-add is the scarce resource at head_dim 128: reductions leave an SM at ~25 bytes
@@ -88,9 +88,10 @@ template <int D> struct BwdCfg {
   static constexpr int kSmem = kOffBar + 256;
   static_assert(kSmem <= 232448, "shared memory of one CTA");
   // Tensor memory, 512 columns. head_dim 64: S^T, dP^T, dV, dK, dQ and P^T (packed half pairs)
-  // each have their own. head_dim 128 fills all 512 with S^T, dP^T, dV and dK: P^T is written over
-  // the first 64 columns of S^T once every warp of the lane quarter has read its scores, and dQ
-  // is computed over dP^T, which the elementwise warps have read by then.
+  // each have their own. head_dim 128 fills all 512 with S^T, dP^T, dV and dK: every warp writes
+  // its 16 packed columns of P^T over the first half of the 32 S^T columns that it alone has read
+  // (no ordering among warps needed; the dV MMA takes its A operand in four pieces), and dQ is
+  // computed over dP^T, which the elementwise warps have read by then.
   static constexpr int kTmemCols = 512;
   static constexpr int kColST = 0, kColDPT = 128, kColDV = 256, kColDK = 256 + D;
   static constexpr bool kAliasDQ = D == 128;
@@ -141,8 +142,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   const uint32_t bar0 = base + Cfg::kOffBar;
   const uint32_t bar_kv = bar0, bar_qfull0 = bar0 + 8, bar_qempty0 = bar0 + 32, bar_sdp = bar0 + 56,
                  bar_pds = bar0 + 64, bar_dq = bar0 + 72, bar_dqfree = bar0 + 80, bar_sdpfree = bar0 + 88,
-                 bar_kvfree = bar0 + 96, bar_dkvfree = bar0 + 104, bar_quarter0 = bar0 + 128,   // four quarter barriers: +128 .. +159
-                 bar_dofull = bar0 + 160, bar_doempty = bar0 + 168;
+                 bar_kvfree = bar0 + 96, bar_dkvfree = bar0 + 104, bar_dofull = bar0 + 128, bar_doempty = bar0 + 136;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + Cfg::kOffBar + 112);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + Cfg::kOffBar + 116);
   float* stat = reinterpret_cast<float*>(base_ptr + Cfg::kOffStat);
@@ -166,7 +166,6 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     mbar_init(bar_dqfree, 32 * kBwdEwWarps);
     mbar_init(bar_sdpfree, kBwdEwWarps);
     mbar_init(bar_kvfree, 1);
-    for (int i = 0; i < 4; ++i) mbar_init(bar_quarter0 + 8 * i, 4);   // one arrival per warp of a lane quarter
     mbar_init(bar_dkvfree, 8 * Cfg::kChunks);       // one arrival per warp that drains a 64-column piece of dK or dV
     mbar_init(bar_dofull, 1); mbar_init(bar_doempty, 1);
     *abort_flag = 0;
@@ -404,7 +403,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             // dV and dK first: they free the dO and Q buffers, and the loads of the next block must
             // enter the TMA queue before the 64 KB of dQ reduce-adds that follow the dQ MMA - a load
             // queued behind those waits a couple of thousand cycles.
-            umma_f16_ts_x8(tmem_base + Cfg::kColDV, tmem_base + Cfg::kColPT, b_dv, idesc_kn, i > 0 ? 1u : 0u);
+            umma_f16_ts_x8_pairs(tmem_base + Cfg::kColDV, tmem_base + Cfg::kColPT, b_dv, idesc_kn, i > 0 ? 1u : 0u);
             umma_commit(bar_doempty);           // dO of this block is not read again
             umma_f16_x8(tmem_base + Cfg::kColDK, a_dk, b_dk, idesc_kn, i > 0 ? 1u : 0u);
             umma_commit(bar_qempty0 + 8 * s);   // Q of this block is not read again
@@ -516,15 +515,6 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             for (int e = 0; e < CPT; ++e)
               if (dead || (diag && hh * CPT + e < t)) s_[e] = 0xff800000u;
           }
-          if (Cfg::kAliasDQ) {
-            // P^T goes over the first S^T columns: every warp of this lane quarter must hold its
-            // scores in registers first
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_quarter0 + 8 * (warp & 3));
-            if (!__all_sync(0xffffffffu, mbar_wait(bar_quarter0 + 8 * (warp & 3), g & 1, abort_flag))) { ok = false; break; }
-            tc_fence_after();
-          }
           if (!Cfg::kAliasDQ && i > 0) {
             // dS^T of the previous block is still an operand of its dQ MMA, which was issued after
             // the S^T/dP^T MMAs of this block: it must have completed before dS^T is overwritten
@@ -561,7 +551,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             for (int e = 0; e < 4; ++e) ptp[c16 * 4 + e] = pp[e];
             *reinterpret_cast<uint4*>(dst_row + off) = make_uint4(dd[0], dd[1], dd[2], dd[3]);
             if ((c16 & 3) == 3)   // 32 finished columns = 16 packed words -> tensor memory
-              tmem_st16(tmem_base + Cfg::kColPT + lane_addr + hh * (CPT / 2) + (c16 >> 2) * 16, ptp + (c16 >> 2) * 16);
+              tmem_st16(tmem_base + Cfg::kColPT + lane_addr + hh * (Cfg::kAliasDQ ? CPT : CPT / 2) + (c16 >> 2) * 16, ptp + (c16 >> 2) * 16);
           }
           tmem_st_wait();
         }

@@ -235,6 +235,35 @@ __device__ __forceinline__ void umma_f16_ts_x8(uint32_t d, uint32_t a_tmem, cons
         "r"(idesc), "r"(acc_first)
       : "memory");
 }
+// The same with the A operand in four separate pieces of 16 columns (two steps each) that start 32
+// columns apart: columns a_tmem, +8, +32, +40, +64, +72, +96, +104.
+__device__ __forceinline__ void umma_f16_ts_x8_pairs(uint32_t d, uint32_t a_tmem, const uint64_t* b, uint32_t idesc, uint32_t acc_first) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p, pt;\n"
+      ".reg .b32 a1, a2, a3, a4, a5, a6, a7;\n"
+      "setp.ne.b32 p, %11, 0;\n"
+      "setp.eq.b32 pt, 0, 0;\n"
+      "add.u32 a1, %1, 8;\n"
+      "add.u32 a2, %1, 32;\n"
+      "add.u32 a3, %1, 40;\n"
+      "add.u32 a4, %1, 64;\n"
+      "add.u32 a5, %1, 72;\n"
+      "add.u32 a6, %1, 96;\n"
+      "add.u32 a7, %1, 104;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %10, p;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a1], %3, %10, pt;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a2], %4, %10, pt;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a3], %5, %10, pt;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a4], %6, %10, pt;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a5], %7, %10, pt;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a6], %8, %10, pt;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a7], %9, %10, pt;\n"
+      "}\n"
+      ::"r"(d), "r"(a_tmem), "l"(b[0]), "l"(b[1]), "l"(b[2]), "l"(b[3]), "l"(b[4]), "l"(b[5]), "l"(b[6]), "l"(b[7]),
+        "r"(idesc), "r"(acc_first)
+      : "memory");
+}
 // Makes `bar` complete once all MMAs issued so far by this thread have finished.
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
