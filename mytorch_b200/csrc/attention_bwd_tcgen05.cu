@@ -142,7 +142,8 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   const uint32_t bar0 = base + Cfg::kOffBar;
   const uint32_t bar_kv = bar0, bar_qfull0 = bar0 + 8, bar_qempty0 = bar0 + 32, bar_sdp = bar0 + 56,
                  bar_pds = bar0 + 64, bar_dq = bar0 + 72, bar_dqfree = bar0 + 80, bar_sdpfree = bar0 + 88,
-                 bar_kvfree = bar0 + 96, bar_dkvfree = bar0 + 104, bar_dofull = bar0 + 128, bar_doempty = bar0 + 136;
+                 bar_kvfree = bar0 + 96, bar_dkvfree = bar0 + 104, bar_dofull = bar0 + 128, bar_doempty = bar0 + 136,
+                 bar_kvissued = bar0 + 144;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + Cfg::kOffBar + 112);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + Cfg::kOffBar + 116);
   float* stat = reinterpret_cast<float*>(base_ptr + Cfg::kOffStat);
@@ -168,6 +169,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     mbar_init(bar_kvfree, 1);
     mbar_init(bar_dkvfree, 8 * Cfg::kChunks);       // one arrival per warp that drains a 64-column piece of dK or dV
     mbar_init(bar_dofull, 1); mbar_init(bar_doempty, 1);
+    mbar_init(bar_kvissued, 1);
     *abort_flag = 0;
     fence_barrier_init();
     fence_proxy_async();
@@ -242,10 +244,13 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       cur.round = 0; cur.tn = 0;
       enter_round(cur);
       if (!Cfg::kSplit) {
+        bool ok = true;
         for (int g = 0; cur.valid; ++g, advance(cur)) {
-          if (cur.i == 0 && !load_kv(cur)) break;
-          if (!load_q(cur, g)) break;
+          if (cur.i == 0 && !load_kv(cur)) { ok = false; break; }
+          if (!load_q(cur, g)) { ok = false; break; }
+          if (cur.i == 0) mbar_arrive(bar_kvissued);   // this tile's first loads are in the TMA queue
         }
+        (void)ok;
       } else {
         // One buffer each for Q and dO: while step g is worked on, step g+1's Q and dO are brought
         // into L2; its dO is loaded as soon as the dV MMA of step g has completed, its Q after the
@@ -261,6 +266,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         if (ok) ok = load_kv(cur);
         if (ok) ok = load_q(cur, 0);
         if (ok) load_do(cur);
+        if (ok) mbar_arrive(bar_kvissued);
         Step nxt = cur;
         if (ok) advance(nxt);
         for (int g = 0; ok && nxt.valid; ++g) {
@@ -272,10 +278,13 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
               prefetch_rows(&tmQ, P.pq, dc * 64, qi * 128, hq, nxt.b);
             }
           }
-          if (!mbar_wait(bar_doempty, g & 1, abort_flag)) break;      // dV of step g has read dO
+          if (!mbar_wait(bar_doempty, g & 1, abort_flag)) { ok = false; break; }   // dV of step g has read dO
           load_do(nxt);
-          if (!load_q(nxt, g + 1)) break;                              // waits for dK of step g
-          if (nxt.i == 0 && !load_kv(nxt)) break;
+          if (!load_q(nxt, g + 1)) { ok = false; break; }              // waits for dK of step g
+          if (nxt.i == 0) {
+            if (!load_kv(nxt)) { ok = false; break; }
+            mbar_arrive(bar_kvissued);                 // the next tile's first loads are in the TMA queue
+          }
           advance(nxt);
         }
       }
@@ -451,7 +460,10 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       __syncwarp();
       return smem_u32(buf);
     };
-    auto flush_dq = [&](int qi, int bh) {             // bh: (batch, query head) index of the block
+    // `gate` >= 0 (a tile's last block): the reduce-adds are held back until the producer has put
+    // the next tile's first loads into the TMA queue - a load queued behind 32-64 KB of reduce-adds,
+    // which leave the SM at ~25 bytes per clock, would wait thousands of cycles.
+    auto flush_dq = [&](int qi, int bh, int gate) {   // bh: (batch, query head) index of the block
       if (hh < kDqChunks) {
         uint32_t r[32];
         tmem_ld32(tmem_base + Cfg::kColDQ + lane_addr + hh * 32, r);
@@ -462,6 +474,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         for (int piece = 0; piece < kPieces; ++piece) {
           const uint32_t src = stage_rows(piece, r);
           if (lane == 0) {
+            if (gate >= 0) mbar_wait(bar_kvissued, (uint32_t)gate, abort_flag);
             tma_reduce_add_3d(&tmDQ, src, hh * 32, qi * 128 + (warp & 3) * 32 + piece * Cfg::kStageRows, bh);
             bulk_commit();
           }
@@ -475,6 +488,8 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       const int tile = tile_of_round(round, n_tiles);
       if (tile < 0) continue;
       const int tn_ew = tcount_ew++;
+      // the parity to wait for before this tile's last dQ reduce-adds, or -1 when no tile follows
+      const int gate_last = ((round + 1) * (int)gridDim.x < n_tiles && tile_of_round(round + 1, n_tiles) >= 0) ? ((tn_ew + 1) & 1) : -1;
       int jb, bkv;
       decode_tile(tile, P.nqb, bh_count, P.gh, jb, bkv);
       const int b = bkv / P.Hkv, h = bkv % P.Hkv;     // h: key/value head
@@ -564,7 +579,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         if (fi >= 0) {
           if (!__all_sync(0xffffffffu, mbar_wait(bar_dq, (g0 + fi) & 1, abort_flag))) { ok = false; break; }
           tc_fence_after();
-          flush_dq(qi_of(fi), bh_of(fi));
+          flush_dq(qi_of(fi), bh_of(fi), fi == n_q - 1 ? gate_last : -1);
         }
       }
       if (!ok) break;
@@ -572,7 +587,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         // the tile's last dQ; its completion also means every MMA of the tile is complete
         if (!__all_sync(0xffffffffu, mbar_wait(bar_dq, (g0 + n_q - 1) & 1, abort_flag))) { ok = false; break; }
         tc_fence_after();
-        flush_dq(qi_of(n_q - 1), bh_of(n_q - 1));
+        flush_dq(qi_of(n_q - 1), bh_of(n_q - 1), gate_last);
       }
       // All MMAs of the tile are complete (its last bar_dq was waited above, in either variant).
       // Each 64-column piece of dK and of dV is drained by one column group: 32 key rows at a time
