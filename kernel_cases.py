@@ -2,11 +2,13 @@
 inputs larger than the 126 MB L2 where DRAM figures matter, under 2 GB held on
 the device, a handful of launches.
 
-    python kernel_cases.py {gemm|attn|mem|adamw|gemm_vs_library|gemm_shapes|power|suite}
+    python kernel_cases.py {gemm|attn|attn128|mem|adamw|gemm_vs_library|gemm_shapes|power|suite}
 
 gemm : the GPT-2 124M qkv projection of one 16x1024-token micro-batch
        (16384x768 @ 768x2304, fp16), five launches
 attn : causal flash attention forward + backward, 4x12x1024x64 fp16, three rounds
+attn128 : the same at head_dim 128, 16x10x2048x128 fp16 (half a nanochat-d20 micro-batch: 160
+       heads, enough for the head-grouped tile order to matter), two rounds
 mem  : LayerNorm forward/backward (16384x768), cross entropy forward/backward
        (4096x50304), GELU backward (16384x3072), softmax (16384x1024), three rounds
 adamw: fused AdamW over one 64M-element fp32 tensor, three steps
@@ -53,6 +55,11 @@ def main(which):
     elif which == "attn":
         q, k, v, do = (randn((4, 12, 1024, 64)) for _ in range(4))
         for _ in range(3):
+            _, _, _, o, m = F.fused_sdpa_forward(q, k, v, causal=True)
+            F.fused_sdpa_backward(do, q, k, v, o, m, causal=True)
+    elif which == "attn128":
+        q, k, v, do = (randn((16, 10, 2048, 128)) for _ in range(4))
+        for _ in range(2):
             _, _, _, o, m = F.fused_sdpa_forward(q, k, v, causal=True)
             F.fused_sdpa_backward(do, q, k, v, o, m, causal=True)
     elif which == "mem":
