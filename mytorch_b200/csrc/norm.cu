@@ -233,15 +233,17 @@ norm_bwd_warp(const T* __restrict__ x, const float* __restrict__ mean, const flo
 // sums of the team's warps meet in shared memory (one __syncthreads per kTeamRows rows, double
 // buffered). The block's column partials need no further reduction: thread t owns columns
 // [t*VN, t*VN+VN). Same partial layout as norm_bwd_warp.
-constexpr int kTeamRows = 2;     // rows in flight per thread (x and dy: 2 x 16 bytes each); three measured the same, four spill
-template <typename T, int WPR, bool RMS, int RB, int THREADS_PER_SM, bool ACC>
-__global__ void __launch_bounds__(WPR * 32, THREADS_PER_SM / (WPR * 32))
+constexpr int kTeamRows = 2;        // rows per iteration and thread (x and dy: 2 x 16 bytes each), plus as many prefetched
+constexpr int kTeamThreadsPerSM = 576;   // resident threads the kernel is compiled for: 768 leaves too few registers for the prefetch (spills, 28 us against 22 at 16384x768)
+template <typename T, int WPR, bool RMS, bool ACC>
+__global__ void __launch_bounds__(WPR * 32, kTeamThreadsPerSM / (WPR * 32))
 norm_bwd_team(const T* __restrict__ x, const float* __restrict__ mean, const float* __restrict__ rstd_in,
               const T* __restrict__ dy, const T* __restrict__ gamma, T* __restrict__ dx,
               float* __restrict__ partial, int64_t rows, bool want_dg, bool want_db, bool dx_acc) {
   allow_dependents();
   grid_dependency_wait();
   constexpr int VN = Vec16<T>::N;
+  constexpr int RB = kTeamRows;
   constexpr int cols = WPR * 32 * VN;
   (void)dx_acc;
   __shared__ float part[2][RB][WPR][2];
@@ -481,24 +483,19 @@ static int norm_bwd_launch(const void* x, const float* mean, const float* rstd, 
     // rows of 2..6 or 8 warps of vectors (512..1536 and 2048 half columns, 256..768 and 1024 fp32
     // columns): one thread per vector
     const int wpr = nvec_all / 32;
-    static const int variant = getenv("MT_LN_V") ? atoi(getenv("MT_LN_V")) : 0;
-    const int rb = variant == 2 ? 1 : 2;
-    const int tps = variant == 1 ? 576 : 768;
-    const int per_sm = tps / (wpr * 32);      // resident blocks (the kernel is compiled for this occupancy)
-    int64_t want = (rows + rb - 1) / rb;
+    const int per_sm = kTeamThreadsPerSM / (wpr * 32);      // resident blocks (the kernel is compiled for this occupancy)
+    int64_t want = (rows + kTeamRows - 1) / kTeamRows;
     int grid = (int)(want < (int64_t)sm_count() * per_sm ? want : (int64_t)sm_count() * per_sm);
     bool wg = dgamma != nullptr, wb = dbeta != nullptr;
     TempBuf part((wg || wb) ? (size_t)grid * 2 * cols * sizeof(float) : 0, st);
     if (!part.ok()) return MT_ERR_CUDA;
     const bool acc = (accumulate & 2) != 0;
-#define MT_TEAM3(W, RBV, TPS, A) MT_CHECK_CUDA(launch_overlapped(norm_bwd_team<T, W, RMS, RBV, TPS, A>, dim3(grid), dim3(W * 32), 0, st, xp, mean, rstd, dyp, gp, dxp, (float*)part.ptr, rows, wg, wb, acc))
-#define MT_TEAM2(W, RBV, TPS) do { if (acc) MT_TEAM3(W, RBV, TPS, true); else MT_TEAM3(W, RBV, TPS, false); } while (0)
-#define MT_TEAM(W) do { if (variant == 1) MT_TEAM2(W, 2, 576); else if (variant == 2) MT_TEAM2(W, 1, 768); else MT_TEAM2(W, 2, 768); } while (0)
+#define MT_TEAM2(W, A) MT_CHECK_CUDA(launch_overlapped(norm_bwd_team<T, W, RMS, A>, dim3(grid), dim3(W * 32), 0, st, xp, mean, rstd, dyp, gp, dxp, (float*)part.ptr, rows, wg, wb, acc))
+#define MT_TEAM(W) do { if (acc) MT_TEAM2(W, true); else MT_TEAM2(W, false); } while (0)
     if (wpr == 2) MT_TEAM(2); else if (wpr == 3) MT_TEAM(3); else if (wpr == 4) MT_TEAM(4); else if (wpr == 5) MT_TEAM(5);
     else if (wpr == 6) MT_TEAM(6); else MT_TEAM(8);
 #undef MT_TEAM
 #undef MT_TEAM2
-#undef MT_TEAM3
     MT_LAUNCH_CHECK();
     if (wg || wb) {
       MT_CHECK_CUDA(launch_overlapped(norm_bwd_finalize, dim3((unsigned)((cols + kFinalizeCols - 1) / kFinalizeCols), 2),
