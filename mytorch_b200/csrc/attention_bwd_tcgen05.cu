@@ -246,8 +246,11 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       if (!Cfg::kSplit) {
         bool ok = true;
         for (int g = 0; cur.valid; ++g, advance(cur)) {
-          if (cur.i == 0 && !load_kv(cur)) { ok = false; break; }
+          // A tile's first Q/dO goes ahead of its K/V: the ring has room long before the previous
+          // tile's last MMA lets go of K and V, and this thread would otherwise sit in that wait
+          // with the Q/dO request still unissued.
           if (!load_q(cur, g)) { ok = false; break; }
+          if (cur.i == 0 && !load_kv(cur)) { ok = false; break; }
           if (cur.i == 0) mbar_arrive(bar_kvissued);   // this tile's first loads are in the TMA queue
         }
         (void)ok;
