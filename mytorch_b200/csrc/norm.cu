@@ -233,10 +233,9 @@ norm_bwd_warp(const T* __restrict__ x, const float* __restrict__ mean, const flo
 // sums of the team's warps meet in shared memory (one __syncthreads per kTeamRows rows, double
 // buffered). The block's column partials need no further reduction: thread t owns columns
 // [t*VN, t*VN+VN). Same partial layout as norm_bwd_warp.
-constexpr int kTeamRows = 2;        // rows per iteration and thread (x and dy: 2 x 16 bytes each), plus as many prefetched
-constexpr int kTeamThreadsPerSM = 576;   // resident threads the kernel is compiled for: 768 leaves too few registers for the prefetch (spills, 28 us against 22 at 16384x768)
-template <typename T, int WPR, bool RMS, bool ACC>
-__global__ void __launch_bounds__(WPR * 32, kTeamThreadsPerSM / (WPR * 32))
+constexpr int kTeamRows = 2;     // rows in flight per thread (x and dy: 2 x 16 bytes each); three measured the same, four spill
+template <typename T, int WPR, bool RMS>
+__global__ void __launch_bounds__(WPR * 32, 768 / (WPR * 32))
 norm_bwd_team(const T* __restrict__ x, const float* __restrict__ mean, const float* __restrict__ rstd_in,
               const T* __restrict__ dy, const T* __restrict__ gamma, T* __restrict__ dx,
               float* __restrict__ partial, int64_t rows, bool want_dg, bool want_db, bool dx_acc) {
@@ -245,7 +244,6 @@ norm_bwd_team(const T* __restrict__ x, const float* __restrict__ mean, const flo
   constexpr int VN = Vec16<T>::N;
   constexpr int RB = kTeamRows;
   constexpr int cols = WPR * 32 * VN;
-  (void)dx_acc;
   __shared__ float part[2][RB][WPR][2];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int c0 = threadIdx.x * VN;
@@ -255,31 +253,18 @@ norm_bwd_team(const T* __restrict__ x, const float* __restrict__ mean, const flo
   Vec16<T> gv;
   if (gamma) gv.load(gamma + c0);
   const float inv_cols = 1.f / cols;
-  // The rows of the NEXT iteration (x, dy, the statistics and, when dx accumulates, the old dx)
-  // are requested before this iteration's arithmetic starts: a block then always has loads in
-  // flight, instead of none between its reduction and its store.
-  Vec16<T> xv[RB], dv[RB], ov[RB];
-  float mu[RB], rs[RB];
-  auto fetch = [&](int64_t r0, Vec16<T>* fx, Vec16<T>* fd, Vec16<T>* fo, float* fm, float* fr) {
+  int it = 0;
+  for (int64_t r0 = (int64_t)blockIdx.x * RB; r0 < rows; r0 += (int64_t)gridDim.x * RB, ++it) {
+    Vec16<T> xv[RB], dv[RB];
+    float mu[RB], rs[RB];
 #pragma unroll
     for (int j = 0; j < RB; ++j) {
       const int64_t row = r0 + j < rows ? r0 + j : rows - 1;   // clamped: rows past the end are recomputed, not stored
-      fx[j].load(x + row * cols + c0);
-      fd[j].load(dy + row * cols + c0);
-      if (ACC) fo[j].load(dx + row * cols + c0);
-      fm[j] = RMS ? 0.f : mean[row];
-      fr[j] = rstd_in[row];
+      xv[j].load(x + row * cols + c0);
+      dv[j].load(dy + row * cols + c0);
+      mu[j] = RMS ? 0.f : mean[row];
+      rs[j] = rstd_in[row];
     }
-  };
-  const int64_t step = (int64_t)gridDim.x * RB;
-  int64_t r0 = (int64_t)blockIdx.x * RB;
-  if (r0 < rows) fetch(r0, xv, dv, ov, mu, rs);
-  int it = 0;
-  for (; r0 < rows; r0 += step, ++it) {
-    Vec16<T> nx[RB], nd[RB], no[RB];
-    float nm[RB], nr[RB];
-    const bool more = r0 + step < rows;
-    if (more) fetch(r0 + step, nx, nd, no, nm, nr);
     float (*pp)[WPR][2] = part[it & 1];
 #pragma unroll
     for (int j = 0; j < RB; ++j) {
@@ -312,15 +297,16 @@ norm_bwd_team(const T* __restrict__ x, const float* __restrict__ mean, const flo
       for (int e = 0; e < VN; ++e) {
         const float xh = (xv[j].get(e) - mu[j]) * rs[j];
         const float dxh = gamma ? dv[j].get(e) * gv.get(e) : dv[j].get(e);
-        float v = rs[j] * (dxh - s1 - xh * s2);
-        if (ACC) v += ov[j].get(e);
-        o.set(e, v);
+        o.set(e, rs[j] * (dxh - s1 - xh * s2));
       }
-      o.store(dx + (r0 + j) * cols + c0);
-    }
-    if (more) {
+      T* dxr = dx + (r0 + j) * cols + c0;
+      if (dx_acc) {
+        Vec16<T> old;
+        old.load(dxr);
 #pragma unroll
-      for (int j = 0; j < RB; ++j) { xv[j] = nx[j]; dv[j] = nd[j]; ov[j] = no[j]; mu[j] = nm[j]; rs[j] = nr[j]; }
+        for (int e = 0; e < VN; ++e) o.set(e, o.get(e) + old.get(e));
+      }
+      o.store(dxr);
     }
   }
   if (want_dg) {
@@ -483,19 +469,16 @@ static int norm_bwd_launch(const void* x, const float* mean, const float* rstd, 
     // rows of 2..6 or 8 warps of vectors (512..1536 and 2048 half columns, 256..768 and 1024 fp32
     // columns): one thread per vector
     const int wpr = nvec_all / 32;
-    const int per_sm = kTeamThreadsPerSM / (wpr * 32);      // resident blocks (the kernel is compiled for this occupancy)
+    const int per_sm = 768 / (wpr * 32);      // resident blocks (the kernel is compiled for this occupancy)
     int64_t want = (rows + kTeamRows - 1) / kTeamRows;
     int grid = (int)(want < (int64_t)sm_count() * per_sm ? want : (int64_t)sm_count() * per_sm);
     bool wg = dgamma != nullptr, wb = dbeta != nullptr;
     TempBuf part((wg || wb) ? (size_t)grid * 2 * cols * sizeof(float) : 0, st);
     if (!part.ok()) return MT_ERR_CUDA;
-    const bool acc = (accumulate & 2) != 0;
-#define MT_TEAM2(W, A) MT_CHECK_CUDA(launch_overlapped(norm_bwd_team<T, W, RMS, A>, dim3(grid), dim3(W * 32), 0, st, xp, mean, rstd, dyp, gp, dxp, (float*)part.ptr, rows, wg, wb, acc))
-#define MT_TEAM(W) do { if (acc) MT_TEAM2(W, true); else MT_TEAM2(W, false); } while (0)
+#define MT_TEAM(W) MT_CHECK_CUDA(launch_overlapped(norm_bwd_team<T, W, RMS>, dim3(grid), dim3(W * 32), 0, st, xp, mean, rstd, dyp, gp, dxp, (float*)part.ptr, rows, wg, wb, (accumulate & 2) != 0))
     if (wpr == 2) MT_TEAM(2); else if (wpr == 3) MT_TEAM(3); else if (wpr == 4) MT_TEAM(4); else if (wpr == 5) MT_TEAM(5);
     else if (wpr == 6) MT_TEAM(6); else MT_TEAM(8);
 #undef MT_TEAM
-#undef MT_TEAM2
     MT_LAUNCH_CHECK();
     if (wg || wb) {
       MT_CHECK_CUDA(launch_overlapped(norm_bwd_finalize, dim3((unsigned)((cols + kFinalizeCols - 1) / kFinalizeCols), 2),
