@@ -26,6 +26,7 @@
 #include "gemm.cuh"
 #include "sm100.cuh"
 #include "prof.cuh"
+#include <atomic>
 #include <mutex>
 #include <string.h>
 #include <type_traits>
@@ -757,13 +758,13 @@ template <bool A_MN, bool B_MN, int BN>
 static int launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& tp,
                      const CUtensorMap& tx, const GemmParams& P, int grid, cudaStream_t st) {
   using Cfg = GemmCfg<BN, false>;
-  static bool attr_set[16] = {false};
+  static std::atomic<bool> attr_set[16];   // per device; racing first calls set the same attribute twice, harmlessly
   int dev = 0;
   cudaGetDevice(&dev);
   auto kern = gemm_tc_kernel<A_MN, B_MN, BN, false>;
-  if (dev < 16 && !attr_set[dev]) {
+  if (dev < 16 && !attr_set[dev].load(std::memory_order_acquire)) {
     MT_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
-    attr_set[dev] = true;
+    attr_set[dev].store(true, std::memory_order_release);
   }
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
@@ -786,13 +787,13 @@ template <bool A_MN, bool B_MN, int BN>
 static int launch_tc_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& tp,
                           const CUtensorMap& tx, const GemmParams& P, int pairs, cudaStream_t st) {
   using Cfg = GemmCfg<BN, true>;
-  static bool attr_set[16] = {false};
+  static std::atomic<bool> attr_set[16];   // per device; racing first calls set the same attribute twice, harmlessly
   int dev = 0;
   cudaGetDevice(&dev);
   auto kern = gemm_tc_kernel<A_MN, B_MN, BN, true>;
-  if (dev < 16 && !attr_set[dev]) {
+  if (dev < 16 && !attr_set[dev].load(std::memory_order_acquire)) {
     MT_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
-    attr_set[dev] = true;
+    attr_set[dev].store(true, std::memory_order_release);
   }
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
@@ -817,11 +818,11 @@ static int launch_tc_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CU
 // Number of two-CTA clusters of the pair kernel that are resident at once on
 // this device (an SM without a free partner in its GPC hosts none).
 static int resident_pairs() {
-  static int cached[16] = {0};
+  static std::atomic<int> cached[16];      // per device; racing first calls compute the same number
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 16) return sm_count() / 2;
-  if (cached[dev]) return cached[dev];
+  if (int c = cached[dev].load(std::memory_order_acquire)) return c;
   using Cfg = GemmCfg<256, true>;
   auto kern = gemm_tc_kernel<false, false, 256, true>;
   int n = 0;
@@ -843,7 +844,7 @@ static int resident_pairs() {
     cudaGetLastError();
   }
   if (n <= 0 || n > sm_count() / 2) n = sm_count() / 2;
-  cached[dev] = n;
+  cached[dev].store(n, std::memory_order_release);
   return n;
 }
 
