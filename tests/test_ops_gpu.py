@@ -339,6 +339,32 @@ def test_attention(mt, dtype, B, H, S, D, causal):
     no_device_flag(mt)
 
 
+@pytest.mark.parametrize("B,H,S,D", [(4, 18, 2048, 128), (6, 24, 2048, 64)])
+def test_attention_head_grouped_tile_order_matches_cuda_core_kernels(mt, B, H, S, D):
+    """Shapes large enough that both tensor-core kernels take the heads in groups (the
+    forward once K and V of all heads exceed 64 MB, the backward once its footprint exceeds
+    96 MB and the grouped dealing stays balanced - 72 and 144 heads at 16 blocks per head do):
+    every tile must still be visited exactly once. The CUDA-core kernels, which walk the
+    tiles in plain order, are the reference; the row sums of dQ/dK/dV would be off by whole
+    tiles if one were skipped or done twice."""
+    F = mt.fused_ops
+    r = np.random.default_rng(21)
+    Q, K, V, DO = (mt.DeviceArray.from_numpy(r.standard_normal((B, H, S, D)).astype(np.float32), "float16") for _ in range(4))
+    _, _, _, o_tc, m_tc = F.fused_sdpa_forward(Q, K, V, causal=True)
+    dq_tc, dk_tc, dv_tc = F.fused_sdpa_backward(DO, Q, K, V, o_tc, m_tc, causal=True)
+    mt._lib.attn_force_simt(1)
+    try:
+        _, _, _, o_cc, m_cc = F.fused_sdpa_forward(Q, K, V, causal=True)
+        dq_cc, dk_cc, dv_cc = F.fused_sdpa_backward(DO, Q, K, V, o_cc, m_cc, causal=True)
+    finally:
+        mt._lib.attn_force_simt(0)
+    t = TOL["float16"]
+    close(o_tc.numpy(), o_cc.numpy(), t, "o"); close(m_tc.numpy(), m_cc.numpy(), 1e-3, "lse")
+    close(dq_tc.numpy(), dq_cc.numpy(), 2 * t, "dq"); close(dk_tc.numpy(), dk_cc.numpy(), 2 * t, "dk")
+    close(dv_tc.numpy(), dv_cc.numpy(), 2 * t, "dv")
+    no_device_flag(mt)
+
+
 @pytest.mark.parametrize("dtype", ["float16", "bfloat16"])
 @pytest.mark.parametrize("B,T,H,D", [(2, 257, 3, 64), (1, 1000, 2, 64), (2, 257, 2, 128), (1, 1000, 3, 128), (2, 1024, 12, 64)])
 def test_attention_on_strided_projection_layouts(mt, dtype, B, T, H, D):
