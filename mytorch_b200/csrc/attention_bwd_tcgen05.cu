@@ -99,17 +99,6 @@ template <int D> struct BwdCfg {
   static constexpr int kColPT = kAliasDQ ? kColST : 256 + 3 * D;
 };
 
-// Tiles are dealt to the persistent CTAs round by round, forwards in even rounds and backwards
-// in odd ones: with tiles sorted heaviest first, the CTA that got the heaviest tile of one round
-// gets the lightest of the next, which keeps the CTAs' totals within a few percent of each other.
-// Returns -1 when this CTA has no tile in the (last, partial) round.
-__device__ __forceinline__ int tile_of_round(int round, int n_tiles) {
-  const int G = (int)gridDim.x;
-  const int idx = (round & 1) ? G - 1 - (int)blockIdx.x : (int)blockIdx.x;
-  const int tile = round * G + idx;
-  return tile < n_tiles ? tile : -1;
-}
-
 struct AttnBwdParams {
   const float* stats;      // [2][B*H][nqb*128]: lse*log2e (+inf on padded rows), then delta*scale (0 on padded rows)
   float* dq_accum;

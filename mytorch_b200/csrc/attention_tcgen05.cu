@@ -1,14 +1,16 @@
 // Tensor-core attention for sm_100a, fp16/bf16, causal or full.
 //
-// Forward: one CTA per (batch, head, block of 128 query rows), 320 threads.
-//   warp 8    TMA producer: Q once, then K and V blocks of 128 keys (two stages
-//             each, K one block ahead of V), 128-byte swizzled, read in place
-//             through 4-D tensor maps {head_dim, seq, head, batch} (any
-//             batch/head/row strides);
+// Forward: persistent, as many CTAs as are resident at once (two per SM at head_dim 64, one at
+// 128), 320 threads each; a tile is one (batch, head, block of 128 query rows), dealt to the CTAs
+// round by round (heads in groups that keep their K/V in L2, heaviest query blocks first).
+//   warp 8    TMA producer: a tile's Q (as soon as the previous tile's last score MMA has read
+//             the Q buffer), then K and V blocks of 128 keys (two stages each, K one block ahead
+//             of V, the rings running on across tiles), 128-byte swizzled, read in place
+//             through 4-D tensor maps {head_dim, seq, head, batch} (any batch/head/row strides);
 //   warp 9    MMA issuer: S = Q K^T (128x128xD) into tensor memory - issued for
-//             block j+1 as soon as the softmax warps have copied S_j to registers -
-//             then O += P V (128xDx128) with P read from tensor memory and the
-//             accumulator kept in tensor memory;
+//             block j+1 (or the next tile's first block) as soon as the softmax warps have
+//             copied S_j to registers - then O += P V (128xDx128) with P read from tensor memory
+//             and the accumulator kept in tensor memory;
 //   warps 0-7 softmax: warps w and w+4 share the 32 query rows of TMEM lane quarter
 //             w&3 and take 64 score columns each. A thread reads its half row once,
 //             agrees with its partner on the row maximum through shared memory,
@@ -16,9 +18,11 @@
 //             memory as packed half pairs. The running maximum only moves (and O is
 //             only rescaled in tensor memory) when it grew by more than 2^8. On the
 //             causal diagonal, 32-column groups that no row of the warp keeps are
-//             skipped altogether.
-// head_dim 64 uses 82 KB of shared memory, 256 TMEM columns and at most 102
-// registers per thread, so two CTAs share an SM.
+//             skipped altogether. After a tile's last block the same warps scale O by 1/l and
+//             send it out through staging buffers of their own (TMA store), while the producer
+//             and the MMA warp are already on the next tile.
+// head_dim 64 uses 99 KB of shared memory, 256 TMEM columns and 96 registers per thread, so two
+// CTAs share an SM.
 //
 // Roofline: tensor pipe, 4*B*H*S^2*D FLOP (half of that when causal); at
 // head_dim 64 the exp2 (MUFU, 16 per clock per SM) rate caps the kernel at half
@@ -45,7 +49,11 @@ template <int D> struct FwdCfg {
   static constexpr int kOffX = kOffBar + 256;          // row statistics exchanged between the two half-row threads
   // No slack for aligning the base: the dynamic shared-memory window of a kernel
   // without static shared memory starts 1024-byte aligned (checked at entry).
-  static constexpr int kSmem = kOffX + 2 * 2 * 128 * 4;
+  // O leaves through a staging area of its own (the K/V buffers already hold the next tile's
+  // blocks by then): one 32-row x 128-byte buffer per storing warp
+  static constexpr int kOffStage = (kOffX + 2 * 2 * 128 * 4 + 1023) / 1024 * 1024;   // swizzled: 1024-byte aligned
+  static constexpr int kStageWarps = D == 64 ? 4 : 8;
+  static constexpr int kSmem = kOffStage + kStageWarps * 4096;
   // Tensor memory: S fp32 [0,128), O fp32 [128,128+D), P as packed half pairs [128+D, 192+D)
   static constexpr int kTmemP = 128 + D;
   static constexpr int kTmemCols = D == 64 ? 256 : 512;
@@ -80,22 +88,35 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   // barrier slots
   const uint32_t bar_q = bar0, bar_kfull0 = bar0 + 8, bar_kempty0 = bar0 + 24, bar_vfull0 = bar0 + 40,
                  bar_vempty0 = bar0 + 56, bar_s = bar0 + 72, bar_p = bar0 + 80, bar_o = bar0 + 88,
-                 bar_sfree = bar0 + 96, bar_pair0 = bar0 + 104;   // four pair barriers: +104 .. +135
+                 bar_sfree = bar0 + 96, bar_pair0 = bar0 + 104,   // four pair barriers: +104 .. +135
+                 bar_qfree = bar0 + 136;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + Cfg::kOffBar + 144);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + Cfg::kOffBar + 148);
   float* xchg = reinterpret_cast<float*>(base_ptr + Cfg::kOffX);   // [2 buffers][2 halves][128 rows]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int bh_count = P.B * P.H;
-  // CTAs start in blockIdx order: heads in groups of P.gh, within a group the heaviest (last) query
-  // blocks first, so that the CTAs resident at one time read the K and V of a few heads only
-  int slot, bh;
-  decode_tile((int)blockIdx.x, P.nqb, bh_count, P.gh, slot, bh);
-  const int qb = P.nqb - 1 - slot;
-  const int b = bh / P.H, h = bh % P.H;
-  const int hk = h / P.group;                            // key/value head of this query head
+  const int n_tiles = P.nqb * bh_count;
   const int n_kv_total = (P.S + 127) / 128;
-  const int n_kv = P.causal ? min(qb + 1, n_kv_total) : n_kv_total;
+  // The kernel is persistent: as many CTAs as are resident at once, each taking one tile per round
+  // of gridDim.x tiles (tile_of_round: forwards in even rounds, backwards in odd ones). Tile order
+  // (decode_tile): heads in groups of P.gh, within a group the heaviest (last) query blocks
+  // first, so that the CTAs working at one time read the K and V of a few heads only. Every role
+  // walks the same tile sequence with a running block count, from which ring stages and barrier
+  // parities follow; barriers and tensor memory are set up once, and the next tile's Q, K and
+  // first scores are under way while this tile's O is still being written out.
+  struct Tile { int qb, b, h, hk, n_kv; };
+  auto tile_at = [&](int round, Tile& t) -> bool {
+    const int tile = tile_of_round(round, n_tiles);
+    if (tile < 0) return false;
+    int slot, bh;
+    decode_tile(tile, P.nqb, bh_count, P.gh, slot, bh);
+    t.qb = P.nqb - 1 - slot;
+    t.b = bh / P.H; t.h = bh % P.H;
+    t.hk = t.h / P.group;                                // key/value head of this query head
+    t.n_kv = P.causal ? min(t.qb + 1, n_kv_total) : n_kv_total;
+    return true;
+  };
 
   if (threadIdx.x == 0) {
     mbar_init(bar_q, 1);
@@ -104,6 +125,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     mbar_init(bar_vfull0, 1); mbar_init(bar_vfull0 + 8, 1);
     mbar_init(bar_vempty0, 1); mbar_init(bar_vempty0 + 8, 1);
     mbar_init(bar_s, 1); mbar_init(bar_p, 32 * kSoftmaxWarps); mbar_init(bar_o, 1); mbar_init(bar_sfree, kSoftmaxWarps);
+    mbar_init(bar_qfree, 1);
     for (int i = 0; i < 4; ++i) mbar_init(bar_pair0 + 8 * i, 2);
     *abort_flag = 0;
     fence_barrier_init();
@@ -123,30 +145,40 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     // ------------------------------------------------------------ producer --
     if (lane == 0) {
       prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV);
-      mbar_expect_tx(bar_q, Cfg::kTile);
-#pragma unroll
-      for (int dc = 0; dc < Cfg::kChunks; ++dc)
-        load_rows(base + Cfg::kOffQ + dc * 16384, &tmQ, bar_q, P.pq, dc * 64, qb * 128, h, b);
-      // K runs one block ahead of V: the scores of block j+1 are issued while the
-      // softmax of block j is still running, so K_{j+1} must already be on its way.
-      auto load_k = [&](int j) -> bool {
-        const int st = j & 1;
-        if (!mbar_wait(bar_kempty0 + 8 * st, ((j >> 1) & 1) ^ 1u, abort_flag)) return false;
-        mbar_expect_tx(bar_kfull0 + 8 * st, Cfg::kTile);
-#pragma unroll
-        for (int dc = 0; dc < Cfg::kChunks; ++dc)
-          load_rows(base + Cfg::kOffK + st * Cfg::kTile + dc * 16384, &tmK, bar_kfull0 + 8 * st, P.pk, dc * 64, j * 128, hk, b);
-        return true;
-      };
-      bool okp = load_k(0);
-      for (int j = 0; j < n_kv && okp; ++j) {
-        if (j + 1 < n_kv && !load_k(j + 1)) break;
-        const int st = j & 1;
-        if (!mbar_wait(bar_vempty0 + 8 * st, ((j >> 1) & 1) ^ 1u, abort_flag)) break;
-        mbar_expect_tx(bar_vfull0 + 8 * st, Cfg::kTile);
+      int gb = 0;                                        // blocks before this tile (running count)
+      bool okp = true;
+      Tile t;
+      for (int round = 0, tn = 0; round * (int)gridDim.x < n_tiles && okp; ++round) {
+        if (!tile_at(round, t)) continue;
+        // Q is read by every score MMA of a tile: the buffer is free once the previous tile's last one is done
+        if (tn > 0 && !mbar_wait(bar_qfree, (tn - 1) & 1, abort_flag)) break;
+        ++tn;
+        mbar_expect_tx(bar_q, Cfg::kTile);
 #pragma unroll
         for (int dc = 0; dc < Cfg::kChunks; ++dc)
-          load_rows(base + Cfg::kOffV + st * Cfg::kTile + dc * 16384, &tmV, bar_vfull0 + 8 * st, P.pv, dc * 64, j * 128, hk, b);
+          load_rows(base + Cfg::kOffQ + dc * 16384, &tmQ, bar_q, P.pq, dc * 64, t.qb * 128, t.h, t.b);
+        // K runs one block ahead of V: the scores of block j+1 are issued while the
+        // softmax of block j is still running, so K_{j+1} must already be on its way.
+        auto load_k = [&](int j) -> bool {
+          const int g = gb + j, st = g & 1;
+          if (!mbar_wait(bar_kempty0 + 8 * st, ((g >> 1) & 1) ^ 1u, abort_flag)) return false;
+          mbar_expect_tx(bar_kfull0 + 8 * st, Cfg::kTile);
+#pragma unroll
+          for (int dc = 0; dc < Cfg::kChunks; ++dc)
+            load_rows(base + Cfg::kOffK + st * Cfg::kTile + dc * 16384, &tmK, bar_kfull0 + 8 * st, P.pk, dc * 64, j * 128, t.hk, t.b);
+          return true;
+        };
+        okp = load_k(0);
+        for (int j = 0; j < t.n_kv && okp; ++j) {
+          if (j + 1 < t.n_kv && !load_k(j + 1)) { okp = false; break; }
+          const int g = gb + j, st = g & 1;
+          if (!mbar_wait(bar_vempty0 + 8 * st, ((g >> 1) & 1) ^ 1u, abort_flag)) { okp = false; break; }
+          mbar_expect_tx(bar_vfull0 + 8 * st, Cfg::kTile);
+#pragma unroll
+          for (int dc = 0; dc < Cfg::kChunks; ++dc)
+            load_rows(base + Cfg::kOffV + st * Cfg::kTile + dc * 16384, &tmV, bar_vfull0 + 8 * st, P.pv, dc * 64, j * 128, t.hk, t.b);
+        }
+        gb += t.n_kv;
       }
     }
   } else if (warp == kSoftmaxWarps + 1) {
@@ -171,9 +203,10 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)
           dv[st][ks] = smem_desc_sw128(base + Cfg::kOffV + st * Cfg::kTile + ks * 2048, 16384, 1024);
-      auto issue_s = [&](int j) -> bool {
-        const int st = j & 1;
-        if (!mbar_wait(bar_kfull0 + 8 * st, (j >> 1) & 1, abort_flag)) return false;
+      // scores of running block g (its K is in ring stage g & 1)
+      auto issue_s = [&](int g) -> bool {
+        const int st = g & 1;
+        if (!mbar_wait(bar_kfull0 + 8 * st, (g >> 1) & 1, abort_flag)) return false;
         tc_fence_after();
         if (st == 0) {
           umma_f16_x4(tmem_s, dq, dk[0], idesc_s, 0u);
@@ -186,25 +219,39 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         umma_commit(bar_s);
         return true;
       };
-      bool ok = mbar_wait(bar_q, 0, abort_flag);
-      if (ok) ok = issue_s(0);
-      for (int j = 0; j < n_kv && ok; ++j) {
-        if (j + 1 < n_kv) {
-          // The softmax warps hold S_j in registers: the next block's scores are
-          // computed while they work on this one.
-          if (!mbar_wait(bar_sfree, j & 1, abort_flag)) break;
+      int gb = 0;
+      bool ok = true;
+      Tile t;
+      for (int round = 0, tn = 0; round * (int)gridDim.x < n_tiles && ok; ++round) {
+        if (!tile_at(round, t)) continue;
+        if (!mbar_wait(bar_q, tn & 1, abort_flag)) break;
+        ++tn;
+        // the softmax warps have copied the previous tile's last scores to registers
+        if (gb > 0 && !mbar_wait(bar_sfree, (gb - 1) & 1, abort_flag)) break;
+        tc_fence_after();
+        if (!issue_s(gb)) break;
+        if (t.n_kv == 1) umma_commit(bar_qfree);        // the tile's last score MMA: Q may be replaced
+        for (int j = 0; j < t.n_kv; ++j) {
+          const int g = gb + j;
+          if (j + 1 < t.n_kv) {
+            // The softmax warps hold S_j in registers: the next block's scores are
+            // computed while they work on this one.
+            if (!mbar_wait(bar_sfree, g & 1, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            if (!issue_s(g + 1)) { ok = false; break; }
+            if (j + 2 == t.n_kv) umma_commit(bar_qfree);
+          }
+          if (!mbar_wait(bar_p, g & 1, abort_flag)) { ok = false; break; }      // P_j written
           tc_fence_after();
-          if (!issue_s(j + 1)) break;
+          if (!mbar_wait(bar_vfull0 + 8 * (g & 1), (g >> 1) & 1, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          // A = P straight from tensor memory: 16 keys = 8 columns of packed half pairs per step
+          if (g & 1) umma_f16_ts_x8(tmem_o, tmem_p, dv[1], idesc_o, j > 0 ? 1u : 0u);
+          else umma_f16_ts_x8(tmem_o, tmem_p, dv[0], idesc_o, j > 0 ? 1u : 0u);
+          umma_commit(bar_vempty0 + 8 * (g & 1));
+          umma_commit(bar_o);
         }
-        if (!mbar_wait(bar_p, j & 1, abort_flag)) break;      // P_j written
-        tc_fence_after();
-        if (!mbar_wait(bar_vfull0 + 8 * (j & 1), (j >> 1) & 1, abort_flag)) break;
-        tc_fence_after();
-        // A = P straight from tensor memory: 16 keys = 8 columns of packed half pairs per step
-        if (j & 1) umma_f16_ts_x8(tmem_o, tmem_p, dv[1], idesc_o, j > 0 ? 1u : 0u);
-        else umma_f16_ts_x8(tmem_o, tmem_p, dv[0], idesc_o, j > 0 ? 1u : 0u);
-        umma_commit(bar_vempty0 + 8 * (j & 1));
-        umma_commit(bar_o);
+        gb += t.n_kv;
       }
     }
   } else {
@@ -215,11 +262,11 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     // partial row sums meet once, after the last block.
     const int qtr = warp & 3, hf = warp >> 2;
     const int row = qtr * 32 + lane;                  // query row within the block = TMEM lane
-    const int q_glob = qb * 128 + row;
     const uint32_t lane_addr = (uint32_t)(qtr * 32) << 16;
     const uint32_t bar_pair = bar_pair0 + 8 * qtr;
-    float m_used = -INFINITY, l = 0.f;
     bool ok = true;
+    int gb = 0, xu = 0;                               // running counts of blocks and of pair exchanges
+    Tile t;
     // Both threads of a row see the same values, so `ok` and the rescale decision agree.
     auto pair_exchange = [&](int use, float mine, float& other) -> bool {
       float* slot = xchg + (use & 1) * 256;
@@ -230,8 +277,14 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       other = slot[(hf ^ 1) * 128 + row];
       return true;
     };
+    for (int round = 0; round * (int)gridDim.x < n_tiles && ok; ++round) {
+    if (!tile_at(round, t)) continue;
+    const int qb = t.qb, b = t.b, h = t.h, n_kv = t.n_kv, bh = b * P.H + h;
+    const int q_glob = qb * 128 + row;
+    float m_used = -INFINITY, l = 0.f;
     for (int j = 0; j < n_kv && ok; ++j) {
-      if (!__all_sync(0xffffffffu, mbar_wait(bar_s, j & 1, abort_flag))) { ok = false; break; }
+      const int g = gb + j;
+      if (!__all_sync(0xffffffffu, mbar_wait(bar_s, g & 1, abort_flag))) { ok = false; break; }
       tc_fence_after();
       // Valid columns of this block for this row: c < lim. Whole 32-column groups
       // past every row of the warp are skipped (no max, no exp2, zeros written);
@@ -268,7 +321,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       }
       const float mx_half = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * P.scale_log2;
       float mx_other;
-      if (!pair_exchange(j, mx_half, mx_other)) { ok = false; break; }
+      if (!pair_exchange(xu++, mx_half, mx_other)) { ok = false; break; }
       const float m_new = fmaxf(m_used, fmaxf(mx_half, mx_other));
       const bool resc = (m_new > m_used) && (m_used == -INFINITY || m_new - m_used > 8.f);
       float alpha = 1.f;
@@ -278,7 +331,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         m_used = m_new;
       }
       if (j > 0) {   // P buffer free and O stable once the previous P V has completed
-        if (!__all_sync(0xffffffffu, mbar_wait(bar_o, (j - 1) & 1, abort_flag))) { ok = false; break; }
+        if (!__all_sync(0xffffffffu, mbar_wait(bar_o, (g - 1) & 1, abort_flag))) { ok = false; break; }
         tc_fence_after();
       }
       const float msub = m_used == -INFINITY ? 0.f : m_used;   // a fully masked row has only -inf entries
@@ -318,22 +371,26 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       tc_fence_before();
       mbar_arrive(bar_p);
     }
+    if (!ok) break;
     float l_other = 0.f;
-    if (ok) ok = pair_exchange(n_kv, l, l_other);
-    if (ok && __all_sync(0xffffffffu, mbar_wait(bar_o, (n_kv - 1) & 1, abort_flag))) {
+    ok = pair_exchange(xu++, l, l_other);
+    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar_o, (gb + n_kv - 1) & 1, abort_flag));
+    if (ok) {
       tc_fence_after();
       const float l_row = l + l_other;
       const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
       // O leaves through shared memory: one warp per 32 rows x 64 columns stages 128-byte rows
-      // (swizzled) in the now idle K buffer and one lane issues a TMA store, which clips rows
-      // past the sequence end. At head_dim 64 the warps of column half 1 have nothing to store.
+      // (swizzled) in its own buffer and one lane issues a TMA store, which clips rows past the
+      // sequence end. At head_dim 64 the warps of column half 1 have nothing to store.
       if (D == 128 || hf == 0) {
         const int dc = D == 128 ? hf : 0;
-        uint8_t* stage = base_ptr + Cfg::kOffK + warp * 4096;
+        uint8_t* stage = base_ptr + Cfg::kOffStage + warp * 4096;
         uint32_t r[64];
         tmem_ld32(tmem_o + lane_addr + dc * 64, r);
         tmem_ld32(tmem_o + lane_addr + dc * 64 + 32, r + 32);
         tmem_ld_wait();
+        if (lane == 0) bulk_wait_read<0>();   // the previous tile's store has read the buffer
+        __syncwarp();
 #pragma unroll
         for (int c16 = 0; c16 < 8; ++c16) {
           uint4 v;
@@ -348,12 +405,15 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         if (lane == 0) {
           store_rows(&tmO, smem_u32(stage), P.po, dc * 64, qb * 128 + qtr * 32, h, b);
           bulk_commit();
-          bulk_wait_all<0>();   // shared memory must stay valid until the store has read it
         }
         __syncwarp();
       }
       if (hf == 0 && q_glob < P.S) P.lse[(int64_t)bh * P.S + q_glob] = (m_used + log2f(l_row)) * kLn2F;
     }
+    gb += n_kv;
+    }   // tiles
+    if (lane == 0) bulk_wait_all<0>();   // the stores must be done with shared memory before the CTA exits
+    __syncwarp();
   }
 
   tc_fence_before();
@@ -403,7 +463,16 @@ static int launch_fwd(const AttnArgs& a, cudaStream_t st) {
   }
   auto kern = attn_fwd_tc_kernel<D, T>;
   MT_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
-  const unsigned grid = (unsigned)(P.nqb * P.B * P.H);
+  const int64_t n_tiles = (int64_t)P.nqb * P.B * P.H;
+  const int64_t resident = (int64_t)sm_count() * (D == 64 ? 2 : 1);
+  int64_t grid_i = n_tiles < resident ? n_tiles : resident;   // persistent
+  // with heads in groups and causal (unequal) tiles, a group should be exactly two rounds of the
+  // grid - one dealt forwards, one backwards - so that every CTA gets a heavy and a light tile of
+  // it; that costs a few CTAs (144 of 148 at 16 blocks per head)
+  if (a.causal && P.gh < P.B * P.H && (P.gh * P.nqb) % 2 == 0 && (int64_t)P.gh * P.nqb / 2 >= resident * 7 / 8 &&
+      (int64_t)P.gh * P.nqb / 2 <= grid_i)
+    grid_i = (int64_t)P.gh * P.nqb / 2;
+  const unsigned grid = (unsigned)grid_i;
   kern<<<grid, kAttnThreads, Cfg::kSmem, st>>>(tq, tk, tv, to, P);
   MT_LAUNCH_CHECK();
   return MT_OK;
