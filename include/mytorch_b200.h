@@ -351,6 +351,12 @@ int mt_attn_decode(const void* q, const void* k_cache, const void* v_cache, void
                    mt_strides3 sq, mt_strides3 skv, mt_strides3 so,
                    int64_t batch, int64_t heads, int64_t q_len, int64_t kv_len, int64_t head_dim,
                    float scale, int causal_offset, int dtype, void* stream);
+/* The same with the cache holding kv_heads heads per batch and query head h reading head
+ * h / (heads / kv_heads) of it (grouped-query attention, nanochat_gpt.py:78-90, 126-160). */
+int mt_attn_decode_gqa(const void* q, const void* k_cache, const void* v_cache, void* o,
+                       mt_strides3 sq, mt_strides3 skv, mt_strides3 so,
+                       int64_t batch, int64_t heads, int64_t kv_heads, int64_t q_len, int64_t kv_len,
+                       int64_t head_dim, float scale, int causal_offset, int dtype, void* stream);
 int mt_kv_append(const void* k_new, const void* v_new, void* k_cache, void* v_cache,
                  mt_strides3 sk, mt_strides3 sv, mt_strides3 scache,
                  int64_t batch, int64_t heads, int64_t n_new, int64_t pos0, int64_t max_len,

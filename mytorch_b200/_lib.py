@@ -121,6 +121,7 @@ _SIG = {
                         _i64, _i64, _i64, _i64, _i64, _f, _i, _i, _p],
     "mt_attn_force_simt": [_i],
     "mt_attn_decode": [_p, _p, _p, _p, _S, _S, _S, _i64, _i64, _i64, _i64, _i64, _f, _i, _i, _p],
+    "mt_attn_decode_gqa": [_p, _p, _p, _p, _S, _S, _S, _i64, _i64, _i64, _i64, _i64, _i64, _f, _i, _i, _p],
     "mt_kv_append": [_p, _p, _p, _p, _S, _S, _S, _i64, _i64, _i64, _i64, _i64, _i64, _i, _p],
     "mt_gradnorm_multi": [C.POINTER(TensorList), _i, _p, _p, _p, _p],
     "mt_adamw_multi": [C.POINTER(TensorList), _i, _i, _f, C.c_double, C.c_double, _f, _p, _p, _f, _p, _i, _p, _i, _p],

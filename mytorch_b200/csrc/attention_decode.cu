@@ -22,8 +22,8 @@ constexpr int kDecWarps = 4;
 template <typename T, int D>
 __global__ void __launch_bounds__(kDecWarps * 32)
 attn_decode_kernel(const T* __restrict__ q, const T* __restrict__ kc, const T* __restrict__ vc, T* __restrict__ o,
-                   mt_strides3 sq, mt_strides3 skv, mt_strides3 so, int heads, int q_len, int kv_len, float scale_log2,
-                   int causal_offset) {
+                   mt_strides3 sq, mt_strides3 skv, mt_strides3 so, int heads, int group, int q_len, int kv_len,
+                   float scale_log2, int causal_offset) {
   constexpr int VN = Vec16<T>::N;
   __shared__ float q_s[D];
   __shared__ float red_m[kDecWarps], red_l[kDecWarps];
@@ -37,8 +37,9 @@ attn_decode_kernel(const T* __restrict__ q, const T* __restrict__ kc, const T* _
   __syncthreads();
   // keys this query may see: all of them, or those at positions <= causal_offset + qi
   const int n_keys = causal_offset < 0 ? kv_len : min(kv_len, causal_offset + qi + 1);
-  const T* kbase = kc + (int64_t)b * skv.b + (int64_t)h * skv.h;
-  const T* vbase = vc + (int64_t)b * skv.b + (int64_t)h * skv.h;
+  const int hk = h / group;                      // key/value head of this query head (grouped-query attention)
+  const T* kbase = kc + (int64_t)b * skv.b + (int64_t)hk * skv.h;
+  const T* vbase = vc + (int64_t)b * skv.b + (int64_t)hk * skv.h;
   float m = -INFINITY, l = 0.f;
   float acc[D];
 #pragma unroll
@@ -127,12 +128,12 @@ kv_append_kernel(const T* __restrict__ k_new, const T* __restrict__ v_new, T* __
 
 template <typename T, int D>
 static int launch_decode(const void* q, const void* kc, const void* vc, void* o, mt_strides3 sq, mt_strides3 skv,
-                         mt_strides3 so, int64_t batch, int64_t heads, int64_t q_len, int64_t kv_len, float scale,
-                         int causal_offset, cudaStream_t st) {
+                         mt_strides3 so, int64_t batch, int64_t heads, int64_t kv_heads, int64_t q_len, int64_t kv_len,
+                         float scale, int causal_offset, cudaStream_t st) {
   const int64_t blocks = batch * heads * q_len;
   attn_decode_kernel<T, D><<<(unsigned)blocks, kDecWarps * 32, 0, st>>>(
-      (const T*)q, (const T*)kc, (const T*)vc, (T*)o, sq, skv, so, (int)heads, (int)q_len, (int)kv_len,
-      scale * 1.4426950408889634f, causal_offset);
+      (const T*)q, (const T*)kc, (const T*)vc, (T*)o, sq, skv, so, (int)heads, (int)(heads / kv_heads), (int)q_len,
+      (int)kv_len, scale * 1.4426950408889634f, causal_offset);
   MT_LAUNCH_CHECK();
   return MT_OK;
 }
@@ -143,11 +144,12 @@ using namespace mt;
 
 extern "C" {
 
-int mt_attn_decode(const void* q, const void* k_cache, const void* v_cache, void* o, mt_strides3 sq, mt_strides3 skv,
-                   mt_strides3 so, int64_t batch, int64_t heads, int64_t q_len, int64_t kv_len, int64_t head_dim,
-                   float scale, int causal_offset, int dtype, void* stream) {
+int mt_attn_decode_gqa(const void* q, const void* k_cache, const void* v_cache, void* o, mt_strides3 sq, mt_strides3 skv,
+                       mt_strides3 so, int64_t batch, int64_t heads, int64_t kv_heads, int64_t q_len, int64_t kv_len,
+                       int64_t head_dim, float scale, int causal_offset, int dtype, void* stream) {
   MT_REQUIRE(q && k_cache && v_cache && o && batch >= 0 && heads > 0 && q_len >= 0 && kv_len >= 0 && head_dim > 0,
              "attn_decode: bad arguments");
+  MT_REQUIRE(kv_heads > 0 && heads % kv_heads == 0, "attn_decode: query heads must be a multiple of key/value heads");
   MT_REQUIRE(head_dim == 64 || head_dim == 128, "attn_decode: head_dim must be 64 or 128");
   MT_REQUIRE(batch * heads * q_len < (1ll << 31), "attn_decode: too many query rows");
   constexpr int64_t kAlign = 8;   // 16-byte vector loads of half rows (4 for fp32 rows is implied)
@@ -156,13 +158,20 @@ int mt_attn_decode(const void* q, const void* k_cache, const void* v_cache, void
   if (batch == 0 || q_len == 0) return MT_OK;
   cudaStream_t st = as_stream(stream);
 #define MT_DEC(T)                                                                                                   \
-  return head_dim == 64 ? launch_decode<T, 64>(q, k_cache, v_cache, o, sq, skv, so, batch, heads, q_len, kv_len,    \
-                                                scale, causal_offset, st)                                            \
-                        : launch_decode<T, 128>(q, k_cache, v_cache, o, sq, skv, so, batch, heads, q_len, kv_len,   \
-                                                 scale, causal_offset, st)
+  return head_dim == 64 ? launch_decode<T, 64>(q, k_cache, v_cache, o, sq, skv, so, batch, heads, kv_heads, q_len,  \
+                                                kv_len, scale, causal_offset, st)                                    \
+                        : launch_decode<T, 128>(q, k_cache, v_cache, o, sq, skv, so, batch, heads, kv_heads, q_len, \
+                                                 kv_len, scale, causal_offset, st)
   MT_DISPATCH_FLOAT(dtype, T, MT_DEC(T));
 #undef MT_DEC
   return MT_OK;
+}
+
+int mt_attn_decode(const void* q, const void* k_cache, const void* v_cache, void* o, mt_strides3 sq, mt_strides3 skv,
+                   mt_strides3 so, int64_t batch, int64_t heads, int64_t q_len, int64_t kv_len, int64_t head_dim,
+                   float scale, int causal_offset, int dtype, void* stream) {
+  return mt_attn_decode_gqa(q, k_cache, v_cache, o, sq, skv, so, batch, heads, heads, q_len, kv_len, head_dim, scale,
+                            causal_offset, dtype, stream);
 }
 
 int mt_kv_append(const void* k_new, const void* v_new, void* k_cache, void* v_cache, mt_strides3 sk, mt_strides3 sv,

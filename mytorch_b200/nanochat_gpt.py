@@ -109,22 +109,21 @@ class Attention(nn.Module):
         v = self.v_proj(x).reshape(B, T, Hk, D)
         cos, sin = cos_sin
         q, k = F.rope_qk_norm(q, k, cos, sin)                    # rotary first, then QK-norm over head_dim: one kernel
-        if cache is not None and Hk != H:
-            raise NotImplementedError("cached decoding with grouped-query heads is not built (training and uncached "
-                                      "inference are)")
         if cache is not None:
             # inference: new keys/values join the cache; the prompt (empty cache) attends causally
             # among its own tokens, later tokens see everything cached (nanochat_gpt.py:126-160)
             past = cache.pos
-            sin3 = _lib.Strides3(T * H * D, D, H * D)
-            kc, vc, kv_len = cache.update(k.data.ptr, v.data.ptr, sin3, T, k.data.dtype, layer_idx)
+            sin3 = _lib.Strides3(T * H * D, D, H * D)               # q [B, T, H, D] as (batch, head, row)
+            skv3 = _lib.Strides3(T * Hk * D, D, Hk * D)             # k, v [B, T, Hk, D]: the cache holds Hk heads
+            kc, vc, kv_len = cache.update(k.data.ptr, v.data.ptr, skv3, T, k.data.dtype, layer_idx)
             if past == 0:
                 out = F.bthd_attention(q, k, v, is_causal=True)
             else:
                 S = cache.cache_shape[3]
                 o = DeviceArray.empty((B, T, E), q.data.dtype)
-                _lib.attn_decode(q.data.ptr, kc.ptr, vc.ptr, o.ptr, sin3, _lib.Strides3(H * S * D, S * D, D),
-                                 _lib.Strides3(T * E, D, E), B, H, T, kv_len, D, float(D) ** -0.5, past, q.data.code, stream())
+                _lib.attn_decode_gqa(q.data.ptr, kc.ptr, vc.ptr, o.ptr, sin3, _lib.Strides3(Hk * S * D, S * D, D),
+                                     _lib.Strides3(T * E, D, E), B, H, Hk, T, kv_len, D, float(D) ** -0.5, past,
+                                     q.data.code, stream())
                 out = Tensor(o)
         else:
             out = F.bthd_attention(q, k, v, is_causal=True)       # [B, T, E], heads read in place
@@ -232,7 +231,7 @@ class GPT(nn.Module):
         cfg = self.config
         rng = np.random.default_rng(seed)
         ids = np.asarray(input_ids.numpy() if isinstance(input_ids, Tensor) else input_ids, dtype=np.int32)
-        cache = KVCache(ids.shape[0], cfg.num_q_heads, cfg.max_seq_len, cfg.embed_dim // cfg.num_q_heads, cfg.num_blocks)
+        cache = KVCache(ids.shape[0], cfg.num_kv_heads, cfg.max_seq_len, cfg.embed_dim // cfg.num_q_heads, cfg.num_blocks)
         was_training = self.training
         self.eval()
         feed = ids

@@ -644,14 +644,17 @@ def test_fused_cross_entropy_backward_trains_like_the_two_pass_form():
             assert np.abs(ga[n] - gb[n]).max() <= 1e-5 * max(1.0, np.abs(ga[n]).max()), (n, upstream)
 
 
-def test_nanochat_kv_cache_decoding_matches_the_full_forward():
+@pytest.mark.parametrize("kv_heads", [2, 1])
+def test_nanochat_kv_cache_decoding_matches_the_full_forward(kv_heads):
     """nanochat inference branch (nanochat_gpt.py:301-340, core/cache.py): prompt then token by
     token through the KVCache (rotary positions continue after the cache, head_dim 128 through the
     decode-attention kernel) gives the soft-capped logits of the uncached forward, which the
-    training parity test pins to the reference."""
+    training parity test pins to the reference. With one key/value head for the two query heads
+    the cache holds that one head and both query heads read it (grouped-query attention)."""
     import mytorch_b200 as mt
     from mytorch_b200.nanochat_gpt import GPT, GPTConfig, KVCache
-    cfg = GPTConfig(vocab_size=160, max_seq_len=48, embed_dim=256, mlp_ratio=4, num_blocks=2, num_q_heads=2, num_kv_heads=2)
+    cfg = GPTConfig(vocab_size=160, max_seq_len=48, embed_dim=256, mlp_ratio=4, num_blocks=2, num_q_heads=2,
+                    num_kv_heads=kv_heads)
     np.random.seed(5)
     model = GPT(cfg)
     r = np.random.default_rng(6)
@@ -663,7 +666,7 @@ def test_nanochat_kv_cache_decoding_matches_the_full_forward():
     with mt.no_grad():
         full = model(mt.Tensor(ids), None)[0].numpy()
         assert np.abs(full).max() <= cfg.softcap
-        cache = KVCache(2, 2, 48, 128, 2)
+        cache = KVCache(2, kv_heads, 48, 128, 2)
         out, cache = model(mt.Tensor(ids[:, :11]), None, cache=cache)
         got = [out.numpy()]
         for n in range(11, 26):
