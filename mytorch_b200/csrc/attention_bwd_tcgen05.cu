@@ -476,6 +476,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       }
     };
     int g0 = 0;                                       // running count of query blocks at the start of the tile
+    int pend_qi = 0, pend_bh = 0;                     // head_dim 64: query block whose dQ is still in tensor memory
     for (int round = 0, tcount_ew = 0; round * (int)gridDim.x < n_tiles && ok; ++round) {
       const int tile = tile_of_round(round, n_tiles);
       if (tile < 0) continue;
@@ -566,12 +567,21 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         tc_fence_before();
         mbar_arrive(bar_pds);
         // dQ read-out. With its own TMEM columns the PREVIOUS block's dQ is flushed here, while the
-        // tensor core works on this block; when dQ aliases S^T it has to be this block's.
-        const int fi = Cfg::kAliasDQ ? i : i - 1;
-        if (fi >= 0) {
-          if (!__all_sync(0xffffffffu, mbar_wait(bar_dq, (g0 + fi) & 1, abort_flag))) { ok = false; break; }
+        // tensor core works on this block - also across a tile boundary: a tile's last dQ stays in
+        // tensor memory until the next tile's first block (the dQ MMA of that block waits for the
+        // read-out as it does for any other), so the tile's end is not held up by a second batch of
+        // reduce-adds right behind the previous one. When dQ aliases dP^T it has to be this block's.
+        if (Cfg::kAliasDQ) {
+          if (!__all_sync(0xffffffffu, mbar_wait(bar_dq, g & 1, abort_flag))) { ok = false; break; }
           tc_fence_after();
-          flush_dq(qi_of(fi), bh_of(fi), fi == n_q - 1 ? gate_last : -1);
+          flush_dq(qi, bh_of(i), i == n_q - 1 ? gate_last : -1);
+        } else {
+          if (g > 0) {
+            if (!__all_sync(0xffffffffu, mbar_wait(bar_dq, (g - 1) & 1, abort_flag))) { ok = false; break; }
+            tc_fence_after();
+            flush_dq(pend_qi, pend_bh, -1);
+          }
+          pend_qi = qi; pend_bh = bh_of(i);
         }
       }
       if (!ok) break;
@@ -579,7 +589,6 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         // the tile's last dQ; its completion also means every MMA of the tile is complete
         if (!__all_sync(0xffffffffu, mbar_wait(bar_dq, (g0 + n_q - 1) & 1, abort_flag))) { ok = false; break; }
         tc_fence_after();
-        flush_dq(qi_of(n_q - 1), bh_of(n_q - 1), gate_last);
       }
       // All MMAs of the tile are complete (its last bar_dq was waited above, in either variant).
       // Each 64-column piece of dK and of dV is drained by one column group: 32 key rows at a time
@@ -618,6 +627,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       }
       g0 += n_q;
     }
+    if (!Cfg::kAliasDQ && ok && g0 > 0) flush_dq(pend_qi, pend_bh, -1);   // the very last block's dQ
     if (lane == 0) bulk_wait_all<0>();   // reduces and stores must be done with shared memory before the CTA exits
     __syncwarp();
   }
