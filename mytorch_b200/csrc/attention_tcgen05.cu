@@ -31,6 +31,7 @@
 #include "attention.cuh"
 #include "sm100.cuh"
 #include "attention_tc.cuh"
+#include "tempbuf.cuh"
 
 namespace mt {
 
@@ -68,6 +69,7 @@ struct AttnFwdParams {
   int gh;               // (batch, head) pairs per group of the CTA order
   float scale_log2;
   int* flag;
+  int* tile_counter;    // zero at launch: the next tile nobody has taken yet
 };
 
 
@@ -89,33 +91,33 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   const uint32_t bar_q = bar0, bar_kfull0 = bar0 + 8, bar_kempty0 = bar0 + 24, bar_vfull0 = bar0 + 40,
                  bar_vempty0 = bar0 + 56, bar_s = bar0 + 72, bar_p = bar0 + 80, bar_o = bar0 + 88,
                  bar_sfree = bar0 + 96, bar_pair0 = bar0 + 104,   // four pair barriers: +104 .. +135
-                 bar_qfree = bar0 + 136;
+                 bar_qfree = bar0 + 136, bar_tfull0 = bar0 + 160, bar_tempty0 = bar0 + 176;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + Cfg::kOffBar + 144);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + Cfg::kOffBar + 148);
   float* xchg = reinterpret_cast<float*>(base_ptr + Cfg::kOffX);   // [2 buffers][2 halves][128 rows]
+  volatile int* tile_ring = reinterpret_cast<volatile int*>(base_ptr + Cfg::kOffBar + 152);   // two slots
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int bh_count = P.B * P.H;
   const int n_tiles = P.nqb * bh_count;
   const int n_kv_total = (P.S + 127) / 128;
-  // The kernel is persistent: as many CTAs as are resident at once, each taking one tile per round
-  // of gridDim.x tiles (tile_of_round: forwards in even rounds, backwards in odd ones). Tile order
-  // (decode_tile): heads in groups of P.gh, within a group the heaviest (last) query blocks
-  // first, so that the CTAs working at one time read the K and V of a few heads only. Every role
-  // walks the same tile sequence with a running block count, from which ring stages and barrier
+  // The kernel is persistent: as many CTAs as are resident at once, each taking the next tile
+  // nobody has taken yet from a global counter (so a CTA that starts late, or shares its SM with
+  // another kernel, simply takes fewer). Tile order (decode_tile): heads in groups of P.gh, within
+  // a group the heaviest (last) query blocks first, so that the CTAs working at one time read the K
+  // and V of a few heads only and the light tiles fill the end. The producer thread takes the
+  // tiles and hands each to the MMA and softmax warps through a two-slot ring in shared memory
+  // (-1 = no more). Every role keeps a running block count, from which ring stages and barrier
   // parities follow; barriers and tensor memory are set up once, and the next tile's Q, K and
   // first scores are under way while this tile's O is still being written out.
   struct Tile { int qb, b, h, hk, n_kv; };
-  auto tile_at = [&](int round, Tile& t) -> bool {
-    const int tile = tile_of_round(round, n_tiles);
-    if (tile < 0) return false;
+  auto decode = [&](int tile, Tile& t) {
     int slot, bh;
     decode_tile(tile, P.nqb, bh_count, P.gh, slot, bh);
     t.qb = P.nqb - 1 - slot;
     t.b = bh / P.H; t.h = bh % P.H;
     t.hk = t.h / P.group;                                // key/value head of this query head
     t.n_kv = P.causal ? min(t.qb + 1, n_kv_total) : n_kv_total;
-    return true;
   };
 
   if (threadIdx.x == 0) {
@@ -126,6 +128,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     mbar_init(bar_vempty0, 1); mbar_init(bar_vempty0 + 8, 1);
     mbar_init(bar_s, 1); mbar_init(bar_p, 32 * kSoftmaxWarps); mbar_init(bar_o, 1); mbar_init(bar_sfree, kSoftmaxWarps);
     mbar_init(bar_qfree, 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(bar_tfull0 + 8 * i, 1); mbar_init(bar_tempty0 + 8 * i, 1 + kSoftmaxWarps); }
     for (int i = 0; i < 4; ++i) mbar_init(bar_pair0 + 8 * i, 2);
     *abort_flag = 0;
     fence_barrier_init();
@@ -148,11 +151,17 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       int gb = 0;                                        // blocks before this tile (running count)
       bool okp = true;
       Tile t;
-      for (int round = 0, tn = 0; round * (int)gridDim.x < n_tiles && okp; ++round) {
-        if (!tile_at(round, t)) continue;
+      for (int tn = 0; okp; ++tn) {
+        // take the next tile and publish it (slot tn & 1 is free once the consumers have read tile tn - 2)
+        if (!mbar_wait(bar_tempty0 + 8 * (tn & 1), ((tn >> 1) & 1) ^ 1u, abort_flag)) break;
+        int tile = atomicAdd(P.tile_counter, 1);
+        if (tile >= n_tiles) tile = -1;
+        tile_ring[tn & 1] = tile;
+        mbar_arrive(bar_tfull0 + 8 * (tn & 1));
+        if (tile < 0) break;
+        decode(tile, t);
         // Q is read by every score MMA of a tile: the buffer is free once the previous tile's last one is done
         if (tn > 0 && !mbar_wait(bar_qfree, (tn - 1) & 1, abort_flag)) break;
-        ++tn;
         mbar_expect_tx(bar_q, Cfg::kTile);
 #pragma unroll
         for (int dc = 0; dc < Cfg::kChunks; ++dc)
@@ -222,10 +231,13 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       int gb = 0;
       bool ok = true;
       Tile t;
-      for (int round = 0, tn = 0; round * (int)gridDim.x < n_tiles && ok; ++round) {
-        if (!tile_at(round, t)) continue;
+      for (int tn = 0; ok; ++tn) {
+        if (!mbar_wait(bar_tfull0 + 8 * (tn & 1), (tn >> 1) & 1, abort_flag)) break;
+        const int tile = tile_ring[tn & 1];
+        mbar_arrive(bar_tempty0 + 8 * (tn & 1));
+        if (tile < 0) break;
+        decode(tile, t);
         if (!mbar_wait(bar_q, tn & 1, abort_flag)) break;
-        ++tn;
         // the softmax warps have copied the previous tile's last scores to registers
         if (gb > 0 && !mbar_wait(bar_sfree, (gb - 1) & 1, abort_flag)) break;
         tc_fence_after();
@@ -277,8 +289,13 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       other = slot[(hf ^ 1) * 128 + row];
       return true;
     };
-    for (int round = 0; round * (int)gridDim.x < n_tiles && ok; ++round) {
-    if (!tile_at(round, t)) continue;
+    for (int tn = 0; ok; ++tn) {
+    if (!__all_sync(0xffffffffu, mbar_wait(bar_tfull0 + 8 * (tn & 1), (tn >> 1) & 1, abort_flag))) { ok = false; break; }
+    const int tile = tile_ring[tn & 1];
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar_tempty0 + 8 * (tn & 1));
+    if (tile < 0) break;
+    decode(tile, t);
     const int qb = t.qb, b = t.b, h = t.h, n_kv = t.n_kv, bh = b * P.H + h;
     const int q_glob = qb * 128 + row;
     float m_used = -INFINITY, l = 0.f;
@@ -465,13 +482,11 @@ static int launch_fwd(const AttnArgs& a, cudaStream_t st) {
   MT_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
   const int64_t n_tiles = (int64_t)P.nqb * P.B * P.H;
   const int64_t resident = (int64_t)sm_count() * (D == 64 ? 2 : 1);
-  int64_t grid_i = n_tiles < resident ? n_tiles : resident;   // persistent
-  // with heads in groups and causal (unequal) tiles, a group should be exactly two rounds of the
-  // grid - one dealt forwards, one backwards - so that every CTA gets a heavy and a light tile of
-  // it; that costs a few CTAs (144 of 148 at 16 blocks per head)
-  if (a.causal && P.gh < P.B * P.H && (P.gh * P.nqb) % 2 == 0 && (int64_t)P.gh * P.nqb / 2 >= resident * 7 / 8 &&
-      (int64_t)P.gh * P.nqb / 2 <= grid_i)
-    grid_i = (int64_t)P.gh * P.nqb / 2;
+  const int64_t grid_i = n_tiles < resident ? n_tiles : resident;   // persistent
+  TempBuf counter(sizeof(int), st);
+  if (!counter.ok()) return MT_ERR_CUDA;
+  MT_CHECK_CUDA(cudaMemsetAsync(counter.ptr, 0, sizeof(int), st));
+  P.tile_counter = (int*)counter.ptr;
   const unsigned grid = (unsigned)grid_i;
   kern<<<grid, kAttnThreads, Cfg::kSmem, st>>>(tq, tk, tv, to, P);
   MT_LAUNCH_CHECK();
