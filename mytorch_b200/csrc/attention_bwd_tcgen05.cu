@@ -2,8 +2,9 @@
 //
 // A tile is one (batch, head, block of 128 key/value rows): the CTA that owns it walks the query
 // blocks that attend to it (all of them, or those at/after the diagonal when causal). The kernel
-// is persistent: one CTA per SM takes one tile per round of gridDim.x tiles (heaviest first,
-// dealt in alternating directions), tensor memory and barriers are set up once, and the roles
+// is persistent: one CTA per SM takes the next tile nobody has taken yet from a global counter
+// (heaviest first; the producer thread fetches and hands the tile to the other roles through a
+// two-slot ring in shared memory), tensor memory and barriers are set up once, and the roles
 // run ahead across tile boundaries - the producer loads the next tile's K/V as soon as the last
 // MMA reading the current ones has completed and keeps the Q/dO ring filled, the MMA warp issues
 // the next tile's first S^T/dP^T while the elementwise warps still flush dQ and drain dK/dV of
@@ -42,11 +43,6 @@
 #include "sm100.cuh"
 #include "attention_tc.cuh"
 #include "tempbuf.cuh"
-#include <algorithm>
-#include <array>
-#include <map>
-#include <mutex>
-#include <vector>
 
 namespace mt {
 
@@ -107,6 +103,7 @@ struct AttnBwdParams {
   int B, H, S, nqb, causal, is_bf16;
   int Hkv, group;       // key/value heads; query heads per key/value head (H = Hkv * group)
   int gh;               // (batch, key/value head) pairs per group of the tile order
+  int* tile_counter;    // zero at launch (the statistics kernel clears it): the next tile nobody has taken yet
   float scale, scale_log2;
   int* flag;
 };
@@ -132,18 +129,18 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   const uint32_t bar_kv = bar0, bar_qfull0 = bar0 + 8, bar_qempty0 = bar0 + 32, bar_sdp = bar0 + 56,
                  bar_pds = bar0 + 64, bar_dq = bar0 + 72, bar_dqfree = bar0 + 80, bar_sdpfree = bar0 + 88,
                  bar_kvfree = bar0 + 96, bar_dkvfree = bar0 + 104, bar_dofull = bar0 + 128, bar_doempty = bar0 + 136,
-                 bar_kvissued = bar0 + 144;
+                 bar_kvissued = bar0 + 144, bar_tfull0 = bar0 + 152, bar_tempty0 = bar0 + 168;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + Cfg::kOffBar + 112);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + Cfg::kOffBar + 116);
   float* stat = reinterpret_cast<float*>(base_ptr + Cfg::kOffStat);
+  volatile int* tile_ring = reinterpret_cast<volatile int*>(base_ptr + Cfg::kOffBar + 120);   // two slots
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int bh_count = P.B * P.Hkv;           // (batch, key/value head) pairs
   const int n_tiles = P.nqb * bh_count;
   // Tile t -> (key block jb, (batch, key/value head)) by decode_tile: heads in groups of P.gh,
-  // within a group small jb first (= most query blocks when causal, so heavy tiles come first; a
-  // group is two rounds of gridDim.x tiles, dealt forwards then backwards, so every CTA gets a heavy
-  // and a light tile of it). The tile's steps are the query blocks of
+  // within a group small jb first (= most query blocks when causal, so heavy tiles come first and
+  // the light ones fill the end). The tile's steps are the query blocks of
   // every query head that reads this key/value head: step i = (query head hk*group + i / n_qb,
   // query block q_start + i % n_qb); dK and dV accumulate over all of them. Every role walks the
   // same tile sequence and keeps a running count `g` of steps, from which ring stages and barrier
@@ -159,6 +156,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     mbar_init(bar_dkvfree, 8 * Cfg::kChunks);       // one arrival per warp that drains a 64-column piece of dK or dV
     mbar_init(bar_dofull, 1); mbar_init(bar_doempty, 1);
     mbar_init(bar_kvissued, 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(bar_tfull0 + 8 * i, 1); mbar_init(bar_tempty0 + 8 * i, 1 + kBwdEwWarps); }
     *abort_flag = 0;
     fence_barrier_init();
     fence_proxy_async();
@@ -178,27 +176,35 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV); prefetch_tmap(&tmDO);
       // One step of this CTA's work: a query block of a tile. Steps are numbered g = 0, 1, ... across
       // tiles; `tn` counts the tiles.
-      struct Step { int round, tn, i, n_q, n_qb, q_start, jb, b, h; bool valid; };
-      auto enter_round = [&](Step& st) {      // finds the tile of st.round (or a later one); i = 0
+      struct Step { int tn, i, n_q, n_qb, q_start, jb, b, h; bool valid; };
+      // Takes the next tile nobody has taken yet as this CTA's tile number st.tn and publishes it
+      // to the other roles (slot tn & 1 of the ring; -1 = no more); i = 0. The slot is free once the
+      // consumers have read tile tn - 2.
+      // (the counter is read one tile ahead: the atomic's round trip to L2 runs under the loads of
+      // the tile before)
+      int tile_ahead = atomicAdd(P.tile_counter, 1);
+      auto fetch = [&](Step& st) {
         st.valid = false;
-        for (; st.round * (int)gridDim.x < n_tiles; ++st.round) {
-          const int tile = tile_of_round(st.round, n_tiles);
-          if (tile < 0) continue;
-          int bkv;
-          decode_tile(tile, P.nqb, bh_count, P.gh, st.jb, bkv);
-          st.b = bkv / P.Hkv; st.h = bkv % P.Hkv;            // h: key/value head
-          st.q_start = P.causal ? st.jb : 0;
-          st.n_qb = P.nqb - st.q_start;
-          st.n_q = st.n_qb * P.group;
-          st.i = 0;
-          st.valid = true;
-          return;
-        }
+        if (!mbar_wait(bar_tempty0 + 8 * (st.tn & 1), ((st.tn >> 1) & 1) ^ 1u, abort_flag)) return;
+        int tile = tile_ahead;
+        if (tile < n_tiles) tile_ahead = atomicAdd(P.tile_counter, 1);
+        if (tile >= n_tiles) tile = -1;
+        tile_ring[st.tn & 1] = tile;
+        mbar_arrive(bar_tfull0 + 8 * (st.tn & 1));
+        if (tile < 0) return;
+        int bkv;
+        decode_tile(tile, P.nqb, bh_count, P.gh, st.jb, bkv);
+        st.b = bkv / P.Hkv; st.h = bkv % P.Hkv;              // h: key/value head
+        st.q_start = P.causal ? st.jb : 0;
+        st.n_qb = P.nqb - st.q_start;
+        st.n_q = st.n_qb * P.group;
+        st.i = 0;
+        st.valid = true;
       };
       auto advance = [&](Step& st) {
         if (++st.i < st.n_q) return;
-        ++st.round; ++st.tn;
-        enter_round(st);
+        ++st.tn;
+        fetch(st);
       };
       auto load_kv = [&](const Step& st) -> bool {
         // K and V of the previous tile are read until its last dQ MMA has completed
@@ -230,8 +236,8 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         return true;
       };
       Step cur;
-      cur.round = 0; cur.tn = 0;
-      enter_round(cur);
+      cur.tn = 0;
+      fetch(cur);
       if (!Cfg::kSplit) {
         bool ok = true;
         for (int g = 0; cur.valid; ++g, advance(cur)) {
@@ -346,10 +352,11 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       };
       int g0 = 0;                                       // running count of query blocks at the start of the tile
       bool ok = true;
-      for (int round = 0, tcount = 0; round * (int)gridDim.x < n_tiles && ok; ++round) {
-        const int tile = tile_of_round(round, n_tiles);
-        if (tile < 0) continue;
-        const int tn = tcount++;
+      for (int tn = 0; ok; ++tn) {
+        if (!mbar_wait(bar_tfull0 + 8 * (tn & 1), (tn >> 1) & 1, abort_flag)) break;
+        const int tile = tile_ring[tn & 1];
+        mbar_arrive(bar_tempty0 + 8 * (tn & 1));
+        if (tile < 0) break;
         int jb, bkv_unused;
         decode_tile(tile, P.nqb, bh_count, P.gh, jb, bkv_unused);
         const int n_q = (P.nqb - (P.causal ? jb : 0)) * P.group;
@@ -477,12 +484,12 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     };
     int g0 = 0;                                       // running count of query blocks at the start of the tile
     int pend_qi = 0, pend_bh = 0;                     // head_dim 64: query block whose dQ is still in tensor memory
-    for (int round = 0, tcount_ew = 0; round * (int)gridDim.x < n_tiles && ok; ++round) {
-      const int tile = tile_of_round(round, n_tiles);
-      if (tile < 0) continue;
-      const int tn_ew = tcount_ew++;
-      // the parity to wait for before this tile's last dQ reduce-adds, or -1 when no tile follows
-      const int gate_last = ((round + 1) * (int)gridDim.x < n_tiles && tile_of_round(round + 1, n_tiles) >= 0) ? ((tn_ew + 1) & 1) : -1;
+    for (int tn_ew = 0; ok; ++tn_ew) {
+      if (!__all_sync(0xffffffffu, mbar_wait(bar_tfull0 + 8 * (tn_ew & 1), (tn_ew >> 1) & 1, abort_flag))) { ok = false; break; }
+      const int tile = tile_ring[tn_ew & 1];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_tempty0 + 8 * (tn_ew & 1));
+      if (tile < 0) break;
       int jb, bkv;
       decode_tile(tile, P.nqb, bh_count, P.gh, jb, bkv);
       const int b = bkv / P.Hkv, h = bkv % P.Hkv;     // h: key/value head
@@ -574,7 +581,14 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         if (Cfg::kAliasDQ) {
           if (!__all_sync(0xffffffffu, mbar_wait(bar_dq, g & 1, abort_flag))) { ok = false; break; }
           tc_fence_after();
-          flush_dq(qi, bh_of(i), i == n_q - 1 ? gate_last : -1);
+          int gate = -1;
+          if (i == n_q - 1) {
+            // the producer published the tile after this one while it looked a step ahead; when
+            // there is one, this tile's last reduce-adds wait until its first loads are queued
+            if (!__all_sync(0xffffffffu, mbar_wait(bar_tfull0 + 8 * ((tn_ew + 1) & 1), ((tn_ew + 1) >> 1) & 1, abort_flag))) { ok = false; break; }
+            if (tile_ring[(tn_ew + 1) & 1] >= 0) gate = (tn_ew + 1) & 1;
+          }
+          flush_dq(qi, bh_of(i), gate);
         } else {
           if (g > 0) {
             if (!__all_sync(0xffffffffu, mbar_wait(bar_dq, (g - 1) & 1, abort_flag))) { ok = false; break; }
@@ -650,7 +664,8 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 attn_bwd_stats_kernel(const T* __restrict__ o, const T* __restrict__ d_o, const float* __restrict__ lse,
                       float* __restrict__ stats, float* __restrict__ dq_accum, mt_strides3 so, mt_strides3 sdo, int heads,
-                      int S, int spad, int D, int64_t total_rows, float scale) {
+                      int S, int spad, int D, int64_t total_rows, float scale, int* __restrict__ tile_counter) {
+  if (blockIdx.x == 0 && threadIdx.x == 0) *tile_counter = 0;   // the backward kernel's tile queue starts at 0
   constexpr int VN = Vec16<T>::N;
   const int sub = threadIdx.x & 7;
   const int64_t row = (int64_t)blockIdx.x * 32 + (threadIdx.x >> 3);   // over [B*H][spad]
@@ -707,36 +722,6 @@ bool attn_bwd_tc_supported(const AttnArgs& a) {
   return true;
 }
 
-// Heaviest CTA's share of query blocks over the ideal share (all of the work / SMs) when causal tiles
-// in the order of decode_tile (heads in groups of gh) are dealt to `grid` CTAs round by round,
-// forwards in even rounds and backwards in odd ones.
-static double dealing_imbalance(int bh_count, int nqb, int gh, int grid, int sms) {
-  // the same few shapes come back every step: remember the answers
-  static std::mutex mu;
-  static std::map<std::array<int, 5>, double> memo;
-  const std::array<int, 5> key = {bh_count, nqb, gh, grid, sms};
-  {
-    std::lock_guard<std::mutex> lock(mu);
-    auto it = memo.find(key);
-    if (it != memo.end()) return it->second;
-  }
-  std::vector<int64_t> load((size_t)grid, 0);
-  const int64_t n_tiles = (int64_t)bh_count * nqb;
-  for (int64_t t = 0; t < n_tiles; ++t) {
-    const int64_t per = (int64_t)gh * nqb, gi = t / per, r = t - gi * per;
-    const int64_t gh_cur = std::min<int64_t>(gh, bh_count - gi * gh);
-    const int jb = (int)(r / gh_cur);
-    const int64_t round = t / grid, idx = t - round * grid;
-    load[(size_t)((round & 1) ? grid - 1 - idx : idx)] += nqb - jb;
-  }
-  int64_t mx = 0, sum = 0;
-  for (int64_t v : load) { mx = std::max(mx, v); sum += v; }
-  const double res = sum ? (double)mx * sms / (double)sum : 1.0;
-  std::lock_guard<std::mutex> lock(mu);
-  if (memo.size() < 256) memo[key] = res;
-  return res;
-}
-
 template <int D, typename T>
 static int launch_bwd(const AttnArgs& a, cudaStream_t st) {
   using Cfg = BwdCfg<D>;
@@ -744,11 +729,12 @@ static int launch_bwd(const AttnArgs& a, cudaStream_t st) {
   int rc;
   const int nqb = (int)((a.seq + 127) / 128);
   const int64_t stat_rows = a.batch * a.heads * nqb * 128;
-  TempBuf stats((size_t)stat_rows * 2 * sizeof(float), st);
+  TempBuf stats((size_t)stat_rows * 2 * sizeof(float) + 16, st);   // + the tile counter
   if (!stats.ok()) return MT_ERR_CUDA;
+  int* tile_counter = reinterpret_cast<int*>(reinterpret_cast<float*>(stats.ptr) + stat_rows * 2);
   attn_bwd_stats_kernel<T><<<(unsigned)((stat_rows + 31) / 32), 256, 0, st>>>(
       (const T*)a.o, (const T*)a.d_o, a.lse, (float*)stats.ptr, a.dq_accum, a.so, a.sdo, (int)a.heads, (int)a.seq, nqb * 128, D,
-      stat_rows, a.scale);
+      stat_rows, a.scale, tile_counter);
   MT_LAUNCH_CHECK();
   const int64_t n_acc = a.batch * a.heads * a.seq * D;
   CUtensorMap tq, tk, tv, tdo;
@@ -774,26 +760,21 @@ static int launch_bwd(const AttnArgs& a, cudaStream_t st) {
   auto kern = attn_bwd_tc_kernel<D, T>;
   MT_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
   const int64_t n_tiles = (int64_t)P.nqb * P.B * P.Hkv;
-  // Persistent, one CTA per SM. Tile order: with every head in one group the CTAs that run at the
-  // same time each stream a different head's Q, dO and dQ, which together no longer fit in L2 once
-  // there are many long heads. Then heads are taken in groups of about 2 * SMs / blocks-per-head -
-  // a group is two rounds of the grid, and its footprint in L2 stays near 30 MB (head_dim 64) or
-  // 60 MB (128) whatever the sequence length - provided the fixed dealing of tiles to CTAs stays
-  // balanced (the last group is smaller, which can leave CTAs idle at the end).
-  int grid_i = (int)(n_tiles < sm_count() ? n_tiles : sm_count());
+  // Persistent, one CTA per SM; CTAs take tiles from a global counter, so the order below is also
+  // the order in time. With every head in one group the CTAs that run at the same time each
+  // stream a different head's Q, dO and dQ, which together no longer fit in L2 once there are many
+  // long heads: then heads are taken in groups of about 2 * SMs / blocks-per-head, whose footprint
+  // in L2 stays near 30 MB (head_dim 64) or 60 MB (128) whatever the sequence length.
+  const int grid_i = (int)(n_tiles < sm_count() ? n_tiles : sm_count());
   P.gh = (int)(P.B * P.Hkv);
+  P.tile_counter = tile_counter;
   const double footprint = (double)a.batch * a.heads * a.seq * D * 12.0;   // Q, dO, K, V (2 bytes each) + fp32 dQ
-  if (a.causal && P.nqb > 1 && n_tiles > 2 * (int64_t)sm_count() && footprint > 96e6) {
+  // (only well beyond the 126 MB of L2: CTAs of one group work on the same heads at the same time
+  // and their dQ reduce-adds then meet on the same rows - at 150 MB the groups cost 5-8 %, at 1 GB
+  // they gain 15 %)
+  if (P.nqb > 1 && n_tiles > 2 * (int64_t)sm_count() && footprint > 200e6) {
     const int gh = 2 * sm_count() / P.nqb > 1 ? 2 * sm_count() / P.nqb : 1;
-    if (gh < P.B * P.Hkv) {
-      int grid_g = grid_i;
-      if ((gh * P.nqb) % 2 == 0 && gh * P.nqb / 2 >= sm_count() * 7 / 8) grid_g = gh * P.nqb / 2;   // rounds line up with groups
-      if (dealing_imbalance(P.B * P.Hkv, P.nqb, gh, grid_g, sm_count()) <=
-          dealing_imbalance(P.B * P.Hkv, P.nqb, P.gh, grid_i, sm_count()) + 0.03) {
-        P.gh = gh;
-        grid_i = grid_g;
-      }
-    }
+    if (gh < P.gh) P.gh = gh;
   }
   const unsigned grid = (unsigned)grid_i;
   kern<<<grid, Cfg::kThreads, Cfg::kSmem, st>>>(tq, tk, tv, tdo, tdq, tdk, tdv, P);

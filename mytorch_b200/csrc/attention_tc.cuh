@@ -28,17 +28,6 @@ __device__ __forceinline__ void decode_tile(int tile, int n_blocks, int bh_count
   bh = gi * gh + (r - slot * gh_cur);
 }
 
-// Tiles are dealt to the persistent CTAs round by round, forwards in even rounds and backwards
-// in odd ones: with tiles sorted heaviest first, the CTA that got the heaviest tile of one round
-// gets the lightest of the next, which keeps the CTAs' totals within a few percent of each other.
-// Returns -1 when this CTA has no tile in the (last, partial) round.
-__device__ __forceinline__ int tile_of_round(int round, int n_tiles) {
-  const int G = (int)gridDim.x;
-  const int idx = (round & 1) ? G - 1 - (int)blockIdx.x : (int)blockIdx.x;
-  const int tile = round * G + idx;
-  return tile < n_tiles ? tile : -1;
-}
-
 __device__ __forceinline__ void load_rows(uint32_t dst, const CUtensorMap* map, uint32_t bar, MapPos pos, int d0, int row0,
                                           int h, int b) {
   int c[4];

@@ -151,10 +151,12 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       int gb = 0;                                        // blocks before this tile (running count)
       bool okp = true;
       Tile t;
+      int tile_ahead = atomicAdd(P.tile_counter, 1);   // read one tile ahead: the round trip runs under the loads before
       for (int tn = 0; okp; ++tn) {
         // take the next tile and publish it (slot tn & 1 is free once the consumers have read tile tn - 2)
         if (!mbar_wait(bar_tempty0 + 8 * (tn & 1), ((tn >> 1) & 1) ^ 1u, abort_flag)) break;
-        int tile = atomicAdd(P.tile_counter, 1);
+        int tile = tile_ahead;
+        if (tile < n_tiles) tile_ahead = atomicAdd(P.tile_counter, 1);
         if (tile >= n_tiles) tile = -1;
         tile_ring[tn & 1] = tile;
         mbar_arrive(bar_tfull0 + 8 * (tn & 1));
