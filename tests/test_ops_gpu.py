@@ -341,12 +341,12 @@ def test_attention(mt, dtype, B, H, S, D, causal):
 
 @pytest.mark.parametrize("B,H,S,D", [(4, 18, 2048, 128), (6, 24, 2048, 64)])
 def test_attention_head_grouped_tile_order_matches_cuda_core_kernels(mt, B, H, S, D):
-    """Shapes large enough that both tensor-core kernels take the heads in groups (the
-    forward once K and V of all heads exceed 64 MB, the backward once its footprint exceeds
-    96 MB and the grouped dealing stays balanced - 72 and 144 heads at 16 blocks per head do):
-    every tile must still be visited exactly once. The CUDA-core kernels, which walk the
-    tiles in plain order, are the reference; the row sums of dQ/dK/dV would be off by whole
-    tiles if one were skipped or done twice."""
+    """Shapes large enough that the tensor-core kernels take the heads in groups (the forward
+    once K and V of all heads exceed 64 MB: both shapes; the backward once its footprint
+    exceeds 200 MB: the first) and that every persistent CTA takes many tiles from the global
+    counter: every tile must still be visited exactly once. The CUDA-core kernels, which walk
+    the tiles in plain order, are the reference; dQ/dK/dV would be off by whole tiles if one
+    were skipped or done twice."""
     F = mt.fused_ops
     r = np.random.default_rng(21)
     Q, K, V, DO = (mt.DeviceArray.from_numpy(r.standard_normal((B, H, S, D)).astype(np.float32), "float16") for _ in range(4))
