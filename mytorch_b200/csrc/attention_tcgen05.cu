@@ -1,9 +1,11 @@
 // Tensor-core attention for sm_100a, fp16/bf16, causal or full.
 //
 // Forward: persistent, as many CTAs as are resident at once (two per SM at head_dim 64, one at
-// 128), 320 threads each; a tile is one (batch, head, block of 128 query rows), dealt to the CTAs
-// round by round (heads in groups that keep their K/V in L2, heaviest query blocks first).
-//   warp 8    TMA producer: a tile's Q (as soon as the previous tile's last score MMA has read
+// 128), 320 threads each; a tile is one (batch, head, block of 128 query rows), and a CTA takes
+// the next tile nobody has taken yet from a global counter (order: heads in groups that keep their
+// K/V in L2, heaviest query blocks first).
+//   warp 8    TMA producer, which also takes the tiles and hands them to the other warps through
+//             a two-slot ring: a tile's Q (as soon as the previous tile's last score MMA has read
 //             the Q buffer), then K and V blocks of 128 keys (two stages each, K one block ahead
 //             of V, the rings running on across tiles), 128-byte swizzled, read in place
 //             through 4-D tensor maps {head_dim, seq, head, batch} (any batch/head/row strides);
