@@ -5,7 +5,9 @@
 // reductions. Because a lane owns the same columns for every row it visits,
 // the backward kernel keeps dgamma/dbeta partial sums in registers across
 // rows; blocks write one partial row each and a second kernel adds them in a
-// fixed order (no atomics: results are bit-reproducible).
+// fixed order (no atomics: results are bit-reproducible). The backward for rows
+// of 2-6 or 8 warps of vectors (the transformer widths) is a staged kernel: one
+// block per SM, rows brought into a shared-memory ring by bulk copies.
 // Fallback (unaligned or very wide rows): one block per row, scalar loads.
 //
 // Algorithmic traffic (HBM roofline): forward 2*rows*cols*sizeof(T); backward
@@ -13,6 +15,7 @@
 #include <atomic>
 
 #include "common.cuh"
+#include "sm100.cuh"
 #include "tempbuf.cuh"
 
 namespace mt {
@@ -226,98 +229,203 @@ norm_bwd_warp(const T* __restrict__ x, const float* __restrict__ mean, const flo
   }
 }
 
-// Row-team variant for rows of exactly WPR*32 16-byte vectors (768 half columns = 3 warps, 1280 =
-// 5, 768 fp32 columns = 6): a block is one team, a thread owns ONE vector (8 half columns) of every row the block
-// visits, so its dgamma/dbeta accumulators are 16 registers instead of the 48-64 of the
-// warp-per-row kernel and more warps fit an SM. kTeamRows rows are in flight per thread; the row
-// sums of the team's warps meet in shared memory (one __syncthreads per kTeamRows rows, double
-// buffered). The block's column partials need no further reduction: thread t owns columns
-// [t*VN, t*VN+VN). Same partial layout as norm_bwd_warp.
-constexpr int kTeamRows = 2;     // rows in flight per thread (x and dy: 2 x 16 bytes each); three measured the same, four spill
-template <typename T, int WPR, bool RMS>
-__global__ void __launch_bounds__(WPR * 32, 768 / (WPR * 32))
-norm_bwd_team(const T* __restrict__ x, const float* __restrict__ mean, const float* __restrict__ rstd_in,
-              const T* __restrict__ dy, const T* __restrict__ gamma, T* __restrict__ dx,
-              float* __restrict__ partial, int64_t rows, bool want_dg, bool want_db, bool dx_acc) {
+// Staged variant for rows of exactly NV*32 16-byte vectors (768 half columns: NV = 3, 1280: 5,
+// 768 fp32 columns: 6). One block per SM:
+// W row warps (15, 7 or 3) and one copy warp. Chunks of W consecutive rows are dealt to the blocks
+// round robin, so at any moment the SMs read one moving window of the tensors (a contiguous range
+// of rows per block balances better but was no faster at 16384 x 768 and slower at 65536 x 1280
+// with three tensors). The copy warp's first
+// lane walks the block's chunks and starts one bulk copy per tensor (x, dy and, when the result is added
+// into dx, the old dx) into a ring of shared-memory stages, as far ahead as the ring allows,
+// so the SM has 100-200 KB of reads in flight whatever the row warps are doing. Row warp w
+// owns row w of every chunk: it waits for the stage, works from shared memory (two shuffle
+// reductions, no block-wide barrier), stores dx straight from registers and hands the stage
+// back. The row statistics are loaded one chunk ahead. A lane owns the same columns for every
+// row, so dgamma/dbeta partials stay in registers; the block folds its W warps in a fixed order
+// at the end and writes ONE partial row (one per SM instead of one per small block).
+// Shared memory: [nstages][ntens][W][cols] of T, then eight "full" and eight "empty" mbarriers,
+// the abort word, and gamma as fp32. Every wait is bounded; an expired one is recorded as 104.
+template <typename T, int NV, bool PART>
+struct StagedCfg {
+  // registers a row warp's thread holds across rows (the column partials) and for one vector
+  static constexpr int kLiveRegs = (PART ? NV * Vec16<T>::N * 2 : 0) + NV * 4;
+  static constexpr int kWarps = (kLiveRegs > 60 || NV >= 8) ? 8 : 16;   // row warps + the copy warp: 255 or 128 registers per thread
+};
+
+template <typename T, int NV, bool RMS, bool PART>
+__global__ void __launch_bounds__(StagedCfg<T, NV, PART>::kWarps * 32, 1)
+norm_bwd_staged(const T* __restrict__ x, const float* __restrict__ mean, const float* __restrict__ rstd_in,
+                const T* __restrict__ dy, const T* __restrict__ gamma, T* dx, float* __restrict__ partial,
+                int64_t rows, int W, int nstages, bool want_dg, bool want_db, bool dx_acc, int* __restrict__ flag) {
   allow_dependents();
-  grid_dependency_wait();
   constexpr int VN = Vec16<T>::N;
-  constexpr int RB = kTeamRows;
-  constexpr int cols = WPR * 32 * VN;
-  __shared__ float part[2][RB][WPR][2];
+  constexpr int cols = NV * 32 * VN;
+  constexpr uint32_t row_bytes = cols * sizeof(T);
+  extern __shared__ __align__(128) uint8_t stage_mem[];
+  const uint32_t ntens = dx_acc ? 3u : 2u;
+  const uint32_t tens_bytes = (uint32_t)W * row_bytes;
+  const uint32_t stage_bytes = tens_bytes * ntens;
+  uint8_t* bars = stage_mem + (size_t)nstages * stage_bytes;           // 144 bytes: full[8], empty[8], abort word
+  const uint32_t bar_full = sm100::smem_u32(bars), bar_empty = bar_full + 64u;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 128);
+  float4* sgamma = reinterpret_cast<float4*>(bars + 144);               // gamma as fp32, [VN / 4][NV * 32] float4
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int c0 = threadIdx.x * VN;
-  float dg[VN], db[VN];
-#pragma unroll
-  for (int e = 0; e < VN; ++e) { dg[e] = 0.f; db[e] = 0.f; }
-  Vec16<T> gv;
-  if (gamma) gv.load(gamma + c0);
-  const float inv_cols = 1.f / cols;
-  int it = 0;
-  for (int64_t r0 = (int64_t)blockIdx.x * RB; r0 < rows; r0 += (int64_t)gridDim.x * RB, ++it) {
-    Vec16<T> xv[RB], dv[RB];
-    float mu[RB], rs[RB];
-#pragma unroll
-    for (int j = 0; j < RB; ++j) {
-      const int64_t row = r0 + j < rows ? r0 + j : rows - 1;   // clamped: rows past the end are recomputed, not stored
-      xv[j].load(x + row * cols + c0);
-      dv[j].load(dy + row * cols + c0);
-      mu[j] = RMS ? 0.f : mean[row];
-      rs[j] = rstd_in[row];
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < nstages; ++s) {
+      sm100::mbar_init(bar_full + 8u * s, 1);
+      sm100::mbar_init(bar_empty + 8u * s, (uint32_t)W);
     }
-    float (*pp)[WPR][2] = part[it & 1];
+    sm100::fence_barrier_init();
+    sm100::fence_proxy_async();
+  }
+  __syncthreads();
+  grid_dependency_wait();      // everything above touches shared memory only and may run under the previous kernel's tail
+  const int64_t nchunks = (rows + W - 1) / W;
+  float dg[PART ? NV : 1][VN], db[PART ? NV : 1][VN];
 #pragma unroll
-    for (int j = 0; j < RB; ++j) {
-      float s1 = 0.f, s2 = 0.f;
+  for (int i = 0; i < (PART ? NV : 1); ++i)
 #pragma unroll
-      for (int e = 0; e < VN; ++e) {
-        const float xh = (xv[j].get(e) - mu[j]) * rs[j];
-        const float d = dv[j].get(e);
-        const float dxh = gamma ? d * gv.get(e) : d;
-        s1 += dxh;
-        s2 += dxh * xh;
-        if (r0 + j < rows) { dg[e] += d * xh; db[e] += d; }
+    for (int e = 0; e < VN; ++e) { dg[i][e] = 0.f; db[i][e] = 0.f; }
+
+  if (warp == W) {
+    if (lane == 0) {
+      int k = 0;
+      for (int64_t c = blockIdx.x; c < nchunks; c += gridDim.x, ++k) {
+        const int s = k % nstages;
+        if (k >= nstages && !sm100::mbar_wait(bar_empty + 8u * s, (uint32_t)(k / nstages - 1) & 1u, abort_flag)) break;
+        const int64_t r0 = c * W;
+        const uint32_t nr = (uint32_t)(rows - r0 < W ? rows - r0 : W);
+        const uint32_t bytes = nr * row_bytes;
+        const uint32_t dst = sm100::smem_u32(stage_mem) + (uint32_t)s * stage_bytes;
+        sm100::mbar_expect_tx(bar_full + 8u * s, bytes * ntens);
+        sm100::bulk_load_1d(dst, x + r0 * cols, bytes, bar_full + 8u * s);
+        sm100::bulk_load_1d(dst + tens_bytes, dy + r0 * cols, bytes, bar_full + 8u * s);
+        if (dx_acc) sm100::bulk_load_1d(dst + 2u * tens_bytes, dx + r0 * cols, bytes, bar_full + 8u * s);
       }
-      s1 = warp_sum(s1);
-      s2 = warp_sum(s2);
-      if (lane == 0) { pp[j][warp][0] = s1; pp[j][warp][1] = s2; }
     }
-    __syncthreads();
+  } else {
+    // gamma is converted to fp32 once and kept in shared memory (quarter q of vector v at
+    // [q][v]: a lane's 16-byte reads are contiguous across the warp); the row warps meet at
+    // their own named barrier, the copy warp is already loading.
+    if (gamma) {
+      for (int v = threadIdx.x; v < NV * 32; v += W * 32) {
+        Vec16<T> g;
+        g.load(gamma + v * VN);
 #pragma unroll
-    for (int j = 0; j < RB; ++j) {
-      if (r0 + j >= rows) break;
-      float s1 = 0.f, s2 = 0.f;
-#pragma unroll
-      for (int w = 0; w < WPR; ++w) { s1 += pp[j][w][0]; s2 += pp[j][w][1]; }
-      s1 *= inv_cols;
-      s2 *= inv_cols;
-      if (RMS) s1 = 0.f;
-      Vec16<T> o;
-#pragma unroll
-      for (int e = 0; e < VN; ++e) {
-        const float xh = (xv[j].get(e) - mu[j]) * rs[j];
-        const float dxh = gamma ? dv[j].get(e) * gv.get(e) : dv[j].get(e);
-        o.set(e, rs[j] * (dxh - s1 - xh * s2));
+        for (int q = 0; q < VN / 4; ++q)
+          sgamma[q * (NV * 32) + v] = make_float4(g.get(4 * q), g.get(4 * q + 1), g.get(4 * q + 2), g.get(4 * q + 3));
       }
-      T* dxr = dx + (r0 + j) * cols + c0;
-      if (dx_acc) {
-        Vec16<T> old;
-        old.load(dxr);
-#pragma unroll
-        for (int e = 0; e < VN; ++e) o.set(e, o.get(e) + old.get(e));
+    }
+    asm volatile("bar.sync 1, %0;" ::"r"(W * 32) : "memory");
+    const float inv_cols = 1.f / cols;
+    float mu_next = 0.f, rs_next = 0.f;
+    {
+      const int64_t row = (int64_t)blockIdx.x * W + warp;
+      if (row < rows) { mu_next = RMS ? 0.f : mean[row]; rs_next = rstd_in[row]; }
+    }
+    int k = 0;
+    for (int64_t c = blockIdx.x; c < nchunks; c += gridDim.x, ++k) {
+      const int s = k % nstages;
+      const int64_t row = c * W + warp;
+      const float mu = mu_next, rs = rs_next;
+      {
+        const int64_t nrow = (c + gridDim.x) * W + warp;    // this warp's row of the block's next chunk
+        if (nrow < rows) { mu_next = RMS ? 0.f : mean[nrow]; rs_next = rstd_in[nrow]; }
       }
-      o.store(dxr);
+      if (!sm100::mbar_wait(bar_full + 8u * s, (uint32_t)(k / nstages) & 1u, abort_flag)) break;
+      if (row < rows) {
+        const uint8_t* sbase = stage_mem + (size_t)s * stage_bytes + (size_t)warp * row_bytes;
+        const T* sx = reinterpret_cast<const T*>(sbase);
+        const T* sdy = reinterpret_cast<const T*>(sbase + tens_bytes);
+        const T* sold = reinterpret_cast<const T*>(sbase + 2u * tens_bytes);
+        const float nmr = -mu * rs;        // x-hat = x * rs + nmr
+        float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+          const int vi = lane + i * 32;
+          Vec16<T> xv, dv;
+          xv.load(sx + vi * VN);
+          dv.load(sdy + vi * VN);
+#pragma unroll
+          for (int q = 0; q < VN / 4; ++q) {
+            float gq[4] = {1.f, 1.f, 1.f, 1.f};
+            if (gamma) { const float4 g4 = sgamma[q * (NV * 32) + vi]; gq[0] = g4.x; gq[1] = g4.y; gq[2] = g4.z; gq[3] = g4.w; }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const int e = 4 * q + j;
+              const float xh = fmaf(xv.get(e), rs, nmr);
+              const float d = dv.get(e);
+              if (PART) { dg[i][e] = fmaf(d, xh, dg[i][e]); db[i][e] += d; }
+              const float dxh = gamma ? d * gq[j] : d;
+              s1 += dxh;
+              s2 = fmaf(dxh, xh, s2);
+            }
+          }
+        }
+        s1 = warp_sum(s1) * inv_cols;
+        s2 = warp_sum(s2) * inv_cols;
+        if (RMS) s1 = 0.f;
+        // dx = rs * (dxh - s1 - xh * s2) = dxh * rs + (xh * (-s2 * rs) - s1 * rs)
+        const float nc1 = -s1 * rs, nc2 = -s2 * rs;
+        // Second pass: x and dy are read from the stage again instead of being held in registers
+        // across the reductions (the column partials already take 16 registers per vector).
+        T* dxr = dx + row * cols;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+          const int vi = lane + i * 32;
+          Vec16<T> xv, dv, o;
+          xv.load(sx + vi * VN);
+          dv.load(sdy + vi * VN);
+#pragma unroll
+          for (int q = 0; q < VN / 4; ++q) {
+            float gq[4] = {1.f, 1.f, 1.f, 1.f};
+            if (gamma) { const float4 g4 = sgamma[q * (NV * 32) + vi]; gq[0] = g4.x; gq[1] = g4.y; gq[2] = g4.z; gq[3] = g4.w; }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const int e = 4 * q + j;
+              const float xh = fmaf(xv.get(e), rs, nmr);
+              const float dxh = gamma ? dv.get(e) * gq[j] : dv.get(e);
+              o.set(e, fmaf(dxh, rs, fmaf(xh, nc2, nc1)));
+            }
+          }
+          if (dx_acc) {
+            Vec16<T> old;
+            old.load(sold + vi * VN);
+#pragma unroll
+            for (int e = 0; e < VN; ++e) o.set(e, o.get(e) + old.get(e));
+          }
+          o.store(dxr + vi * VN);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) sm100::mbar_arrive(bar_empty + 8u * s);
     }
   }
-  if (want_dg) {
-    float* pg = partial + (size_t)blockIdx.x * 2 * cols + c0;
-#pragma unroll
-    for (int e = 0; e < VN; ++e) pg[e] = dg[e];
+  __syncthreads();   // every wait is over: the abort word is final and no copy is in flight
+  if (*abort_flag) {
+    if (threadIdx.x == 0 && flag) atomicMax(flag, 104);   // a stage did not arrive (or was not handed back) in time
+    return;
   }
-  if (want_db) {
-    float* pb = partial + (size_t)blockIdx.x * 2 * cols + cols + c0;
+  if (!PART || (!want_dg && !want_db)) return;
+  // Fold the W warps' column partials in warp order through the (now idle) stage memory.
+  float* red = reinterpret_cast<float*>(stage_mem);      // [W][2][cols]
+  if (warp < W) {
 #pragma unroll
-    for (int e = 0; e < VN; ++e) pb[e] = db[e];
+    for (int i = 0; i < (PART ? NV : 1); ++i)
+#pragma unroll
+      for (int e = 0; e < VN; ++e) {
+        red[(size_t)(warp * 2) * cols + (lane + i * 32) * VN + e] = dg[i][e];
+        red[(size_t)(warp * 2 + 1) * cols + (lane + i * 32) * VN + e] = db[i][e];
+      }
+  }
+  __syncthreads();
+  float* pg = partial + (size_t)blockIdx.x * 2 * cols;
+  for (int t = threadIdx.x; t < 2 * cols; t += blockDim.x) {
+    if (t < cols ? !want_dg : !want_db) continue;
+    float a = 0.f;
+    for (int w = 0; w < W; ++w) a += red[(size_t)w * 2 * cols + t];
+    pg[t] = a;
   }
 }
 
@@ -455,6 +563,51 @@ static int norm_bwd_no_rows(float* dgamma, float* dbeta, int64_t cols, int accum
   return MT_OK;
 }
 
+// Launches norm_bwd_staged (+ the finalize pass) for rows of NV*32 vectors. W row warps and the
+// number of stages follow from the shared memory: the most warps that still leave three stages.
+template <typename T, int NV, bool RMS, bool PART>
+static int norm_bwd_staged_launch(const T* xp, const float* mean, const float* rstd, const T* dyp, const T* gp, T* dxp,
+                                  float* dgamma, float* dbeta, int64_t rows, int accumulate, cudaStream_t st) {
+  constexpr int VN = Vec16<T>::N;
+  constexpr int cols = NV * 32 * VN;
+  constexpr int row_bytes = cols * (int)sizeof(T);
+  constexpr int kSmemMax = 232448;                 // dynamic shared memory one block may have
+  constexpr int kBarBytes = 16 * 8 + 16;           // at most 8 stages of two mbarriers, and the abort word
+  const int ntens = (accumulate & 2) ? 3 : 2;
+  const int gamma_bytes = gp ? cols * (int)sizeof(float) : 0;
+  int W = 0, nst = 0;
+  for (int warps = StagedCfg<T, NV, PART>::kWarps;; warps /= 2) {
+    W = warps - 1;
+    nst = (kSmemMax - kBarBytes - gamma_bytes) / (W * row_bytes * ntens);
+    if (nst >= 3 || warps == 4) break;
+  }
+  if (nst > 6) nst = 6;
+  MT_REQUIRE(nst >= 2, "norm_bwd: a row of %d bytes does not fit the staged kernel", row_bytes);
+  static std::atomic<bool> attr_set[16];
+  int dev = 0;
+  MT_CHECK_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 16 || !attr_set[dev].load(std::memory_order_acquire)) {
+    MT_CHECK_CUDA(cudaFuncSetAttribute(norm_bwd_staged<T, NV, RMS, PART>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemMax));
+    if (dev >= 0 && dev < 16) attr_set[dev].store(true, std::memory_order_release);
+  }
+  const int64_t nchunks = (rows + W - 1) / W;
+  const int grid = (int)(nchunks < sm_count() ? nchunks : sm_count());
+  const bool wg = PART && dgamma != nullptr, wb = PART && dbeta != nullptr;
+  TempBuf part((wg || wb) ? (size_t)grid * 2 * cols * sizeof(float) : 0, st);
+  if (!part.ok()) return MT_ERR_CUDA;
+  const size_t smem = (size_t)nst * W * row_bytes * ntens + kBarBytes + gamma_bytes;
+  MT_CHECK_CUDA(launch_overlapped(norm_bwd_staged<T, NV, RMS, PART>, dim3(grid), dim3((W + 1) * 32), smem, st, xp, mean, rstd,
+                                  dyp, gp, dxp, (float*)part.ptr, rows, W, nst, wg, wb, (accumulate & 2) != 0, device_flag_ptr()));
+  MT_LAUNCH_CHECK();
+  if (wg || wb) {
+    MT_CHECK_CUDA(launch_overlapped(norm_bwd_finalize, dim3((unsigned)((cols + kFinalizeCols - 1) / kFinalizeCols), 2),
+                                    dim3(kFinalizeCols * kFinalizeGroups), 0, st, (const float*)part.ptr, grid, cols,
+                                    dgamma, dbeta, accumulate & 1));
+    MT_LAUNCH_CHECK();
+  }
+  return MT_OK;
+}
+
 template <typename T, bool RMS>
 static int norm_bwd_launch(const void* x, const float* mean, const float* rstd, const void* dy,
                            const void* gamma, void* dx, float* dgamma, float* dbeta, int64_t rows,
@@ -467,26 +620,15 @@ static int norm_bwd_launch(const void* x, const float* mean, const float* rstd, 
   const int nvec_all = (int)(cols / VN);
   if (al && cols % (32 * VN) == 0 && nvec_all / 32 >= 2 && (nvec_all / 32 <= 6 || nvec_all / 32 == 8)) {
     // rows of 2..6 or 8 warps of vectors (512..1536 and 2048 half columns, 256..768 and 1024 fp32
-    // columns): one thread per vector
+    // columns): staged through shared memory, one block per SM
     const int wpr = nvec_all / 32;
-    const int per_sm = 768 / (wpr * 32);      // resident blocks (the kernel is compiled for this occupancy)
-    int64_t want = (rows + kTeamRows - 1) / kTeamRows;
-    int grid = (int)(want < (int64_t)sm_count() * per_sm ? want : (int64_t)sm_count() * per_sm);
-    bool wg = dgamma != nullptr, wb = dbeta != nullptr;
-    TempBuf part((wg || wb) ? (size_t)grid * 2 * cols * sizeof(float) : 0, st);
-    if (!part.ok()) return MT_ERR_CUDA;
-#define MT_TEAM(W) MT_CHECK_CUDA(launch_overlapped(norm_bwd_team<T, W, RMS>, dim3(grid), dim3(W * 32), 0, st, xp, mean, rstd, dyp, gp, dxp, (float*)part.ptr, rows, wg, wb, (accumulate & 2) != 0))
-    if (wpr == 2) MT_TEAM(2); else if (wpr == 3) MT_TEAM(3); else if (wpr == 4) MT_TEAM(4); else if (wpr == 5) MT_TEAM(5);
-    else if (wpr == 6) MT_TEAM(6); else MT_TEAM(8);
-#undef MT_TEAM
-    MT_LAUNCH_CHECK();
-    if (wg || wb) {
-      MT_CHECK_CUDA(launch_overlapped(norm_bwd_finalize, dim3((unsigned)((cols + kFinalizeCols - 1) / kFinalizeCols), 2),
-                                      dim3(kFinalizeCols * kFinalizeGroups), 0, st, (const float*)part.ptr, grid, (int)cols,
-                                      dgamma, dbeta, accumulate & 1));
-      MT_LAUNCH_CHECK();
-    }
-    return MT_OK;
+    const bool part = dgamma != nullptr || dbeta != nullptr || !RMS;
+#define MT_STAGED(NV)                                                                                                      \
+  return part ? norm_bwd_staged_launch<T, NV, RMS, true>(xp, mean, rstd, dyp, gp, dxp, dgamma, dbeta, rows, accumulate, st) \
+              : norm_bwd_staged_launch<T, NV, RMS, RMS ? false : true>(xp, mean, rstd, dyp, gp, dxp, dgamma, dbeta, rows, accumulate, st)
+    if (wpr == 2) MT_STAGED(2); else if (wpr == 3) MT_STAGED(3); else if (wpr == 4) MT_STAGED(4); else if (wpr == 5) MT_STAGED(5);
+    else if (wpr == 6) MT_STAGED(6); else MT_STAGED(8);
+#undef MT_STAGED
   }
   if (vec) {
     int nvec = (int)(cols / VN);
