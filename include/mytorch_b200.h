@@ -62,8 +62,12 @@ int mt_event_elapsed_ms(void* start, void* stop, float* ms);
 int mt_stream_wait_event(void* stream, void* event);
 int mt_mem_info(size_t* free_bytes, size_t* total_bytes);
 /* Device status word: kernels that give up on a bounded wait or see an
- * out-of-range index record a code here instead of trapping. Reads it back
- * (synchronising `stream`) and clears it. */
+ * out-of-range index record a code here instead of trapping (the largest code
+ * seen is kept). Reads it back (synchronising `stream`) and clears it.
+ * 0 = nothing recorded; 1 = embedding index out of range (row skipped);
+ * 2 = cross-entropy label out of range (row ignored); an expired bounded wait:
+ * 100 = tensor-core GEMM, 101 = attention forward, 102 = attention backward,
+ * 103 = staged cross entropy, 104 = staged LayerNorm / RMSNorm backward. */
 int mt_device_flag_read(int* flag, void* stream);
 
 /* Per-kernel-class timing with CUDA events on the launching stream.
