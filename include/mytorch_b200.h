@@ -75,6 +75,12 @@ int mt_device_flag_read(int* flag, void* stream);
 int mt_prof_begin(int kind);
 int mt_prof_end(double* total_ms, int64_t* launches, double* total_flops);
 int64_t mt_launch_count(void);            /* kernels launched by this library so far */
+/* NVTX range on the calling thread (visible in a timeline profiler, free without one). The
+ * ctypes layer opens one per library call when MT_TRACE=nvtx is set in the environment, and
+ * times every call with CUDA events when MT_TRACE=time is (the reference's per-closure timer
+ * of mytorch/tensor.py:221-261 is Tensor.backward(time_backward=True)). */
+int mt_range_push(const char* name);
+int mt_range_pop(void);
 
 /* ---- elementwise (CuPy ufuncs reached through mytorch/_array.py:422-470 and
  * the autograd closures of mytorch/tensor.py:272-330, 596-640) -------------- */

@@ -71,6 +71,8 @@ _SIG = {
     "mt_stream_wait_event": [_p, _p],
     "mt_mem_info": [C.POINTER(_sz), C.POINTER(_sz)],
     "mt_device_flag_read": [C.POINTER(_i), _p],
+    "mt_range_push": [C.c_char_p],
+    "mt_range_pop": [],
     "mt_prof_begin": [_i],
     "mt_prof_end": [C.POINTER(C.c_double), C.POINTER(_i64), C.POINTER(C.c_double)],
     "mt_cast": [_p, _i, _p, _i, _i64, _p],
@@ -167,6 +169,110 @@ for _name, (_args, _res) in _RAW.items():
     _g[_name[3:]] = _fn
 
 DECLARED = sorted(list(_SIG) + list(_RAW))
+
+
+# ---- optional tracing of every compute call (environment variable MT_TRACE) ---------------------
+# MT_TRACE=nvtx  one NVTX range per library call, named after the function (timeline profilers)
+# MT_TRACE=time  a pair of CUDA events on the compute stream around every call; trace_report()
+#                (also run at interpreter exit) prints calls and device milliseconds per function.
+# Unset (the default) nothing is wrapped: the bindings above are used as they are.
+# Runtime plumbing (allocation, copies, streams, events, communicator set-up) is never wrapped.
+_TRACE = os.environ.get("MT_TRACE", "").strip().lower()
+_NOT_TRACED = {"mt_device_count", "mt_set_device", "mt_get_device", "mt_device_sm_count", "mt_malloc", "mt_free",
+               "mt_host_alloc", "mt_host_free", "mt_memcpy_h2d", "mt_memcpy_d2h", "mt_memcpy_d2d", "mt_stream_create",
+               "mt_stream_destroy", "mt_stream_sync", "mt_device_sync", "mt_event_create", "mt_event_destroy",
+               "mt_event_record", "mt_event_sync", "mt_event_elapsed_ms", "mt_stream_wait_event", "mt_mem_info",
+               "mt_device_flag_read", "mt_range_push", "mt_range_pop", "mt_prof_begin", "mt_prof_end",
+               "mt_gemm_force_simt", "mt_gemm_tile_policy", "mt_attn_force_simt", "mt_comm_unique_id",
+               "mt_comm_init", "mt_comm_abort", "mt_comm_destroy"}
+TRACED = sorted(n for n in _SIG if n not in _NOT_TRACED)
+
+
+class _OpTimer:
+    """Device time per library function: events are recorded on the compute stream around each
+    call and read back in batches (one synchronisation per batch, none per call)."""
+    BATCH = 4096
+
+    def __init__(self):
+        self.pending, self.spare, self.table = [], [], {}
+
+    def _event(self):
+        if self.spare:
+            return self.spare.pop()
+        e = C.c_void_p()
+        _g["event_create"](C.byref(e))
+        return e
+
+    def wrap(self, name, fn):
+        def call(*args):
+            from .array import stream
+            e0, e1 = self._event(), self._event()
+            _g["event_record"](e0, stream())
+            try:
+                return fn(*args)
+            finally:
+                _g["event_record"](e1, stream())
+                self.pending.append((name, e0, e1))
+                if len(self.pending) >= self.BATCH:
+                    self.collect()
+        call.__name__ = name
+        return call
+
+    def collect(self):
+        ms = C.c_float()
+        for name, e0, e1 in self.pending:
+            _g["event_sync"](e1)
+            _g["event_elapsed_ms"](e0, e1, C.byref(ms))
+            row = self.table.setdefault(name, [0.0, 0])
+            row[0] += ms.value
+            row[1] += 1
+            self.spare += [e0, e1]
+        self.pending = []
+
+    def report(self, top=25, file=None):
+        import sys
+        self.collect()
+        rows = sorted(((v[0], v[1], k) for k, v in self.table.items()), reverse=True)
+        out = file or sys.stderr
+        total = sum(r[0] for r in rows) or 1.0
+        for ms, calls, name in rows[:top if top > 0 else None]:
+            print(f"{name:28s} calls={calls:7d} total={ms:10.3f} ms avg={1e3 * ms / calls:9.1f} us share={100 * ms / total:5.1f}%", file=out)
+        return [(name, calls, ms) for ms, calls, name in rows]
+
+
+def _nvtx_wrap(name, fn):
+    label = name.encode()
+
+    def call(*args):
+        lib.mt_range_push(label)
+        try:
+            return fn(*args)
+        finally:
+            lib.mt_range_pop()
+    call.__name__ = name
+    return call
+
+
+_timer = None
+if _TRACE == "nvtx":
+    for _name in TRACED:
+        _g[_name[3:]] = _nvtx_wrap(_name, _g[_name[3:]])
+elif _TRACE == "time":
+    import atexit
+    _timer = _OpTimer()
+    for _name in TRACED:
+        _g[_name[3:]] = _timer.wrap(_name, _g[_name[3:]])
+    atexit.register(lambda: _timer.report() if _timer.table or _timer.pending else None)
+elif _TRACE:
+    raise ImportError(f"MT_TRACE={_TRACE!r}: expected 'nvtx' or 'time'")
+
+
+def trace_report(top=25, file=None):
+    """With MT_TRACE=time: prints and returns [(function, calls, device milliseconds)], largest
+    first, for the calls made so far. Raises when the timer is not on."""
+    if _timer is None:
+        raise RuntimeError("the per-call timer is off: set MT_TRACE=time before importing mytorch_b200")
+    return _timer.report(top, file)
 
 
 def device_count():

@@ -3,6 +3,7 @@
 #include "common.cuh"
 #include <cstdlib>
 #include "prof.cuh"
+#include <nvtx3/nvToolsExt.h>
 #include <stdarg.h>
 #include <atomic>
 #include <mutex>
@@ -95,6 +96,18 @@ extern "C" {
 const char* mt_last_error(void) { return g_err.c_str(); }
 int mt_version(void) { return 100; }
 int64_t mt_launch_count(void) { return g_launches.load(); }
+
+// NVTX ranges on the calling thread. The header-only NVTX 3 binding looks for an attached tool on
+// first use; without one both calls return at once, so they cost nothing outside a profiler.
+int mt_range_push(const char* name) {
+  MT_REQUIRE(name != nullptr, "range_push: no name");
+  nvtxRangePushA(name);
+  return MT_OK;
+}
+int mt_range_pop(void) {
+  nvtxRangePop();
+  return MT_OK;
+}
 
 int mt_device_count(int* count) {
   int n = 0;
